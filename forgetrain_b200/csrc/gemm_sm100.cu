@@ -1,0 +1,434 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a:
+//   D[M,N] (=|+=) alpha * sum_k A[m,k] * B[n,k]
+// * operands are staged by TMA (128-byte swizzle, one CTA per load) into a multi-stage ring,
+// * one thread issues tcgen05.mma (128 x BN x 16 per instruction) into TMEM accumulators,
+// * two accumulator buffers in TMEM let the epilogue of tile i overlap the main loop of
+//   tile i+1,
+// * the epilogue reads TMEM with tcgen05.ld, converts, stages through swizzled shared memory
+//   and leaves through TMA stores (bf16 / fp32) or TMA reduce-adds (fp32 accumulate, which
+//   is also what makes split-K need no separate reduction pass).
+// Both operands may be K-major (reduction index contiguous) or MN-major (row index
+// contiguous), so forward (x W^T), dgrad (dy W) and wgrad (dy^T x) all run on this kernel
+// without any transposed copy. Row / column / reduction tails are handled by TMA
+// out-of-bounds fill and clipping, so no padded copies are needed either.
+//
+// Covers the role of the reference's per-projection GEMM kernels and their launchers
+// (ops/gemm_fc1/gemm_sm90.cu, ops/gemm_*/gemm_cutedsl.cpp, ops/gemm_qkv_proj/_aot_reduce.cu).
+#include <mutex>
+#include <unordered_map>
+#include <string>
+#include <string.h>
+
+#include "ptx.cuh"
+#include "tma_host.h"
+
+namespace ft {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int GEMM_GROUP_M = 16;
+
+enum : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ADD = 2 };
+
+struct GemmParams {
+  int M, N, K;
+  int a_mn, b_mn;     // 1: operand is MN-major
+  int out_mode;       // OUT_*
+  float alpha;
+  int splitk;
+  int m_tiles, n_tiles, k_iters;
+  int* status;
+};
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int EPI_BUF_BYTES = 4096;                 // 32 rows x 128 B
+  static constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;    // 4 warps x 2 buffers
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES + EPI_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;      // + barriers + alignment slack
+};
+
+__device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int& mt, int& nt,
+                                            int& kb, int& kn) {
+  const int per_split = p.m_tiles * p.n_tiles;
+  const int ks = tile / per_split;
+  const int r = tile - ks * per_split;
+  const int group_sz = GEMM_GROUP_M * p.n_tiles;
+  const int g = r / group_sz;
+  const int first_m = g * GEMM_GROUP_M;
+  const int gm = min(p.m_tiles - first_m, GEMM_GROUP_M);
+  const int in = r - g * group_sz;
+  mt = first_m + in % gm;
+  nt = in / gm;
+  const int base = p.k_iters / p.splitk, rem = p.k_iters % p.splitk;
+  kb = ks * base + min(ks, rem);
+  kn = base + (ks < rem ? 1 : 0);
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
+  using L = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* epi_base = smem + STAGES * L::STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // 256 or 512: two fp32 accumulators of BN columns
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull_bar[b], 1);
+      mbar_init(&tempty_bar[b], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    prefetch_tmap(&tmD);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = p.m_tiles * p.n_tiles * p.splitk;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        int mt, nt, kb, kn;
+        decode_tile(p, tile, mt, nt, kb, kn);
+        for (int ki = kb; ki < kb + kn; ++ki) {
+          mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
+          uint8_t* sA = smem + stage * L::STAGE_BYTES;
+          uint8_t* sB = sA + L::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+          if (!p.a_mn) {
+            tma_load_2d(sA, &tmA, &full_bar[stage], ki * GEMM_BK, mt * GEMM_BM);
+          } else {
+#pragma unroll
+            for (int c = 0; c < GEMM_BM / 64; ++c)
+              tma_load_2d(sA + c * 8192, &tmA, &full_bar[stage], mt * GEMM_BM + c * 64,
+                          ki * GEMM_BK);
+          }
+          if (!p.b_mn) {
+            tma_load_2d(sB, &tmB, &full_bar[stage], ki * GEMM_BK, nt * BN);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sB + c * 8192, &tmB, &full_bar[stage], nt * BN + c * 64, ki * GEMM_BK);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (*abort_flag) {
+        // Give copies still in flight time to land before the CTA's shared memory goes away.
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(GEMM_BM, BN, p.a_mn, p.b_mn);
+      const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
+      const uint32_t a_kstep = p.a_mn ? (2048u >> 4) : (32u >> 4);
+      const uint32_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+        int mt, nt, kb, kn;
+        decode_tile(p, tile, mt, nt, kb, kn);
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        mbar_wait(&tempty_bar[buf], acc_phase ^ 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int ki = 0; ki < kn; ++ki) {
+          mbar_wait(&full_bar[stage], phase, abort_flag, p.status, FT_ERR_WAIT_FULL);
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + stage * L::STAGE_BYTES);
+          const uint32_t sB = sA + L::A_BYTES;
+          const uint64_t adesc = make_smem_desc(sA, a_lbo, 1024);
+          const uint64_t bdesc = make_smem_desc(sB, b_lbo, 1024);
+#pragma unroll
+          for (int kk = 0; kk < GEMM_BK / 16; ++kk) {
+            umma_ss(tmem_d, adesc + kk * a_kstep, bdesc + kk * b_kstep, idesc,
+                    (ki > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        umma_commit(&tfull_bar[buf]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    uint8_t* my_epi = epi_base + q * 2 * L::EPI_BUF_BYTES;
+    int it = 0;
+    int nstores = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+      int mt, nt, kb, kn;
+      decode_tile(p, tile, mt, nt, kb, kn);
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      mbar_wait(&tfull_bar[buf], acc_phase, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+      const int row0 = mt * GEMM_BM + q * 32;
+      const bool rows_live = row0 < p.M;
+      if (p.out_mode == OUT_BF16) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col0 = nt * BN + c * 64;
+          if (col0 >= p.N || !rows_live) break;
+          uint32_t r[64];
+          tmem_ld32(taddr + c * 64, r);
+          tmem_ld32(taddr + c * 64 + 32, r + 32);
+          tmem_ld_wait();
+          uint8_t* sbuf = my_epi + (nstores & 1) * L::EPI_BUF_BYTES;
+          if (nstores >= 2) {
+            if (lane == 0) tma_wait_group_read<1>();
+            __syncwarp();
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]) * p.alpha,
+                              __uint_as_float(r[8 * j + 1]) * p.alpha);
+            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * p.alpha,
+                              __uint_as_float(r[8 * j + 3]) * p.alpha);
+            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * p.alpha,
+                              __uint_as_float(r[8 * j + 5]) * p.alpha);
+            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * p.alpha,
+                              __uint_as_float(r[8 * j + 7]) * p.alpha);
+            *reinterpret_cast<uint4*>(sbuf + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmD, sbuf, col0, row0);
+            tma_commit_group();
+          }
+          ++nstores;
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = nt * BN + c * 32;
+          if (col0 >= p.N || !rows_live) break;
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          uint8_t* sbuf = my_epi + (nstores & 1) * L::EPI_BUF_BYTES;
+          if (nstores >= 2) {
+            if (lane == 0) tma_wait_group_read<1>();
+            __syncwarp();
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 v;
+            v.x = __uint_as_float(r[4 * j + 0]) * p.alpha;
+            v.y = __uint_as_float(r[4 * j + 1]) * p.alpha;
+            v.z = __uint_as_float(r[4 * j + 2]) * p.alpha;
+            v.w = __uint_as_float(r[4 * j + 3]) * p.alpha;
+            *reinterpret_cast<float4*>(sbuf + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (p.out_mode == OUT_F32_ADD)
+              tma_reduce_add_2d(&tmD, sbuf, col0, row0);
+            else
+              tma_store_2d(&tmD, sbuf, col0, row0);
+            tma_commit_group();
+          }
+          ++nstores;
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+    }
+    if (lane == 0) tma_wait_group<0>();
+    __syncwarp();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+struct TmapKey {
+  const void* base;
+  uint64_t rows, cols, ld;
+  uint32_t box_r, box_c, elt;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_r == o.box_r &&
+           box_c == o.box_c && elt == o.elt;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    auto mix = [&](uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); };
+    mix(k.rows); mix(k.cols); mix(k.ld); mix(k.box_r); mix(k.box_c); mix(k.elt);
+    return h;
+  }
+};
+
+static std::mutex g_tmap_mu;
+static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmap_cache;
+
+// Cached 128-byte-swizzled 2-D tensor map. A map only encodes address + geometry, so a cached
+// entry stays valid for as long as the same geometry is asked for at the same address.
+int get_tmap_2d(CUtensorMap* out, const void* base, int elt, uint64_t rows, uint64_t cols,
+                uint64_t ld, uint32_t box_r, uint32_t box_c) {
+  TmapKey k{base, rows, cols, ld, box_r, box_c, static_cast<uint32_t>(elt)};
+  std::lock_guard<std::mutex> g(g_tmap_mu);
+  auto it = g_tmap_cache.find(k);
+  if (it != g_tmap_cache.end()) {
+    *out = it->second;
+    return 0;
+  }
+  CUtensorMap tm;
+  int rc = make_tmap_2d(&tm, base, elt, rows, cols, ld, box_r, box_c, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  if (g_tmap_cache.size() > 65536) g_tmap_cache.clear();
+  g_tmap_cache.emplace(k, tm);
+  *out = tm;
+  return 0;
+}
+
+static int g_num_sms = 0;
+static int num_sms() {
+  if (!g_num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD,
+                       const GemmParams& p, int max_ctas, cudaStream_t stream) {
+  using L = GemmSmem<BN, STAGES>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return -10;
+    attr_set = true;
+  }
+  const int total = p.m_tiles * p.n_tiles * p.splitk;
+  int grid = total < max_ctas ? total : max_ctas;
+  if (grid < 1) grid = 1;
+  gemm_bf16_kernel<BN, STAGES><<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmD, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace ft
+
+// D[M,N] (=|+=) alpha * A * B^T with bf16 operands.
+//   a_mn == 0: A is stored [M][lda] (reduction index contiguous); a_mn == 1: A is stored
+//   [K][lda] (row index contiguous). Same for B with N. out_dtype: 0 bf16, 1 fp32.
+//   accumulate != 0 (fp32 only): D += result. splitk <= 0 picks a split automatically
+//   (fp32 only); bn in {0 (auto), 128, 256}. All leading dimensions in elements; every base
+//   pointer 16-byte aligned and every leading dimension a multiple of 8 (bf16) / 4 (fp32).
+extern "C" int ft_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int lda,
+                            int ldb, int ldd, int a_mn, int b_mn, int out_dtype, int accumulate,
+                            float alpha, int splitk, int bn, int max_ctas, int* status,
+                            cudaStream_t stream) {
+  using namespace ft;
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  if (out_dtype == 0 && accumulate) return -2;
+  const int sms = num_sms();
+  if (max_ctas <= 0 || max_ctas > sms) max_ctas = sms;
+  const int m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
+  const int k_iters = (K + GEMM_BK - 1) / GEMM_BK;
+  if (bn != 128 && bn != 256) bn = (N <= 128) ? 128 : 256;  // 256-wide tiles measured faster at every N > 128
+  const int n_tiles = (N + bn - 1) / bn;
+  if (out_dtype == 0) splitk = 1;
+  if (splitk <= 0) {
+    const int tiles = m_tiles * n_tiles;
+    splitk = 1;
+    if (tiles < max_ctas) {
+      splitk = max_ctas / tiles;
+      const int max_by_k = k_iters / 8 > 0 ? k_iters / 8 : 1;
+      if (splitk > max_by_k) splitk = max_by_k;
+      if (splitk > 16) splitk = 16;
+    }
+  }
+  if (splitk > k_iters) splitk = k_iters;
+  if (splitk < 1) splitk = 1;
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn = a_mn ? 1 : 0; p.b_mn = b_mn ? 1 : 0;
+  p.alpha = alpha;
+  p.splitk = splitk;
+  p.m_tiles = m_tiles; p.n_tiles = n_tiles; p.k_iters = k_iters;
+  p.status = status;
+  if (out_dtype == 0) p.out_mode = OUT_BF16;
+  else p.out_mode = (accumulate || splitk > 1) ? OUT_F32_ADD : OUT_F32;
+  if (out_dtype == 1 && !accumulate && splitk > 1) {
+    if (cudaMemset2DAsync(D, static_cast<size_t>(ldd) * 4, 0, static_cast<size_t>(N) * 4, M,
+                          stream) != cudaSuccess)
+      return -3;
+  }
+
+  CUtensorMap tmA, tmB, tmD;
+  int rc;
+  if (!a_mn) rc = get_tmap_2d(&tmA, A, 2, M, K, lda, GEMM_BM, GEMM_BK);
+  else       rc = get_tmap_2d(&tmA, A, 2, K, M, lda, GEMM_BK, 64);
+  if (rc) return -4;
+  if (!b_mn) rc = get_tmap_2d(&tmB, B, 2, N, K, ldb, bn, GEMM_BK);
+  else       rc = get_tmap_2d(&tmB, B, 2, K, N, ldb, GEMM_BK, 64);
+  if (rc) return -5;
+  if (out_dtype == 0) rc = get_tmap_2d(&tmD, D, 2, M, N, ldd, 32, 64);
+  else                rc = get_tmap_2d(&tmD, D, 4, M, N, ldd, 32, 32);
+  if (rc) return -6;
+
+  if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, tmD, p, max_ctas, stream);
+  return launch_gemm<128, 6>(tmA, tmB, tmD, p, max_ctas, stream);
+}
+
+extern "C" void ft_tmap_cache_clear() {
+  std::lock_guard<std::mutex> g(ft::g_tmap_mu);
+  ft::g_tmap_cache.clear();
+}

@@ -1,0 +1,104 @@
+"""ctypes loader for the native sm_100a library.
+
+The library is built in-tree by :mod:`forgetrain_b200.build` and exposes a plain C ABI
+(raw device pointers + a CUDA stream handle). Loading is lazy; on a machine with a GPU a
+missing library is an error (ops never fall back silently to PyTorch on CUDA tensors).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from pathlib import Path
+
+import torch
+
+_LIB = None
+_LOCK = threading.Lock()
+LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libft_b200.so"
+
+c_int = ctypes.c_int
+c_long = ctypes.c_int64
+c_float = ctypes.c_float
+c_void_p = ctypes.c_void_p
+
+
+class NativeLibraryMissing(RuntimeError):
+    pass
+
+
+def lib():
+    """Return the loaded native library, building it first when it is absent."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    with _LOCK:
+        if _LIB is not None:
+            return _LIB
+        if not LIB_PATH.exists():
+            if os.environ.get("FT_B200_NO_AUTOBUILD") == "1":
+                raise NativeLibraryMissing(
+                    f"{LIB_PATH} is missing; run `python -m forgetrain_b200.build`")
+            from .. import build as _build
+            _build.build()
+        try:
+            _LIB = ctypes.CDLL(str(LIB_PATH))
+        except OSError as e:  # pragma: no cover - depends on the box
+            raise NativeLibraryMissing(f"cannot load {LIB_PATH}: {e}") from e
+        return _LIB
+
+
+def available() -> bool:
+    """True when CUDA kernels can run here (a GPU is visible and the library loads)."""
+    if not torch.cuda.is_available():
+        return False
+    lib()
+    return True
+
+
+def ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+_STATUS: dict[int, torch.Tensor] = {}
+
+STATUS_MESSAGES = {
+    1: "consumer timed out waiting for a TMA stage",
+    2: "producer timed out waiting for a free stage",
+    3: "epilogue timed out waiting for an accumulator",
+    4: "MMA issuer timed out waiting for a drained accumulator",
+    5: "a peer flag did not arrive in time",
+    6: "bounded wait ran out",
+}
+
+
+def status_word(device: torch.device | int | None = None) -> torch.Tensor:
+    """Per-device int32 word that kernels set when one of their bounded waits gives up."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    if dev is None:
+        dev = torch.cuda.current_device()
+    t = _STATUS.get(dev)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=f"cuda:{dev}")
+        _STATUS[dev] = t
+    return t
+
+
+def check_status(device=None, reset: bool = True) -> None:
+    """Synchronising check of the status word; raises if a kernel reported a failed wait."""
+    t = status_word(device)
+    code = int(t[0].item())
+    if code != 0:
+        if reset:
+            t.zero_()
+        raise RuntimeError(
+            f"forgetrain_b200 kernel reported status {code}: {STATUS_MESSAGES.get(code, '?')}")
+
+
+def check_rc(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")
