@@ -1,0 +1,357 @@
+// Causal GQA FlashAttention forward for sm_100a (head_dim 64 or 128), reading q/k/v straight out
+// of the interleaved projection buffer qkv[T][n_groups*(g+2)*D] through strided TMA boxes and
+// writing out[T][Hq*D] plus the log-sum-exp.
+//
+// One CTA owns two consecutive 128-row query tiles of one (batch, head) and ping-pongs them:
+//   warp 0      TMA producer  (Q once, then K_j / V_j rings)
+//   warp 1      MMA issuer    (tcgen05.mma: S_w = Q_w K_j^T, O_w += P_w V_j; TMEM accumulators)
+//   warps 4-7   softmax of tile 0 (one thread per query row, no shuffles)
+//   warps 8-11  softmax of tile 1
+// While one warpgroup exponentiates, the tensor core works for the other tile. The running
+// maximum is only refreshed when it grew by more than 2^8 ("lazy rescale"), which keeps the
+// TMEM round-trip of O off the common path. P goes through shared memory in the 128-byte
+// swizzled K-major layout the MMA reads.
+//
+// Replaces the reference's Hopper FlashAttention forward kernels
+// (ops/attention/flash_attn_dsl/flash_fwd.py:31-660, src/flash_attn_dsl/flash_fwd.py:1-803).
+#include "ptx.cuh"
+#include "tma_host.h"
+
+namespace ft {
+
+int get_tmap_2d(CUtensorMap* out, const void* base, int elt, uint64_t rows, uint64_t cols,
+                uint64_t ld, uint32_t box_r, uint32_t box_c);
+
+constexpr int FA_THREADS = 384;
+constexpr int FA_BLK = 128;
+
+struct FaFwdParams {
+  int S, Hq, g, n_groups, batch;
+  float scale_log2;  // softmax scale * log2(e)
+  float* lse;        // [B][Hq][S]
+  int* status;
+};
+
+template <int D, int KS, int VS>
+struct FaFwdSmem {
+  static constexpr int TILE = FA_BLK * D * 2;        // one 128 x D bf16 tile
+  static constexpr int Q_OFF = 0;                    // 2 tiles
+  static constexpr int K_OFF = 2 * TILE;
+  static constexpr int V_OFF = K_OFF + KS * TILE;
+  static constexpr int P_OFF = V_OFF + VS * TILE;    // 2 x (128 x 128 bf16)
+  static constexpr int BAR_OFF = P_OFF + 2 * 32768;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+template <int D, int KS, int VS>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_out,
+              const FaFwdParams p) {
+  using L = FaFwdSmem<D, KS, VS>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* q_full = bars;            // 1
+  uint64_t* k_full = bars + 1;        // KS (<=2)
+  uint64_t* k_empty = bars + 3;
+  uint64_t* v_full = bars + 5;
+  uint64_t* v_empty = bars + 7;
+  uint64_t* s_full = bars + 9;        // 2
+  uint64_t* p_ready = bars + 11;      // 2
+  uint64_t* o_done = bars + 13;       // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // heavy (late) query tiles first; heads of one KV group adjacent for L2 reuse of K/V
+  const int n_pairs = p.S / (2 * FA_BLK);
+  const int head = blockIdx.x % p.Hq;
+  const int rest = blockIdx.x / p.Hq;
+  const int b = rest % p.batch;
+  const int pair = n_pairs - 1 - rest / p.batch;
+  const int grp = head / p.g;
+  const int q_col = (grp * (p.g + 2) + head % p.g) * D;
+  const int k_col = (grp * (p.g + 2) + p.g) * D;
+  const int v_col = k_col + D;
+  const int row_base = b * p.S;
+  const int n_kv[2] = {2 * pair + 1, 2 * pair + 2};
+  const int n_total = n_kv[1];
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_ready[s], 128);
+      mbar_init(&o_done[s], 1);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tm_qkv);
+    prefetch_tmap(&tm_out);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tmem_O[2] = {tmem_base + 256, tmem_base + 256 + D};
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- producer ----------------
+      mbar_expect_tx(q_full, 2 * L::TILE);
+      for (int w = 0; w < 2; ++w)
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_2d(smem + L::Q_OFF + w * L::TILE + c * 16384, &tm_qkv, q_full, q_col + c * 64,
+                      row_base + (2 * pair + w) * FA_BLK);
+      for (int j = 0; j < n_total; ++j) {
+        const int ks = j % KS, vs = j % VS;
+        mbar_wait(&k_empty[ks], ((j / KS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
+        mbar_expect_tx(&k_full[ks], L::TILE);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_2d(smem + L::K_OFF + ks * L::TILE + c * 16384, &tm_qkv, &k_full[ks],
+                      k_col + c * 64, row_base + j * FA_BLK);
+        mbar_wait(&v_empty[vs], ((j / VS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
+        mbar_expect_tx(&v_full[vs], L::TILE);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_2d(smem + L::V_OFF + vs * L::TILE + c * 16384, &tm_qkv, &v_full[vs],
+                      v_col + c * 64, row_base + j * FA_BLK);
+      }
+      if (*abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer ----------------
+      const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
+      const uint32_t sQ = smem_u32(smem + L::Q_OFF), sK = smem_u32(smem + L::K_OFF);
+      const uint32_t sV = smem_u32(smem + L::V_OFF), sP = smem_u32(smem + L::P_OFF);
+      auto issue_S = [&](int w, int j) {
+        const int ks = j % KS;
+        const uint32_t qa = sQ + w * L::TILE, ka = sK + ks * L::TILE;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+          umma_ss(tmem_S[w], make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024),
+                  idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[w]);
+      };
+      auto issue_PV = [&](int w, int j) {
+        const int vs = j % VS;
+        const uint32_t pa = sP + w * 32768, va = sV + vs * L::TILE;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t poff = (kk / 4) * 16384 + (kk % 4) * 32;
+          umma_ss(tmem_O[w], make_smem_desc(pa + poff, 16, 1024),
+                  make_smem_desc(va + kk * 2048, 16384, 1024), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&o_done[w]);
+      };
+      mbar_wait(q_full, 0, abort_flag, p.status, FT_ERR_WAIT_FULL);
+      mbar_wait(&k_full[0], 0, abort_flag, p.status, FT_ERR_WAIT_FULL);
+      tc_fence_after();
+      issue_S(0, 0);
+      issue_S(1, 0);
+      umma_commit(&k_empty[0]);
+      for (int j = 0; j < n_total; ++j) {
+        const int vs = j % VS;
+        mbar_wait(&v_full[vs], (j / VS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
+        bool next_k_ready = false;
+        for (int w = 0; w < 2; ++w) {
+          if (j >= n_kv[w]) continue;
+          mbar_wait(&p_ready[w], j & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+          tc_fence_after();
+          issue_PV(w, j);
+          if (w == 1) umma_commit(&v_empty[vs]);
+          if (j + 1 < n_kv[w]) {
+            if (!next_k_ready) {
+              mbar_wait(&k_full[(j + 1) % KS], ((j + 1) / KS) & 1, abort_flag, p.status,
+                        FT_ERR_WAIT_FULL);
+              tc_fence_after();
+              next_k_ready = true;
+            }
+            issue_S(w, j + 1);
+            if (w == 1) umma_commit(&k_empty[(j + 1) % KS]);
+          }
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------- softmax warpgroups ----------------
+    const int w = (warp - 4) >> 2;           // query tile of this warpgroup
+    const int r = threadIdx.x - 128 - w * 128;  // row inside the tile == TMEM lane
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int qt = 2 * pair + w;
+    const int q_row = qt * FA_BLK + r;  // position inside the sequence
+    uint8_t* sP = smem + L::P_OFF + w * 32768;
+    float m_ref = -INFINITY, l = 0.f;
+    const int nk = n_kv[w];
+    for (int j = 0; j < nk; ++j) {
+      mbar_wait(&s_full[w], j & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
+      tc_fence_after();
+      const bool diag = (j == qt);
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32];
+        tmem_ld32(tmem_S[w] + lane_off + c * 32, s);
+        tmem_ld_wait();
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          float v = __uint_as_float(s[k]);
+          if (diag && (c * 32 + k) > r) v = -INFINITY;
+          mx = fmaxf(mx, v);
+        }
+      }
+      const float m_new = fmaxf(m_ref, mx * p.scale_log2);
+      const bool need = (m_new - m_ref) > 8.0f;  // also true while m_ref is still -inf
+      if (j > 0) {
+        mbar_wait(&o_done[w], (j - 1) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+        tc_fence_after();
+      }
+      if (__any_sync(0xffffffffu, need)) {
+        const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
+        m_ref = m_new;
+        l *= alpha;
+        if (j > 0) {
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tmem_O[w] + lane_off + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
+            tmem_st32(tmem_O[w] + lane_off + c * 32, o);
+          }
+          tmem_st_wait();
+        }
+      }
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32];
+        tmem_ld32(tmem_S[w] + lane_off + c * 32, s);
+        tmem_ld_wait();
+        float pv[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          float v = exp2f(__uint_as_float(s[k]) * p.scale_log2 - m_ref);
+          if (diag && (c * 32 + k) > r) v = 0.f;
+          pv[k] = v;
+          l += v;
+        }
+        uint8_t* rowp = sP + (c >> 1) * 16384 + r * 128;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          uint4 u;
+          u.x = pack_bf16x2(pv[8 * jj + 0], pv[8 * jj + 1]);
+          u.y = pack_bf16x2(pv[8 * jj + 2], pv[8 * jj + 3]);
+          u.z = pack_bf16x2(pv[8 * jj + 4], pv[8 * jj + 5]);
+          u.w = pack_bf16x2(pv[8 * jj + 6], pv[8 * jj + 7]);
+          const int chunk = (c & 1) * 4 + jj;
+          *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) = u;
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(&p_ready[w]);
+    }
+    // ---------------- epilogue: O / l -> bf16 -> TMA store; LSE ----------------
+    mbar_wait(&o_done[w], (nk - 1) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+    tc_fence_after();
+    const float inv_l = 1.f / l;
+#pragma unroll 1
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t o[32];
+      tmem_ld32(tmem_O[w] + lane_off + c * 32, o);
+      tmem_ld_wait();
+      uint8_t* rowp = sP + (c >> 1) * 16384 + r * 128;
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        uint4 u;
+        u.x = pack_bf16x2(__uint_as_float(o[8 * jj + 0]) * inv_l, __uint_as_float(o[8 * jj + 1]) * inv_l);
+        u.y = pack_bf16x2(__uint_as_float(o[8 * jj + 2]) * inv_l, __uint_as_float(o[8 * jj + 3]) * inv_l);
+        u.z = pack_bf16x2(__uint_as_float(o[8 * jj + 4]) * inv_l, __uint_as_float(o[8 * jj + 5]) * inv_l);
+        u.w = pack_bf16x2(__uint_as_float(o[8 * jj + 6]) * inv_l, __uint_as_float(o[8 * jj + 7]) * inv_l);
+        const int chunk = (c & 1) * 4 + jj;
+        *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) = u;
+      }
+    }
+    p.lse[(static_cast<long>(b) * p.Hq + head) * p.S + q_row] =
+        (m_ref + log2f(l)) * 0.6931471805599453f;
+    fence_proxy_async_smem();
+    named_bar_sync(1 + w, 128);
+    if (r == 0) {
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c)
+        tma_store_2d(&tm_out, sP + c * 16384, head * D + c * 64, row_base + qt * FA_BLK);
+      tma_commit_group();
+      tma_wait_group<0>();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D, int KS, int VS>
+static int launch_fa_fwd(const CUtensorMap& tq, const CUtensorMap& to, const FaFwdParams& p,
+                         cudaStream_t st) {
+  using L = FaFwdSmem<D, KS, VS>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(fa_fwd_kernel<D, KS, VS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             L::TOTAL) != cudaSuccess)
+      return -10;
+    attr = true;
+  }
+  const int grid = (p.S / (2 * FA_BLK)) * p.batch * p.Hq;
+  fa_fwd_kernel<D, KS, VS><<<grid, FA_THREADS, L::TOTAL, st>>>(tq, to, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+}  // namespace ft
+
+// qkv: [batch*S][ld_qkv] bf16 interleaved per KV group as [q_0..q_{g-1} | k | v]; out:
+// [batch*S][ld_out] bf16 with head h at columns [h*D, (h+1)*D); lse: [batch][Hq][S] fp32
+// (natural log). S must be a multiple of 256, D 64 or 128.
+extern "C" int ft_attn_fwd(const void* qkv, void* out, void* lse, int batch, int S, int n_groups,
+                           int g, int D, int ld_qkv, int ld_out, float scale, int* status,
+                           cudaStream_t st) {
+  using namespace ft;
+  if (S % (2 * FA_BLK) || (D != 64 && D != 128)) return -1;
+  const long T = static_cast<long>(batch) * S;
+  CUtensorMap tq, to;
+  if (get_tmap_2d(&tq, qkv, 2, T, static_cast<uint64_t>(n_groups) * (g + 2) * D, ld_qkv, FA_BLK, 64))
+    return -2;
+  if (get_tmap_2d(&to, out, 2, T, static_cast<uint64_t>(n_groups) * g * D, ld_out, FA_BLK, 64))
+    return -3;
+  FaFwdParams p;
+  p.S = S; p.Hq = n_groups * g; p.g = g; p.n_groups = n_groups; p.batch = batch;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse = static_cast<float*>(lse);
+  p.status = status;
+  if (D == 64) return launch_fa_fwd<64, 2, 2>(tq, to, p, st);
+  return launch_fa_fwd<128, 1, 1>(tq, to, p, st);
+}

@@ -1,0 +1,230 @@
+"""Run-time configuration: one frozen :class:`EngineConfig` installed once per process.
+
+Third tier of the configuration plane (model spec -> constants -> engine switches). Keeps the
+field names of the reference's ``EngineConfig``
+(exports/train_engine_0.5B/src/training_engine_tensor/engine_config.py:132-277 and
+exports/train_engine_8b/src/training_engine_tensor/engine_config.py:107-192) for everything
+that is a hyper-parameter, a communication knob, a graph switch or a logging/profiling
+switch. The reference's per-fusion on/off flags have no counterpart: the fused sm_100a
+kernels are the only GPU path.
+"""
+from __future__ import annotations
+
+import dataclasses
+import os
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+# Environment variables that come from the launcher / libraries, not from this package.
+EXTERNAL_ENV_WHITELIST = frozenset({
+    "RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT", "LOCAL_WORLD_SIZE",
+    "CUDA_VISIBLE_DEVICES", "CUDA_DEVICE_MAX_CONNECTIONS", "NCCL_DEBUG", "NCCL_ALGO",
+    "NCCL_PROTO", "NCCL_MIN_NCHANNELS", "NCCL_NVLS_ENABLE", "NCCL_IB_QPS",
+    "TORCH_NCCL_HEARTBEAT_TIMEOUT_SEC", "OUTPUT_DIR", "HF_HOME", "TOKENIZERS_PARALLELISM",
+    "FT_PEAK_TFLOPS", "FT_B200_NO_AUTOBUILD",
+})
+
+
+@dataclass(frozen=True)
+class EngineConfig:
+    # ---- precision / debug ----
+    dtype: str = "bf16"                  # compute dtype: bf16 (GPU) or fp32 (CPU plumbing runs)
+    no_grad_clip: bool = False
+    grad_diag: bool = False
+    grad_norm_diag: bool = False
+    emit_loss_lines: bool = False
+    serial_streams: bool = False         # force every side stream onto the main stream
+    # ---- communication ----
+    comm: str = "fused"                  # "fused": peer-memory kernels; "nccl": library baseline
+    wgrad_overlap: bool = True           # reduce buckets while backward is still running
+    wgrad_bucket_target_elems: int = 100 * 1024 * 1024
+    opt_allgather_overlap: bool = True
+    async_loss_ar: bool = True
+    sharded_optimizer: bool = True       # ZeRO-1
+    data_prefetch_depth: int = 2
+    rs_buckets: int = 32                 # 8B-style: number of layer-aligned buckets (0 = by size)
+    tensor_parallel_size: int = 1
+    sequence_parallel: bool = True
+    # ---- CUDA graphs ----
+    forward_cuda_graph: bool = False
+    step_cuda_graph: bool = False
+    step_cuda_graph_warmup: int = 3
+    step_cuda_graph_tol: float = 1e-3
+    step_cuda_graph_sanity: bool = False
+    # ---- muP ----
+    mup_emb_scale: float = 12.0
+    mup_depth_scale: float = 1.4
+    # ---- MTP ----
+    mtp_num_layers: int = 0
+    mtp_loss_scaling_factor: float = 0.1
+    # ---- LR schedule (WSD) ----
+    max_lr: float = 3e-4
+    min_lr: float = 0.0
+    warmup_iters: int = 2000
+    lr_decay_iters: int = 240000
+    wsd_decay_iters: int = 3000
+    # ---- AdamW ----
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.95
+    adam_eps: float = 1e-8
+    weight_decay: float = 0.1
+    max_grad_norm: float = 1.0
+    mup_lr_scaling: bool = True          # hidden matrices use lr / (hidden / base width)
+    # ---- init ----
+    random_init: bool = True
+    init_scheme: str = "spec"            # "spec": muP-aware std from the model spec; "normal": N(0, init_std)
+    init_std: float = 0.02
+    # ---- profiling ----
+    profile_range: str = ""              # "start,end" (step indices, end exclusive)
+    profile_output: str = ""
+    profile_deep: bool = False
+    host_timer: bool = False
+
+    def replace(self, **kw: Any) -> "EngineConfig":
+        return dataclasses.replace(self, **kw)
+
+
+_BOOL_TRUE = {"1", "true", "yes", "on"}
+
+
+def _env_bool(env: dict, key: str, default: bool) -> bool:
+    v = env.get(key)
+    return default if v is None else v.strip().lower() in _BOOL_TRUE
+
+
+# env name -> (field, parser)
+_ENV_MAP: dict[str, tuple[str, Callable[[str], Any]]] = {
+    "FT_DTYPE": ("dtype", str),
+    "NO_GRAD_CLIP": ("no_grad_clip", lambda v: v.lower() in _BOOL_TRUE),
+    "GRAD_DIAG": ("grad_diag", lambda v: v.lower() in _BOOL_TRUE),
+    "GRAD_NORM_DIAG": ("grad_norm_diag", lambda v: v.lower() in _BOOL_TRUE),
+    "EMIT_LOSS_LINES": ("emit_loss_lines", lambda v: v.lower() in _BOOL_TRUE),
+    "SERIAL_STREAMS": ("serial_streams", lambda v: v.lower() in _BOOL_TRUE),
+    "FT_COMM": ("comm", str),
+    "WGRAD_OVERLAP": ("wgrad_overlap", lambda v: v.lower() in _BOOL_TRUE),
+    "WGRAD_BUCKET_TARGET_ELEMS": ("wgrad_bucket_target_elems", int),
+    "OPT_ALLGATHER_OVERLAP": ("opt_allgather_overlap", lambda v: v.lower() in _BOOL_TRUE),
+    "ASYNC_LOSS_AR": ("async_loss_ar", lambda v: v.lower() in _BOOL_TRUE),
+    "SHARDED_OPTIMIZER": ("sharded_optimizer", lambda v: v.lower() in _BOOL_TRUE),
+    "DATA_PREFETCH_DEPTH": ("data_prefetch_depth", int),
+    "RS_BUCKETS": ("rs_buckets", int),
+    "TENSOR_PARALLEL_SIZE": ("tensor_parallel_size", int),
+    "SEQUENCE_PARALLEL": ("sequence_parallel", lambda v: v.lower() in _BOOL_TRUE),
+    "FORWARD_CUDA_GRAPH": ("forward_cuda_graph", lambda v: v.lower() in _BOOL_TRUE),
+    "STEP_CUDA_GRAPH": ("step_cuda_graph", lambda v: v.lower() in _BOOL_TRUE),
+    "STEP_CUDA_GRAPH_WARMUP": ("step_cuda_graph_warmup", int),
+    "STEP_CUDA_GRAPH_TOL": ("step_cuda_graph_tol", float),
+    "STEP_CUDA_GRAPH_SANITY": ("step_cuda_graph_sanity", lambda v: v.lower() in _BOOL_TRUE),
+    "MUP_EMB_SCALE": ("mup_emb_scale", float),
+    "MUP_DEPTH_SCALE": ("mup_depth_scale", float),
+    "MTP_NUM_LAYERS": ("mtp_num_layers", int),
+    "MTP_LOSS_SCALING_FACTOR": ("mtp_loss_scaling_factor", float),
+    "MAX_LR": ("max_lr", float),
+    "MIN_LR": ("min_lr", float),
+    "WARMUP_ITERS": ("warmup_iters", int),
+    "LR_DECAY_ITERS": ("lr_decay_iters", int),
+    "WSD_DECAY_ITERS": ("wsd_decay_iters", int),
+    "ADAM_BETA1": ("adam_beta1", float),
+    "ADAM_BETA2": ("adam_beta2", float),
+    "ADAM_EPS": ("adam_eps", float),
+    "WEIGHT_DECAY": ("weight_decay", float),
+    "MAX_GRAD_NORM": ("max_grad_norm", float),
+    "RANDOM_INIT": ("random_init", lambda v: v.lower() in _BOOL_TRUE),
+    "PROFILE_RANGE": ("profile_range", str),
+    "PROFILE_OUTPUT": ("profile_output", str),
+    "PROFILE_DEEP": ("profile_deep", lambda v: v.lower() in _BOOL_TRUE),
+    "HOST_TIMER": ("host_timer", lambda v: v.lower() in _BOOL_TRUE),
+}
+
+DECLARED_ENV_VARS = frozenset(_ENV_MAP) | EXTERNAL_ENV_WHITELIST
+
+
+def from_env(env: dict | None = None, **overrides: Any) -> EngineConfig:
+    """Build a config from environment variables (legacy bridge) plus keyword overrides."""
+    env = dict(os.environ if env is None else env)
+    kw: dict[str, Any] = {}
+    for name, (fld, parse) in _ENV_MAP.items():
+        if name in env and env[name] != "":
+            kw[fld] = parse(env[name])
+    kw.update({k: v for k, v in overrides.items() if v is not None})
+    cfg = EngineConfig(**kw)
+    validate_config(cfg)
+    return cfg
+
+
+def from_spec(spec, **overrides: Any) -> EngineConfig:
+    """Defaults taken from a :class:`~forgetrain_b200.config.ModelSpec`'s training section."""
+    kw = dict(
+        mup_emb_scale=spec.mup_emb_scale if spec.mup_enabled else 0.0,
+        mup_depth_scale=spec.mup_depth_scale if spec.mup_enabled else 0.0,
+        max_lr=spec.lr, min_lr=spec.min_lr, warmup_iters=spec.lr_warmup_iters,
+        lr_decay_iters=spec.lr_decay_iters, wsd_decay_iters=spec.lr_wsd_decay_iters,
+        adam_beta1=spec.adam_beta1, adam_beta2=spec.adam_beta2, adam_eps=spec.adam_eps,
+        weight_decay=spec.weight_decay, max_grad_norm=spec.clip_grad,
+        tensor_parallel_size=spec.tensor_model_parallel_size,
+        sequence_parallel=spec.sequence_parallel,
+        sharded_optimizer=spec.use_distributed_optimizer,
+        init_std=spec.init_method_std,
+    )
+    kw.update({k: v for k, v in overrides.items() if v is not None})
+    cfg = EngineConfig(**kw)
+    validate_config(cfg)
+    return cfg
+
+
+def validate_config(cfg: EngineConfig) -> None:
+    if cfg.dtype not in ("bf16", "fp32"):
+        raise ValueError(f"dtype must be bf16 or fp32, got {cfg.dtype!r}")
+    if cfg.comm not in ("fused", "nccl"):
+        raise ValueError(f"comm must be 'fused' or 'nccl', got {cfg.comm!r}")
+    if cfg.wgrad_bucket_target_elems <= 0:
+        raise ValueError("wgrad_bucket_target_elems must be positive")
+    if bool(cfg.profile_range) != bool(cfg.profile_output):
+        raise ValueError("PROFILE_RANGE and PROFILE_OUTPUT must be given together")
+    if cfg.tensor_parallel_size < 1:
+        raise ValueError("tensor_parallel_size must be >= 1")
+    if not 1 <= cfg.data_prefetch_depth <= 4:
+        raise ValueError("data_prefetch_depth must be in 1..4")
+
+
+# -----------------------------------------------------------------------------------------
+# process-wide singleton
+# -----------------------------------------------------------------------------------------
+_GLOBAL: EngineConfig | None = None
+_RESET_HOOKS: list[Callable[[], None]] = []
+
+
+def set_global_config(cfg: EngineConfig) -> None:
+    """Install the process-wide config. Installing twice is an error (reset first)."""
+    global _GLOBAL
+    if _GLOBAL is not None:
+        raise RuntimeError("EngineConfig already installed; call reset_global_config() first")
+    _GLOBAL = cfg
+
+
+def get_config() -> EngineConfig:
+    """The installed config, or the defaults when none was installed."""
+    return _GLOBAL if _GLOBAL is not None else EngineConfig()
+
+
+def has_global_config() -> bool:
+    return _GLOBAL is not None
+
+
+def register_reset_hook(fn: Callable[[], None]) -> None:
+    """Register a callable run by :func:`reset_global_config` (caches keyed on the config)."""
+    _RESET_HOOKS.append(fn)
+
+
+def reset_global_config() -> None:
+    global _GLOBAL
+    _GLOBAL = None
+    for fn in list(_RESET_HOOKS):
+        fn()
+
+
+def print_config_summary(cfg: EngineConfig, prefix: str = "[CONFIG]") -> str:
+    parts = [f"{f.name}={getattr(cfg, f.name)}" for f in dataclasses.fields(cfg)]
+    line = f"{prefix} " + " ".join(parts)
+    print(line, flush=True)
+    return line
