@@ -40,7 +40,7 @@ def attention_fwd(qkv: torch.Tensor, batch: int, n_groups: int, heads_per_group:
 
 def attention_bwd(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse: torch.Tensor,
                   batch: int, n_groups: int, heads_per_group: int, head_dim: int,
-                  scale: float | None = None) -> torch.Tensor:
+                  scale: float | None = None, heads_per_cta: int = 0) -> torch.Tensor:
     """Gradient wrt the interleaved qkv buffer (bf16, same layout as ``qkv``)."""
     T = qkv.shape[0]
     S = T // batch
@@ -50,13 +50,13 @@ def attention_bwd(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse:
         raise _lib.NativeLibraryMissing("native library was built without the attention backward")
     dqkv = torch.empty_like(qkv)
     Hq = n_groups * heads_per_group
-    # fp32 scratch: dq accumulator [T, Hq*D] and delta = rowsum(dout * out) [B, Hq, S]
-    dq_acc = torch.zeros(T, Hq * head_dim, dtype=torch.float32, device=qkv.device)
-    delta = torch.empty(batch, Hq, S, dtype=torch.float32, device=qkv.device)
-    rc = L.ft_attn_bwd(P(dout), P(qkv), P(out), P(lse), P(dqkv), P(dq_acc), P(delta),
+    # fp32 scratch: accumulator laid out like qkv, and [delta | lse*log2(e)] per (b, head, s)
+    acc = torch.empty(T, qkv.shape[1], dtype=torch.float32, device=qkv.device)
+    delta = torch.empty(2, batch, Hq, S, dtype=torch.float32, device=qkv.device)
+    rc = L.ft_attn_bwd(P(dout), P(qkv), P(out), P(lse), P(dqkv), P(acc), P(delta),
                        c_int(batch), c_int(S), c_int(n_groups), c_int(heads_per_group),
                        c_int(head_dim), c_int(qkv.stride(0)), c_int(out.stride(0)),
-                       c_int(dout.stride(0)), c_float(scale), P(_lib.status_word(qkv.device)),
-                       _lib.stream())
+                       c_int(dout.stride(0)), c_float(scale), c_int(heads_per_cta),
+                       P(_lib.status_word(qkv.device)), _lib.stream())
     _lib.check_rc(rc, "ft_attn_bwd")
     return dqkv
