@@ -1,0 +1,174 @@
+"""Command line: ``python -m training_engine_tensor pretrain ...`` (also ``python -m
+forgetrain_b200 ...``).
+
+Sub-commands and flags follow the reference's CLIs
+(exports/train_engine_0.5B/src/training_engine_tensor/__main__.py:65-235 and
+exports/train_engine_8b/src/training_engine_tensor/__main__.py:57-224):
+
+* ``pretrain``               random-init (or ``--resume``) training; synthetic uniform tokens
+                             unless ``--hf-dataset`` is given
+* ``train``                  continue from ``--checkpoint-root`` (a checkpoint to import)
+* ``checkpoint-train-loop``  train with periodic checkpoints (defaults to 200 steps)
+
+Every :class:`~forgetrain_b200.engine_config.EngineConfig` field is also exposed as
+``--<field>`` / ``--no-<field>``. Additions over the reference: ``--model``, ``--dtype``,
+``--backend``, ``--tensor-parallel-size``, ``--sequence-parallel``, ``--tie-embeddings``,
+``--comm {fused,nccl}``.
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import json
+import os
+import sys
+from pathlib import Path
+
+from . import engine_config as ec
+from .config import load_model_spec
+
+
+def _add_engine_config_args(p: argparse.ArgumentParser) -> None:
+    grp = p.add_argument_group("engine config (one flag per EngineConfig field)")
+    for f in dataclasses.fields(ec.EngineConfig):
+        flag = "--" + f.name.replace("_", "-")
+        if f.type in ("bool", bool):
+            grp.add_argument(flag, dest=f"cfg_{f.name}", action=argparse.BooleanOptionalAction,
+                             default=None)
+        else:
+            typ = {"int": int, "float": float, "str": str}.get(str(f.type), str)
+            grp.add_argument(flag, dest=f"cfg_{f.name}", type=typ, default=None)
+
+
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(prog="training_engine_tensor",
+                                description="B200-native MiniCPM4 pretraining engine")
+    p.add_argument("command", choices=["pretrain", "train", "checkpoint-train-loop"])
+    p.add_argument("--model", default="0.5b", help="built-in spec (tiny, 0.5b, 8b) or a model_spec.toml")
+    p.add_argument("--num-steps", type=int, default=None)
+    p.add_argument("--global-batch-size", type=int, default=None)
+    p.add_argument("--micro-batch-size", type=int, default=None)
+    p.add_argument("--grad-accum-steps", type=int, default=None)
+    p.add_argument("--seq-length", type=int, default=None)
+    p.add_argument("--num-local-microbatches", type=int, default=None)
+    p.add_argument("--num-workers", type=int, default=0)
+    p.add_argument("--dump-inputs-dir", default=None)
+    p.add_argument("--save-interval", type=int, default=0)
+    p.add_argument("--save-dir", "--save-checkpoint-dir", dest="save_dir", default=None)
+    p.add_argument("--resume", default=None)
+    p.add_argument("--checkpoint-root", default=None)
+    p.add_argument("--export-checkpoint-root", default=None)
+    p.add_argument("--export-report", default=None)
+    p.add_argument("--data-parallel-rank", type=int, default=None)
+    p.add_argument("--data-parallel-ranks", type=int, default=None)
+    p.add_argument("--seed", type=int, default=1234)
+    p.add_argument("--device", default=None)
+    p.add_argument("--backend", choices=["nccl", "gloo"], default=None)
+    p.add_argument("--tie-embeddings", action=argparse.BooleanOptionalAction, default=None)
+    p.add_argument("--vocab-size", type=int, default=None)
+    hf = p.add_argument_group("HuggingFace dataset")
+    hf.add_argument("--hf-dataset", default=None)
+    hf.add_argument("--tokenizer-path", default=None)
+    hf.add_argument("--hf-dataset-config", default=None)
+    hf.add_argument("--hf-dataset-split", default="train")
+    hf.add_argument("--hf-text-field", default="text")
+    hf.add_argument("--hf-text-template", default=None)
+    hf.add_argument("--hf-data-format", default=None)
+    hf.add_argument("--hf-data-files", default=None)
+    hf.add_argument("--max-packed-rows", type=int, default=None)
+    _add_engine_config_args(p)
+    return p
+
+
+def _validate_resume_save_dir_mutex(args) -> None:
+    if args.resume and args.save_dir:
+        a, b = Path(args.resume).resolve(), Path(args.save_dir).resolve()
+        if a == b or b in a.parents:
+            raise SystemExit("--resume and --save-dir must not point into the same directory: a "
+                             "resumed run would overwrite the checkpoints it was started from")
+
+
+def _resolve_local_microbatches(args, spec, dp_size: int, mbs: int) -> int:
+    if args.num_local_microbatches:
+        return args.num_local_microbatches
+    if args.grad_accum_steps:
+        return args.grad_accum_steps
+    gbs = args.global_batch_size
+    if gbs:
+        if gbs % (mbs * dp_size):
+            raise SystemExit(f"global batch {gbs} is not a multiple of micro-batch {mbs} x DP {dp_size}")
+        return gbs // (mbs * dp_size)
+    return max(1, spec.grad_accum_steps or 1)
+
+
+def main(argv: list[str] | None = None) -> int:
+    args = build_parser().parse_args(argv)
+    _validate_resume_save_dir_mutex(args)
+    spec = load_model_spec(args.model, tie_embeddings=args.tie_embeddings, vocab_size=args.vocab_size)
+    overrides = {k[4:]: v for k, v in vars(args).items() if k.startswith("cfg_") and v is not None}
+    env_cfg = ec.from_env()
+    base = ec.from_spec(spec)
+    # precedence: CLI > environment > model spec defaults
+    defaults = ec.EngineConfig()
+    merged = {}
+    for f in dataclasses.fields(ec.EngineConfig):
+        v_spec, v_env = getattr(base, f.name), getattr(env_cfg, f.name)
+        merged[f.name] = v_env if v_env != getattr(defaults, f.name) else v_spec
+    merged.update(overrides)
+    device = args.device
+    import torch
+    if device is None:
+        device = "cuda" if torch.cuda.is_available() else "cpu"
+    if device == "cpu" and "dtype" not in overrides and "FT_DTYPE" not in os.environ:
+        merged["dtype"] = "fp32"
+    cfg = ec.EngineConfig(**merged)
+    ec.validate_config(cfg)
+    if ec.has_global_config():
+        ec.reset_global_config()
+    ec.set_global_config(cfg)
+
+    from .parallel.topology import init_topology, shutdown
+    from .trainer import run_training_loop
+    topo = init_topology(cfg.tensor_parallel_size, device=device, backend=args.backend,
+                         num_kv_groups=spec.num_query_groups)
+    if topo.rank == 0:
+        ec.print_config_summary(cfg)
+    mbs = args.micro_batch_size or spec.micro_batch_size
+    seq = args.seq_length or spec.seq_length
+    n_mb = _resolve_local_microbatches(args, spec, topo.dp_size, mbs)
+    num_steps = args.num_steps or (200 if args.command == "checkpoint-train-loop" else 1)
+    resume = args.resume
+    if args.command == "train":
+        if not args.checkpoint_root:
+            raise SystemExit("train needs --checkpoint-root")
+        resume = resume or args.checkpoint_root
+    save_dir = args.save_dir or args.export_checkpoint_root
+    if args.command == "checkpoint-train-loop" and not save_dir:
+        raise SystemExit("checkpoint-train-loop needs --save-dir")
+    source = None
+    if args.hf_dataset or args.hf_data_files:
+        from .data.hf_dataloader import build_hf_dataloader
+        source = build_hf_dataloader(args, spec, mbs, seq, topo)
+    elif topo.rank == 0:
+        print("no --hf-dataset given: using synthetic uniform token ids", flush=True)
+    out_dir = os.environ.get("OUTPUT_DIR")
+    report_path = args.export_report or (str(Path(out_dir) / "training_report.json") if out_dir else None)
+    rep = run_training_loop(spec=spec, cfg=cfg, topo=topo, num_steps=num_steps, micro_batch_size=mbs,
+                            seq_length=seq, num_local_microbatches=n_mb, seed=args.seed,
+                            save_dir=save_dir, save_interval=args.save_interval, resume=resume,
+                            data_source=source, dump_inputs_dir=args.dump_inputs_dir,
+                            report_path=report_path)
+    if topo.rank == 0:
+        if out_dir:
+            d = Path(out_dir) / f"{num_steps}step"
+            d.mkdir(parents=True, exist_ok=True)
+            with open(d / "ours_results.jsonl", "w") as f:
+                for s in rep["steps"]:
+                    f.write(json.dumps(s) + "\n")
+        print("DONE", flush=True)
+    shutdown()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

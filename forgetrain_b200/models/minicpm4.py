@@ -1,0 +1,230 @@
+"""MiniCPM4 decoder: hand-written forward and backward over the op layer.
+
+There is no ``nn.Module`` and no autograd: parameters are views into the flat buffers of a
+:class:`~forgetrain_b200.models.params.ParamStore`, the forward keeps what the backward needs
+in plain lists, and the backward is an explicit reverse pass that writes every weight gradient
+straight into the flat fp32 gradient buffer (store on the first micro-batch, accumulate
+afterwards) and reports each finished parameter through ``grad_ready`` so bucket reductions
+can start while earlier layers are still running. Same structure as the reference
+(exports/train_engine_0.5B/src/training_engine_tensor/forward.py:81-217, backward.py:125-393)
+with these differences: activations are token-major ``[B*S, H]``; q/k/v are never split out of
+the projection buffer (RoPE runs in place on it and attention reads it through strided TMA
+boxes); the muP residual multiplier and the logit divisor ride in GEMM epilogues.
+
+Block (pre-norm):  h += r * Wo·attn(rope(Wqkv·rmsnorm(h)));  h += r * W2·swiglu(Wfc1·rmsnorm(h))
+with r = depth_scale/sqrt(L); embedding * emb_scale; logits = Wout·(rmsnorm(h) / (H/256)).
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+
+from .. import ops
+from ..config import ModelSpec
+from ..parallel.tp import NO_TP, TPContext
+from .params import ParamStore, vocab_shard_rows
+
+
+class LayerSaved:
+    __slots__ = ("h_in", "rs1", "n1_full", "qkv", "attn", "lse", "h_mid", "rs2", "n2_full", "y1",
+                 "act")
+
+
+class MiniCPM4:
+    def __init__(self, spec: ModelSpec, store: ParamStore, tp: TPContext = NO_TP,
+                 max_seq_len: int | None = None, save_act: bool = True):
+        self.spec = spec
+        self.store = store
+        self.tp = tp
+        self.p = store.params
+        self.g = store.grads
+        self.save_act = save_act
+        dev = store.device
+        S = max_seq_len or max(spec.seq_length, spec.max_position_embeddings)
+        self.cos, self.sin = ops.rope_tables(S, spec.head_dim, spec.rotary_base, device=dev)
+        tpn = tp.size
+        G = spec.num_query_groups
+        if tpn <= G:
+            assert G % tpn == 0, "num_query_groups must be a multiple of the TP degree"
+            self.local_groups, self.local_g = G // tpn, spec.heads_per_group
+        else:
+            rep = tpn // G
+            assert tpn % G == 0 and spec.heads_per_group % rep == 0
+            self.local_groups, self.local_g = 1, spec.heads_per_group // rep
+        self.vocab_rows = vocab_shard_rows(spec.vocab_size, tpn) if tpn > 1 else spec.vocab_size
+        self.vocab_start = tp.rank * self.vocab_rows if tpn > 1 else 0
+        self._saved: list[LayerSaved] = []
+        self._head_saved = None
+        self._ensure_rope(S)
+
+    def _ensure_rope(self, S: int) -> None:
+        if self.cos.shape[0] < S:
+            self.cos, self.sin = ops.rope_tables(S, self.spec.head_dim, self.spec.rotary_base,
+                                                 device=self.store.device)
+
+    # ------------------------------------------------------------------------------ forward
+    def embed(self, tokens: torch.Tensor) -> torch.Tensor:
+        """Token embedding * emb_scale, returned on this rank's token shard."""
+        w = self.p["tok_embeddings.weight"]
+        e = ops.embedding_fwd(tokens, w, self.spec.emb_scale, self.vocab_start)
+        if self.tp.enabled:
+            e = self.tp.scatter_reduce(e)
+        return e
+
+    def layer_forward(self, prefix: str, h_prev, branch, batch: int, position_ids=None):
+        """One decoder block. ``h_prev + branch`` is the block input (the add is fused into the
+        first norm); returns ``(h_mid, ffn_branch, saved)`` with the output being their sum."""
+        sp, p, tp = self.spec, self.p, self.tp
+        r = sp.mup_residual_scale
+        sv = LayerSaved()
+        h_in, n1, sv.rs1 = ops.add_rmsnorm_fwd(branch if h_prev is not None else None,
+                                               h_prev if h_prev is not None else branch,
+                                               p[f"{prefix}.attention_norm.weight"], sp.norm_epsilon)
+        sv.h_in = h_in
+        sv.n1_full = tp.gather(n1)
+        qkv = ops.linear_fwd(sv.n1_full, p[f"{prefix}.attention.wqkv.weight"])
+        ops.rope_(qkv, self.cos, self.sin, batch, self.local_groups, self.local_g, sp.head_dim,
+                  position_ids=position_ids)
+        sv.qkv = qkv
+        sv.attn, sv.lse = ops.attention_fwd(qkv, batch, self.local_groups, self.local_g, sp.head_dim)
+        o = ops.linear_fwd(sv.attn, p[f"{prefix}.attention.wo.weight"], alpha=r)
+        o = tp.scatter_reduce(o)
+        sv.h_mid, n2, sv.rs2 = ops.add_rmsnorm_fwd(h_in, o, p[f"{prefix}.ffn_norm.weight"],
+                                                   sp.norm_epsilon)
+        sv.n2_full = tp.gather(n2)
+        sv.y1 = ops.linear_fwd(sv.n2_full, p[f"{prefix}.feed_forward.wfc1.weight"])
+        sv.act = ops.swiglu_fwd(sv.y1)
+        f = ops.linear_fwd(sv.act, p[f"{prefix}.feed_forward.w2.weight"], alpha=r)
+        f = tp.scatter_reduce(f)
+        return sv.h_mid, f, sv
+
+    def forward_hidden(self, tokens: torch.Tensor, position_ids=None):
+        """Embedding + all blocks. Returns (h, branch): the final hidden state is h + branch."""
+        B, S = tokens.shape
+        self._ensure_rope(S)
+        self._saved = []
+        h, branch = None, self.embed(tokens)
+        for i in range(self.spec.num_layers):
+            h, branch, sv = self.layer_forward(f"layers.{i}", h, branch, B, position_ids)
+            self._saved.append(sv)
+        return h, branch
+
+    def head_forward(self, h, branch):
+        """Final norm, logit divisor, LM head. Returns logits of this rank's vocabulary shard."""
+        sp, p = self.spec, self.p
+        h_fin, nf, rsf = ops.add_rmsnorm_fwd(h, branch, p["norm.weight"], sp.norm_epsilon)
+        nf_full = self.tp.gather(nf)
+        logits = ops.linear_fwd(nf_full, p["output.weight"], alpha=1.0 / sp.mup_width_scale)
+        self._head_saved = (h_fin, rsf, nf_full)
+        return logits
+
+    def forward(self, tokens: torch.Tensor, position_ids=None) -> torch.Tensor:
+        h, branch = self.forward_hidden(tokens, position_ids)
+        return self.head_forward(h, branch)
+
+    def loss_and_dlogits(self, logits, labels, loss_mask, loss_scale: float):
+        tp = self.tp
+        return ops.cross_entropy_fwd_bwd(
+            logits, labels, loss_mask, loss_scale, vocab_start=self.vocab_start,
+            stats_reduce=tp.stats_reduce if tp.enabled else None)
+
+    # ----------------------------------------------------------------------------- backward
+    def head_backward(self, dlogits, accumulate: bool, emit):
+        sp, p, g, tp = self.spec, self.p, self.g, self.tp
+        h_fin, rsf, nf_full = self._head_saved
+        a = 1.0 / sp.mup_width_scale
+        ops.linear_wgrad(dlogits, nf_full, g["output.weight"], accumulate, alpha=a)
+        if not sp.tie_embeddings:
+            emit("output.weight")
+        dnf = ops.linear_dgrad(dlogits, p["output.weight"], alpha=a)
+        dnf = tp.scatter_reduce(dnf)
+        dh = ops.rmsnorm_bwd(dnf, h_fin, p["norm.weight"], rsf, None, g["norm.weight"], accumulate)
+        emit("norm.weight")
+        self._head_saved = None
+        return dh
+
+    def layer_backward(self, prefix: str, dh, sv: LayerSaved, batch: int, accumulate: bool, emit,
+                       position_ids=None):
+        """``dh``: gradient wrt the block output (token shard). Returns the gradient wrt the
+        block input."""
+        sp, p, g, tp = self.spec, self.p, self.g, self.tp
+        r = sp.mup_residual_scale
+        n_w2, n_fc1 = f"{prefix}.feed_forward.w2.weight", f"{prefix}.feed_forward.wfc1.weight"
+        n_qkv, n_wo = f"{prefix}.attention.wqkv.weight", f"{prefix}.attention.wo.weight"
+        n_fn, n_an = f"{prefix}.ffn_norm.weight", f"{prefix}.attention_norm.weight"
+        # ---- feed-forward branch
+        dh_full = tp.gather(dh)
+        ops.linear_wgrad(dh_full, sv.act, g[n_w2], accumulate, alpha=r)
+        emit(n_w2)
+        dact = ops.linear_dgrad(dh_full, p[n_w2], alpha=r)
+        dy1 = ops.swiglu_bwd(dact, sv.y1)
+        del dact
+        ops.linear_wgrad(dy1, sv.n2_full, g[n_fc1], accumulate)
+        emit(n_fc1)
+        dn2 = ops.linear_dgrad(dy1, p[n_fc1])
+        del dy1
+        dn2 = tp.scatter_reduce(dn2)
+        dh = ops.rmsnorm_bwd(dn2, sv.h_mid, p[n_fn], sv.rs2, dh, g[n_fn], accumulate)
+        emit(n_fn)
+        # ---- attention branch
+        dh_full = tp.gather(dh)
+        ops.linear_wgrad(dh_full, sv.attn, g[n_wo], accumulate, alpha=r)
+        dattn = ops.linear_dgrad(dh_full, p[n_wo], alpha=r)
+        dqkv = ops.attention_bwd(dattn, sv.qkv, sv.attn, sv.lse, batch, self.local_groups,
+                                 self.local_g, sp.head_dim)
+        del dattn
+        ops.rope_(dqkv, self.cos, self.sin, batch, self.local_groups, self.local_g, sp.head_dim,
+                  inverse=True, position_ids=position_ids)
+        ops.linear_wgrad(dqkv, sv.n1_full, g[n_qkv], accumulate)
+        if tp.replica_size > 1:
+            self._reduce_kv_replicas(g[n_qkv])
+        emit(n_qkv)
+        dn1 = ops.linear_dgrad(dqkv, p[n_qkv])
+        del dqkv
+        dn1 = tp.scatter_reduce(dn1)
+        dh = ops.rmsnorm_bwd(dn1, sv.h_in, p[n_an], sv.rs1, dh, g[n_an], accumulate)
+        emit(n_an)
+        emit(n_wo)
+        return dh
+
+    def _reduce_kv_replicas(self, gqkv: torch.Tensor) -> None:
+        """k / v rows are replicated over the ranks of one KV group: sum their gradients."""
+        D = self.spec.head_dim
+        kv = gqkv[self.local_g * D:]
+        self.tp.replica_all_reduce_(kv)
+
+    def embedding_backward(self, tokens, dh, accumulate: bool, emit):
+        sp, g, tp = self.spec, self.g, self.tp
+        gw = g["tok_embeddings.weight"]
+        if not accumulate and not sp.tie_embeddings:
+            gw.zero_()
+        dfull = tp.gather(dh) if tp.enabled else dh
+        ops.embedding_bwd(tokens, dfull, sp.emb_scale, gw, self.vocab_start)
+        emit("tok_embeddings.weight")
+
+    def backward(self, tokens, dlogits, accumulate: bool,
+                 grad_ready: Callable[[str], None] | None = None, position_ids=None,
+                 dh_extra: torch.Tensor | None = None) -> None:
+        """Reverse pass from ``dlogits``. ``dh_extra`` (MTP) is added to the gradient of the
+        final hidden state before the blocks are walked."""
+        emit = grad_ready or (lambda name: None)
+        B = tokens.shape[0]
+        dh = self.head_backward(dlogits, accumulate, emit)
+        if dh_extra is not None:
+            dh = dh + dh_extra
+        for i in reversed(range(self.spec.num_layers)):
+            sv = self._saved[i]
+            dh = self.layer_backward(f"layers.{i}", dh, sv, B, accumulate, emit, position_ids)
+            self._saved[i] = None
+        self.embedding_backward(tokens, dh, accumulate, emit)
+        self._saved = []
+
+    # -------------------------------------------------------------------- one micro-batch
+    def forward_backward(self, tokens, labels, loss_mask=None, loss_scale: float = 1.0,
+                         accumulate: bool = False, grad_ready=None, position_ids=None):
+        """Forward + loss + backward of one micro-batch; returns the (unscaled) mean loss."""
+        logits = self.forward(tokens, position_ids)
+        loss, dlogits = self.loss_and_dlogits(logits, labels, loss_mask, loss_scale)
+        self.backward(tokens, dlogits, accumulate, grad_ready, position_ids)
+        return loss

@@ -1,0 +1,280 @@
+"""Parameter registry, initialisation and flat-buffer storage.
+
+* :func:`all_param_specs` is the single enumeration of trainable parameters (names, shapes,
+  norm / weight-decay / muP-LR classes) in forward-registration order; the names are the
+  reference's (exports/train_engine_0.5B/src/training_engine_tensor/parameters.py:76-118,
+  786-844) so checkpoints stay interchangeable.
+* :class:`ParamStore` owns ONE flat buffer of parameters in the compute dtype and ONE flat
+  fp32 gradient buffer with identical offsets, laid out in reverse registration order
+  (output head first, embedding last) so that backward fills the front of the buffer first and
+  early buckets can be reduced while later layers are still running
+  (reference: nccl.py:97-149). Per-parameter tensors are views into the two buffers; weight
+  gradients are written in place by the wgrad GEMM, never copied.
+* Tensor parallelism: column-parallel weights (wqkv, wfc1, embeddings, head) are sharded on
+  rows, row-parallel weights (wo, w2) on columns; every rank initialises the full tensor from
+  the same seed and keeps its shard, so results do not depend on the TP degree.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from ..config import ModelSpec
+
+ALIGN_ELEMS = 128  # every parameter starts on a multiple of this many elements (TMA: 16 B)
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    name: str
+    shape: tuple[int, ...]          # full (unsharded) shape
+    is_norm: bool
+    has_weight_decay: bool
+    mup_lr_scaled: bool             # hidden matrix: lr / width multiplier under muP
+    tp_axis: int | None = None      # axis sharded under tensor parallelism (None: replicated)
+    init: str = "normal"            # "normal" | "mup" | "ones"
+
+    @property
+    def numel(self) -> int:
+        return math.prod(self.shape)
+
+
+def mtp_layer_prefix(k: int) -> str:
+    return f"mtp.layers.{k}"
+
+
+def _layer_specs(prefix: str, spec: ModelSpec) -> list[ParamSpec]:
+    h = spec.hidden_size
+    return [
+        ParamSpec(f"{prefix}.attention_norm.weight", (h,), True, False, False, None, "ones"),
+        ParamSpec(f"{prefix}.attention.wqkv.weight", (spec.qkv_dim, h), False, True, True, 0, "mup"),
+        ParamSpec(f"{prefix}.attention.wo.weight", (h, spec.q_dim), False, True, True, 1, "mup"),
+        ParamSpec(f"{prefix}.ffn_norm.weight", (h,), True, False, False, None, "ones"),
+        ParamSpec(f"{prefix}.feed_forward.wfc1.weight", (2 * spec.ffn_hidden_size, h), False, True,
+                  True, 0, "mup"),
+        ParamSpec(f"{prefix}.feed_forward.w2.weight", (h, spec.ffn_hidden_size), False, True, True,
+                  1, "mup"),
+    ]
+
+
+def all_param_specs(spec: ModelSpec, mtp_num_layers: int = 0) -> list[ParamSpec]:
+    """Every trainable parameter in forward-registration order."""
+    h, v = spec.hidden_size, spec.vocab_size
+    out = [ParamSpec("tok_embeddings.weight", (v, h), False, True, False, 0, "normal")]
+    for i in range(spec.num_layers):
+        out.extend(_layer_specs(f"layers.{i}", spec))
+    out.append(ParamSpec("norm.weight", (h,), True, False, False, None, "ones"))
+    for k in range(mtp_num_layers):
+        p = mtp_layer_prefix(k)
+        out.append(ParamSpec(f"{p}.enorm.weight", (h,), True, False, False, None, "ones"))
+        out.append(ParamSpec(f"{p}.hnorm.weight", (h,), True, False, False, None, "ones"))
+        out.append(ParamSpec(f"{p}.eh_proj.weight", (h, 2 * h), False, True, True, None, "mup"))
+        out.extend(_layer_specs(p, spec))
+        out.append(ParamSpec(f"{p}.final_layernorm.weight", (h,), True, False, False, None, "ones"))
+    if not spec.tie_embeddings:
+        out.append(ParamSpec("output.weight", (v, h), False, True, False, 0, "normal"))
+    return out
+
+
+def trainable_param_names(spec: ModelSpec, mtp_num_layers: int = 0) -> list[str]:
+    return [s.name for s in all_param_specs(spec, mtp_num_layers)]
+
+
+def flat_buffer_order(spec: ModelSpec, mtp_num_layers: int = 0) -> list[ParamSpec]:
+    """Reverse registration order: output head, MTP, final norm, layers L-1..0 each as
+    [w2, wfc1, ffn_norm, wqkv, attention_norm, wo], embedding last."""
+    by_name = {s.name: s for s in all_param_specs(spec, mtp_num_layers)}
+    order: list[str] = []
+    if not spec.tie_embeddings:
+        order.append("output.weight")
+    for k in reversed(range(mtp_num_layers)):
+        p = mtp_layer_prefix(k)
+        order += [f"{p}.final_layernorm.weight", f"{p}.feed_forward.w2.weight",
+                  f"{p}.feed_forward.wfc1.weight", f"{p}.ffn_norm.weight",
+                  f"{p}.attention.wqkv.weight", f"{p}.attention_norm.weight",
+                  f"{p}.attention.wo.weight", f"{p}.eh_proj.weight", f"{p}.hnorm.weight",
+                  f"{p}.enorm.weight"]
+    order.append("norm.weight")
+    for i in reversed(range(spec.num_layers)):
+        p = f"layers.{i}"
+        order += [f"{p}.feed_forward.w2.weight", f"{p}.feed_forward.wfc1.weight",
+                  f"{p}.ffn_norm.weight", f"{p}.attention.wqkv.weight",
+                  f"{p}.attention_norm.weight", f"{p}.attention.wo.weight"]
+    order.append("tok_embeddings.weight")
+    assert len(order) == len(by_name) and set(order) == set(by_name)
+    return [by_name[n] for n in order]
+
+
+# -----------------------------------------------------------------------------------------
+# tensor-parallel sharding
+# -----------------------------------------------------------------------------------------
+def kv_replication(spec: ModelSpec, tp: int) -> int:
+    """How many TP ranks share one KV group (1 while tp <= num_query_groups)."""
+    return max(1, tp // spec.num_query_groups)
+
+
+def shard_for_tp(ps: ParamSpec, full: torch.Tensor, spec: ModelSpec, tp_rank: int, tp: int) -> torch.Tensor:
+    """This rank's shard of a full parameter tensor."""
+    if tp == 1 or ps.tp_axis is None:
+        return full
+    name = ps.name
+    G, g, D = spec.num_query_groups, spec.heads_per_group, spec.head_dim
+    if name.endswith("attention.wqkv.weight"):
+        # rows: per KV group [q_0..q_{g-1} | k | v]
+        w = full.view(G, g + 2, D, full.shape[1])
+        if tp <= G:
+            gpr = G // tp
+            return w[tp_rank * gpr:(tp_rank + 1) * gpr].reshape(-1, full.shape[1])
+        rep = tp // G                      # ranks per group: split q heads, replicate k / v
+        grp, sub = tp_rank // rep, tp_rank % rep
+        qpr = g // rep
+        q = w[grp, sub * qpr:(sub + 1) * qpr]
+        kv = w[grp, g:g + 2]
+        return torch.cat([q, kv], dim=0).reshape(-1, full.shape[1])
+    if name.endswith("attention.wo.weight"):
+        # columns follow query heads in natural order
+        hq = spec.num_attention_heads // tp
+        return full[:, tp_rank * hq * D:(tp_rank + 1) * hq * D]
+    if name.endswith("feed_forward.wfc1.weight"):
+        F = spec.ffn_hidden_size
+        fpr = F // tp
+        gate = full[tp_rank * fpr:(tp_rank + 1) * fpr]
+        up = full[F + tp_rank * fpr:F + (tp_rank + 1) * fpr]
+        return torch.cat([gate, up], dim=0)
+    if name.endswith("feed_forward.w2.weight"):
+        fpr = spec.ffn_hidden_size // tp
+        return full[:, tp_rank * fpr:(tp_rank + 1) * fpr]
+    if name in ("tok_embeddings.weight", "output.weight"):
+        vpr = vocab_shard_rows(spec.vocab_size, tp)
+        lo = tp_rank * vpr
+        hi = min(spec.vocab_size, lo + vpr)
+        out = torch.zeros(vpr, full.shape[1], dtype=full.dtype)
+        if hi > lo:
+            out[:hi - lo] = full[lo:hi]
+        return out
+    size = full.shape[ps.tp_axis] // tp
+    return full.narrow(ps.tp_axis, tp_rank * size, size)
+
+
+def vocab_shard_rows(vocab: int, tp: int) -> int:
+    """Rows per vocabulary shard (padded so every shard has the same, 8-aligned size)."""
+    per = (vocab + tp - 1) // tp
+    return (per + 7) // 8 * 8
+
+
+def local_shape(ps: ParamSpec, spec: ModelSpec, tp: int) -> tuple[int, ...]:
+    if tp == 1 or ps.tp_axis is None:
+        return ps.shape
+    name = ps.name
+    G, g, D = spec.num_query_groups, spec.heads_per_group, spec.head_dim
+    if name.endswith("attention.wqkv.weight"):
+        if tp <= G:
+            return ((G // tp) * (g + 2) * D, ps.shape[1])
+        rep = tp // G
+        return ((g // rep + 2) * D, ps.shape[1])
+    if name in ("tok_embeddings.weight", "output.weight"):
+        return (vocab_shard_rows(spec.vocab_size, tp), ps.shape[1])
+    s = list(ps.shape)
+    s[ps.tp_axis] //= tp
+    return tuple(s)
+
+
+def init_std_for(ps: ParamSpec, spec: ModelSpec, scheme: str, init_std: float) -> float:
+    """``spec`` scheme: embeddings / head use init_std, hidden matrices init_std/sqrt(width
+    multiplier) under muP (reference parameters.py:181-262); ``normal``: N(0, init_std)."""
+    if ps.init == "ones":
+        return 0.0
+    if scheme == "normal" or not spec.mup_enabled or ps.init == "normal":
+        return init_std
+    return init_std / math.sqrt(spec.mup_width_scale)
+
+
+class ParamStore:
+    """Flat parameter / gradient storage with per-parameter views."""
+
+    def __init__(self, spec: ModelSpec, device, dtype: torch.dtype, mtp_num_layers: int = 0,
+                 tp_rank: int = 0, tp_size: int = 1, pad_to: int = 1,
+                 grad_buffer: torch.Tensor | None = None, align: int = ALIGN_ELEMS):
+        self.spec = spec
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.tp_rank, self.tp_size = tp_rank, tp_size
+        self.mtp_num_layers = mtp_num_layers
+        self.specs = all_param_specs(spec, mtp_num_layers)
+        self.by_name = {s.name: s for s in self.specs}
+        self.order = flat_buffer_order(spec, mtp_num_layers)
+        self.offsets: dict[str, int] = {}
+        self.shapes: dict[str, tuple[int, ...]] = {}
+        off = 0
+        for ps in self.order:
+            shp = local_shape(ps, spec, tp_size)
+            self.offsets[ps.name] = off
+            self.shapes[ps.name] = shp
+            off += (math.prod(shp) + align - 1) // align * align
+        self.raw_total = off
+        self.total = (off + pad_to - 1) // pad_to * pad_to
+        self.flat_params = torch.zeros(self.total, dtype=dtype, device=self.device)
+        if grad_buffer is not None:
+            assert grad_buffer.numel() >= self.total and grad_buffer.dtype == torch.float32
+            self.flat_grads = grad_buffer[:self.total]
+            self.flat_grads.zero_()
+        else:
+            self.flat_grads = torch.zeros(self.total, dtype=torch.float32, device=self.device)
+        self.params: dict[str, torch.Tensor] = {}
+        self.grads: dict[str, torch.Tensor] = {}
+        for ps in self.order:
+            o, shp = self.offsets[ps.name], self.shapes[ps.name]
+            n = math.prod(shp)
+            self.params[ps.name] = self.flat_params[o:o + n].view(shp)
+            self.grads[ps.name] = self.flat_grads[o:o + n].view(shp)
+        if spec.tie_embeddings:
+            self.params["output.weight"] = self.params["tok_embeddings.weight"]
+            self.grads["output.weight"] = self.grads["tok_embeddings.weight"]
+
+    @staticmethod
+    def layout_total(spec: ModelSpec, mtp_num_layers: int, tp_size: int, align: int) -> int:
+        """Number of elements of the flat buffers for this layout (no allocation)."""
+        off = 0
+        for ps in flat_buffer_order(spec, mtp_num_layers):
+            n = math.prod(local_shape(ps, spec, tp_size))
+            off += (n + align - 1) // align * align
+        return off
+
+    # -- helpers -------------------------------------------------------------------------
+    def entries(self) -> list[tuple[str, int, int]]:
+        """(name, offset, padded numel) in flat-buffer order."""
+        out = []
+        names = [ps.name for ps in self.order]
+        for i, n in enumerate(names):
+            end = self.offsets[names[i + 1]] if i + 1 < len(names) else self.raw_total
+            out.append((n, self.offsets[n], end - self.offsets[n]))
+        return out
+
+    def numel(self, name: str) -> int:
+        return math.prod(self.shapes[name])
+
+    def init_random(self, seed: int, scheme: str = "spec", init_std: float | None = None) -> None:
+        """Seeded init: every rank draws the full tensor on CPU and keeps its shard."""
+        std0 = self.spec.init_method_std if init_std is None else init_std
+        gen = torch.Generator(device="cpu")
+        gen.manual_seed(seed)
+        for ps in self.specs:  # registration order => layout-independent stream of draws
+            if ps.init == "ones":
+                self.params[ps.name].fill_(1.0)
+                continue
+            std = init_std_for(ps, self.spec, scheme, std0)
+            full = torch.randn(ps.shape, dtype=torch.float32, generator=gen).mul_(std)
+            shard = shard_for_tp(ps, full, self.spec, self.tp_rank, self.tp_size)
+            self.params[ps.name].copy_(shard.to(self.dtype))
+
+    def load_named(self, tensors: dict[str, torch.Tensor], full_tensors: bool = True) -> None:
+        for ps in self.specs:
+            t = tensors[ps.name]
+            if full_tensors:
+                t = shard_for_tp(ps, t, self.spec, self.tp_rank, self.tp_size)
+            self.params[ps.name].copy_(t.to(self.dtype))
+
+    def named_cpu_params(self) -> dict[str, torch.Tensor]:
+        return {ps.name: self.params[ps.name].detach().to("cpu").clone() for ps in self.specs}

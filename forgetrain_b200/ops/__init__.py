@@ -1,0 +1,91 @@
+"""Op layer: one function per op, routed by device.
+
+CUDA tensors always run the hand-written sm_100a kernels of the native library
+(:mod:`forgetrain_b200.ops.cuda_ops`); CPU tensors run the plain PyTorch statement of the same
+op (:mod:`forgetrain_b200.ops.reference`), which is also the oracle of the kernel tests. There
+is no library fallback for CUDA tensors: if the native library cannot be loaded the call
+raises.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import reference as _ref
+
+
+def _cuda():
+    from . import cuda_ops
+    return cuda_ops
+
+
+def _pick(t: torch.Tensor):
+    return _cuda() if t.is_cuda else _ref
+
+
+def embedding_fwd(ids, w, scale, vocab_start: int = 0):
+    if w.is_cuda:
+        return _cuda().embedding_fwd(ids, w, scale, vocab_start)
+    if vocab_start == 0 and int(ids.max()) < w.shape[0]:
+        return _ref.embedding_fwd(ids, w, scale)
+    flat = ids.reshape(-1) - vocab_start
+    ok = (flat >= 0) & (flat < w.shape[0])
+    out = torch.zeros(flat.numel(), w.shape[1], dtype=w.dtype)
+    out[ok] = (w[flat[ok]].float() * scale).to(w.dtype)
+    return out
+
+
+def embedding_bwd(ids, dy, scale, dw, vocab_start: int = 0):
+    return _pick(dy).embedding_bwd(ids, dy, scale, dw, vocab_start)
+
+
+def add_rmsnorm_fwd(res, x, w, eps):
+    return _pick(x).add_rmsnorm_fwd(res, x, w, eps)
+
+
+def rmsnorm_bwd(dy, h, w, rstd, dres, dw, accumulate):
+    return _pick(dy).rmsnorm_bwd(dy, h, w, rstd, dres, dw, accumulate)
+
+
+def rope_(qkv, cos, sin, batch, n_groups, heads_per_group, head_dim, inverse=False,
+          position_ids=None):
+    return _pick(qkv).rope_(qkv, cos, sin, batch, n_groups, heads_per_group, head_dim,
+                            inverse=inverse, position_ids=position_ids)
+
+
+def attention_fwd(qkv, batch, n_groups, heads_per_group, head_dim, scale=None):
+    return _pick(qkv).attention_fwd(qkv, batch, n_groups, heads_per_group, head_dim, scale)
+
+
+def attention_bwd(dout, qkv, out, lse, batch, n_groups, heads_per_group, head_dim, scale=None):
+    return _pick(qkv).attention_bwd(dout, qkv, out, lse, batch, n_groups, heads_per_group,
+                                    head_dim, scale)
+
+
+def swiglu_fwd(y1):
+    return _pick(y1).swiglu_fwd(y1)
+
+
+def swiglu_bwd(dact, y1):
+    return _pick(y1).swiglu_bwd(dact, y1)
+
+
+def linear_fwd(x, w, alpha: float = 1.0):
+    return _pick(x).linear_fwd(x, w, alpha)
+
+
+def linear_dgrad(dy, w, alpha: float = 1.0):
+    return _pick(dy).linear_dgrad(dy, w, alpha)
+
+
+def linear_wgrad(dy, x, out, accumulate: bool, alpha: float = 1.0):
+    return _pick(dy).linear_wgrad(dy, x, out, accumulate, alpha)
+
+
+def cross_entropy_fwd_bwd(logits, labels, mask, loss_scale, valid=None, vocab_start=0,
+                          stats_reduce=None):
+    return _pick(logits).cross_entropy_fwd_bwd(logits, labels, mask, loss_scale, valid,
+                                               vocab_start, stats_reduce)
+
+
+def rope_tables(seq_len, head_dim, base, device=None):
+    return _ref.rope_tables(seq_len, head_dim, base, device=device)

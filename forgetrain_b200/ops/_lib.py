@@ -42,10 +42,47 @@ def lib():
             from .. import build as _build
             _build.build()
         try:
-            _LIB = ctypes.CDLL(str(LIB_PATH))
+            _LIB = _CountingLib(ctypes.CDLL(str(LIB_PATH)))
         except OSError as e:  # pragma: no cover - depends on the box
             raise NativeLibraryMissing(f"cannot load {LIB_PATH}: {e}") from e
         return _LIB
+
+
+# kernels launched per entry point (entry points not listed launch one kernel)
+_KERNELS_PER_CALL = {"ft_rmsnorm_bwd": 2, "ft_attn_bwd": 3, "ft_rmsnorm_bwd_partials": 0,
+                     "ft_tmap_cache_clear": 0}
+_LAUNCHES = [0]
+
+
+class _CountingLib:
+    """Forwards to the ctypes library and counts the kernels this process launched."""
+
+    def __init__(self, cdll):
+        self._cdll = cdll
+        self._cache = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._cdll, name)
+            n = _KERNELS_PER_CALL.get(name, 1)
+
+            def fn(*a, _raw=raw, _n=n):
+                _LAUNCHES[0] += _n
+                return _raw(*a)
+            self._cache[name] = fn
+        return fn
+
+    def has(self, name: str) -> bool:
+        return hasattr(self._cdll, name)
+
+
+def launch_count() -> int:
+    return _LAUNCHES[0]
+
+
+def reset_launch_count() -> None:
+    _LAUNCHES[0] = 0
 
 
 def available() -> bool:

@@ -46,8 +46,6 @@ def attention_bwd(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse:
     S = T // batch
     scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
     L = _lib.lib()
-    if not hasattr(L, "ft_attn_bwd"):
-        raise _lib.NativeLibraryMissing("native library was built without the attention backward")
     dqkv = torch.empty_like(qkv)
     Hq = n_groups * heads_per_group
     # fp32 scratch: accumulator laid out like qkv, and [delta | lse*log2(e)] per (b, head, s)

@@ -102,8 +102,8 @@ def rope_(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, batch: int, n
     if inverse:
         s = -s
     for col in _qk_column_slices(n_groups, heads_per_group, head_dim):
-        x1 = qkv[:, col:col + half].float()
-        x2 = qkv[:, col + half:col + head_dim].float()
+        x1 = qkv[:, col:col + half].float().clone()
+        x2 = qkv[:, col + half:col + head_dim].float().clone()
         qkv[:, col:col + half] = (x1 * c - x2 * s).to(qkv.dtype)
         qkv[:, col + half:col + head_dim] = (x2 * c + x1 * s).to(qkv.dtype)
     return qkv

@@ -1,0 +1,226 @@
+"""ZeRO-1 sharded AdamW over the flat buffers.
+
+Each data-parallel rank keeps fp32 master weights and both moments only for its shard of every
+gradient bucket. One fused kernel launch per bucket applies clip * grad, the moment updates,
+bias correction, decoupled weight decay and the per-parameter muP learning-rate multiplier
+(from a small segment table), and writes the new bf16 value directly at the shard's position in
+the flat parameter buffer, which is the all-gather destination, so the all-gather runs in
+place with no packing. Every per-step scalar (lr, bias corrections, clip coefficient) lives in
+a device vector, which keeps the launches graph-capturable.
+
+Numerics follow the reference's fused kernel
+(exports/train_engine_0.5B/src/training_engine_tensor/triton_kernels.py:414-607) and its
+sharded driver (optimizer.py:633-748): beta = (0.9, 0.95), eps 1e-8, weight decay only on
+matrices, hidden matrices at lr / (hidden / 256) under muP.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ops import reference as ref_ops
+from ..parallel.buckets import Bucket
+
+
+class ShardedAdamW:
+    def __init__(self, store, buckets: list[Bucket], world: int, rank: int, group, *,
+                 beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, max_grad_norm=1.0,
+                 mup_lr_scaling=True, norm_reduce=None, comm_stream=None, fused=None):
+        self.store = store
+        self.buckets = buckets
+        self.world, self.rank, self.group = world, rank, group
+        self.beta1, self.beta2, self.eps = beta1, beta2, eps
+        self.weight_decay = weight_decay
+        self.max_grad_norm = max_grad_norm
+        self.norm_reduce = norm_reduce    # callable summing the squared norm over all ranks
+        self.step_count = 0
+        self.fused = fused
+        dev = store.device
+        self.is_cuda = dev.type == "cuda"
+        self.comm_stream = comm_stream
+        total_shard = sum(b.shard_size(world) for b in buckets)
+        self.master = torch.empty(total_shard, dtype=torch.float32, device=dev)
+        self.exp_avg = torch.zeros(total_shard, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(total_shard, dtype=torch.float32, device=dev)
+        self.shard_off: list[int] = []
+        off = 0
+        for b in buckets:
+            self.shard_off.append(off)
+            off += b.shard_size(world)
+        lr_div = store.spec.mup_width_scale if (mup_lr_scaling and store.spec.mup_enabled) else 1.0
+        # per-bucket segment tables over the shard
+        self.segments: list[list[tuple[int, float, float, str]]] = []
+        self.seg_dev: list[tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = []
+        for b in buckets:
+            s_lo, s_hi = b.shard_range(rank, world)
+            segs = []
+            for name in b.params:
+                p_lo = b.start + b.param_offsets[name]
+                p_hi = p_lo + b.param_sizes[name]
+                a, z = max(p_lo, s_lo), min(p_hi, s_hi)
+                if z <= a:
+                    continue
+                ps = store.by_name[name]
+                wd = weight_decay if ps.has_weight_decay else 0.0
+                lrm = 1.0 / lr_div if ps.mup_lr_scaled else 1.0
+                segs.append((z - s_lo, wd, lrm, name))
+            if not segs:
+                segs.append((s_hi - s_lo, 0.0, 1.0, ""))
+            self.segments.append(segs)
+            if self.is_cuda:
+                self.seg_dev.append((
+                    torch.tensor([s[0] for s in segs], dtype=torch.int64, device=dev),
+                    torch.tensor([s[1] for s in segs], dtype=torch.float32, device=dev),
+                    torch.tensor([s[2] for s in segs], dtype=torch.float32, device=dev)))
+        self.hyper = torch.zeros(8, dtype=torch.float32, device=dev)
+        self.hyper_host = torch.zeros(8, dtype=torch.float32)
+        if self.is_cuda:
+            self.hyper_host = self.hyper_host.pin_memory()
+        self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.sumsq_total = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.ag_events: list = [None] * len(buckets)
+        self.sync_master_from_params()
+
+    # ------------------------------------------------------------------ state plumbing
+    def master_view(self, i: int) -> torch.Tensor:
+        o = self.shard_off[i]
+        return self.master[o:o + self.buckets[i].shard_size(self.world)]
+
+    def _views(self, i: int):
+        o = self.shard_off[i]
+        n = self.buckets[i].shard_size(self.world)
+        return self.master[o:o + n], self.exp_avg[o:o + n], self.exp_avg_sq[o:o + n]
+
+    def sync_master_from_params(self) -> None:
+        for i, b in enumerate(self.buckets):
+            lo, hi = b.shard_range(self.rank, self.world)
+            self.master_view(i).copy_(self.store.flat_params[lo:hi].float())
+
+    def sync_params_from_master(self) -> None:
+        for i, b in enumerate(self.buckets):
+            lo, hi = b.shard_range(self.rank, self.world)
+            self.store.flat_params[lo:hi].copy_(self.master_view(i).to(self.store.dtype))
+        self.all_gather_params()
+
+    # ------------------------------------------------------------------ one step
+    def compute_clip(self, local_sumsq: torch.Tensor) -> None:
+        """All-reduce the squared norm, derive ``clip = min(1, max/(norm+1e-6))`` on device."""
+        self.sumsq_total.copy_(local_sumsq)
+        if self.norm_reduce is not None:
+            self.norm_reduce(self.sumsq_total)
+        if self.is_cuda:
+            from ..ops import cuda_ops
+            cuda_ops.clip_coef(self.sumsq_total, float(self.max_grad_norm), self.hyper,
+                               self.grad_norm)
+        else:
+            nrm = self.sumsq_total.sqrt()
+            self.grad_norm.copy_(nrm)
+            clip = 1.0 if self.max_grad_norm <= 0 else min(1.0, self.max_grad_norm / (float(nrm) + 1e-6))
+            self.hyper[6] = clip
+
+    def step(self, lr: float) -> None:
+        """Update this rank's shard of every bucket, then all-gather the bf16 parameters."""
+        self.step_count += 1
+        t = self.step_count
+        h = self.hyper_host
+        h[0], h[1], h[2], h[3] = lr, self.beta1, self.beta2, self.eps
+        h[4], h[5] = 1.0 - self.beta1 ** t, 1.0 - self.beta2 ** t
+        # slots 6 (clip) and 7 are device-owned: copy only the first six
+        self.hyper[:6].copy_(h[:6], non_blocking=True)
+        flat_g, flat_p = self.store.flat_grads, self.store.flat_params
+        for i, b in enumerate(self.buckets):
+            lo, hi = b.shard_range(self.rank, self.world)
+            p32, m, v = self._views(i)
+            if self.is_cuda:
+                from ..ops import cuda_ops
+                se, sw, sl = self.seg_dev[i]
+                cuda_ops.adamw_flat(p32, m, v, flat_g[lo:hi], flat_p[lo:hi], self.hyper, se, sw, sl)
+            else:
+                clip = float(self.hyper[6])
+                a = 0
+                for end, wd, lrm, _ in self.segments[i]:
+                    ref_ops.adamw_step(p32[a:end], m[a:end], v[a:end], flat_g[lo + a:lo + end],
+                                       flat_p[lo + a:lo + end], lr * lrm, self.beta1, self.beta2,
+                                       self.eps, wd, t, clip)
+                    a = end
+            self._all_gather_bucket(i, b)
+
+    def _all_gather_bucket(self, i: int, b: Bucket) -> None:
+        if self.world == 1:
+            return
+        lo, hi = b.shard_range(self.rank, self.world)
+        full = self.store.flat_params[b.start:b.start + b.size]
+        shard = self.store.flat_params[lo:hi]
+        if self.fused is not None:
+            self.fused.all_gather_bucket(b)
+            return
+        if self.is_cuda and self.comm_stream is not None:
+            ev = torch.cuda.Event()
+            ev.record()
+            self.comm_stream.wait_event(ev)
+            with torch.cuda.stream(self.comm_stream):
+                dist.all_gather_into_tensor(full, shard, group=self.group)
+                done = torch.cuda.Event()
+                done.record()
+                self.ag_events[i] = done
+        elif self.is_cuda:
+            dist.all_gather_into_tensor(full, shard, group=self.group)
+        else:
+            parts = [torch.empty_like(shard) for _ in range(self.world)]
+            dist.all_gather(parts, shard.clone(), group=self.group)
+            full.copy_(torch.cat(parts))
+
+    def all_gather_params(self) -> None:
+        for i, b in enumerate(self.buckets):
+            self._all_gather_bucket(i, b)
+        self.wait_all_gathers()
+
+    def wait_all_gathers(self) -> None:
+        if self.fused is not None:
+            self.fused.wait_all_gathers()
+        for i, ev in enumerate(self.ag_events):
+            if ev is not None:
+                torch.cuda.current_stream().wait_event(ev)
+                self.ag_events[i] = None
+
+    # ------------------------------------------------------------------ checkpoint support
+    def gather_full_state(self) -> dict[str, dict[str, torch.Tensor]]:
+        """Rank-count independent optimizer state: per-parameter fp32 tensors on CPU."""
+        out = {"master_weights": {}, "exp_avg": {}, "exp_avg_sq": {}}
+        for field, flat in (("master_weights", self.master), ("exp_avg", self.exp_avg),
+                            ("exp_avg_sq", self.exp_avg_sq)):
+            for i, b in enumerate(self.buckets):
+                n = b.shard_size(self.world)
+                shard = flat[self.shard_off[i]:self.shard_off[i] + n]
+                if self.world > 1:
+                    if self.is_cuda:
+                        full = torch.empty(b.size, dtype=torch.float32, device=shard.device)
+                        dist.all_gather_into_tensor(full, shard.contiguous(), group=self.group)
+                    else:
+                        parts = [torch.empty_like(shard) for _ in range(self.world)]
+                        dist.all_gather(parts, shard.contiguous(), group=self.group)
+                        full = torch.cat(parts)
+                else:
+                    full = shard
+                for name in b.params:
+                    o = b.param_offsets[name]
+                    n_el = self.store.numel(name)
+                    out[field][name] = full[o:o + n_el].view(self.store.shapes[name]).cpu().clone()
+        return out
+
+    def load_full_state(self, state: dict, step_count: int) -> None:
+        for field, flat in (("master_weights", self.master), ("exp_avg", self.exp_avg),
+                            ("exp_avg_sq", self.exp_avg_sq)):
+            src = state[field]
+            for i, b in enumerate(self.buckets):
+                s_lo, s_hi = b.shard_range(self.rank, self.world)
+                base = self.shard_off[i]
+                for name in b.params:
+                    p_lo = b.start + b.param_offsets[name]
+                    n_el = self.store.numel(name)
+                    a, z = max(p_lo, s_lo), min(p_lo + n_el, s_hi)
+                    if z <= a:
+                        continue
+                    t = src[name].reshape(-1)[a - p_lo:z - p_lo]
+                    flat[base + a - s_lo:base + z - s_lo].copy_(t.to(flat.device))
+        self.step_count = int(step_count)

@@ -1,0 +1,94 @@
+"""Process topology: DP x TP mesh on one node, process groups, device binding.
+
+Tensor-parallel groups are consecutive ranks, data-parallel groups are strided by the TP
+degree (reference: exports/train_engine_8b/src/training_engine_tensor/nccl.py:36-67). One
+process drives one GPU; on CPU (gloo) the same code runs for plumbing tests.
+"""
+from __future__ import annotations
+
+import datetime
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class Topology:
+    rank: int = 0
+    world: int = 1
+    local_rank: int = 0
+    tp_size: int = 1
+    dp_size: int = 1
+    tp_rank: int = 0
+    dp_rank: int = 0
+    tp_group: object = None
+    dp_group: object = None
+    replica_group: object = None
+    replica_size: int = 1
+    device: torch.device = torch.device("cpu")
+    backend: str = "none"
+
+    @property
+    def distributed(self) -> bool:
+        return self.world > 1
+
+
+def resolve_env() -> tuple[int, int, int]:
+    return (int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
+            int(os.environ.get("LOCAL_RANK", "0")))
+
+
+def init_topology(tp_size: int = 1, device: str | None = None, backend: str | None = None,
+                  timeout_s: int = 600, num_kv_groups: int | None = None) -> Topology:
+    """Bring up ``torch.distributed`` (when WORLD_SIZE > 1) and the DP / TP groups."""
+    rank, world, local_rank = resolve_env()
+    use_cuda = torch.cuda.is_available() and (device is None or str(device).startswith("cuda"))
+    if use_cuda:
+        torch.cuda.set_device(local_rank % torch.cuda.device_count())
+        dev = torch.device("cuda", torch.cuda.current_device())
+    else:
+        dev = torch.device("cpu")
+    backend = backend or ("nccl" if use_cuda else "gloo")
+    if world % tp_size:
+        raise ValueError(f"world size {world} is not a multiple of the TP degree {tp_size}")
+    topo = Topology(rank=rank, world=world, local_rank=local_rank, tp_size=tp_size,
+                    dp_size=world // tp_size, tp_rank=rank % tp_size, dp_rank=rank // tp_size,
+                    device=dev, backend=backend if world > 1 else "none")
+    if world == 1:
+        return topo
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        kw = dict(backend=backend, rank=rank, world_size=world,
+                  timeout=datetime.timedelta(seconds=timeout_s))
+        if use_cuda:
+            kw["device_id"] = dev
+        dist.init_process_group(**kw)
+    # every rank must create every group, in the same order
+    for d in range(topo.dp_size):
+        ranks = list(range(d * tp_size, (d + 1) * tp_size))
+        g = dist.new_group(ranks) if tp_size > 1 else None
+        if d == topo.dp_rank:
+            topo.tp_group = g
+    for t in range(tp_size):
+        ranks = list(range(t, world, tp_size))
+        g = dist.new_group(ranks) if topo.dp_size > 1 else None
+        if t == topo.tp_rank:
+            topo.dp_group = g
+    if num_kv_groups and tp_size > num_kv_groups:
+        rep = tp_size // num_kv_groups
+        topo.replica_size = rep
+        for d in range(topo.dp_size):
+            for kg in range(num_kv_groups):
+                ranks = [d * tp_size + kg * rep + i for i in range(rep)]
+                g = dist.new_group(ranks)
+                if rank in ranks:
+                    topo.replica_group = g
+    return topo
+
+
+def shutdown() -> None:
+    if dist.is_available() and dist.is_initialized():
+        dist.destroy_process_group()

@@ -1,0 +1,303 @@
+"""Training engine: one object that owns parameters, model, gradient reducer and optimizer,
+and a loop around it.
+
+``Trainer.train_step`` is the public per-step call: micro-batch loop (forward, fused
+cross-entropy, backward writing gradients into the flat buffer), bucket reductions overlapped
+with the last backward, device-side gradient norm and clip coefficient, sharded fused AdamW and
+the in-place bf16 parameter all-gather. Nothing in the step synchronises the host; the returned
+loss and gradient norm are device tensors. ``run_training_loop`` wraps it with the data
+pipeline, logging (same line formats as the reference), MFU accounting, the segment profiler
+and periodic asynchronous checkpoints. Counterpart of the reference's
+``run_training_loop`` (exports/train_engine_0.5B/src/training_engine_tensor/train_loop.py:400-1061)
+and ``_run_training_distributed`` (exports/train_engine_8b/src/training_engine_tensor/entry.py:298-780).
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+import time
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+from . import config as cfgmod
+from .ckpt import checkpoint as ckpt
+from .config import ModelSpec
+from .data.prefetch import DataPrefetcher
+from .data.synthetic import SyntheticTokenSource
+from .engine_config import EngineConfig
+from .models.minicpm4 import MiniCPM4
+from .models.params import ALIGN_ELEMS, ParamStore
+from .optim.adamw import ShardedAdamW
+from .optim.lr import compute_lr
+from .parallel.dp import BucketedGradReducer
+from .parallel.topology import Topology
+from .parallel.tp import TPContext
+from .utils.profiler import StepProfiler, profiler_from_config
+
+
+def _dtype_of(cfg: EngineConfig, device: torch.device) -> torch.dtype:
+    return torch.bfloat16 if cfg.dtype == "bf16" else torch.float32
+
+
+class Trainer:
+    def __init__(self, spec: ModelSpec, cfg: EngineConfig, topo: Topology, *, seq_length: int,
+                 micro_batch_size: int, seed: int = 1234, max_seq_len: int | None = None):
+        self.spec, self.cfg, self.topo = spec, cfg, topo
+        self.seq_length, self.mbs = seq_length, micro_batch_size
+        dev = topo.device
+        self.device = dev
+        self.dtype = _dtype_of(cfg, dev)
+        if dev.type == "cuda" and self.dtype != torch.bfloat16:
+            raise ValueError("the CUDA path is bf16-only; use --dtype bf16 on GPUs")
+        dp, tp = topo.dp_size, topo.tp_size
+        self.tp_ctx = TPContext(topo.tp_group, tp, topo.tp_rank, cfg.sequence_parallel,
+                                topo.replica_group, topo.replica_size)
+        # --- fused peer-memory communication (GPU, >1 rank, comm == "fused")
+        self.fused_dp = None
+        self.symm = None
+        grad_buffer = None
+        want_fused = (cfg.comm == "fused" and dev.type == "cuda" and dp > 1)
+        pad = ALIGN_ELEMS * dp
+        self.store = None
+        if want_fused:
+            from .parallel import fused_dp
+            probe = ParamStore.layout_total(spec, cfg.mtp_num_layers, tp, pad)
+            self.symm = fused_dp.SymmetricGradBuffer(probe, topo)
+            grad_buffer = self.symm.local_tensor
+        self.store = ParamStore(spec, dev, self.dtype, cfg.mtp_num_layers, topo.tp_rank, tp,
+                                pad_to=pad, grad_buffer=grad_buffer, align=pad)
+        if cfg.random_init:
+            self.store.init_random(seed, cfg.init_scheme, cfg.init_std)
+        self.model = MiniCPM4(spec, self.store, self.tp_ctx, max_seq_len=max_seq_len or seq_length)
+        self.mtp = None
+        if cfg.mtp_num_layers > 0:
+            from .models.mtp import MTPHead
+            self.mtp = MTPHead(self.model, cfg.mtp_num_layers, cfg.mtp_loss_scaling_factor)
+        target = cfg.wgrad_bucket_target_elems
+        if cfg.rs_buckets > 0 and tp > 1:
+            target = max(1, self.store.total // cfg.rs_buckets)
+        norm_exclude = []
+        if tp > 1 and topo.tp_rank > 0:
+            for ps in self.store.order:
+                if ps.is_norm:
+                    o = self.store.offsets[ps.name]
+                    norm_exclude.append((o, o + self.store.numel(ps.name)))
+        if want_fused:
+            from .parallel import fused_dp
+            self.fused_dp = fused_dp.FusedDPComm(self.symm, self.store, topo)
+        self.reducer = BucketedGradReducer(
+            self.store.flat_grads, self.store.entries(), dp, topo.dp_rank, topo.dp_group, target,
+            backend=cfg.comm, overlap=cfg.wgrad_overlap and not cfg.serial_streams,
+            norm_exclude=norm_exclude, fused=self.fused_dp)
+        norm_reduce = None
+        if topo.world > 1:
+            norm_reduce = (lambda t: dist.all_reduce(t))  # world group: DP shards x TP shards
+        self.opt = ShardedAdamW(
+            self.store, self.reducer.buckets, dp, topo.dp_rank, topo.dp_group,
+            beta1=cfg.adam_beta1, beta2=cfg.adam_beta2, eps=cfg.adam_eps,
+            weight_decay=cfg.weight_decay,
+            max_grad_norm=0.0 if cfg.no_grad_clip else cfg.max_grad_norm,
+            mup_lr_scaling=cfg.mup_lr_scaling, norm_reduce=norm_reduce,
+            comm_stream=self.reducer.comm_stream if cfg.opt_allgather_overlap else None,
+            fused=self.fused_dp)
+        self.num_samples = 0
+        self.loss_buf = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.graph = None
+        self.launch_count = 0
+
+    # ------------------------------------------------------------------ helpers
+    def _grad_ready(self, name: str) -> None:
+        ps = self.store.by_name.get(name)
+        if ps is not None and ps.is_norm and self.tp_ctx.sequence_parallel:
+            self.tp_ctx.all_reduce_(self.store.grads[name])
+        self.reducer.on_grad_ready(name)
+
+    def current_lr(self) -> float:
+        c = self.cfg
+        return compute_lr(self.opt.step_count, c.max_lr, c.min_lr, c.warmup_iters, c.lr_decay_iters,
+                          c.wsd_decay_iters)
+
+    def _micro_batch(self, batch, loss_scale: float, accumulate: bool, last: bool):
+        grad_ready = self._grad_ready if last else None
+        tokens, labels = batch["tokens"], batch["labels"]
+        mask = batch.get("loss_mask")
+        pos = batch.get("position_ids")
+        m = self.model
+        if self.mtp is None:
+            return m.forward_backward(tokens, labels, mask, loss_scale, accumulate, grad_ready, pos)
+        return self.mtp.forward_backward(tokens, labels, mask, loss_scale, accumulate, grad_ready, pos)
+
+    # ------------------------------------------------------------------ the step
+    def train_step(self, micro_batches: list[dict], profiler: StepProfiler | None = None) -> dict:
+        """One optimizer step over ``micro_batches`` (device tensors). Returns device-side
+        ``loss`` (mean over micro-batches and DP ranks) and ``grad_norm`` plus the ``lr`` used."""
+        n = len(micro_batches)
+        prof = profiler
+        if prof:
+            prof.mark("step_start")
+        self.opt.wait_all_gathers()
+        self.reducer.start_step()
+        self.loss_buf.zero_()
+        for i, batch in enumerate(micro_batches):
+            loss = self._micro_batch(batch, 1.0 / n, accumulate=i > 0, last=(i == n - 1))
+            self.loss_buf += loss.detach().reshape(1) / n
+            self.num_samples += batch["tokens"].shape[0] * self.topo.dp_size
+        if prof:
+            prof.mark("microbatches")
+        self.reducer.wait_all()
+        if prof:
+            prof.mark("reduce_scatter")
+        self.opt.compute_clip(self.reducer.local_sumsq())
+        if prof:
+            prof.mark("grad_norm")
+        lr = self.current_lr()
+        self.opt.step(lr)
+        if prof:
+            prof.mark("optimizer")
+        if self.topo.dp_size > 1:
+            dist.all_reduce(self.loss_buf, group=self.topo.dp_group)
+            self.loss_buf /= self.topo.dp_size
+        if prof:
+            prof.mark("loss_allreduce")
+        return {"loss": self.loss_buf, "grad_norm": self.opt.grad_norm, "lr": lr}
+
+    # ------------------------------------------------------------------ checkpoint
+    def save(self, save_dir, step: int, dataloader_state=None, async_io=True):
+        """Rank-count independent checkpoint: DP shards of the optimizer state are gathered;
+        with TP > 1 every TP rank of DP rank 0 writes its own ``rank_<R>.pt`` shard."""
+        opt_state = self.opt.gather_full_state()
+        opt_state["step_count"] = self.opt.step_count
+        opt_state["num_samples"] = self.num_samples
+        names = [ps.name for ps in self.store.specs]
+        params = {n: self.store.params[n] for n in names}
+        if self.topo.tp_size == 1:
+            return ckpt.save_checkpoint(save_dir, step, params=params, param_names=names,
+                                        optimizer_state=opt_state, num_samples=self.num_samples,
+                                        dataloader_state=dataloader_state, rank=self.topo.rank,
+                                        async_io=async_io)
+        writer = 0 if self.topo.dp_rank == 0 else 1
+        return ckpt.save_checkpoint(save_dir, step, params=params, param_names=names,
+                                    optimizer_state=opt_state, num_samples=self.num_samples,
+                                    dataloader_state=dataloader_state, rank=writer,
+                                    async_io=async_io, filename=f"rank_{self.topo.tp_rank}.pt",
+                                    extra={"tp_size": self.topo.tp_size, "tp_rank": self.topo.tp_rank})
+
+    def load(self, path) -> dict:
+        p = Path(path)
+        if self.topo.tp_size > 1:
+            if p.is_dir() and not (p / f"rank_{self.topo.tp_rank}.pt").exists():
+                cands = sorted(q for q in p.glob("step_*") if (q / f"rank_{self.topo.tp_rank}.pt").exists())
+                p = cands[-1]
+            state = torch.load(p / f"rank_{self.topo.tp_rank}.pt", map_location="cpu", weights_only=False)
+            self.store.load_named(state["params"], full_tensors=False)
+        else:
+            state = ckpt.load_resume_checkpoint(p, expected_vocab=self.spec.vocab_size)
+            self.store.load_named(state["params"], full_tensors=True)
+        ost = state.get("optimizer_state")
+        if ost:
+            self.opt.load_full_state(ost, ost.get("step_count", state.get("step", 0)))
+            self.num_samples = int(ost.get("num_samples", state.get("num_samples", 0)))
+        else:
+            self.opt.sync_master_from_params()
+        return state
+
+
+# ---------------------------------------------------------------------------------------------
+# loop
+# ---------------------------------------------------------------------------------------------
+def _log(topo: Topology, msg: str) -> None:
+    if topo.rank == 0:
+        print(msg, flush=True)
+
+
+def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num_steps: int,
+                      micro_batch_size: int, seq_length: int, num_local_microbatches: int = 1,
+                      seed: int = 1234, save_dir: str | None = None, save_interval: int = 0,
+                      resume: str | None = None, data_source=None, dump_inputs_dir: str | None = None,
+                      report_path: str | None = None, log_every: int = 1) -> dict:
+    """Train ``num_steps`` optimizer steps; returns ``{"steps": [per-step dicts], ...}``."""
+    trainer = Trainer(spec, cfg, topo, seq_length=seq_length, micro_batch_size=micro_batch_size,
+                      seed=seed)
+    start_step = 0
+    source = data_source or SyntheticTokenSource(spec.vocab_size, micro_batch_size, seq_length,
+                                                 seed=seed, dp_rank=topo.dp_rank,
+                                                 pin=topo.device.type == "cuda")
+    if resume:
+        state = trainer.load(resume)
+        start_step = int(state.get("step", 0))
+        if hasattr(source, "load_state_dict"):
+            source.load_state_dict(state.get("dataloader_state") or {})
+        _log(topo, f"resumed from {resume} at step {start_step}")
+    prefetch = DataPrefetcher(source, topo.device, depth=cfg.data_prefetch_depth)
+    profiler = profiler_from_config(cfg, rank=topo.rank)
+    tokens_per_step = micro_batch_size * seq_length * num_local_microbatches * topo.dp_size
+    flops_hw = cfgmod.compute_training_flops(spec, tokens_per_step, seq_length, cfg.mtp_num_layers)
+    flops_std = cfgmod.compute_training_flops_standard(spec, tokens_per_step, seq_length,
+                                                       cfg.mtp_num_layers)
+    peak = cfgmod.peak_tflops() * 1e12 * topo.world
+    cuda = topo.device.type == "cuda"
+    results = []
+    _log(topo, f"[engine] model={spec.name} params={spec.num_parameters(cfg.mtp_num_layers)/1e6:.1f}M "
+               f"world={topo.world} dp={topo.dp_size} tp={topo.tp_size} mbs={micro_batch_size} "
+               f"seq={seq_length} microbatches={num_local_microbatches} dtype={cfg.dtype} "
+               f"comm={cfg.comm} data={'synthetic' if data_source is None else 'custom'}")
+    for step in range(start_step, start_step + num_steps):
+        if cuda:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+        t0 = time.perf_counter()
+        if profiler:
+            profiler.begin_step(step)
+        mbs = [next(prefetch) for _ in range(num_local_microbatches)]
+        if dump_inputs_dir and topo.rank == 0:
+            Path(dump_inputs_dir).mkdir(parents=True, exist_ok=True)
+            torch.save({k: v.cpu() for k, v in mbs[0].items()},
+                       Path(dump_inputs_dir) / f"inputs_step{step:07d}.pt")
+        out = trainer.train_step(mbs, profiler)
+        if cuda:
+            ev1.record()
+            torch.cuda.synchronize()
+            dt = ev0.elapsed_time(ev1) / 1e3
+            from .ops import _lib
+            _lib.check_status(topo.device)
+        else:
+            dt = time.perf_counter() - t0
+        if topo.world > 1:  # step time = max over ranks
+            tt = torch.tensor([dt], dtype=torch.float64, device=topo.device)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            dt = float(tt)
+        if profiler:
+            profiler.end_step()
+        loss, gnorm = float(out["loss"]), float(out["grad_norm"])
+        rec = {"step": step + 1, "loss": loss, "local_loss": loss, "grad_norm": gnorm,
+               "lr": out["lr"], "total_step_time": dt, "mfu_e2e": flops_hw / dt / peak,
+               "mfu_e2e_standard": flops_std / dt / peak,
+               "tokens_per_sec_per_gpu": tokens_per_step / dt / topo.world}
+        results.append(rec)
+        if (step + 1) % log_every == 0:
+            _log(topo, f" iteration {step + 1:8d} | loss {loss:.6E} | local_loss {loss:.6E} | "
+                       f"grad norm {gnorm:.4f} | lr {out['lr']:.4E} | time(ms) {dt * 1e3:.1f} | "
+                       f"tok/s/gpu {rec['tokens_per_sec_per_gpu']:.0f} | mfu {rec['mfu_e2e_standard'] * 100:.2f}%")
+            if cfg.emit_loss_lines:
+                _log(topo, f"[LOSS] step={step + 1} global_loss={loss:.8f} grad_norm={gnorm:.6f} "
+                           f"time_s={dt:.4f} mfu_e2e_standard={rec['mfu_e2e_standard']:.4f}")
+        if not math.isfinite(loss):
+            raise FloatingPointError(f"non-finite loss at step {step + 1}")
+        done = step + 1
+        if save_dir and ckpt.should_save_after_step(done, start_step + num_steps, save_interval,
+                                                    start_step):
+            trainer.save(save_dir, done, dataloader_state=getattr(source, "state_dict", dict)())
+    ckpt.wait_for_async_save()
+    if profiler:
+        profiler.write()
+    report = {"steps": results, "model": spec.name, "world": topo.world,
+              "tokens_per_step": tokens_per_step}
+    if report_path and topo.rank == 0:
+        tmp = Path(report_path).with_suffix(".tmp")
+        tmp.write_text(json.dumps(report, indent=1))
+        os.replace(tmp, report_path)
+    report["trainer"] = trainer
+    return report
