@@ -52,8 +52,9 @@ struct FaBwdSmem {
   static constexpr int V_OFF = TILE;
   static constexpr int QDO_OFF = 2 * TILE;             // QS x (Q tile, dO tile)
   static constexpr int PDS_OFF = QDO_OFF + QS * 2 * TILE;  // PB x (P^T 32 KB, dS^T 32 KB)
-  static constexpr int BAR_OFF = PDS_OFF + PB * 65536;
-  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+  static constexpr int STAT_OFF = PDS_OFF + PB * 65536;   // QS x (lse2[128], delta[128]) fp32
+  static constexpr int BAR_OFF = STAT_OFF + QS * 1024;
+  static constexpr int TOTAL = BAR_OFF + 256;             // base must come 1024-byte aligned
 };
 
 template <int D, int QS, int PB>
@@ -63,8 +64,11 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   using L = FaBwdSmem<D, QS, PB>;
   constexpr bool ALIAS = (D == 128);  // dQ shares the TMEM columns of S^T
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {  // swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, FT_ERR_WAIT_MISC);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* kv_full = bars;          // 1
   uint64_t* qdo_full = bars + 1;     // 2
@@ -146,8 +150,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
         const int head = step_head(n), qt = step_qtile(n);
         const int q_col = (grp * (p.g + 2) + head % p.g) * D;
         mbar_wait(&qdo_empty[s], ((n / QS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
-        mbar_expect_tx(&qdo_full[s], 2 * L::TILE);
+        mbar_expect_tx(&qdo_full[s], 2 * L::TILE + 1024);
         uint8_t* dst = smem + L::QDO_OFF + s * 2 * L::TILE;
+        {
+          const long soff = (static_cast<long>(b) * p.Hq + head) * p.S + qt * FAB_BLK;
+          float* st = reinterpret_cast<float*>(smem + L::STAT_OFF + s * 1024);
+          bulk_load_1d(st, p.lse2 + soff, 512, &qdo_full[s]);
+          bulk_load_1d(st + 128, p.delta + soff, 512, &qdo_full[s]);
+        }
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
           tma_load_2d(dst + c * 16384, &tm_qkv, &qdo_full[s], q_col + c * 64,
@@ -239,10 +249,11 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       const int pb = n % PB;
       const int head = step_head(n), qt = step_qtile(n);
       const bool diag = (qt == j);
-      const float* lse2 = p.lse2 + (static_cast<long>(b) * p.Hq + head) * p.S + qt * FAB_BLK;
-      const float* dlt = p.delta + (static_cast<long>(b) * p.Hq + head) * p.S + qt * FAB_BLK;
+      const float* lse2 = reinterpret_cast<const float*>(smem + L::STAT_OFF + (n % QS) * 1024);
+      const float* dlt = lse2 + 128;
       uint8_t* sPt = smem + L::PDS_OFF + pb * 65536;
       uint8_t* sdSt = sPt + 32768;
+      mbar_wait(&qdo_full[n % QS], (n / QS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
       mbar_wait(sdp_full, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
       mbar_wait(&pds_free[pb], ((n / PB) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
       tc_fence_after();
@@ -255,14 +266,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
         float pv[32], ds[32];
 #pragma unroll
         for (int k4 = 0; k4 < 8; ++k4) {
-          const float4 l4 = __ldg(reinterpret_cast<const float4*>(lse2 + c * 32) + k4);
-          const float4 d4 = __ldg(reinterpret_cast<const float4*>(dlt + c * 32) + k4);
+          const float4 l4 = reinterpret_cast<const float4*>(lse2 + c * 32)[k4];
+          const float4 d4 = reinterpret_cast<const float4*>(dlt + c * 32)[k4];
           const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
           const float dv[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int k = k4 * 4 + e;
-            float pe = exp2f(__uint_as_float(s[k]) * p.scale_log2 - lv[e]);
+            float pe = fast_exp2(__uint_as_float(s[k]) * p.scale_log2 - lv[e]);
             if (diag && (c * 32 + k) < r) pe = 0.f;
             pv[k] = pe;
             ds[k] = pe * (__uint_as_float(dp[k]) - dv[e]);

@@ -228,7 +228,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
         tc_fence_after();
       }
       if (__any_sync(0xffffffffu, need)) {
-        const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
+        const float alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
         m_ref = m_new;
         l *= alpha;
         if (j > 0) {
@@ -252,7 +252,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
         float pv[32];
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
-          float v = exp2f(__uint_as_float(s[k]) * p.scale_log2 - m_ref);
+          float v = fast_exp2(__uint_as_float(s[k]) * p.scale_log2 - m_ref);
           if (diag && (c * 32 + k) > r) v = 0.f;
           pv[k] = v;
           l += v;

@@ -232,14 +232,24 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
-// out[c] (=|+=) sum_p partial[p][c]
-__global__ void colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ out,
-                                       int P, int H, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= H) return;
+// out[c] (=|+=) sum_p partial[p][c]. One CTA per 32 columns; 8 row-groups of 32 lanes each
+// walk the partial rows with stride 8 and are folded through shared memory.
+__global__ void __launch_bounds__(256)
+colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ out, int P, int H,
+                       int accumulate) {
+  __shared__ float red[8][32];
+  const int cx = threadIdx.x & 31, px = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float s = 0.f;
-  for (int p = 0; p < P; ++p) s += partial[(long)p * H + c];
-  out[c] = accumulate ? out[c] + s : s;
+  if (c < H)
+    for (int p = px; p < P; p += 8) s += partial[(long)p * H + c];
+  red[px][cx] = s;
+  __syncthreads();
+  if (px == 0 && c < H) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k) s += red[k][cx];
+    out[c] = accumulate ? out[c] + s : s;
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -626,7 +636,7 @@ extern "C" int ft_rmsnorm_bwd_partials(int T, int H) {
   int nv, tpr;
   if (!norm_cfg(H, &nv, &tpr)) return -1;
   const int rows_per_cta = 128 / tpr;
-  return grid_for((long)(T + rows_per_cta - 1) / rows_per_cta, 1, 4);
+  return grid_for((long)(T + rows_per_cta - 1) / rows_per_cta, 1, tpr == 32 ? 6 : 8);
 }
 
 extern "C" int ft_rmsnorm_bwd(const void* dy, const void* h, const void* w, const void* rstd,
@@ -649,8 +659,8 @@ extern "C" int ft_rmsnorm_bwd(const void* dy, const void* h, const void* w, cons
   FT_NORM_DISPATCH(8, 128, CALL_BWD)
 #undef CALL_BWD
   if (cudaGetLastError() != cudaSuccess) return -100;
-  colsum_partials_kernel<<<(H + 255) / 256, 256, 0, st>>>((const float*)dw_partial, (float*)dw,
-                                                          grid, H, accumulate);
+  colsum_partials_kernel<<<(H + 31) / 32, 256, 0, st>>>((const float*)dw_partial, (float*)dw,
+                                                        grid, H, accumulate);
   return FT_LAUNCH_OK();
 }
 
