@@ -15,7 +15,7 @@ import torch
 
 class SyntheticTokenSource:
     def __init__(self, vocab_size: int, micro_batch_size: int, seq_length: int, seed: int = 1234,
-                 dp_rank: int = 0, pin: bool | None = None):
+                 dp_rank: int = 0, pin: bool | None = None, distinct_batches: int = 0):
         self.vocab_size = vocab_size
         self.mbs = micro_batch_size
         self.seq = seq_length
@@ -25,13 +25,21 @@ class SyntheticTokenSource:
         self.gen.manual_seed(seed + 1000003 * dp_rank)
         self.batches_drawn = 0
         self.pin = torch.cuda.is_available() if pin is None else pin
+        # > 0: cycle over that many fixed batches (memorisation runs / loss-decrease checks)
+        self.distinct = distinct_batches
+        self._cache: list[torch.Tensor] = []
 
     def __iter__(self):
         return self
 
     def __next__(self) -> dict[str, torch.Tensor]:
-        chunk = torch.randint(0, self.vocab_size, (self.mbs, self.seq + 1), generator=self.gen,
-                              dtype=torch.int64)
+        if self.distinct > 0 and len(self._cache) == self.distinct:
+            chunk = self._cache[self.batches_drawn % self.distinct]
+        else:
+            chunk = torch.randint(0, self.vocab_size, (self.mbs, self.seq + 1), generator=self.gen,
+                                  dtype=torch.int64)
+            if self.distinct > 0:
+                self._cache.append(chunk)
         self.batches_drawn += 1
         batch = {
             "tokens": chunk[:, :-1].contiguous(),

@@ -231,6 +231,7 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
         if hasattr(source, "load_state_dict"):
             source.load_state_dict(state.get("dataloader_state") or {})
         _log(topo, f"resumed from {resume} at step {start_step}")
+    consumed = int(getattr(source, "batches_drawn", 0))   # batches the model has actually seen
     prefetch = DataPrefetcher(source, topo.device, depth=cfg.data_prefetch_depth)
     profiler = profiler_from_config(cfg, rank=topo.rank)
     tokens_per_step = micro_batch_size * seq_length * num_local_microbatches * topo.dp_size
@@ -252,6 +253,7 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
         if profiler:
             profiler.begin_step(step)
         mbs = [next(prefetch) for _ in range(num_local_microbatches)]
+        consumed += num_local_microbatches
         if dump_inputs_dir and topo.rank == 0:
             Path(dump_inputs_dir).mkdir(parents=True, exist_ok=True)
             torch.save({k: v.cpu() for k, v in mbs[0].items()},
@@ -289,7 +291,10 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
         done = step + 1
         if save_dir and ckpt.should_save_after_step(done, start_step + num_steps, save_interval,
                                                     start_step):
-            trainer.save(save_dir, done, dataloader_state=getattr(source, "state_dict", dict)())
+            ds = dict(getattr(source, "state_dict", dict)())
+            if "batches_drawn" in ds:   # the prefetcher reads ahead: record what was consumed
+                ds["batches_drawn"] = consumed
+            trainer.save(save_dir, done, dataloader_state=ds)
     ckpt.wait_for_async_save()
     if profiler:
         profiler.write()

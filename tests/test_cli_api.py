@@ -1,0 +1,81 @@
+import ast
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_public_api_all_is_importable():
+    import forgetrain_b200 as pkg
+    tree = ast.parse((ROOT / "forgetrain_b200" / "__init__.py").read_text())
+    names = None
+    for node in tree.body:
+        if isinstance(node, ast.Assign) and getattr(node.targets[0], "id", "") == "__all__":
+            names = [e.value for e in node.value.elts]
+    assert names
+    for n in names:
+        assert hasattr(pkg, n), n
+
+
+def test_cli_flags_cover_reference_surface():
+    from forgetrain_b200.cli import build_parser
+    p = build_parser()
+    opts = {o for a in p._actions for o in a.option_strings}
+    for flag in ["--num-steps", "--global-batch-size", "--micro-batch-size", "--seq-length",
+                 "--num-local-microbatches", "--save-interval", "--save-dir", "--resume",
+                 "--mup-emb-scale", "--mup-depth-scale", "--max-lr", "--min-lr", "--warmup-iters",
+                 "--lr-decay-iters", "--wsd-decay-iters", "--mtp-num-layers",
+                 "--mtp-loss-scaling-factor", "--dump-inputs-dir", "--seed", "--device",
+                 "--export-checkpoint-root", "--checkpoint-root", "--hf-dataset", "--tokenizer-path",
+                 "--grad-accum-steps", "--export-report", "--tensor-parallel-size",
+                 "--sequence-parallel", "--no-sequence-parallel", "--comm", "--dtype"]:
+        assert flag in opts, flag
+
+
+def test_resume_save_dir_mutex(tmp_path):
+    from forgetrain_b200.cli import main
+    with pytest.raises(SystemExit):
+        main(["pretrain", "--model", "tiny", "--resume", str(tmp_path), "--save-dir", str(tmp_path)])
+
+
+def test_no_undeclared_environment_reads():
+    """Every os.environ access in the package names a declared variable."""
+    from forgetrain_b200.engine_config import DECLARED_ENV_VARS
+    declared = set(DECLARED_ENV_VARS) | {"FT_BENCH_GRAPH"}
+    for path in (ROOT / "forgetrain_b200").rglob("*.py"):
+        tree = ast.parse(path.read_text())
+        for node in ast.walk(tree):
+            key = None
+            if isinstance(node, ast.Call) and isinstance(node.func, ast.Attribute) \
+                    and node.func.attr in ("get", "setdefault") \
+                    and isinstance(node.func.value, ast.Attribute) and node.func.value.attr == "environ" \
+                    and node.args and isinstance(node.args[0], ast.Constant):
+                key = node.args[0].value
+            if isinstance(node, ast.Subscript) and isinstance(node.value, ast.Attribute) \
+                    and node.value.attr == "environ" and isinstance(node.slice, ast.Constant):
+                key = node.slice.value
+            if key is not None:
+                assert key in declared, f"{path.name}: undeclared env var {key}"
+
+
+def test_cli_pretrain_tiny_cpu_writes_report_and_checkpoint(tmp_path):
+    env = dict(os.environ, OUTPUT_DIR=str(tmp_path / "out"), PYTHONPATH=str(ROOT))
+    (tmp_path / "out").mkdir()
+    r = subprocess.run([sys.executable, "-m", "training_engine_tensor", "pretrain", "--model", "tiny",
+                        "--num-steps", "3", "--device", "cpu", "--micro-batch-size", "1",
+                        "--global-batch-size", "2", "--seq-length", "64", "--save-dir",
+                        str(tmp_path / "ck"), "--save-interval", "2", "--emit-loss-lines"],
+                       capture_output=True, text=True, env=env, cwd=ROOT, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "DONE" in r.stdout and "[LOSS] step=3" in r.stdout and "iteration" in r.stdout
+    rep = json.loads((tmp_path / "out" / "training_report.json").read_text())
+    assert len(rep["steps"]) == 3 and {"loss", "grad_norm", "lr", "total_step_time", "mfu_e2e",
+                                       "mfu_e2e_standard"} <= set(rep["steps"][0])
+    assert (tmp_path / "out" / "3step" / "ours_results.jsonl").exists()
+    assert (tmp_path / "ck" / "step_0000002" / "training_state.pt").exists()
+    assert (tmp_path / "ck" / "step_0000003" / "training_state.pt").exists()

@@ -1,0 +1,83 @@
+import math
+
+import pytest
+
+from forgetrain_b200 import config as C
+from forgetrain_b200 import engine_config as ec
+
+
+def test_builtin_specs_load():
+    s05 = C.load_model_spec("0.5b")
+    assert (s05.hidden_size, s05.num_layers, s05.num_attention_heads, s05.num_query_groups,
+            s05.head_dim, s05.ffn_hidden_size, s05.vocab_size) == (1024, 24, 16, 2, 64, 4096, 73448)
+    s8 = C.load_model_spec("8b")
+    assert (s8.hidden_size, s8.num_layers, s8.head_dim, s8.ffn_hidden_size) == (4096, 32, 128, 16384)
+    assert s8.tensor_model_parallel_size == 2 and s8.sequence_parallel
+    t = C.load_model_spec("tiny")
+    assert t.tie_embeddings and t.vocab_size == 4096
+
+
+def test_mup_helpers():
+    s = C.load_model_spec("0.5b")
+    assert s.mup_width_scale == 4.0
+    assert math.isclose(s.mup_residual_scale, 1.4 / math.sqrt(24))
+    assert s.emb_scale == 12.0
+    off = s.replace(mup_enabled=False)
+    assert off.mup_width_scale == 1.0 and off.mup_residual_scale == 1.0 and off.emb_scale == 1.0
+
+
+def test_param_count_matches_0p5b():
+    s = C.load_model_spec("0.5b")
+    n = s.num_parameters()
+    assert 505e6 < n < 515e6
+
+
+def test_flops_formulas():
+    s = C.load_model_spec("0.5b")
+    hw = C.compute_training_flops(s, 4096, 4096)
+    std = C.compute_training_flops_standard(s, 4096, 4096)
+    assert hw > std
+    # attention core is the only difference: 3 * tokens * L * 2*S*q_dim
+    assert math.isclose(hw - std, 3 * 4096 * s.num_layers * 2 * 4096 * s.q_dim, rel_tol=1e-9)
+    # published per-token figure for seq 4096 is 3.207 GFLOP (fwd+bwd, causal attention)
+    per_tok = std / 4096
+    assert 3.0e9 < per_tok < 3.4e9
+    with_mtp = C.compute_training_flops(s, 4096, 4096, mtp_layers=1)
+    assert with_mtp > hw
+
+
+def test_engine_config_singleton_and_hooks():
+    calls = []
+    ec.register_reset_hook(lambda: calls.append(1))
+    cfg = ec.EngineConfig(max_lr=1e-2)
+    ec.set_global_config(cfg)
+    assert ec.get_config().max_lr == 1e-2
+    with pytest.raises(RuntimeError):
+        ec.set_global_config(cfg)
+    ec.reset_global_config()
+    assert calls and ec.get_config().max_lr == ec.EngineConfig().max_lr
+
+
+def test_engine_config_from_env_and_validation():
+    cfg = ec.from_env({"MAX_LR": "0.01", "WGRAD_BUCKET_TARGET_ELEMS": "4096", "SHARDED_OPTIMIZER": "0",
+                       "FT_COMM": "nccl"})
+    assert cfg.max_lr == 0.01 and cfg.wgrad_bucket_target_elems == 4096
+    assert cfg.sharded_optimizer is False and cfg.comm == "nccl"
+    with pytest.raises(ValueError):
+        ec.from_env({"PROFILE_RANGE": "1,3"})
+    with pytest.raises(ValueError):
+        ec.from_env({"FT_COMM": "mpi"})
+    with pytest.raises(ValueError):
+        ec.from_env({"WGRAD_BUCKET_TARGET_ELEMS": "0"})
+
+
+def test_config_is_frozen():
+    cfg = ec.EngineConfig()
+    with pytest.raises(Exception):
+        cfg.max_lr = 1.0
+
+
+def test_from_spec_takes_training_defaults():
+    s = C.load_model_spec("8b")
+    cfg = ec.from_spec(s)
+    assert cfg.max_lr == s.lr and cfg.tensor_parallel_size == 2 and cfg.wsd_decay_iters == 0

@@ -1,0 +1,130 @@
+"""Multi-process CPU (gloo) runs: data parallel, tensor parallel, checkpoint round-trip."""
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from dist_util import run_ranks  # noqa: E402
+
+
+def _spec(**kw):
+    from forgetrain_b200.config import load_model_spec
+    base = dict(num_layers=2, vocab_size=512, hidden_size=128, ffn_hidden_size=256,
+                num_attention_heads=4, num_query_groups=2, head_dim=32, seq_length=64,
+                max_position_embeddings=64, tie_embeddings=True)
+    base.update(kw)
+    return load_model_spec("tiny", **base)
+
+
+def _cfg(spec, **kw):
+    from forgetrain_b200.engine_config import from_spec
+    base = dict(dtype="fp32", comm="nccl", wgrad_bucket_target_elems=60_000, max_lr=1e-3,
+                warmup_iters=0, rs_buckets=0)
+    base.update(kw)
+    return from_spec(spec, **base)
+
+
+def _batches(seed, n, mbs, seq, vocab):
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for _ in range(n):
+        c = torch.randint(0, vocab, (mbs, seq + 1), generator=g)
+        out.append({"tokens": c[:, :-1].contiguous(), "labels": c[:, 1:].contiguous(),
+                    "loss_mask": torch.ones(mbs, seq)})
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+def _dp_worker(rank, world, steps):
+    from forgetrain_b200.parallel.topology import init_topology
+    from forgetrain_b200.trainer import Trainer
+    spec = _spec()
+    topo = init_topology(1, device="cpu")
+    tr = Trainer(spec, _cfg(spec), topo, seq_length=64, micro_batch_size=2, seed=0)
+    data = _batches(100 + rank, 1, 2, 64, spec.vocab_size)      # one fixed batch per rank
+    losses = []
+    for _ in range(steps):
+        out = tr.train_step(data)
+        losses.append(float(out["loss"]))
+    return losses, tr.store.named_cpu_params(), float(out["grad_norm"])
+
+
+def _single_worker_equivalent(steps):
+    from forgetrain_b200.parallel.topology import Topology
+    from forgetrain_b200.trainer import Trainer
+    spec = _spec()
+    tr = Trainer(spec, _cfg(spec), Topology(), seq_length=64, micro_batch_size=2, seed=0)
+    data = _batches(100, 1, 2, 64, spec.vocab_size) + _batches(101, 1, 2, 64, spec.vocab_size)
+    losses = []
+    for _ in range(steps):
+        out = tr.train_step(data)           # two micro-batches == two DP ranks
+        losses.append(float(out["loss"]))
+    return losses, tr.store.named_cpu_params(), float(out["grad_norm"])
+
+
+def test_dp2_matches_gradient_accumulation_and_loss_decreases():
+    res = run_ranks(_dp_worker, 2, 5)
+    (l0, p0, n0), (l1, p1, n1) = res
+    assert l0 == l1 and n0 == n1 and all(torch.equal(p0[k], p1[k]) for k in p0)   # replicas identical
+    assert l0[-1] < l0[0]
+    ls, ps, ns = _single_worker_equivalent(5)
+    assert max(abs(a - b) for a, b in zip(l0, ls)) < 1e-4
+    assert all(torch.allclose(p0[k], ps[k], atol=2e-5) for k in ps)
+    assert abs(n0 - ns) < 1e-4
+
+
+# ------------------------------------------------------------------------------------------
+def _tp_worker(rank, world, sp, steps):
+    from forgetrain_b200.parallel.topology import init_topology
+    from forgetrain_b200.trainer import Trainer
+    spec = _spec(tie_embeddings=False)
+    topo = init_topology(2, device="cpu", num_kv_groups=spec.num_query_groups)
+    tr = Trainer(spec, _cfg(spec, tensor_parallel_size=2, sequence_parallel=sp), topo, seq_length=64,
+                 micro_batch_size=2, seed=0)
+    data = _batches(7, 1, 2, 64, spec.vocab_size)
+    losses, norms = [], []
+    for _ in range(steps):
+        out = tr.train_step(data)
+        losses.append(float(out["loss"]))
+        norms.append(float(out["grad_norm"]))
+    return losses, norms
+
+
+@pytest.mark.parametrize("sp", [True, False])
+def test_tp2_matches_tp1(sp):
+    from forgetrain_b200.parallel.topology import Topology
+    from forgetrain_b200.trainer import Trainer
+    res = run_ranks(_tp_worker, 2, sp, 3)
+    assert res[0][0] == pytest.approx(res[1][0], abs=1e-6)
+    spec = _spec(tie_embeddings=False)
+    tr = Trainer(spec, _cfg(spec), Topology(), seq_length=64, micro_batch_size=2, seed=0)
+    data = _batches(7, 1, 2, 64, spec.vocab_size)
+    for i in range(3):
+        out = tr.train_step(data)
+        assert float(out["loss"]) == pytest.approx(res[0][0][i], abs=2e-4)
+        assert float(out["grad_norm"]) == pytest.approx(res[0][1][i], rel=2e-3)
+
+
+# ------------------------------------------------------------------------------------------
+def _ckpt_worker(rank, world, root):
+    from forgetrain_b200.parallel.topology import init_topology
+    from forgetrain_b200.trainer import run_training_loop
+    spec = _spec()
+    topo = init_topology(1, device="cpu")
+    cfg = _cfg(spec)
+    a = run_training_loop(spec=spec, cfg=cfg, topo=topo, num_steps=4, micro_batch_size=1, seq_length=64,
+                          seed=3, save_dir=os.path.join(root, "full"), save_interval=2)
+    losses_full = [s["loss"] for s in a["steps"]]
+    b = run_training_loop(spec=spec, cfg=cfg, topo=topo, num_steps=2, micro_batch_size=1, seq_length=64,
+                          seed=3, resume=os.path.join(root, "full", "step_0000002"))
+    losses_resumed = [s["loss"] for s in b["steps"]]
+    return losses_full, losses_resumed
+
+
+def test_dp2_checkpoint_resume_continues_the_run(tmp_path):
+    res = run_ranks(_ckpt_worker, 2, str(tmp_path))
+    full, resumed = res[0]
+    assert (tmp_path / "full" / "step_0000002" / "training_state.pt").exists()
+    assert resumed == pytest.approx(full[2:], abs=1e-5)
