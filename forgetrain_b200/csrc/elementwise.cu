@@ -358,7 +358,9 @@ constexpr int CE_THREADS = 512;
 
 __device__ __forceinline__ void online_merge(float& m, float& s, float m2, float s2) {
   const float nm = fmaxf(m, m2);
-  s = s * __expf(m - nm) + s2 * __expf(m2 - nm);
+  const float a = (m == -INFINITY) ? 0.f : __expf(m - nm);   // empty partials carry (-inf, 0)
+  const float b = (m2 == -INFINITY) ? 0.f : __expf(m2 - nm);
+  s = s * a + s2 * b;
   m = nm;
 }
 

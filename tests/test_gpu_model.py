@@ -1,0 +1,82 @@
+"""End-to-end checks on a GPU: bf16 native path vs the fp32 CPU statement of the same model."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _spec():
+    from forgetrain_b200.config import load_model_spec
+    return load_model_spec("0.5b", num_layers=2, vocab_size=4096, seq_length=256,
+                           max_position_embeddings=256)
+
+
+def _batch(spec, B=2, S=256, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    c = torch.randint(0, spec.vocab_size, (B, S + 1), generator=g)
+    return c[:, :-1].contiguous(), c[:, 1:].contiguous()
+
+
+def test_bf16_gpu_step_matches_fp32_cpu_reference():
+    from forgetrain_b200.models.minicpm4 import MiniCPM4
+    from forgetrain_b200.models.params import ParamStore
+    from forgetrain_b200.ops import _lib
+    spec = _spec()
+    cpu = ParamStore(spec, "cpu", torch.float32)
+    cpu.init_random(0, "normal", 0.02)
+    gpu = ParamStore(spec, "cuda", torch.bfloat16)
+    gpu.init_random(0, "normal", 0.02)
+    for ps in cpu.specs:       # identical (bf16-representable) weights on both sides
+        cpu.params[ps.name].copy_(gpu.params[ps.name].float().cpu())
+    tok, lab = _batch(spec)
+    l_cpu = MiniCPM4(spec, cpu).forward_backward(tok, lab, None, 1.0)
+    l_gpu = MiniCPM4(spec, gpu).forward_backward(tok.cuda(), lab.cuda(), None, 1.0)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert abs(float(l_gpu) - float(l_cpu)) / float(l_cpu) < 5e-3
+    for ps in cpu.specs:
+        a, b = gpu.grads[ps.name].float().cpu(), cpu.grads[ps.name]
+        cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0)
+        assert cos > 0.99, (ps.name, float(cos))
+        assert abs(float(a.norm()) / float(b.norm()) - 1) < 0.05, ps.name
+
+
+def test_training_reduces_loss_and_is_deterministic():
+    from forgetrain_b200.engine_config import from_spec
+    from forgetrain_b200.parallel.topology import Topology
+    from forgetrain_b200.trainer import Trainer
+    spec = _spec()
+    cfg = from_spec(spec, dtype="bf16", comm="nccl", warmup_iters=0, max_lr=2e-3)
+    tok, lab = _batch(spec)
+    batch = {"tokens": tok.cuda(), "labels": lab.cuda(), "loss_mask": torch.ones(2, 256, device="cuda")}
+    runs = []
+    for _ in range(2):
+        tr = Trainer(spec, cfg, Topology(device=torch.device("cuda", 0)), seq_length=256,
+                     micro_batch_size=2, seed=0)
+        losses = [float(tr.train_step([batch])["loss"]) for _ in range(6)]
+        runs.append(losses)
+    assert runs[0][-1] < runs[0][0] - 0.05
+    # same state, same step, twice: every stream dependency is in place iff results repeat
+    assert runs[0][:2] == pytest.approx(runs[1][:2], rel=1e-3)
+
+
+def test_gradient_accumulation_on_gpu():
+    from forgetrain_b200.models.minicpm4 import MiniCPM4
+    from forgetrain_b200.models.params import ParamStore
+    spec = _spec()
+    st = ParamStore(spec, "cuda", torch.bfloat16)
+    st.init_random(0, "normal", 0.02)
+    m = MiniCPM4(spec, st)
+    t1, l1 = _batch(spec, 1, 256, 1)
+    t2, l2 = _batch(spec, 1, 256, 2)
+    m.forward_backward(t1.cuda(), l1.cuda(), None, 0.5, accumulate=False)
+    m.forward_backward(t2.cuda(), l2.cuda(), None, 0.5, accumulate=True)
+    acc = st.flat_grads.clone()
+    m.forward_backward(t1.cuda(), l1.cuda(), None, 0.5, accumulate=False)
+    g1 = st.flat_grads.clone()
+    m.forward_backward(t2.cuda(), l2.cuda(), None, 0.5, accumulate=False)
+    g2 = st.flat_grads.clone()
+    err = (acc - (g1 + g2)).abs().max() / (g1 + g2).abs().max()
+    # the attention backward reduces dQ tiles with fp32 atomics, so two runs of the same step
+    # differ by bf16 rounding noise (~2e-3 of the largest gradient); accumulation adds none
+    assert float(err) < 1e-2
