@@ -1,0 +1,323 @@
+// Peer-memory collectives over NVLink / NVSwitch for the data-parallel path, written as plain
+// sm_100a kernels on symmetric buffers (every rank maps every peer's buffer at the same offsets):
+//
+//   * bucket reduce-scatter fused with the 1/W (x loss scale) multiply and the squared-norm
+//     partial of the reduced shard: each rank sums ITS shard of the bucket over all peers,
+//     either with one in-switch reduction per 16 bytes (multimem.ld_reduce on the NVLS multicast
+//     mapping) or with W plain peer loads, and writes the result in place into its own buffer;
+//   * bucket all-gather of updated bf16 parameters: each rank pushes its shard into every
+//     peer's parameter buffer (multimem.st, or W plain peer stores);
+//   * a flag barrier between ranks: a rank signals by storing a monotonically increasing epoch
+//     into a slot of every peer's flag array (st.release.sys) and waits for its own slots
+//     (ld.acquire.sys). Every wait is bounded by a time limit passed by the host; a wait that
+//     runs out records FT_ERR_WAIT_PEER in the status word, and the kernel still terminates.
+//
+// Stand in for the reference's NCCL reduce_scatter_tensor / all_gather_into_tensor / all_reduce
+// calls plus the aten scale, cast and norm kernels around them
+// (exports/train_engine_0.5B/src/training_engine_tensor/nccl.py:1093-1137, 1357-1390, 1454-1513).
+#include "ptx.cuh"
+
+namespace ft {
+
+constexpr int COMM_MAX_RANKS = 16;
+constexpr int COMM_THREADS = 512;
+
+struct CommPeers {
+  void* buf[COMM_MAX_RANKS];         // peer base pointers of the data buffer
+  uint32_t* flags[COMM_MAX_RANKS];   // peer base pointers of the flag arrays [slots][world]
+  void* mc;                          // multicast mapping of the data buffer (nullptr: none)
+  int rank, world;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const void* mc_addr) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_b32x4(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
+}
+__device__ __forceinline__ float4 ld_peer_f32x4(const float* p) {
+  float4 v;
+  asm volatile("ld.global.relaxed.sys.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_peer_b32x4(void* p, uint4 v) {
+  asm volatile("st.global.relaxed.sys.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// Signal `epoch` into slot [slot][rank] of every peer (threads 0..world-1 of the calling CTA).
+__device__ __forceinline__ void signal_peers(const CommPeers& c, int slot, uint32_t epoch) {
+  if (threadIdx.x < c.world) {
+    __threadfence_system();
+    st_release_sys(c.flags[threadIdx.x] + slot * c.world + c.rank, epoch);
+  }
+}
+
+// Wait until every peer has signalled at least `epoch` into this rank's slot. Bounded:
+// returns false (and records the status) when `limit_ns` passes first. Whole CTA must call.
+__device__ __forceinline__ bool wait_peers(const CommPeers& c, int slot, uint32_t epoch,
+                                           uint64_t limit_ns, int* status) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    const uint32_t* f = c.flags[c.rank] + slot * c.world + threadIdx.x;
+    const uint64_t t0 = globaltimer_ns();
+    while (true) {
+      // epochs only grow; the signed difference is safe across 32-bit wrap-around
+      if (static_cast<int32_t>(ld_acquire_sys(f) - epoch) >= 0) break;
+      if (globaltimer_ns() - t0 > limit_ns) {
+        s_fail = 1;
+        if (status) atomicCAS(status, 0, FT_ERR_WAIT_PEER);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  return s_fail == 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Barrier only (used by tests of the timeout path and as a building block).
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(COMM_THREADS)
+peer_barrier_kernel(CommPeers c, int slot, uint32_t epoch, uint64_t limit_ns, int do_signal,
+                    int* status) {
+  if (do_signal) signal_peers(c, slot, epoch);
+  wait_peers(c, slot, epoch, limit_ns, status);
+}
+
+// ---------------------------------------------------------------------------------------
+// Reduce-scatter of one bucket, in place, fused with scale and squared-norm partial.
+//   bucket = elements [start, start + n_per_rank * world) of the fp32 buffer; this rank owns
+//   [start + rank*n_per_rank, +n_per_rank). n_per_rank % 4 == 0.
+// Protocol: entry barrier (slot 0) -> reduce -> exit barrier (slot 1, last CTA to finish).
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(COMM_THREADS)
+bucket_reduce_scatter_kernel(CommPeers c, long start, long n_per_rank, float scale,
+                             float* __restrict__ sumsq, uint32_t epoch, uint64_t limit_ns,
+                             unsigned int* __restrict__ done_ctr, int* status) {
+  __shared__ float red[COMM_THREADS / 32];
+  if (blockIdx.x == 0) signal_peers(c, 0, epoch);
+  const bool ok = wait_peers(c, 0, epoch, limit_ns, status);
+  float ss = 0.f;
+  if (ok) {
+    const long base = start + static_cast<long>(c.rank) * n_per_rank;
+    float* mine = static_cast<float*>(c.buf[c.rank]) + base;
+    const long nvec = n_per_rank / 4;
+    if (c.mc) {
+      const float* mc = static_cast<const float*>(c.mc) + base;
+      for (long i = static_cast<long>(blockIdx.x) * COMM_THREADS + threadIdx.x; i < nvec;
+           i += static_cast<long>(gridDim.x) * COMM_THREADS) {
+        float4 v = multimem_ld_reduce_f32x4(mc + 4 * i);
+        v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        reinterpret_cast<float4*>(mine)[i] = v;
+      }
+    } else {
+      for (long i = static_cast<long>(blockIdx.x) * COMM_THREADS + threadIdx.x; i < nvec;
+           i += static_cast<long>(gridDim.x) * COMM_THREADS) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int p = 0; p < c.world; ++p) {
+          const int q = (c.rank + p) % c.world;  // start at self, spread the peers
+          const float4 a = ld_peer_f32x4(static_cast<const float*>(c.buf[q]) + base + 4 * i);
+          v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+        }
+        v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        reinterpret_cast<float4*>(mine)[i] = v;
+      }
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < COMM_THREADS / 32 ? red[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0 && sumsq) atomicAdd(sumsq, t);
+  }
+  // exit barrier: the last CTA of this rank tells the peers that it no longer reads their
+  // memory and waits until no peer reads ours, so later kernels may overwrite the bucket.
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int prev = atomicAdd(done_ctr, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+    if (s_last) *done_ctr = 0;  // re-arm for the next launch (stream-ordered)
+  }
+  __syncthreads();
+  if (s_last) {
+    signal_peers(c, 1, epoch);
+    wait_peers(c, 1, epoch, limit_ns, status);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// All-gather of one bucket of 2-byte parameters: push this rank's shard to every peer.
+//   shard = elements [start + rank*n_per_rank, +n_per_rank) of the bf16 buffer (already holds
+//   the new values locally). n_per_rank % 8 == 0. Exit barrier on slot 2.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(COMM_THREADS)
+bucket_all_gather_kernel(CommPeers c, long start, long n_per_rank, uint32_t epoch,
+                         uint64_t limit_ns, unsigned int* __restrict__ done_ctr, int* status) {
+  const long base = start + static_cast<long>(c.rank) * n_per_rank;  // in 2-byte elements
+  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(c.buf[c.rank]) + base);
+  const long nvec = n_per_rank / 8;
+  if (c.mc) {
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(c.mc) + base);
+    for (long i = static_cast<long>(blockIdx.x) * COMM_THREADS + threadIdx.x; i < nvec;
+         i += static_cast<long>(gridDim.x) * COMM_THREADS)
+      multimem_st_b32x4(dst + i, src[i]);
+  } else {
+    for (long i = static_cast<long>(blockIdx.x) * COMM_THREADS + threadIdx.x; i < nvec;
+         i += static_cast<long>(gridDim.x) * COMM_THREADS) {
+      const uint4 v = src[i];
+      for (int p = 1; p < c.world; ++p) {
+        const int q = (c.rank + p) % c.world;
+        st_peer_b32x4(reinterpret_cast<uint4*>(static_cast<uint16_t*>(c.buf[q]) + base) + i, v);
+      }
+    }
+  }
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(done_ctr, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+    if (s_last) *done_ctr = 0;
+  }
+  __syncthreads();
+  if (s_last) {
+    signal_peers(c, 2, epoch);
+    wait_peers(c, 2, epoch, limit_ns, status);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Small all-reduce (sum) of a few floats through the flag-protected symmetric scratch area:
+// every rank writes its values into its own slot of every peer, barrier, each rank sums.
+//   scratch layout per rank: [world][n] floats at float offset `scratch_off`. n <= 64.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(COMM_THREADS)
+small_all_reduce_kernel(CommPeers c, long scratch_off, float* __restrict__ vals, int n,
+                        uint32_t epoch, uint64_t limit_ns, int* status) {
+  const int tid = threadIdx.x;
+  for (int i = tid; i < n * c.world; i += COMM_THREADS) {
+    const int p = i / n, k = i % n;
+    float* dst = static_cast<float*>(c.buf[p]) + scratch_off + static_cast<long>(c.rank) * n + k;
+    asm volatile("st.global.relaxed.sys.f32 [%0], %1;" ::"l"(dst), "f"(vals[k]) : "memory");
+  }
+  __syncthreads();
+  signal_peers(c, 3, epoch);
+  const bool ok = wait_peers(c, 3, epoch, limit_ns, status);
+  if (ok && tid < n) {
+    const float* mine = static_cast<const float*>(c.buf[c.rank]) + scratch_off;
+    float s = 0.f;
+    for (int p = 0; p < c.world; ++p) {
+      float v;
+      asm volatile("ld.global.relaxed.sys.f32 %0, [%1];" : "=f"(v) : "l"(mine + p * n + tid) : "memory");
+      s += v;
+    }
+    vals[tid] = s;
+  }
+  // second phase so that nobody overwrites a slot that a slower peer has not read yet
+  __syncthreads();
+  signal_peers(c, 4, epoch);
+  wait_peers(c, 4, epoch, limit_ns, status);
+}
+
+}  // namespace ft
+
+using namespace ft;
+
+static void fill_peers(CommPeers& c, const void* const* bufs, const void* const* flags, void* mc,
+                       int rank, int world) {
+  for (int i = 0; i < COMM_MAX_RANKS; ++i) {
+    c.buf[i] = i < world ? const_cast<void*>(bufs[i]) : nullptr;
+    c.flags[i] = i < world ? static_cast<uint32_t*>(const_cast<void*>(flags[i])) : nullptr;
+  }
+  c.mc = mc;
+  c.rank = rank;
+  c.world = world;
+}
+
+// bufs / flags: host arrays of `world` device pointers (peer mappings, own rank included).
+// The flag array of every rank holds at least 8 * world uint32 (zero-initialised once).
+extern "C" int ft_peer_barrier(const void* const* flags, int rank, int world, int slot,
+                               unsigned int epoch, unsigned long long limit_ns, int do_signal,
+                               int* status, cudaStream_t st) {
+  if (world > COMM_MAX_RANKS || slot < 0 || slot > 7) return -1;
+  CommPeers c;
+  fill_peers(c, flags, flags, nullptr, rank, world);
+  peer_barrier_kernel<<<1, COMM_THREADS, 0, st>>>(c, slot, epoch, limit_ns, do_signal, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+extern "C" int ft_bucket_reduce_scatter(const void* const* bufs, const void* const* flags, void* mc,
+                                        int rank, int world, long start, long n_per_rank,
+                                        float scale, void* sumsq, unsigned int epoch,
+                                        unsigned long long limit_ns, void* done_ctr, int ctas,
+                                        int* status, cudaStream_t st) {
+  if (world > COMM_MAX_RANKS || n_per_rank % 4) return -1;
+  CommPeers c;
+  fill_peers(c, bufs, flags, mc, rank, world);
+  if (ctas <= 0) ctas = 64;
+  const long need = (n_per_rank / 4 + COMM_THREADS - 1) / COMM_THREADS;
+  if (ctas > need) ctas = need < 1 ? 1 : static_cast<int>(need);
+  bucket_reduce_scatter_kernel<<<ctas, COMM_THREADS, 0, st>>>(
+      c, start, n_per_rank, scale, static_cast<float*>(sumsq), epoch, limit_ns,
+      static_cast<unsigned int*>(done_ctr), status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+extern "C" int ft_bucket_all_gather(const void* const* bufs, const void* const* flags, void* mc,
+                                    int rank, int world, long start, long n_per_rank,
+                                    unsigned int epoch, unsigned long long limit_ns,
+                                    void* done_ctr, int ctas, int* status, cudaStream_t st) {
+  if (world > COMM_MAX_RANKS || n_per_rank % 8) return -1;
+  CommPeers c;
+  fill_peers(c, bufs, flags, mc, rank, world);
+  if (ctas <= 0) ctas = 64;
+  const long need = (n_per_rank / 8 + COMM_THREADS - 1) / COMM_THREADS;
+  if (ctas > need) ctas = need < 1 ? 1 : static_cast<int>(need);
+  bucket_all_gather_kernel<<<ctas, COMM_THREADS, 0, st>>>(c, start, n_per_rank, epoch, limit_ns,
+                                                          static_cast<unsigned int*>(done_ctr),
+                                                          status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+extern "C" int ft_small_all_reduce(const void* const* bufs, const void* const* flags, int rank,
+                                   int world, long scratch_off, void* vals, int n,
+                                   unsigned int epoch, unsigned long long limit_ns, int* status,
+                                   cudaStream_t st) {
+  if (world > COMM_MAX_RANKS || n > 64 || n < 1) return -1;
+  CommPeers c;
+  fill_peers(c, bufs, flags, nullptr, rank, world);
+  small_all_reduce_kernel<<<1, COMM_THREADS, 0, st>>>(c, scratch_off, static_cast<float*>(vals), n,
+                                                      epoch, limit_ns, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}

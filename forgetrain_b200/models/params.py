@@ -196,7 +196,8 @@ class ParamStore:
 
     def __init__(self, spec: ModelSpec, device, dtype: torch.dtype, mtp_num_layers: int = 0,
                  tp_rank: int = 0, tp_size: int = 1, pad_to: int = 1,
-                 grad_buffer: torch.Tensor | None = None, align: int = ALIGN_ELEMS):
+                 grad_buffer: torch.Tensor | None = None, align: int = ALIGN_ELEMS,
+                 param_buffer: torch.Tensor | None = None):
         self.spec = spec
         self.device = torch.device(device)
         self.dtype = dtype
@@ -215,7 +216,12 @@ class ParamStore:
             off += (math.prod(shp) + align - 1) // align * align
         self.raw_total = off
         self.total = (off + pad_to - 1) // pad_to * pad_to
-        self.flat_params = torch.zeros(self.total, dtype=dtype, device=self.device)
+        if param_buffer is not None:
+            assert param_buffer.numel() >= self.total and param_buffer.dtype == dtype
+            self.flat_params = param_buffer[:self.total]
+            self.flat_params.zero_()
+        else:
+            self.flat_params = torch.zeros(self.total, dtype=dtype, device=self.device)
         if grad_buffer is not None:
             assert grad_buffer.numel() >= self.total and grad_buffer.dtype == torch.float32
             self.flat_grads = grad_buffer[:self.total]

@@ -1,0 +1,137 @@
+"""Data-parallel collectives as hand-written peer-memory kernels (``csrc/comm.cu``).
+
+The flat fp32 gradient buffer and the flat bf16 parameter buffer live in symmetric memory
+(``torch.distributed._symmetric_memory``: the same allocation on every rank of the
+data-parallel group, every peer mapped into this process, plus an NVLS multicast mapping when
+the fabric offers one). On top of the raw pointers:
+
+* ``reduce_scatter_bucket``: ONE kernel per bucket does entry barrier, in-switch (``multimem``)
+  or peer-load reduction of this rank's shard, the 1/W scale, the squared-norm partial and the
+  exit barrier: no separate scale / norm kernels and no staging copy;
+* ``all_gather_bucket``: one kernel pushes the freshly updated bf16 shard into every peer's
+  parameter buffer (``multimem.st`` or peer stores) and waits for every peer's push;
+* ``all_reduce_small``: a one-CTA all-reduce for a handful of floats (gradient norm, loss).
+
+Every device-side wait is bounded (``timeout_ms``); a wait that runs out sets the status word
+that :func:`forgetrain_b200.ops._lib.check_status` reports. ``use_multimem=False`` keeps all
+traffic on plain peer loads / stores (used by the failure-handling tests).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+
+NUM_FLAG_SLOTS = 8
+SCRATCH_FLOATS = 64 * 16
+
+
+class SymmetricBuffers:
+    """Symmetric allocations shared by the ranks of one process group."""
+
+    def __init__(self, n_elems: int, device: torch.device, group, rank: int, world: int,
+                 use_multimem: bool | None = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group, self.rank, self.world = group, rank, world
+        self.n = n_elems
+        gname = group.group_name if group is not None else dist.group.WORLD.group_name
+        try:
+            symm_mem.enable_symm_mem_for_group(gname)
+        except Exception:
+            pass
+        self.grads = symm_mem.empty(n_elems, dtype=torch.float32, device=device)
+        self.params = symm_mem.empty(n_elems, dtype=torch.bfloat16, device=device)
+        self.flags = symm_mem.empty(NUM_FLAG_SLOTS * 16, dtype=torch.int32, device=device)
+        self.scratch = symm_mem.empty(SCRATCH_FLOATS, dtype=torch.float32, device=device)
+        self.grads.zero_()
+        self.params.zero_()
+        self.flags.zero_()
+        self.scratch.zero_()
+        torch.cuda.synchronize(device)
+        self.h_grads = symm_mem.rendezvous(self.grads, gname)
+        self.h_params = symm_mem.rendezvous(self.params, gname)
+        self.h_flags = symm_mem.rendezvous(self.flags, gname)
+        self.h_scratch = symm_mem.rendezvous(self.scratch, gname)
+        if use_multimem is None:
+            use_multimem = os.environ.get("FT_COMM_MULTIMEM", "1") != "0"
+        self.mc_grads = int(self.h_grads.multicast_ptr or 0) if use_multimem else 0
+        self.mc_params = int(self.h_params.multicast_ptr or 0) if use_multimem else 0
+        VP = ctypes.c_void_p * world
+        self.p_grads = VP(*[int(p) for p in self.h_grads.buffer_ptrs])
+        self.p_params = VP(*[int(p) for p in self.h_params.buffer_ptrs])
+        self.p_flags = VP(*[int(p) for p in self.h_flags.buffer_ptrs])
+        self.p_scratch = VP(*[int(p) for p in self.h_scratch.buffer_ptrs])
+        self.done_ctr = torch.zeros(4, dtype=torch.int32, device=device)
+        self.epoch = [0] * NUM_FLAG_SLOTS
+        dist.barrier(group=group)
+
+    def next_epoch(self, slot: int) -> int:
+        self.epoch[slot] = (self.epoch[slot] + 1) & 0x7FFFFFFF
+        return self.epoch[slot]
+
+
+class FusedDPComm:
+    def __init__(self, symm: SymmetricBuffers, timeout_ms: int | None = None, ctas: int = 0):
+        self.s = symm
+        if timeout_ms is None:
+            timeout_ms = int(os.environ.get("FT_COMM_TIMEOUT_MS", "30000"))
+        self.limit_ns = int(timeout_ms) * 1_000_000
+        self.ctas = ctas or int(os.environ.get("FT_COMM_CTAS", "64"))
+        self.status = _lib.status_word(symm.grads.device)
+        self.comm_stream = None
+        self.ag_events: list = []
+
+    # -- gradient reduce-scatter ---------------------------------------------------------
+    def reduce_scatter_bucket(self, b, sumsq: torch.Tensor, scale: float | None = None) -> None:
+        s = self.s
+        ep = s.next_epoch(0)
+        s.epoch[1] = ep
+        rc = _lib.lib().ft_bucket_reduce_scatter(
+            s.p_grads, s.p_flags, ctypes.c_void_p(s.mc_grads), ctypes.c_int(s.rank),
+            ctypes.c_int(s.world), ctypes.c_long(b.start), ctypes.c_long(b.size // s.world),
+            ctypes.c_float(1.0 / s.world if scale is None else scale), _lib.ptr(sumsq),
+            ctypes.c_uint(ep), ctypes.c_ulonglong(self.limit_ns), _lib.ptr(s.done_ctr),
+            ctypes.c_int(self.ctas), _lib.ptr(self.status), _lib.stream())
+        _lib.check_rc(rc, "ft_bucket_reduce_scatter")
+
+    # -- parameter all-gather ------------------------------------------------------------
+    def all_gather_bucket(self, b) -> None:
+        s = self.s
+        ep = s.next_epoch(2)
+        rc = _lib.lib().ft_bucket_all_gather(
+            s.p_params, s.p_flags, ctypes.c_void_p(s.mc_params), ctypes.c_int(s.rank),
+            ctypes.c_int(s.world), ctypes.c_long(b.start), ctypes.c_long(b.size // s.world),
+            ctypes.c_uint(ep), ctypes.c_ulonglong(self.limit_ns),
+            _lib.c_void_p(s.done_ctr.data_ptr() + 4), ctypes.c_int(self.ctas),
+            _lib.ptr(self.status), _lib.stream())
+        _lib.check_rc(rc, "ft_bucket_all_gather")
+
+    def wait_all_gathers(self) -> None:
+        return  # the kernels run on the caller's stream; stream order is the dependency
+
+    # -- a few floats ----------------------------------------------------------------------
+    def all_reduce_small(self, vals: torch.Tensor) -> None:
+        """In-place sum over the group of up to 64 fp32 values."""
+        s = self.s
+        assert vals.dtype == torch.float32 and vals.numel() <= 64
+        ep = s.next_epoch(3)
+        s.epoch[4] = ep
+        rc = _lib.lib().ft_small_all_reduce(
+            s.p_scratch, s.p_flags, ctypes.c_int(s.rank), ctypes.c_int(s.world), ctypes.c_long(0),
+            _lib.ptr(vals), ctypes.c_int(vals.numel()), ctypes.c_uint(ep),
+            ctypes.c_ulonglong(self.limit_ns), _lib.ptr(self.status), _lib.stream())
+        _lib.check_rc(rc, "ft_small_all_reduce")
+
+    def barrier(self, slot: int = 5, signal: bool = True, timeout_ms: int | None = None) -> None:
+        s = self.s
+        ep = s.next_epoch(slot)
+        limit = self.limit_ns if timeout_ms is None else int(timeout_ms) * 1_000_000
+        rc = _lib.lib().ft_peer_barrier(s.p_flags, ctypes.c_int(s.rank), ctypes.c_int(s.world),
+                                        ctypes.c_int(slot), ctypes.c_uint(ep),
+                                        ctypes.c_ulonglong(limit), ctypes.c_int(int(signal)),
+                                        _lib.ptr(self.status), _lib.stream())
+        _lib.check_rc(rc, "ft_peer_barrier")

@@ -58,17 +58,17 @@ class Trainer:
         # --- fused peer-memory communication (GPU, >1 rank, comm == "fused")
         self.fused_dp = None
         self.symm = None
-        grad_buffer = None
+        grad_buffer = param_buffer = None
         want_fused = (cfg.comm == "fused" and dev.type == "cuda" and dp > 1)
         pad = ALIGN_ELEMS * dp
-        self.store = None
         if want_fused:
             from .parallel import fused_dp
-            probe = ParamStore.layout_total(spec, cfg.mtp_num_layers, tp, pad)
-            self.symm = fused_dp.SymmetricGradBuffer(probe, topo)
-            grad_buffer = self.symm.local_tensor
+            total = ParamStore.layout_total(spec, cfg.mtp_num_layers, tp, pad)
+            self.symm = fused_dp.SymmetricBuffers(total, dev, topo.dp_group, topo.dp_rank, dp)
+            grad_buffer, param_buffer = self.symm.grads, self.symm.params
         self.store = ParamStore(spec, dev, self.dtype, cfg.mtp_num_layers, topo.tp_rank, tp,
-                                pad_to=pad, grad_buffer=grad_buffer, align=pad)
+                                pad_to=pad, grad_buffer=grad_buffer, align=pad,
+                                param_buffer=param_buffer)
         if cfg.random_init:
             self.store.init_random(seed, cfg.init_scheme, cfg.init_std)
         self.model = MiniCPM4(spec, self.store, self.tp_ctx, max_seq_len=max_seq_len or seq_length)
@@ -87,14 +87,17 @@ class Trainer:
                     norm_exclude.append((o, o + self.store.numel(ps.name)))
         if want_fused:
             from .parallel import fused_dp
-            self.fused_dp = fused_dp.FusedDPComm(self.symm, self.store, topo)
+            self.fused_dp = fused_dp.FusedDPComm(self.symm)
         self.reducer = BucketedGradReducer(
             self.store.flat_grads, self.store.entries(), dp, topo.dp_rank, topo.dp_group, target,
             backend=cfg.comm, overlap=cfg.wgrad_overlap and not cfg.serial_streams,
             norm_exclude=norm_exclude, fused=self.fused_dp)
         norm_reduce = None
         if topo.world > 1:
-            norm_reduce = (lambda t: dist.all_reduce(t))  # world group: DP shards x TP shards
+            if self.fused_dp is not None and tp == 1:
+                norm_reduce = self.fused_dp.all_reduce_small
+            else:
+                norm_reduce = (lambda t: dist.all_reduce(t))  # world: DP shards x TP shards
         self.opt = ShardedAdamW(
             self.store, self.reducer.buckets, dp, topo.dp_rank, topo.dp_group,
             beta1=cfg.adam_beta1, beta2=cfg.adam_beta2, eps=cfg.adam_eps,
@@ -158,7 +161,10 @@ class Trainer:
         if prof:
             prof.mark("optimizer")
         if self.topo.dp_size > 1:
-            dist.all_reduce(self.loss_buf, group=self.topo.dp_group)
+            if self.fused_dp is not None:
+                self.fused_dp.all_reduce_small(self.loss_buf)
+            else:
+                dist.all_reduce(self.loss_buf, group=self.topo.dp_group)
             self.loss_buf /= self.topo.dp_size
         if prof:
             prof.mark("loss_allreduce")
