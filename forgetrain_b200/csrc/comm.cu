@@ -126,28 +126,48 @@ bucket_reduce_scatter_kernel(CommPeers c, long start, long n_per_rank, float sca
     const long base = start + static_cast<long>(c.rank) * n_per_rank;
     float* mine = static_cast<float*>(c.buf[c.rank]) + base;
     const long nvec = n_per_rank / 4;
+    constexpr int U = 4;  // independent 16-byte requests in flight per thread
+    const long stride = static_cast<long>(gridDim.x) * COMM_THREADS;
+    const long i0 = static_cast<long>(blockIdx.x) * COMM_THREADS + threadIdx.x;
     if (c.mc) {
       const float* mc = static_cast<const float*>(c.mc) + base;
-      for (long i = static_cast<long>(blockIdx.x) * COMM_THREADS + threadIdx.x; i < nvec;
-           i += static_cast<long>(gridDim.x) * COMM_THREADS) {
-        float4 v = multimem_ld_reduce_f32x4(mc + 4 * i);
-        v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
-        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        reinterpret_cast<float4*>(mine)[i] = v;
+      for (long i = i0; i < nvec; i += stride * U) {
+        float4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i + u * stride < nvec) v[u] = multimem_ld_reduce_f32x4(mc + 4 * (i + u * stride));
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i + u * stride < nvec) {
+            float4 w = v[u];
+            w.x *= scale; w.y *= scale; w.z *= scale; w.w *= scale;
+            ss += w.x * w.x + w.y * w.y + w.z * w.z + w.w * w.w;
+            reinterpret_cast<float4*>(mine)[i + u * stride] = w;
+          }
       }
     } else {
-      for (long i = static_cast<long>(blockIdx.x) * COMM_THREADS + threadIdx.x; i < nvec;
-           i += static_cast<long>(gridDim.x) * COMM_THREADS) {
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
+      for (long i = i0; i < nvec; i += stride * U) {
+        float4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int p = 0; p < c.world; ++p) {
           const int q = (c.rank + p) % c.world;  // start at self, spread the peers
-          const float4 a = ld_peer_f32x4(static_cast<const float*>(c.buf[q]) + base + 4 * i);
-          v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+          const float* src = static_cast<const float*>(c.buf[q]) + base;
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            if (i + u * stride < nvec) {
+              const float4 a = ld_peer_f32x4(src + 4 * (i + u * stride));
+              v[u].x += a.x; v[u].y += a.y; v[u].z += a.z; v[u].w += a.w;
+            }
         }
-        v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
-        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        reinterpret_cast<float4*>(mine)[i] = v;
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i + u * stride < nvec) {
+            float4 w = v[u];
+            w.x *= scale; w.y *= scale; w.z *= scale; w.w *= scale;
+            ss += w.x * w.x + w.y * w.y + w.z * w.z + w.w * w.w;
+            reinterpret_cast<float4*>(mine)[i + u * stride] = w;
+          }
       }
     }
   }
@@ -187,18 +207,32 @@ bucket_all_gather_kernel(CommPeers c, long start, long n_per_rank, uint32_t epoc
   const long base = start + static_cast<long>(c.rank) * n_per_rank;  // in 2-byte elements
   const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(c.buf[c.rank]) + base);
   const long nvec = n_per_rank / 8;
+  constexpr int U = 4;
+  const long stride = static_cast<long>(gridDim.x) * COMM_THREADS;
+  const long i0 = static_cast<long>(blockIdx.x) * COMM_THREADS + threadIdx.x;
   if (c.mc) {
     uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(c.mc) + base);
-    for (long i = static_cast<long>(blockIdx.x) * COMM_THREADS + threadIdx.x; i < nvec;
-         i += static_cast<long>(gridDim.x) * COMM_THREADS)
-      multimem_st_b32x4(dst + i, src[i]);
+    for (long i = i0; i < nvec; i += stride * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i + u * stride < nvec) v[u] = src[i + u * stride];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i + u * stride < nvec) multimem_st_b32x4(dst + i + u * stride, v[u]);
+    }
   } else {
-    for (long i = static_cast<long>(blockIdx.x) * COMM_THREADS + threadIdx.x; i < nvec;
-         i += static_cast<long>(gridDim.x) * COMM_THREADS) {
-      const uint4 v = src[i];
+    for (long i = i0; i < nvec; i += stride * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i + u * stride < nvec) v[u] = src[i + u * stride];
       for (int p = 1; p < c.world; ++p) {
         const int q = (c.rank + p) % c.world;
-        st_peer_b32x4(reinterpret_cast<uint4*>(static_cast<uint16_t*>(c.buf[q]) + base) + i, v);
+        uint4* dq = reinterpret_cast<uint4*>(static_cast<uint16_t*>(c.buf[q]) + base);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i + u * stride < nvec) st_peer_b32x4(dq + i + u * stride, v[u]);
       }
     }
   }
@@ -285,8 +319,8 @@ extern "C" int ft_bucket_reduce_scatter(const void* const* bufs, const void* con
   if (world > COMM_MAX_RANKS || n_per_rank % 4) return -1;
   CommPeers c;
   fill_peers(c, bufs, flags, mc, rank, world);
-  if (ctas <= 0) ctas = 64;
-  const long need = (n_per_rank / 4 + COMM_THREADS - 1) / COMM_THREADS;
+  if (ctas <= 0) ctas = 96;
+  const long need = (n_per_rank / 16 + COMM_THREADS - 1) / COMM_THREADS;
   if (ctas > need) ctas = need < 1 ? 1 : static_cast<int>(need);
   bucket_reduce_scatter_kernel<<<ctas, COMM_THREADS, 0, st>>>(
       c, start, n_per_rank, scale, static_cast<float*>(sumsq), epoch, limit_ns,
@@ -301,8 +335,8 @@ extern "C" int ft_bucket_all_gather(const void* const* bufs, const void* const* 
   if (world > COMM_MAX_RANKS || n_per_rank % 8) return -1;
   CommPeers c;
   fill_peers(c, bufs, flags, mc, rank, world);
-  if (ctas <= 0) ctas = 64;
-  const long need = (n_per_rank / 8 + COMM_THREADS - 1) / COMM_THREADS;
+  if (ctas <= 0) ctas = 96;
+  const long need = (n_per_rank / 32 + COMM_THREADS - 1) / COMM_THREADS;
   if (ctas > need) ctas = need < 1 ? 1 : static_cast<int>(need);
   bucket_all_gather_kernel<<<ctas, COMM_THREADS, 0, st>>>(c, start, n_per_rank, epoch, limit_ns,
                                                           static_cast<unsigned int*>(done_ctr),

@@ -39,10 +39,6 @@ class SymmetricBuffers:
         self.group, self.rank, self.world = group, rank, world
         self.n = n_elems
         gname = group.group_name if group is not None else dist.group.WORLD.group_name
-        try:
-            symm_mem.enable_symm_mem_for_group(gname)
-        except Exception:
-            pass
         self.grads = symm_mem.empty(n_elems, dtype=torch.float32, device=device)
         self.params = symm_mem.empty(n_elems, dtype=torch.bfloat16, device=device)
         self.flags = symm_mem.empty(NUM_FLAG_SLOTS * 16, dtype=torch.int32, device=device)
@@ -60,6 +56,10 @@ class SymmetricBuffers:
             use_multimem = os.environ.get("FT_COMM_MULTIMEM", "1") != "0"
         self.mc_grads = int(self.h_grads.multicast_ptr or 0) if use_multimem else 0
         self.mc_params = int(self.h_params.multicast_ptr or 0) if use_multimem else 0
+        if world <= 2:
+            # with a single peer a multicast store also rewrites the local copy: plain peer
+            # stores move half the bytes
+            self.mc_params = 0
         VP = ctypes.c_void_p * world
         self.p_grads = VP(*[int(p) for p in self.h_grads.buffer_ptrs])
         self.p_params = VP(*[int(p) for p in self.h_params.buffer_ptrs])
@@ -80,7 +80,7 @@ class FusedDPComm:
         if timeout_ms is None:
             timeout_ms = int(os.environ.get("FT_COMM_TIMEOUT_MS", "30000"))
         self.limit_ns = int(timeout_ms) * 1_000_000
-        self.ctas = ctas or int(os.environ.get("FT_COMM_CTAS", "64"))
+        self.ctas = ctas or int(os.environ.get("FT_COMM_CTAS", "96"))
         self.status = _lib.status_word(symm.grads.device)
         self.comm_stream = None
         self.ag_events: list = []

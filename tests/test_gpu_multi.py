@@ -196,3 +196,42 @@ def test_dp2_fused_matches_nccl_training():
     assert fused[0][0][-1] < fused[0][0][0]
     assert fused[0][0] == pytest.approx(nccl[0][0], rel=2e-3)
     assert fused[0][1] == pytest.approx(nccl[0][1], rel=2e-2)
+
+
+# ------------------------------------------------------------------------------------------
+def _tp_train(rank, world, tp, sp):
+    from forgetrain_b200.config import load_model_spec
+    from forgetrain_b200.engine_config import from_spec
+    from forgetrain_b200.ops import _lib
+    from forgetrain_b200.parallel.topology import init_topology
+    from forgetrain_b200.trainer import Trainer
+    spec = load_model_spec("8b", num_layers=2, vocab_size=4096, hidden_size=1024, ffn_hidden_size=2048,
+                           num_attention_heads=8, num_query_groups=2, head_dim=128, seq_length=512,
+                           max_position_embeddings=512)
+    cfg = from_spec(spec, dtype="bf16", comm="nccl", warmup_iters=0, max_lr=1e-3,
+                    tensor_parallel_size=tp, sequence_parallel=sp, rs_buckets=4)
+    topo = init_topology(tp, num_kv_groups=spec.num_query_groups)
+    tr = Trainer(spec, cfg, topo, seq_length=512, micro_batch_size=1, seed=0)
+    g = torch.Generator().manual_seed(11 + topo.dp_rank)
+    c = torch.randint(0, spec.vocab_size, (1, 513), generator=g)
+    batch = {"tokens": c[:, :-1].contiguous().cuda(), "labels": c[:, 1:].contiguous().cuda(),
+             "loss_mask": torch.ones(1, 512, device="cuda")}
+    losses, norms = [], []
+    for _ in range(4):
+        out = tr.train_step([batch, batch])          # two micro-batches: accumulation path
+        losses.append(float(out["loss"]))
+        norms.append(float(out["grad_norm"]))
+    torch.cuda.synchronize()
+    _lib.check_status()
+    return losses, norms
+
+
+@needs2
+@pytest.mark.parametrize("sp", [True, False])
+def test_tp2_matches_tp1_on_gpu(sp):
+    tp2 = run_gpus(_tp_train, 2, 2, sp)
+    tp1 = run_gpus(_tp_train, 1, 1, False)
+    assert tp2[0][0] == pytest.approx(tp2[1][0], rel=1e-4)
+    assert tp2[0][0] == pytest.approx(tp1[0][0], rel=5e-3)
+    assert tp2[0][1] == pytest.approx(tp1[0][1], rel=3e-2)
+    assert tp2[0][0][-1] < tp2[0][0][0]
