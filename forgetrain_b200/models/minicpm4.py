@@ -82,21 +82,19 @@ class MiniCPM4:
                                                h_prev if h_prev is not None else branch,
                                                p[f"{prefix}.attention_norm.weight"], sp.norm_epsilon)
         sv.h_in = h_in
-        sv.n1_full = tp.gather(n1)
-        qkv = ops.linear_fwd(sv.n1_full, p[f"{prefix}.attention.wqkv.weight"])
+        qkv, sv.n1_full = tp.linear_gather(n1, p[f"{prefix}.attention.wqkv.weight"],
+                                           key=f"{prefix}.n1")
         ops.rope_(qkv, self.cos, self.sin, batch, self.local_groups, self.local_g, sp.head_dim,
                   position_ids=position_ids)
         sv.qkv = qkv
         sv.attn, sv.lse = ops.attention_fwd(qkv, batch, self.local_groups, self.local_g, sp.head_dim)
-        o = ops.linear_fwd(sv.attn, p[f"{prefix}.attention.wo.weight"], alpha=r)
-        o = tp.scatter_reduce(o)
+        o = tp.linear_scatter(sv.attn, p[f"{prefix}.attention.wo.weight"], alpha=r)
         sv.h_mid, n2, sv.rs2 = ops.add_rmsnorm_fwd(h_in, o, p[f"{prefix}.ffn_norm.weight"],
                                                    sp.norm_epsilon)
-        sv.n2_full = tp.gather(n2)
-        sv.y1 = ops.linear_fwd(sv.n2_full, p[f"{prefix}.feed_forward.wfc1.weight"])
+        sv.y1, sv.n2_full = tp.linear_gather(n2, p[f"{prefix}.feed_forward.wfc1.weight"],
+                                             key=f"{prefix}.n2")
         sv.act = ops.swiglu_fwd(sv.y1)
-        f = ops.linear_fwd(sv.act, p[f"{prefix}.feed_forward.w2.weight"], alpha=r)
-        f = tp.scatter_reduce(f)
+        f = tp.linear_scatter(sv.act, p[f"{prefix}.feed_forward.w2.weight"], alpha=r)
         return sv.h_mid, f, sv
 
     def forward_hidden(self, tokens: torch.Tensor, position_ids=None):
@@ -114,8 +112,8 @@ class MiniCPM4:
         """Final norm, logit divisor, LM head. Returns logits of this rank's vocabulary shard."""
         sp, p = self.spec, self.p
         h_fin, nf, rsf = ops.add_rmsnorm_fwd(h, branch, p["norm.weight"], sp.norm_epsilon)
-        nf_full = self.tp.gather(nf)
-        logits = ops.linear_fwd(nf_full, p["output.weight"], alpha=1.0 / sp.mup_width_scale)
+        logits, nf_full = self.tp.linear_gather(nf, p["output.weight"],
+                                                alpha=1.0 / sp.mup_width_scale, key="head.nf")
         self._head_saved = (h_fin, rsf, nf_full)
         return logits
 
@@ -137,8 +135,7 @@ class MiniCPM4:
         ops.linear_wgrad(dlogits, nf_full, g["output.weight"], accumulate, alpha=a)
         if not sp.tie_embeddings:
             emit("output.weight")
-        dnf = ops.linear_dgrad(dlogits, p["output.weight"], alpha=a)
-        dnf = tp.scatter_reduce(dnf)
+        dnf = tp.dgrad_scatter(dlogits, p["output.weight"], alpha=a)
         dh = ops.rmsnorm_bwd(dnf, h_fin, p["norm.weight"], rsf, None, g["norm.weight"], accumulate)
         emit("norm.weight")
         self._head_saved = None
@@ -154,23 +151,20 @@ class MiniCPM4:
         n_qkv, n_wo = f"{prefix}.attention.wqkv.weight", f"{prefix}.attention.wo.weight"
         n_fn, n_an = f"{prefix}.ffn_norm.weight", f"{prefix}.attention_norm.weight"
         # ---- feed-forward branch
-        dh_full = tp.gather(dh)
+        dact, dh_full = tp.dgrad_gather(dh, p[n_w2], alpha=r, key="bwd.ffn")
         ops.linear_wgrad(dh_full, sv.act, g[n_w2], accumulate, alpha=r)
         emit(n_w2)
-        dact = ops.linear_dgrad(dh_full, p[n_w2], alpha=r)
         dy1 = ops.swiglu_bwd(dact, sv.y1)
         del dact
         ops.linear_wgrad(dy1, sv.n2_full, g[n_fc1], accumulate)
         emit(n_fc1)
-        dn2 = ops.linear_dgrad(dy1, p[n_fc1])
+        dn2 = tp.dgrad_scatter(dy1, p[n_fc1])
         del dy1
-        dn2 = tp.scatter_reduce(dn2)
         dh = ops.rmsnorm_bwd(dn2, sv.h_mid, p[n_fn], sv.rs2, dh, g[n_fn], accumulate)
         emit(n_fn)
         # ---- attention branch
-        dh_full = tp.gather(dh)
+        dattn, dh_full = tp.dgrad_gather(dh, p[n_wo], alpha=r, key="bwd.attn")
         ops.linear_wgrad(dh_full, sv.attn, g[n_wo], accumulate, alpha=r)
-        dattn = ops.linear_dgrad(dh_full, p[n_wo], alpha=r)
         dqkv = ops.attention_bwd(dattn, sv.qkv, sv.attn, sv.lse, batch, self.local_groups,
                                  self.local_g, sp.head_dim)
         del dattn
@@ -180,9 +174,8 @@ class MiniCPM4:
         if tp.replica_size > 1:
             self._reduce_kv_replicas(g[n_qkv])
         emit(n_qkv)
-        dn1 = ops.linear_dgrad(dqkv, p[n_qkv])
+        dn1 = tp.dgrad_scatter(dqkv, p[n_qkv])
         del dqkv
-        dn1 = tp.scatter_reduce(dn1)
         dh = ops.rmsnorm_bwd(dn1, sv.h_in, p[n_an], sv.rs1, dh, g[n_an], accumulate)
         emit(n_an)
         emit(n_wo)

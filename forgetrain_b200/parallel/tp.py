@@ -66,6 +66,29 @@ class TPContext:
         n = x.shape[0] // self.size
         return x[self.rank * n:(self.rank + 1) * n]
 
+    # -- GEMM + collective pairs (overridden by the fused peer-memory implementation) --------
+    def linear_gather(self, x, w, alpha: float = 1.0, key: str | None = None):
+        """``(alpha * gather(x) @ w.T, gather(x))`` for a column-parallel weight."""
+        from .. import ops
+        xf = self.gather(x)
+        return ops.linear_fwd(xf, w, alpha), xf
+
+    def linear_scatter(self, x, w, alpha: float = 1.0):
+        """``scatter_reduce(alpha * x @ w.T)`` for a row-parallel weight."""
+        from .. import ops
+        return self.scatter_reduce(ops.linear_fwd(x, w, alpha))
+
+    def dgrad_gather(self, dy, w, alpha: float = 1.0, key: str | None = None):
+        """``(alpha * gather(dy) @ w, gather(dy))``: backward of ``linear_scatter``."""
+        from .. import ops
+        df = self.gather(dy)
+        return ops.linear_dgrad(df, w, alpha), df
+
+    def dgrad_scatter(self, dy, w, alpha: float = 1.0):
+        """``scatter_reduce(alpha * dy @ w)``: backward of ``linear_gather``."""
+        from .. import ops
+        return self.scatter_reduce(ops.linear_dgrad(dy, w, alpha))
+
     # -- small statistics (vocab-parallel cross-entropy) -----------------------------------
     def stats_reduce(self, x: torch.Tensor, op: str) -> torch.Tensor:
         if self.size == 1:

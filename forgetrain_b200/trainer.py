@@ -53,8 +53,16 @@ class Trainer:
         if dev.type == "cuda" and self.dtype != torch.bfloat16:
             raise ValueError("the CUDA path is bf16-only; use --dtype bf16 on GPUs")
         dp, tp = topo.dp_size, topo.tp_size
-        self.tp_ctx = TPContext(topo.tp_group, tp, topo.tp_rank, cfg.sequence_parallel,
-                                topo.replica_group, topo.replica_size)
+        if (cfg.comm == "fused" and dev.type == "cuda" and tp > 1 and cfg.sequence_parallel
+                and (micro_batch_size * seq_length) % (128 * tp) == 0):
+            from .parallel.fused_tp import FusedTPContext
+            n_slots = 2 * (spec.num_layers + cfg.mtp_num_layers) + 4
+            self.tp_ctx = FusedTPContext(topo.tp_group, tp, topo.tp_rank, dev,
+                                         micro_batch_size * seq_length, spec.hidden_size, n_slots,
+                                         topo.replica_group, topo.replica_size)
+        else:
+            self.tp_ctx = TPContext(topo.tp_group, tp, topo.tp_rank, cfg.sequence_parallel,
+                                    topo.replica_group, topo.replica_size)
         # --- fused peer-memory communication (GPU, >1 rank, comm == "fused")
         self.fused_dp = None
         self.symm = None
