@@ -36,7 +36,9 @@ constexpr int TP_BM = 128;
 constexpr int TP_BK = 64;
 constexpr int TP_BN = 256;
 constexpr int TP_STAGES = 4;
-constexpr int TP_THREADS = 256;  // warp 0 TMA, 1 MMA, 2-5 epilogue, 6-7 peer copy
+constexpr int TP_THREADS = 320;  // warp 0 TMA, 1 MMA, 2-5 epilogue, 6-9 peer copy
+constexpr int TP_COPY_THREADS = 128;
+constexpr int TP_COPY_UNROLL = 8;
 constexpr int TP_GROUP_M = 16;
 constexpr int TP_MAX = 8;
 
@@ -51,6 +53,7 @@ struct TpGemmParams {
   const uint8_t* a_peers[TP_MAX];  // peer base pointers of the gathered A buffer (own = local)
   long a_row_bytes;                // bytes per row (rows are contiguous)
   int* chunk_ready;                // [(tp-1) * tiles_per_slot] counters, zero at launch
+  int copy_group;                  // CTAs that share one chunk (= arrivals expected per chunk)
   // flags / barriers
   uint32_t* flags[TP_MAX];         // peer flag arrays [8 slots][tp]
   uint32_t epoch;
@@ -182,11 +185,11 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (p.mode == 1) {
           const int owner = mt / p.tiles_per_slot;
           if (owner != p.rank) {
-            // wait until every CTA has copied its slice of this 128-row chunk
+            // wait until the CTAs that share this 128-row chunk have copied their slices
             const int hop = (owner - p.rank + p.tp) % p.tp;
             const int* ctr = p.chunk_ready + (hop - 1) * p.tiles_per_slot + mt % p.tiles_per_slot;
             const uint64_t t0 = globaltimer_ns();
-            while (tp_ld_acquire_gpu(ctr) < static_cast<int>(gridDim.x)) {
+            while (tp_ld_acquire_gpu(ctr) < p.copy_group) {
               if (*abort_flag) break;
               if (globaltimer_ns() - t0 > p.limit_ns) {
                 *abort_flag = 1;
@@ -316,50 +319,71 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncwarp();
   } else if (p.mode == 1) {
     // ------------------------------ peer copy warps (all-gather) ------------------------------
-    const int ct = threadIdx.x - 6 * 32;  // 0..63
+    const int ct = threadIdx.x - 6 * 32;  // 0..127
     // tell the peers that this rank's slot is complete (it was written before this launch)
     if (blockIdx.x == 0 && ct < p.tp && ct != p.rank) {
       __threadfence_system();
       tp_st_release_sys(p.flags[ct] + 0 * p.tp + p.rank, p.epoch);
     }
     uint8_t* local = const_cast<uint8_t*>(p.a_peers[p.rank]);
-    for (int hop = 1; hop < p.tp; ++hop) {
+    // Chunks (128-row blocks of the peers' slots) are copied in parallel: a group of
+    // `copy_group` CTAs shares one chunk, so every copy thread has dozens of independent
+    // 16-byte peer loads to keep in flight and all chunks land at about the same time.
+    const int n_chunks = (p.tp - 1) * p.tiles_per_slot;
+    const int G = p.copy_group;
+    int c_begin, c_step, part;
+    if (G > 1 || n_chunks <= static_cast<int>(gridDim.x)) {
+      c_begin = blockIdx.x / G;
+      part = blockIdx.x % G;
+      c_step = n_chunks;  // at most one chunk per CTA
+    } else {
+      c_begin = blockIdx.x;
+      part = 0;
+      c_step = gridDim.x;
+    }
+    int waited_src = -1;
+    for (int c = c_begin; c < n_chunks; c += c_step) {
+      const int hop = c / p.tiles_per_slot + 1;
+      const int j = c % p.tiles_per_slot;
       const int src = (p.rank + hop) % p.tp;
-      // one thread waits for the peer's "slot written" flag and publishes the verdict, so
-      // that all 64 copy threads take the same branch around the named barriers below
-      if (ct == 0) {
-        const bool ok = tp_wait_flag(p.flags[p.rank] + 0 * p.tp + src, p.epoch, p.limit_ns,
-                                     p.status, abort_flag);
-        s_last[1] = ok ? 1 : 0;
-      }
-      named_bar_sync(2, 64);
-      const int go = s_last[1];
-      named_bar_sync(2, 64);
-      if (!go) break;
-      const uint8_t* remote = p.a_peers[src];
-      for (int j = 0; j < p.tiles_per_slot; ++j) {
-        const long row_begin = static_cast<long>(src) * p.slot_rows + static_cast<long>(j) * TP_BM;
-        long rows = p.slot_rows - static_cast<long>(j) * TP_BM;
-        if (rows > TP_BM) rows = TP_BM;
-        const long off = row_begin * p.a_row_bytes;
-        const long nvec = rows * p.a_row_bytes / 16;
-        const long per = (nvec + gridDim.x - 1) / gridDim.x;
-        const long v0 = per * blockIdx.x;
-        long v1 = v0 + per;
-        if (v1 > nvec) v1 = nvec;
-        for (long v = v0 + ct; v < v1; v += 64 * 4) {
-          uint4 x[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (v + u * 64 < v1) x[u] = tp_ld_peer16(remote + off + (v + u * 64) * 16);
-#pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (v + u * 64 < v1) *reinterpret_cast<uint4*>(local + off + (v + u * 64) * 16) = x[u];
+      if (src != waited_src) {
+        // one thread waits for the peer's "slot written" flag and publishes the verdict, so
+        // that all copy threads take the same branch around the named barriers below
+        if (ct == 0) {
+          const bool ok = tp_wait_flag(p.flags[p.rank] + 0 * p.tp + src, p.epoch, p.limit_ns,
+                                       p.status, abort_flag);
+          s_last[1] = ok ? 1 : 0;
         }
-        __threadfence();
-        named_bar_sync(2, 64);
-        if (ct == 0) atomicAdd(p.chunk_ready + (hop - 1) * p.tiles_per_slot + j, 1);
+        named_bar_sync(2, TP_COPY_THREADS);
+        const int go = s_last[1];
+        named_bar_sync(2, TP_COPY_THREADS);
+        if (!go) break;
+        waited_src = src;
       }
+      const uint8_t* remote = p.a_peers[src];
+      const long row_begin = static_cast<long>(src) * p.slot_rows + static_cast<long>(j) * TP_BM;
+      long rows = p.slot_rows - static_cast<long>(j) * TP_BM;
+      if (rows > TP_BM) rows = TP_BM;
+      const long off = row_begin * p.a_row_bytes;
+      const long nvec = rows * p.a_row_bytes / 16;
+      const long per = (nvec + G - 1) / G;
+      const long v0 = per * part;
+      long v1 = v0 + per;
+      if (v1 > nvec) v1 = nvec;
+      for (long v = v0 + ct; v < v1; v += TP_COPY_THREADS * TP_COPY_UNROLL) {
+        uint4 x[TP_COPY_UNROLL];
+#pragma unroll
+        for (int u = 0; u < TP_COPY_UNROLL; ++u)
+          if (v + u * TP_COPY_THREADS < v1)
+            x[u] = tp_ld_peer16(remote + off + (v + u * TP_COPY_THREADS) * 16);
+#pragma unroll
+        for (int u = 0; u < TP_COPY_UNROLL; ++u)
+          if (v + u * TP_COPY_THREADS < v1)
+            *reinterpret_cast<uint4*>(local + off + (v + u * TP_COPY_THREADS) * 16) = x[u];
+      }
+      __threadfence();
+      named_bar_sync(2, TP_COPY_THREADS);
+      if (ct == 0) atomicAdd(p.chunk_ready + c, 1);
     }
   }
 
@@ -474,15 +498,17 @@ extern "C" int ft_gemm_ag(const void* const* a_peers, const void* B, void* D, in
   p.epoch = epoch; p.limit_ns = limit_ns;
   p.done_ctr = static_cast<unsigned int*>(done_ctr);
   p.status = status;
-  if (cudaMemsetAsync(chunk_ready, 0, sizeof(int) * (tp - 1) * p.tiles_per_slot, st) != cudaSuccess)
-    return -3;
+  const int grid = tp_grid();
+  const int n_chunks = (tp - 1) * p.tiles_per_slot;
+  p.copy_group = n_chunks <= grid ? grid / n_chunks : 1;
+  if (cudaMemsetAsync(chunk_ready, 0, sizeof(int) * n_chunks, st) != cudaSuccess) return -3;
   CUtensorMap tA, tB, tD[8];
   if (get_tmap_2d(&tA, a_peers[rank], 2, M, K, K, TP_BM, TP_BK)) return -4;
   int rc = b_mn ? get_tmap_2d(&tB, B, 2, K, N, ldb, TP_BK, 64) : get_tmap_2d(&tB, B, 2, N, K, ldb, TP_BN, TP_BK);
   if (rc) return -5;
   if (get_tmap_2d(&tD[0], D, 2, M, N, ldd, 32, 64)) return -6;
   for (int i = 1; i < 8; ++i) tD[i] = tD[0];
-  return tp_launch(tA, tB, tD, p, tp_grid(), st);
+  return tp_launch(tA, tB, tD, p, grid, st);
 }
 
 // partial planes: every rank owns `partials` = [tp][M/tp][N] bf16 in symmetric memory;

@@ -78,9 +78,10 @@ class MiniCPM4:
         sp, p, tp = self.spec, self.p, self.tp
         r = sp.mup_residual_scale
         sv = LayerSaved()
-        h_in, n1, sv.rs1 = ops.add_rmsnorm_fwd(branch if h_prev is not None else None,
-                                               h_prev if h_prev is not None else branch,
-                                               p[f"{prefix}.attention_norm.weight"], sp.norm_epsilon)
+        x_in = h_prev if h_prev is not None else branch
+        h_in, n1, sv.rs1 = ops.add_rmsnorm_fwd(
+            branch if h_prev is not None else None, x_in, p[f"{prefix}.attention_norm.weight"],
+            sp.norm_epsilon, tp.gather_dest(f"{prefix}.n1", x_in.shape[0], x_in.shape[1]))
         sv.h_in = h_in
         qkv, sv.n1_full = tp.linear_gather(n1, p[f"{prefix}.attention.wqkv.weight"],
                                            key=f"{prefix}.n1")
@@ -89,8 +90,9 @@ class MiniCPM4:
         sv.qkv = qkv
         sv.attn, sv.lse = ops.attention_fwd(qkv, batch, self.local_groups, self.local_g, sp.head_dim)
         o = tp.linear_scatter(sv.attn, p[f"{prefix}.attention.wo.weight"], alpha=r)
-        sv.h_mid, n2, sv.rs2 = ops.add_rmsnorm_fwd(h_in, o, p[f"{prefix}.ffn_norm.weight"],
-                                                   sp.norm_epsilon)
+        sv.h_mid, n2, sv.rs2 = ops.add_rmsnorm_fwd(
+            h_in, o, p[f"{prefix}.ffn_norm.weight"], sp.norm_epsilon,
+            tp.gather_dest(f"{prefix}.n2", o.shape[0], o.shape[1]))
         sv.y1, sv.n2_full = tp.linear_gather(n2, p[f"{prefix}.feed_forward.wfc1.weight"],
                                              key=f"{prefix}.n2")
         sv.act = ops.swiglu_fwd(sv.y1)
@@ -111,7 +113,9 @@ class MiniCPM4:
     def head_forward(self, h, branch):
         """Final norm, logit divisor, LM head. Returns logits of this rank's vocabulary shard."""
         sp, p = self.spec, self.p
-        h_fin, nf, rsf = ops.add_rmsnorm_fwd(h, branch, p["norm.weight"], sp.norm_epsilon)
+        h_fin, nf, rsf = ops.add_rmsnorm_fwd(
+            h, branch, p["norm.weight"], sp.norm_epsilon,
+            self.tp.gather_dest("head.nf", branch.shape[0], branch.shape[1]))
         logits, nf_full = self.tp.linear_gather(nf, p["output.weight"],
                                                 alpha=1.0 / sp.mup_width_scale, key="head.nf")
         self._head_saved = (h_fin, rsf, nf_full)

@@ -38,8 +38,8 @@ def embedding_bwd(ids, dy, scale, dw, vocab_start: int = 0):
     return _pick(dy).embedding_bwd(ids, dy, scale, dw, vocab_start)
 
 
-def add_rmsnorm_fwd(res, x, w, eps):
-    return _pick(x).add_rmsnorm_fwd(res, x, w, eps)
+def add_rmsnorm_fwd(res, x, w, eps, y_out=None):
+    return _pick(x).add_rmsnorm_fwd(res, x, w, eps, y_out)
 
 
 def rmsnorm_bwd(dy, h, w, rstd, dres, dw, accumulate):

@@ -49,11 +49,12 @@ def embedding_bwd(ids, dy, scale, dw, vocab_start: int = 0):
 
 
 # ------------------------------------------------------------------------------- RMSNorm
-def add_rmsnorm_fwd(res, x, w, eps):
+def add_rmsnorm_fwd(res, x, w, eps, y_out=None):
     _bf16(x, "x")
     assert x.is_contiguous() and (res is None or res.is_contiguous())
     T, H = x.shape
-    y = torch.empty_like(x)
+    y = torch.empty_like(x) if y_out is None else y_out
+    assert y.is_contiguous() and y.shape == x.shape
     h = torch.empty_like(x) if res is not None else x
     rstd = torch.empty(T, dtype=torch.float32, device=x.device)
     rc = _L().ft_add_rmsnorm_fwd(P(res), P(x), P(w), P(h if res is not None else None), P(y),

@@ -34,12 +34,16 @@ def embedding_bwd(ids: torch.Tensor, dy: torch.Tensor, scale: float, dw: torch.T
 
 
 # ------------------------------------------------------------------------------- RMSNorm
-def add_rmsnorm_fwd(res: torch.Tensor | None, x: torch.Tensor, w: torch.Tensor, eps: float):
+def add_rmsnorm_fwd(res: torch.Tensor | None, x: torch.Tensor, w: torch.Tensor, eps: float,
+                    y_out: torch.Tensor | None = None):
     """``h = round(res + x)``; ``y = h * rsqrt(mean(h^2) + eps) * w``. Returns (h, y, rstd)."""
     h = x if res is None else (res.float() + x.float()).to(x.dtype)
     hf = h.float()
     rstd = torch.rsqrt(hf.pow(2).mean(dim=-1) + eps)
     y = (hf * rstd[:, None] * w.float()).to(x.dtype)
+    if y_out is not None:
+        y_out.copy_(y)
+        y = y_out
     return h, y, rstd
 
 

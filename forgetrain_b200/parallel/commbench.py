@@ -80,3 +80,53 @@ def main(args) -> None:
     torch.cuda.synchronize()
     _lib.check_status()
     dist.barrier()
+
+
+def tp_main(args) -> None:
+    """Fused all-gather->GEMM / GEMM->reduce-scatter vs NCCL collective + the same GEMM, at the
+    8B tensor-parallel shapes (hidden 4096, ffn 16384, 32 q / 2 kv heads of 128)."""
+    from ..ops import _lib
+    from .fused_tp import FusedTPContext
+    from .topology import init_topology
+    from .tp import TPContext
+    W = int(os.environ.get("WORLD_SIZE", "1"))
+    topo = init_topology(W)
+    tp, r = topo.tp_size, topo.tp_rank
+    assert tp >= 2, "run under torchrun with at least 2 ranks"
+    T, H, F = args.tokens, 4096, 16384
+    ctx = FusedTPContext(topo.tp_group, tp, r, topo.device, T, H, 8)
+    base = TPContext(topo.tp_group, tp, r, True)
+    torch.manual_seed(1234)
+    qkv_n = (32 // tp + 2 * max(1, 2 // tp)) * 128
+    peak = 1652.5
+    cases = [("ag_gemm_qkv", "ag", qkv_n, H), ("ag_gemm_fc1", "ag", 2 * F // tp, H),
+             ("gemm_rs_attn_out", "rs", H, 32 * 128 // tp), ("gemm_rs_fc2", "rs", H, F // tp)]
+    for name, kind, N, K in cases:
+        w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+        g = torch.Generator(device="cuda").manual_seed(10 + r)
+        if kind == "ag":
+            x = torch.randn(T // tp, K, device="cuda", generator=g).to(torch.bfloat16)
+            f_fused = lambda: ctx.linear_gather(x, w, 1.0, key=name)
+            f_base = lambda: base.linear_gather(x, w, 1.0)
+            link_bytes = (tp - 1) / tp * T * K * 2
+        else:
+            x = torch.randn(T, K, device="cuda", generator=g).to(torch.bfloat16)
+            f_fused = lambda: ctx.linear_scatter(x, w, 1.0)
+            f_base = lambda: base.linear_scatter(x, w, 1.0)
+            link_bytes = (tp - 1) / tp * T * N * 2
+        a, b = f_fused(), f_base()
+        a = a[0] if isinstance(a, tuple) else a
+        b = b[0] if isinstance(b, tuple) else b
+        err = float((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-9))
+        t_f = _time(f_fused, 20, topo.tp_group)
+        t_b = _time(f_base, 20, topo.tp_group)
+        flops = 2.0 * T * N * K
+        roof_ms = max(flops / (peak * 1e12), link_bytes / (LINK_GBS * 1e9)) * 1e3
+        if r == 0:
+            print(json.dumps({"op": name, "tp": tp, "M": T, "N": N, "K": K, "fused_ms": t_f,
+                              "nccl_plus_gemm_ms": t_b, "fused_tflops": flops / t_f / 1e9,
+                              "roofline_ms": roof_ms, "fused_roofline_frac": roof_ms / t_f,
+                              "max_rel_diff_vs_nccl_path": err}), flush=True)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    dist.barrier()

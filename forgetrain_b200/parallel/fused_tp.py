@@ -84,6 +84,13 @@ class FusedTPContext(TPContext):
         return (rows_full % self.size == 0 and (rows_full // self.size) % 128 == 0 and n_out >= 64
                 and k % 8 == 0 and rows_full * max(k, n_out) <= self.T * self.H * 4)
 
+    def gather_dest(self, key: str, rows_local: int, cols: int):
+        M = rows_local * self.size
+        if cols != self.H or M > self.T or not self._fusable(M, 64, cols):
+            return None
+        xg = self._gather_view(self._slot(key), M, cols)
+        return xg[self.rank * rows_local:(self.rank + 1) * rows_local]
+
     # ------------------------------------------------------------------ all-gather -> GEMM
     def _ag_gemm(self, x_local, w, alpha, key, b_mn: bool):
         rows_local, K = x_local.shape
@@ -93,7 +100,9 @@ class FusedTPContext(TPContext):
             return None
         slot = self._slot(key)
         xg = self._gather_view(slot, M, K)
-        xg[self.rank * rows_local:(self.rank + 1) * rows_local].copy_(x_local)
+        mine = xg[self.rank * rows_local:(self.rank + 1) * rows_local]
+        if mine.data_ptr() != x_local.data_ptr():
+            mine.copy_(x_local)
         out = torch.empty(M, N, dtype=torch.bfloat16, device=x_local.device)
         base = slot * self.T * self.H * 2
         VP = ctypes.c_void_p * self.size

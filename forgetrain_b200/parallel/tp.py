@@ -66,6 +66,11 @@ class TPContext:
         n = x.shape[0] // self.size
         return x[self.rank * n:(self.rank + 1) * n]
 
+    def gather_dest(self, key: str, rows_local: int, cols: int):
+        """Where the producer of a to-be-gathered activation should write its token shard so
+        that ``linear_gather(key=...)`` needs no staging copy (None: anywhere)."""
+        return None
+
     # -- GEMM + collective pairs (overridden by the fused peer-memory implementation) --------
     def linear_gather(self, x, w, alpha: float = 1.0, key: str | None = None):
         """``(alpha * gather(x) @ w.T, gather(x))`` for a column-parallel weight."""

@@ -6,6 +6,7 @@ iterations, bf16 inputs N(0,1) from a fixed seed).
     python microbench.py gemm  [--tokens 16384] [--shape 0.5b|8b-tp2]
     python microbench.py elem  [--tokens 16384]
     python microbench.py comm  (under torchrun, N >= 2)  bucket reduce-scatter / all-gather sweep
+    python microbench.py tp    (under torchrun, N = TP degree)  fused AG->GEMM / GEMM->RS [--tokens 4096]
 
 Every sub-command prints one JSON line per case with the achieved rate and its fraction of the
 measured peak (``MEASURED_PEAKS.json`` when present, else the stated fallback). ``--once`` runs
@@ -186,9 +187,14 @@ def bench_comm(args):
     commbench.main(args)
 
 
+def bench_tp(args):
+    from forgetrain_b200.parallel import commbench
+    commbench.tp_main(args)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["attn", "gemm", "elem", "comm"])
+    ap.add_argument("what", choices=["attn", "gemm", "elem", "comm", "tp"])
     ap.add_argument("--batch", type=int, default=4)
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=16384)
@@ -200,7 +206,8 @@ def main():
     ap.add_argument("--min-mb", type=float, default=1.0)
     ap.add_argument("--max-mb", type=float, default=1024.0)
     args = ap.parse_args()
-    {"attn": bench_attn, "gemm": bench_gemm, "elem": bench_elem, "comm": bench_comm}[args.what](args)
+    {"attn": bench_attn, "gemm": bench_gemm, "elem": bench_elem, "comm": bench_comm,
+     "tp": bench_tp}[args.what](args)
 
 
 if __name__ == "__main__":

@@ -199,7 +199,7 @@ def test_dp2_fused_matches_nccl_training():
 
 
 # ------------------------------------------------------------------------------------------
-def _tp_train(rank, world, tp, sp):
+def _tp_train(rank, world, tp, sp, comm="nccl"):
     from forgetrain_b200.config import load_model_spec
     from forgetrain_b200.engine_config import from_spec
     from forgetrain_b200.ops import _lib
@@ -208,7 +208,7 @@ def _tp_train(rank, world, tp, sp):
     spec = load_model_spec("8b", num_layers=2, vocab_size=4096, hidden_size=1024, ffn_hidden_size=2048,
                            num_attention_heads=8, num_query_groups=2, head_dim=128, seq_length=512,
                            max_position_embeddings=512)
-    cfg = from_spec(spec, dtype="bf16", comm="nccl", warmup_iters=0, max_lr=1e-3,
+    cfg = from_spec(spec, dtype="bf16", comm=comm, warmup_iters=0, max_lr=1e-3,
                     tensor_parallel_size=tp, sequence_parallel=sp, rs_buckets=4)
     topo = init_topology(tp, num_kv_groups=spec.num_query_groups)
     tr = Trainer(spec, cfg, topo, seq_length=512, micro_batch_size=1, seed=0)
@@ -235,3 +235,13 @@ def test_tp2_matches_tp1_on_gpu(sp):
     assert tp2[0][0] == pytest.approx(tp1[0][0], rel=5e-3)
     assert tp2[0][1] == pytest.approx(tp1[0][1], rel=3e-2)
     assert tp2[0][0][-1] < tp2[0][0][0]
+
+
+@needs2
+def test_tp2_fused_gemm_collectives_match_nccl_path():
+    """all-gather->GEMM and GEMM->reduce-scatter kernels inside the full training step."""
+    fused = run_gpus(_tp_train, 2, 2, True, "fused")
+    nccl = run_gpus(_tp_train, 2, 2, True, "nccl")
+    assert fused[0][0] == pytest.approx(fused[1][0], rel=1e-4)
+    assert fused[0][0] == pytest.approx(nccl[0][0], rel=5e-3)
+    assert fused[0][1] == pytest.approx(nccl[0][1], rel=3e-2)
