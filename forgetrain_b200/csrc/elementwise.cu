@@ -745,3 +745,54 @@ extern "C" int ft_clip_coef(const void* sumsq, float max_norm, void* hyper_clip,
                                     (float*)norm_out);
   return FT_LAUNCH_OK();
 }
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant of ft_rmsnorm_bwd (declared and documented in ft_noalloc.h).
+// The weight-gradient partials go to a scratch array that is part of the library image.
+// ---------------------------------------------------------------------------------------
+#include "ft_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_dw_partial[FT_NOALLOC_MAX_PARTIALS * FT_NOALLOC_MAX_HIDDEN];
+
+// In host code the symbol above is only a handle; the kernels need its device address, which
+// is looked up once per device (with that device current) and cached here.
+static float* g_noalloc_ptr[64] = {nullptr};
+
+static float* noalloc_scratch() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!g_noalloc_ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_dw_partial) != cudaSuccess || !p) return nullptr;
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  return g_noalloc_ptr[dev];
+}
+
+extern "C" int ft_rmsnorm_bwd_noalloc(const void* dy, const void* h, const void* w,
+                                      const void* rstd, const void* dres, void* dx_out, void* dw,
+                                      int accumulate, int T, int H, cudaStream_t st) {
+  if (H > FT_NOALLOC_MAX_HIDDEN) return -2;
+  int nv, tpr;
+  if (!norm_cfg(H, &nv, &tpr)) return -1;
+  float* scratch = noalloc_scratch();
+  if (!scratch) return -3;
+  const int rows_per_cta = 128 / tpr;
+  long want = (static_cast<long>(T) + rows_per_cta - 1) / rows_per_cta;
+  const int grid = want < 1 ? 1 : (want > FT_NOALLOC_MAX_PARTIALS ? FT_NOALLOC_MAX_PARTIALS : (int)want);
+  const size_t smem = tpr == 32 ? (size_t)H * 4 : 0;
+#define CALL_BWD_NA                                                                       \
+  rmsnorm_bwd_kernel<NV, TPR><<<grid, 128, smem, st>>>(                                   \
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w,         \
+      (const float*)rstd, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx_out, scratch, T, H)
+  FT_NORM_DISPATCH(1, 32, CALL_BWD_NA)
+  FT_NORM_DISPATCH(2, 32, CALL_BWD_NA)
+  FT_NORM_DISPATCH(4, 32, CALL_BWD_NA)
+  FT_NORM_DISPATCH(2, 128, CALL_BWD_NA)
+  FT_NORM_DISPATCH(4, 128, CALL_BWD_NA)
+  FT_NORM_DISPATCH(8, 128, CALL_BWD_NA)
+#undef CALL_BWD_NA
+  if (cudaGetLastError() != cudaSuccess) return -100;
+  colsum_partials_kernel<<<(H + 31) / 32, 256, 0, st>>>(scratch, (float*)dw, grid, H, accumulate);
+  return FT_LAUNCH_OK();
+}
