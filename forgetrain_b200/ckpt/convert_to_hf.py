@@ -1,0 +1,119 @@
+#!/usr/bin/env python
+"""Export a ``training_state.pt`` checkpoint to a HuggingFace ``MiniCPMForCausalLM`` folder.
+
+    python -m forgetrain_b200.ckpt.convert_to_hf --checkpoint <step dir | training_state.pt> \\
+        --output <dir> [--model 0.5b] [--dtype bfloat16]
+
+Writes ``model.safetensors`` and ``config.json``. The fused projection weights are taken apart:
+``attention.wqkv`` is interleaved per KV group as ``[q_0..q_{g-1} | k | v]`` and becomes
+``q_proj / k_proj / v_proj``; ``feed_forward.wfc1`` is ``[gate ; up]``. ``tie_word_embeddings``
+is decided by comparing the two tables. Same mapping as the reference's export script
+(exports/train_engine_0.5B/scripts/convert_to_hf.py:58-227).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+from ..config import ModelSpec, load_model_spec
+from .checkpoint import load_resume_checkpoint
+
+
+def split_qkv_interleaved(wqkv: torch.Tensor, spec: ModelSpec):
+    G, g, D, H = spec.num_query_groups, spec.heads_per_group, spec.head_dim, spec.hidden_size
+    grouped = wqkv.view(G, (g + 2) * D, H)
+    q = grouped[:, :g * D].reshape(G * g * D, H)
+    k = grouped[:, g * D:(g + 1) * D].reshape(G * D, H)
+    v = grouped[:, (g + 1) * D:].reshape(G * D, H)
+    return q.contiguous(), k.contiguous(), v.contiguous()
+
+
+def merge_qkv_interleaved(q, k, v, spec: ModelSpec) -> torch.Tensor:
+    """Inverse of :func:`split_qkv_interleaved` (used to import HF weights and by the tests)."""
+    G, g, D, H = spec.num_query_groups, spec.heads_per_group, spec.head_dim, spec.hidden_size
+    return torch.cat([q.view(G, g * D, H), k.view(G, D, H), v.view(G, D, H)], dim=1).reshape(-1, H)
+
+
+def to_hf_state_dict(params: dict[str, torch.Tensor], spec: ModelSpec, dtype=torch.bfloat16):
+    out: dict[str, torch.Tensor] = {}
+    cast = lambda t: t.to(dtype).contiguous()
+    out["model.embed_tokens.weight"] = cast(params["tok_embeddings.weight"])
+    for i in range(spec.num_layers):
+        p, hp = f"layers.{i}", f"model.layers.{i}"
+        out[f"{hp}.input_layernorm.weight"] = cast(params[f"{p}.attention_norm.weight"])
+        out[f"{hp}.post_attention_layernorm.weight"] = cast(params[f"{p}.ffn_norm.weight"])
+        q, k, v = split_qkv_interleaved(params[f"{p}.attention.wqkv.weight"], spec)
+        out[f"{hp}.self_attn.q_proj.weight"] = cast(q)
+        out[f"{hp}.self_attn.k_proj.weight"] = cast(k)
+        out[f"{hp}.self_attn.v_proj.weight"] = cast(v)
+        out[f"{hp}.self_attn.o_proj.weight"] = cast(params[f"{p}.attention.wo.weight"])
+        gate, up = params[f"{p}.feed_forward.wfc1.weight"].chunk(2, dim=0)
+        out[f"{hp}.mlp.gate_proj.weight"] = cast(gate)
+        out[f"{hp}.mlp.up_proj.weight"] = cast(up)
+        out[f"{hp}.mlp.down_proj.weight"] = cast(params[f"{p}.feed_forward.w2.weight"])
+    out["model.norm.weight"] = cast(params["norm.weight"])
+    head = params.get("output.weight", params["tok_embeddings.weight"])
+    tied = head.shape == params["tok_embeddings.weight"].shape and \
+        torch.equal(head, params["tok_embeddings.weight"])
+    if not tied:
+        out["lm_head.weight"] = cast(head)
+    return out, tied
+
+
+def hf_config(spec: ModelSpec, tied: bool, dtype: str = "bfloat16") -> dict:
+    return {
+        "architectures": ["MiniCPMForCausalLM"],
+        "model_type": "minicpm",
+        "vocab_size": spec.vocab_size,
+        "hidden_size": spec.hidden_size,
+        "intermediate_size": spec.ffn_hidden_size,
+        "num_hidden_layers": spec.num_layers,
+        "num_attention_heads": spec.num_attention_heads,
+        "num_key_value_heads": spec.num_query_groups,
+        "head_dim": spec.head_dim,
+        "hidden_act": "silu",
+        "max_position_embeddings": spec.max_position_embeddings,
+        "rms_norm_eps": spec.norm_epsilon,
+        "rope_theta": spec.rotary_base,
+        "scale_emb": spec.mup_emb_scale if spec.mup_enabled else 1.0,
+        "dim_model_base": spec.mup_base_hidden_size if spec.mup_enabled else spec.hidden_size,
+        "scale_depth": spec.mup_depth_scale if spec.mup_enabled else (spec.num_layers ** 0.5),
+        "tie_word_embeddings": bool(tied),
+        "torch_dtype": dtype,
+        "use_cache": True,
+        "bos_token_id": 1,
+        "eos_token_id": 2,
+    }
+
+
+def convert(checkpoint: str, output: str, model: str = "0.5b", dtype: str = "bfloat16") -> Path:
+    from safetensors.torch import save_file
+    state = load_resume_checkpoint(checkpoint)
+    params = state["params"]
+    spec = load_model_spec(model, vocab_size=params["tok_embeddings.weight"].shape[0],
+                           tie_embeddings="output.weight" not in params)
+    sd, tied = to_hf_state_dict(params, spec, getattr(torch, dtype))
+    out = Path(output)
+    out.mkdir(parents=True, exist_ok=True)
+    save_file(sd, str(out / "model.safetensors"), metadata={"format": "pt"})
+    (out / "config.json").write_text(json.dumps(hf_config(spec, tied, dtype), indent=2))
+    return out
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    ap.add_argument("--checkpoint", required=True)
+    ap.add_argument("--output", required=True)
+    ap.add_argument("--model", default="0.5b")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16", "float32"])
+    a = ap.parse_args(argv)
+    out = convert(a.checkpoint, a.output, a.model, a.dtype)
+    print(f"wrote {out / 'model.safetensors'} and {out / 'config.json'}")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

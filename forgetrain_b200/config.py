@@ -109,7 +109,7 @@ class ModelSpec:
         h = self.hidden_size
         per_layer = 2 * h + self.qkv_dim * h + h * self.q_dim + 3 * self.ffn_hidden_size * h
         n = self.vocab_size * h * (1 if self.tie_embeddings else 2) + self.num_layers * per_layer + h
-        n += include_mtp_layers * (per_layer + 2 * h + 2 * h * h)
+        n += include_mtp_layers * (per_layer + 2 * h + 2 * h * h)   # + enorm, hnorm, eh_proj
         return n
 
     def to_json(self) -> str:

@@ -1,0 +1,110 @@
+"""HuggingFace dataset -> packed token batches.
+
+``datasets.load_dataset`` (or local ``--hf-data-files`` in ``json`` / ``text`` / ``parquet``
+format) -> tokenizer -> EOS-joined token stream -> fixed ``seq + 1`` chunks -> ``tokens =
+chunk[:-1]``, ``labels = chunk[1:]``, ``loss_mask = 1``. Documents are sharded ``rank::world``
+over the data-parallel ranks; the tokenizer is loaded rank by rank so a cold cache is written
+once. ``max_packed_rows`` caps the pre-tokenised rows kept in memory. Behavioural spec:
+exports/train_engine_0.5B/src/training_engine_tensor/hf_dataloader.py:28-269 and
+exports/train_engine_8b/src/training_engine_tensor/hf_dataloader.py:42-469.
+"""
+from __future__ import annotations
+
+from typing import Callable, Iterable, Iterator
+
+import torch
+
+
+def pack_token_stream(docs: Iterable[list[int]], eos_id: int, seq_length: int,
+                      max_rows: int | None = None) -> torch.Tensor:
+    """Join documents with EOS and cut the stream into rows of ``seq_length + 1`` tokens."""
+    row = seq_length + 1
+    buf: list[int] = []
+    rows: list[list[int]] = []
+    for d in docs:
+        buf.extend(d)
+        buf.append(eos_id)
+        while len(buf) >= row:
+            rows.append(buf[:row])
+            buf = buf[row:]
+            if max_rows and len(rows) >= max_rows:
+                return torch.tensor(rows, dtype=torch.int64)
+    if not rows:
+        raise ValueError("dataset too small: not a single full sequence could be packed")
+    return torch.tensor(rows, dtype=torch.int64)
+
+
+class PackedTokenLoader:
+    """Cycles over pre-packed rows in micro-batches; the cursor is the only state."""
+
+    def __init__(self, rows: torch.Tensor, micro_batch_size: int, pin: bool = False):
+        if rows.shape[0] < micro_batch_size:
+            raise ValueError(f"only {rows.shape[0]} packed rows for micro-batch {micro_batch_size}")
+        self.rows, self.mbs, self.pin = rows, micro_batch_size, pin
+        self.cursor = 0
+        self.batches_drawn = 0
+
+    def __iter__(self) -> Iterator[dict]:
+        return self
+
+    def __next__(self) -> dict:
+        n = self.rows.shape[0]
+        idx = [(self.cursor + i) % n for i in range(self.mbs)]
+        self.cursor = (self.cursor + self.mbs) % n
+        self.batches_drawn += 1
+        chunk = self.rows[idx]
+        b = {"tokens": chunk[:, :-1].contiguous(), "labels": chunk[:, 1:].contiguous(),
+             "loss_mask": torch.ones(self.mbs, chunk.shape[1] - 1, dtype=torch.float32)}
+        return {k: v.pin_memory() for k, v in b.items()} if self.pin else b
+
+    def state_dict(self) -> dict:
+        return {"kind": "packed", "cursor": self.cursor, "batches_drawn": self.batches_drawn}
+
+    def load_state_dict(self, st: dict) -> None:
+        if st and st.get("kind") == "packed":
+            n = self.rows.shape[0]
+            self.batches_drawn = int(st.get("batches_drawn", 0))
+            self.cursor = (self.batches_drawn * self.mbs) % n
+
+
+def render_text(example: dict, text_field: str, template: str | None) -> str:
+    return template.format(**example) if template else str(example[text_field])
+
+
+def build_hf_dataloader(args, spec, micro_batch_size: int, seq_length: int, topo,
+                        tokenizer=None, dataset=None) -> PackedTokenLoader:
+    """Build the loader from CLI arguments. ``tokenizer`` / ``dataset`` may be injected (tests,
+    offline use); otherwise ``transformers`` / ``datasets`` are imported here."""
+    import torch.distributed as dist
+    if tokenizer is None:
+        from transformers import AutoTokenizer
+        if not args.tokenizer_path:
+            raise SystemExit("--hf-dataset needs --tokenizer-path")
+        # rank-serialised load: rank 0 warms the cache, the others follow
+        for turn in range(2):
+            if (topo.rank == 0) == (turn == 0):
+                tokenizer = AutoTokenizer.from_pretrained(args.tokenizer_path, trust_remote_code=True)
+            if topo.world > 1 and dist.is_initialized():
+                dist.barrier()
+    if dataset is None:
+        from datasets import load_dataset
+        if args.hf_data_files:
+            fmt = args.hf_data_format or "json"
+            dataset = load_dataset(fmt, data_files=args.hf_data_files, split=args.hf_dataset_split)
+        else:
+            dataset = load_dataset(args.hf_dataset, args.hf_dataset_config, split=args.hf_dataset_split)
+    eos = getattr(tokenizer, "eos_token_id", None)
+    if eos is None:
+        eos = 2
+    vocab = spec.vocab_size
+
+    def docs():
+        for i, ex in enumerate(dataset):
+            if i % topo.dp_size != topo.dp_rank:
+                continue
+            ids = tokenizer(render_text(ex, args.hf_text_field, args.hf_text_template),
+                            add_special_tokens=False)["input_ids"]
+            yield [t if t < vocab else vocab - 1 for t in ids]
+
+    rows = pack_token_stream(docs(), eos, seq_length, getattr(args, "max_packed_rows", None))
+    return PackedTokenLoader(rows, micro_batch_size, pin=topo.device.type == "cuda")

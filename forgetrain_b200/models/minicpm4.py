@@ -132,14 +132,20 @@ class MiniCPM4:
             stats_reduce=tp.stats_reduce if tp.enabled else None)
 
     # ----------------------------------------------------------------------------- backward
-    def head_backward(self, dlogits, accumulate: bool, emit):
+    def head_backward(self, dlogits, accumulate: bool, emit, dnf_extra=None, emit_output=True,
+                      skip_wgrad=False):
+        """Backward of head + final norm. ``dnf_extra`` is added to the gradient of the final
+        norm's OUTPUT (used by the MTP head, which consumes that tensor)."""
         sp, p, g, tp = self.spec, self.p, self.g, self.tp
         h_fin, rsf, nf_full = self._head_saved
         a = 1.0 / sp.mup_width_scale
-        ops.linear_wgrad(dlogits, nf_full, g["output.weight"], accumulate, alpha=a)
-        if not sp.tie_embeddings:
+        if not skip_wgrad:
+            ops.linear_wgrad(dlogits, nf_full, g["output.weight"], accumulate, alpha=a)
+        if not sp.tie_embeddings and emit_output:
             emit("output.weight")
         dnf = tp.dgrad_scatter(dlogits, p["output.weight"], alpha=a)
+        if dnf_extra is not None:
+            dnf = dnf + dnf_extra
         dh = ops.rmsnorm_bwd(dnf, h_fin, p["norm.weight"], rsf, None, g["norm.weight"], accumulate)
         emit("norm.weight")
         self._head_saved = None
@@ -191,13 +197,15 @@ class MiniCPM4:
         kv = gqkv[self.local_g * D:]
         self.tp.replica_all_reduce_(kv)
 
-    def embedding_backward(self, tokens, dh, accumulate: bool, emit):
+    def embedding_backward(self, tokens, dh, accumulate: bool, emit, extra=None):
         sp, g, tp = self.spec, self.g, self.tp
         gw = g["tok_embeddings.weight"]
         if not accumulate and not sp.tie_embeddings:
             gw.zero_()
         dfull = tp.gather(dh) if tp.enabled else dh
         ops.embedding_bwd(tokens, dfull, sp.emb_scale, gw, self.vocab_start)
+        for ids_x, d_x in extra or ():     # further lookups of the same table (MTP heads)
+            ops.embedding_bwd(ids_x, d_x, sp.emb_scale, gw, self.vocab_start)
         emit("tok_embeddings.weight")
 
     def backward(self, tokens, dlogits, accumulate: bool,

@@ -72,7 +72,6 @@ def all_param_specs(spec: ModelSpec, mtp_num_layers: int = 0) -> list[ParamSpec]
         out.append(ParamSpec(f"{p}.hnorm.weight", (h,), True, False, False, None, "ones"))
         out.append(ParamSpec(f"{p}.eh_proj.weight", (h, 2 * h), False, True, True, None, "mup"))
         out.extend(_layer_specs(p, spec))
-        out.append(ParamSpec(f"{p}.final_layernorm.weight", (h,), True, False, False, None, "ones"))
     if not spec.tie_embeddings:
         out.append(ParamSpec("output.weight", (v, h), False, True, False, 0, "normal"))
     return out
@@ -91,7 +90,7 @@ def flat_buffer_order(spec: ModelSpec, mtp_num_layers: int = 0) -> list[ParamSpe
         order.append("output.weight")
     for k in reversed(range(mtp_num_layers)):
         p = mtp_layer_prefix(k)
-        order += [f"{p}.final_layernorm.weight", f"{p}.feed_forward.w2.weight",
+        order += [f"{p}.feed_forward.w2.weight",
                   f"{p}.feed_forward.wfc1.weight", f"{p}.ffn_norm.weight",
                   f"{p}.attention.wqkv.weight", f"{p}.attention_norm.weight",
                   f"{p}.attention.wo.weight", f"{p}.eh_proj.weight", f"{p}.hnorm.weight",

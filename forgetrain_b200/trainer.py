@@ -117,7 +117,10 @@ class Trainer:
         self.num_samples = 0
         self.loss_buf = torch.zeros(1, dtype=torch.float32, device=dev)
         self.graph = None
-        self.launch_count = 0
+        if cfg.step_cuda_graph and dev.type == "cuda" and self.mtp is None:
+            from .graph.step_graph import GraphedComputeStep
+            self.graph = GraphedComputeStep(self.model, cfg.step_cuda_graph_warmup,
+                                            cfg.step_cuda_graph_sanity, cfg.step_cuda_graph_tol)
 
     # ------------------------------------------------------------------ helpers
     def _grad_ready(self, name: str) -> None:
@@ -137,6 +140,12 @@ class Trainer:
         mask = batch.get("loss_mask")
         pos = batch.get("position_ids")
         m = self.model
+        if self.graph is not None:
+            loss = self.graph(batch, loss_scale, accumulate)
+            if last:      # gradients are complete only after the replay: release every bucket now
+                for ps in self.store.order:
+                    self._grad_ready(ps.name)
+            return loss
         if self.mtp is None:
             return m.forward_backward(tokens, labels, mask, loss_scale, accumulate, grad_ready, pos)
         return self.mtp.forward_backward(tokens, labels, mask, loss_scale, accumulate, grad_ready, pos)

@@ -1,0 +1,86 @@
+"""Failure handling, exercised on the host: a rank that dies, a rank that never joins, a
+collective that times out, a checkpoint writer that fails. No GPU is involved."""
+import os
+import sys
+import time
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from dist_util import run_ranks  # noqa: E402
+
+
+def _rank_raises(rank, world):
+    import datetime
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    t = torch.ones(4)
+    dist.all_reduce(t)                       # healthy step
+    if rank == 1:
+        raise RuntimeError("injected failure on rank 1")
+    try:
+        dist.all_reduce(t)                   # the peer is gone: must end with an error, not hang
+    except Exception as e:  # noqa: BLE001
+        return f"collective failed: {type(e).__name__}"
+    return "collective unexpectedly succeeded"
+
+
+def test_a_failing_rank_surfaces_as_an_error_on_every_rank():
+    t0 = time.time()
+    with pytest.raises(RuntimeError, match="injected failure on rank 1|collective failed"):
+        run_ranks(_rank_raises, 2, timeout=120)
+    assert time.time() - t0 < 120
+
+
+def _late_rank(rank, world):
+    """Rank 1 never joins the second collective; rank 0's short timeout ends it."""
+    import datetime
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    t = torch.ones(2)
+    dist.all_reduce(t)
+    if rank == 1:
+        time.sleep(8)
+        return "absent"
+    try:
+        dist.all_reduce(t)
+        return "no error"
+    except Exception as e:  # noqa: BLE001
+        return f"timeout: {type(e).__name__}"
+
+
+def test_missing_rank_ends_the_collective_with_a_timeout():
+    res = run_ranks(_late_rank, 2, timeout=120)
+    assert res[0].startswith("timeout") and res[1] == "absent"
+
+
+def test_reducer_detects_a_gradient_that_never_arrives():
+    from forgetrain_b200.config import load_model_spec
+    from forgetrain_b200.models.params import ParamStore
+    from forgetrain_b200.parallel.dp import BucketedGradReducer
+    spec = load_model_spec("tiny", num_layers=1, vocab_size=128, hidden_size=128, ffn_hidden_size=256,
+                           num_attention_heads=4, num_query_groups=2, head_dim=32, tie_embeddings=False)
+    st = ParamStore(spec, "cpu", torch.float32)
+    red = BucketedGradReducer(st.flat_grads, st.entries(), 1, 0, None, 10 ** 9)
+    red.start_step()
+    for ps in st.order[:-1]:                 # the embedding's gradient is "lost"
+        red.on_grad_ready(ps.name)
+    with pytest.raises(RuntimeError, match="never became ready"):
+        red.wait_all()
+
+
+def test_truncated_checkpoint_is_rejected(tmp_path):
+    from forgetrain_b200.ckpt import checkpoint as ck
+    p = ck.save_checkpoint(tmp_path, 1, params={"a": torch.randn(64, 64)}, param_names=["a"],
+                           optimizer_state=None, async_io=False)
+    data = p.read_bytes()
+    p.write_bytes(data[: len(data) // 2])
+    with pytest.raises(Exception):
+        ck.load_resume_checkpoint(tmp_path)
+
+
+def test_status_word_codes_have_messages():
+    from forgetrain_b200.ops import _lib
+    assert set(_lib.STATUS_MESSAGES) == {1, 2, 3, 4, 5, 6}
+    assert "peer" in _lib.STATUS_MESSAGES[5]

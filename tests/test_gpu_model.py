@@ -80,3 +80,23 @@ def test_gradient_accumulation_on_gpu():
     # the attention backward reduces dQ tiles with fp32 atomics, so two runs of the same step
     # differ by bf16 rounding noise (~2e-3 of the largest gradient); accumulation adds none
     assert float(err) < 1e-2
+
+
+def test_cuda_graph_step_matches_eager():
+    from forgetrain_b200.engine_config import from_spec
+    from forgetrain_b200.parallel.topology import Topology
+    from forgetrain_b200.trainer import Trainer
+    spec = _spec()
+    tok, lab = _batch(spec)
+    batch = {"tokens": tok.cuda(), "labels": lab.cuda(), "loss_mask": torch.ones(2, 256, device="cuda")}
+    out = {}
+    for graph in (False, True):
+        cfg = from_spec(spec, dtype="bf16", comm="nccl", warmup_iters=0, max_lr=2e-3,
+                        step_cuda_graph=graph, step_cuda_graph_sanity=True)
+        tr = Trainer(spec, cfg, Topology(device=torch.device("cuda", 0)), seq_length=256,
+                     micro_batch_size=2, seed=0)
+        out[graph] = [float(tr.train_step([batch, batch])["loss"]) for _ in range(4)]
+        if graph:
+            assert tr.graph.replays == 8 and len(tr.graph._graphs) == 2
+    assert out[True] == pytest.approx(out[False], rel=2e-3)
+    assert out[True][-1] < out[True][0]

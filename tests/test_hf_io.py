@@ -1,0 +1,90 @@
+import json
+import types
+
+import pytest
+import torch
+
+from forgetrain_b200.ckpt import checkpoint as ck
+from forgetrain_b200.ckpt.convert_to_hf import (convert, hf_config, merge_qkv_interleaved,
+                                                  split_qkv_interleaved, to_hf_state_dict)
+from forgetrain_b200.config import load_model_spec
+from forgetrain_b200.data.hf_dataloader import (PackedTokenLoader, build_hf_dataloader,
+                                                 pack_token_stream)
+from forgetrain_b200.models.params import ParamStore
+from forgetrain_b200.parallel.topology import Topology
+
+
+def _spec(tie=False):
+    return load_model_spec("tiny", num_layers=2, vocab_size=128, hidden_size=128, ffn_hidden_size=256,
+                           num_attention_heads=4, num_query_groups=2, head_dim=32, tie_embeddings=tie)
+
+
+def test_qkv_split_is_per_group_and_invertible():
+    spec = _spec()
+    G, g, D, H = 2, 2, 32, 128
+    w = torch.arange(spec.qkv_dim * H, dtype=torch.float32).view(spec.qkv_dim, H)
+    q, k, v = split_qkv_interleaved(w, spec)
+    assert q.shape == (G * g * D, H) and k.shape == (G * D, H) and v.shape == (G * D, H)
+    # group 1's first q row sits after group 0's (g + 2) heads
+    assert torch.equal(q[g * D], w[(g + 2) * D])
+    assert torch.equal(k[0], w[g * D]) and torch.equal(v[0], w[(g + 1) * D])
+    assert torch.equal(merge_qkv_interleaved(q, k, v, spec), w)
+
+
+@pytest.mark.parametrize("tie", [False, True])
+def test_export_writes_safetensors_and_config(tmp_path, tie):
+    from safetensors.torch import load_file
+    spec = _spec(tie)
+    st = ParamStore(spec, "cpu", torch.float32)
+    st.init_random(0)
+    names = [p.name for p in st.specs]
+    ck.save_checkpoint(tmp_path, 5, params={n: st.params[n] for n in names}, param_names=names,
+                       optimizer_state=None, async_io=False)
+    spec_path = tmp_path / "spec.toml"
+    spec_path.write_text(
+        "[model]\nname='t'\nvocab_size=128\nhidden_size=128\nnum_layers=2\nnum_attention_heads=4\n"
+        "num_query_groups=2\nhead_dim=32\nffn_hidden_size=256\nseq_length=64\n"
+        "max_position_embeddings=64\nnorm_epsilon=1e-6\nrotary_base=10000.0\ninit_method_std=0.02\n")
+    out = convert(str(tmp_path / "step_0000005"), str(tmp_path / "hf"), model=str(spec_path), dtype="float32")
+    sd = load_file(str(out / "model.safetensors"))
+    cfg = json.loads((out / "config.json").read_text())
+    assert cfg["architectures"] == ["MiniCPMForCausalLM"] and cfg["tie_word_embeddings"] is tie
+    assert cfg["scale_emb"] == 12.0 and cfg["dim_model_base"] == 256 and cfg["scale_depth"] == 1.4
+    assert cfg["num_key_value_heads"] == 2 and cfg["rms_norm_eps"] == 1e-6
+    assert ("lm_head.weight" in sd) is (not tie)
+    gate = sd["model.layers.1.mlp.gate_proj.weight"]
+    assert torch.equal(gate, st.params["layers.1.feed_forward.wfc1.weight"][:256])
+    assert torch.equal(sd["model.layers.0.self_attn.o_proj.weight"], st.params["layers.0.attention.wo.weight"])
+    assert len(sd) == 2 + 9 * 2 + (0 if tie else 1)
+
+
+def test_packing_and_loader_cursor():
+    rows = pack_token_stream([[1, 2, 3], [4, 5], [6, 7, 8, 9]], eos_id=0, seq_length=3)
+    assert rows.tolist() == [[1, 2, 3, 0], [4, 5, 0, 6], [7, 8, 9, 0]]
+    ld = PackedTokenLoader(rows, 2)
+    b = next(ld)
+    assert b["tokens"].tolist() == [[1, 2, 3], [4, 5, 0]] and b["labels"].tolist() == [[2, 3, 0], [5, 0, 6]]
+    assert b["loss_mask"].sum() == 6
+    st = ld.state_dict()
+    nxt = next(ld)
+    ld2 = PackedTokenLoader(rows, 2)
+    ld2.load_state_dict(st)
+    assert torch.equal(next(ld2)["tokens"], nxt["tokens"])
+    with pytest.raises(ValueError):
+        pack_token_stream([[1]], eos_id=0, seq_length=8)
+
+
+def test_build_loader_with_injected_tokenizer_and_rank_sharding():
+    class Tok:
+        eos_token_id = 9
+
+        def __call__(self, text, add_special_tokens=False):
+            return {"input_ids": [ord(c) % 50 + 10 for c in text]}
+    data = [{"text": "abcdefgh" * 4} for _ in range(8)]
+    args = types.SimpleNamespace(hf_text_field="text", hf_text_template=None, max_packed_rows=None,
+                                 tokenizer_path=None, hf_data_files=None)
+    spec = _spec()
+    a = build_hf_dataloader(args, spec, 1, 16, Topology(dp_size=2, dp_rank=0), tokenizer=Tok(), dataset=data)
+    b = build_hf_dataloader(args, spec, 1, 16, Topology(dp_size=2, dp_rank=1), tokenizer=Tok(), dataset=data)
+    assert a.rows.shape[1] == 17 and a.rows.shape[0] == b.rows.shape[0] > 0
+    assert int(a.rows.max()) < spec.vocab_size
