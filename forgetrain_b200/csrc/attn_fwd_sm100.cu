@@ -107,6 +107,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   const uint32_t tmem_S[2] = {tmem_base, tmem_base + 128};
   const uint32_t tmem_O[2] = {tmem_base + 256, tmem_base + 256 + D};
 
+  if (warp < 4) {
+  reg_dealloc<96>();   // TMA / MMA warps need few registers, the softmax warps a whole score row
   if (warp == 0) {
     if (lane == 0) {
       // ---------------- producer ----------------
@@ -194,7 +196,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
         }
       }
     }
-  } else if (warp >= 4) {
+  }
+  } else {
+    reg_alloc<200>();
     // ---------------- softmax warpgroups ----------------
     const int w = (warp - 4) >> 2;           // query tile of this warpgroup
     const int r = threadIdx.x - 128 - w * 128;  // row inside the tile == TMEM lane
@@ -204,23 +208,30 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
     uint8_t* sP = smem + L::P_OFF + w * 32768;
     float m_ref = -INFINITY, l = 0.f;
     const int nk = n_kv[w];
+    const uint64_t sl2x2 = pack_f32x2(p.scale_log2, p.scale_log2);
+    uint64_t lsum2 = pack_f32x2(0.f, 0.f);
     for (int j = 0; j < nk; ++j) {
       mbar_wait(&s_full[w], j & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
-      const bool diag = (j == qt);
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        tmem_ld32(tmem_S[w] + lane_off + c * 32, s);
-        tmem_ld_wait();
+      // one pass over TMEM: the whole score row (128 fp32) lives in registers
+      uint32_t s[128];
+      tmem_ld32(tmem_S[w] + lane_off, s);
+      tmem_ld32(tmem_S[w] + lane_off + 32, s + 32);
+      tmem_ld32(tmem_S[w] + lane_off + 64, s + 64);
+      tmem_ld32(tmem_S[w] + lane_off + 96, s + 96);
+      tmem_ld_wait();
+      if (j == qt) {  // diagonal tile: columns beyond the row are masked
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          float v = __uint_as_float(s[k]);
-          if (diag && (c * 32 + k) > r) v = -INFINITY;
-          mx = fmaxf(mx, v);
-        }
+        for (int k = 0; k < 128; ++k)
+          if (k > r) s[k] = 0xff800000u;  // -inf
       }
+      float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]);
+#pragma unroll
+      for (int k = 2; k < 128; k += 4) {
+        mx0 = max3(mx0, __uint_as_float(s[k]), __uint_as_float(s[k + 1]));
+        if (k + 3 < 128) mx1 = max3(mx1, __uint_as_float(s[k + 2]), __uint_as_float(s[k + 3]));
+      }
+      const float mx = fmaxf(mx0, mx1);
       const float m_new = fmaxf(m_ref, mx * p.scale_log2);
       const bool need = (m_new - m_ref) > 8.0f;  // also true while m_ref is still -inf
       if (j > 0) {
@@ -230,7 +241,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       if (__any_sync(0xffffffffu, need)) {
         const float alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
         m_ref = m_new;
-        l *= alpha;
+        lsum2 = mul_f32x2(lsum2, pack_f32x2(alpha, alpha));
         if (j > 0) {
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
@@ -244,34 +255,33 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
           tmem_st_wait();
         }
       }
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        tmem_ld32(tmem_S[w] + lane_off + c * 32, s);
-        tmem_ld_wait();
-        float pv[32];
+      const uint64_t negm2 = pack_f32x2(-m_ref, -m_ref);
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          float v = fast_exp2(__uint_as_float(s[k]) * p.scale_log2 - m_ref);
-          if (diag && (c * 32 + k) > r) v = 0.f;
-          pv[k] = v;
-          l += v;
-        }
-        uint8_t* rowp = sP + (c >> 1) * 16384 + r * 128;
+      for (int c = 0; c < 16; ++c) {  // 16 chunks of 8 columns = one 16-byte store each
+        uint32_t packed[4];
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          uint4 u;
-          u.x = pack_bf16x2(pv[8 * jj + 0], pv[8 * jj + 1]);
-          u.y = pack_bf16x2(pv[8 * jj + 2], pv[8 * jj + 3]);
-          u.z = pack_bf16x2(pv[8 * jj + 4], pv[8 * jj + 5]);
-          u.w = pack_bf16x2(pv[8 * jj + 6], pv[8 * jj + 7]);
-          const int chunk = (c & 1) * 4 + jj;
-          *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) = u;
+        for (int q2 = 0; q2 < 4; ++q2) {
+          const int k = c * 8 + q2 * 2;
+          const uint64_t t = fma_f32x2(pack_f32x2(__uint_as_float(s[k]), __uint_as_float(s[k + 1])),
+                                       sl2x2, negm2);
+          float t0, t1;
+          unpack_f32x2(t, t0, t1);
+          const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+          lsum2 = add_f32x2(lsum2, pack_f32x2(p0, p1));
+          packed[q2] = pack_bf16x2(p0, p1);
         }
+        uint8_t* rowp = sP + (c >> 3) * 16384 + r * 128;
+        *reinterpret_cast<uint4*>(rowp + (((c & 7) ^ (r & 7)) << 4)) =
+            make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(&p_ready[w]);
+    }
+    {
+      float l0, l1;
+      unpack_f32x2(lsum2, l0, l1);
+      l = l0 + l1;
     }
     // ---------------- epilogue: O / l -> bf16 -> TMA store; LSE ----------------
     mbar_wait(&o_done[w], (nk - 1) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
