@@ -26,7 +26,7 @@ namespace ft {
 int get_tmap_2d(CUtensorMap* out, const void* base, int elt, uint64_t rows, uint64_t cols,
                 uint64_t ld, uint32_t box_r, uint32_t box_c);
 
-constexpr int FAB_THREADS = 384;
+constexpr int FAB_THREADS = 512;  // WG0: TMA + MMA, WG1/WG2: softmax halves, WG3: dQ / dK / dV drain
 constexpr int FAB_BLK = 128;
 
 struct FaBwdParams {
@@ -45,23 +45,25 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
-template <int D, int QS, int PB>
+// QS: Q/dO stages, NP: P^T buffers, NDS: dS^T buffers, NST: (lse2, delta) buffers
+template <int D, int QS, int NP, int NDS, int NST>
 struct FaBwdSmem {
   static constexpr int TILE = FAB_BLK * D * 2;
   static constexpr int K_OFF = 0;
   static constexpr int V_OFF = TILE;
-  static constexpr int QDO_OFF = 2 * TILE;             // QS x (Q tile, dO tile)
-  static constexpr int PDS_OFF = QDO_OFF + QS * 2 * TILE;  // PB x (P^T 32 KB, dS^T 32 KB)
-  static constexpr int STAT_OFF = PDS_OFF + PB * 65536;   // QS x (lse2[128], delta[128]) fp32
-  static constexpr int BAR_OFF = STAT_OFF + QS * 1024;
-  static constexpr int TOTAL = BAR_OFF + 256;             // base must come 1024-byte aligned
+  static constexpr int QDO_OFF = 2 * TILE;                 // QS x (Q tile, dO tile)
+  static constexpr int P_OFF = QDO_OFF + QS * 2 * TILE;    // NP x P^T (128 x 128 bf16)
+  static constexpr int DS_OFF = P_OFF + NP * 32768;        // NDS x dS^T
+  static constexpr int STAT_OFF = DS_OFF + NDS * 32768;    // NST x (lse2[128], delta[128]) fp32
+  static constexpr int BAR_OFF = STAT_OFF + NST * 1024;
+  static constexpr int TOTAL = BAR_OFF + 256;              // base must come 1024-byte aligned
 };
 
-template <int D, int QS, int PB>
+template <int D, int QS, int NP, int NDS, int NST>
 __global__ void __launch_bounds__(FAB_THREADS, 1)
 fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
               const FaBwdParams p) {
-  using L = FaBwdSmem<D, QS, PB>;
+  using L = FaBwdSmem<D, QS, NP, NDS, NST>;
   constexpr bool ALIAS = (D == 128);  // dQ shares the TMEM columns of S^T
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
@@ -71,15 +73,16 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* kv_full = bars;          // 1
-  uint64_t* qdo_full = bars + 1;     // 2
-  uint64_t* qdo_empty = bars + 3;    // 2
-  uint64_t* sdp_full = bars + 5;     // 1
-  uint64_t* pds_ready = bars + 6;    // 2 (count 128)
-  uint64_t* pds_free = bars + 8;     // 2
-  uint64_t* dq_full = bars + 10;     // 1
-  uint64_t* dq_drained = bars + 11;  // 1 (count 128)
-  uint64_t* dkv_full = bars + 12;    // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* qdo_full = bars + 1;     // 3
+  uint64_t* qdo_empty = bars + 4;    // 3
+  uint64_t* sdp_full = bars + 7;     // 1
+  uint64_t* pds_ready = bars + 8;    // 2 (count 256): P^T and dS^T of a step are written
+  uint64_t* ds_free = bars + 10;     // 2: dS^T buffer consumed by dK and dQ
+  uint64_t* p_free = bars + 12;      // 2: P^T buffer consumed by dV
+  uint64_t* dq_full = bars + 14;     // 1
+  uint64_t* dq_drained = bars + 15;  // 1 (count 128)
+  uint64_t* dkv_full = bars + 16;    // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -101,11 +104,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < 3; ++s) {
       mbar_init(&qdo_full[s], 1);
       mbar_init(&qdo_empty[s], 1);
-      mbar_init(&pds_ready[s], 128);
-      mbar_init(&pds_free[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&pds_ready[s], 256);
+      mbar_init(&ds_free[s], 1);
+      mbar_init(&p_free[s], 1);
     }
     mbar_init(sdp_full, 1);
     mbar_init(dq_full, 1);
@@ -134,6 +140,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   auto step_head = [&](int n) { return grp * p.g + hc * p.hpc + n / n_q; };
   auto step_qtile = [&](int n) { return j + n % n_q; };
 
+  if (warp < 4) {
+  reg_dealloc<88>();
   if (warp == 0) {
     if (lane == 0) {
       // ---------------- producer ----------------
@@ -154,7 +162,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
         uint8_t* dst = smem + L::QDO_OFF + s * 2 * L::TILE;
         {
           const long soff = (static_cast<long>(b) * p.Hq + head) * p.S + qt * FAB_BLK;
-          float* st = reinterpret_cast<float*>(smem + L::STAT_OFF + s * 1024);
+          if (n >= NST)   // the (lse2, delta) slot is free once the softmax of step n-NST is done
+            mbar_wait(&pds_ready[(n - NST) % NDS], ((n - NST) / NDS) & 1, abort_flag, p.status,
+                      FT_ERR_WAIT_MISC);
+          float* st = reinterpret_cast<float*>(smem + L::STAT_OFF + (n % NST) * 1024);
           bulk_load_1d(st, p.lse2 + soff, 512, &qdo_full[s]);
           bulk_load_1d(st + 128, p.delta + soff, 512, &qdo_full[s]);
         }
@@ -178,7 +189,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       const uint32_t idesc_dkv = make_idesc_bf16(128, D, 0, 1);
       const uint32_t idesc_dq = make_idesc_bf16(128, D, 1, 1);
       const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
-      const uint32_t sQDO = smem_u32(smem + L::QDO_OFF), sPDS = smem_u32(smem + L::PDS_OFF);
+      const uint32_t sQDO = smem_u32(smem + L::QDO_OFF);
+      const uint32_t sP = smem_u32(smem + L::P_OFF), sDS = smem_u32(smem + L::DS_OFF);
       auto issue_sdp = [&](int n) {
         const int s = n % QS;
         mbar_wait(&qdo_full[s], (n / QS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
@@ -201,12 +213,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       mbar_wait(kv_full, 0, abort_flag, p.status, FT_ERR_WAIT_FULL);
       issue_sdp(0);
       for (int n = 0; n < N; ++n) {
-        const int s = n % QS, pb = n % PB;
-        mbar_wait(&pds_ready[pb], (n / PB) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+        const int s = n % QS;
+        mbar_wait(&pds_ready[n % NDS], (n / NDS) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
         tc_fence_after();
         if (!ALIAS && n + 1 < N) issue_sdp(n + 1);
         const uint32_t q = sQDO + s * 2 * L::TILE, dO = q + L::TILE;
-        const uint32_t pT = sPDS + pb * 65536, dsT = pT + 32768;
+        const uint32_t pT = sP + (n % NP) * 32768, dsT = sDS + (n % NDS) * 32768;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t aoff = (kk / 4) * 16384 + (kk % 4) * 32;
@@ -214,6 +226,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
                   make_smem_desc(dO + kk * 2048, 16384, 1024), idesc_dkv,
                   (n > 0 || kk > 0) ? 1u : 0u);
         }
+        umma_commit(&p_free[n % NP]);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t aoff = (kk / 4) * 16384 + (kk % 4) * 32;
@@ -221,6 +234,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
                   make_smem_desc(q + kk * 2048, 16384, 1024), idesc_dkv,
                   (n > 0 || kk > 0) ? 1u : 0u);
         }
+        // Q_n / dO_n are last read by dK / dV: hand the stage back to the producer now
+        umma_commit(&qdo_empty[s]);
         if (n > 0) {
           mbar_wait(dq_drained, (n - 1) & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
           tc_fence_after();
@@ -231,8 +246,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
                   make_smem_desc(sK + kk * 2048, 16384, 1024), idesc_dq, kk > 0 ? 1u : 0u);
         }
         umma_commit(dq_full);
-        umma_commit(&qdo_empty[s]);
-        umma_commit(&pds_free[pb]);
+        umma_commit(&ds_free[n % NDS]);
         if (ALIAS && n + 1 < N) {
           mbar_wait(dq_drained, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
           tc_fence_after();
@@ -241,91 +255,76 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       }
       umma_commit(dkv_full);
     }
-  } else if (warp >= 4 && warp < 8) {
-    // ---------------- softmax warpgroup: thread r owns kv row r ----------------
-    const int r = threadIdx.x - 128;
+  }
+  } else if (warp < 12) {
+    reg_alloc<176>();
+    // ---------------- two softmax warpgroups: thread owns kv row r and 64 of the 128 query
+    // columns (warpgroup 1: columns 0-63, warpgroup 2: columns 64-127) ----------------
+    const int half = (warp - 4) >> 2;
+    const int r = (threadIdx.x - 128) & 127;
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint64_t sl2x2 = pack_f32x2(p.scale_log2, p.scale_log2);
     for (int n = 0; n < N; ++n) {
-      const int pb = n % PB;
-      const int head = step_head(n), qt = step_qtile(n);
-      const bool diag = (qt == j);
-      const float* lse2 = reinterpret_cast<const float*>(smem + L::STAT_OFF + (n % QS) * 1024);
+      const int qt = step_qtile(n);
+      const float* lse2 = reinterpret_cast<const float*>(smem + L::STAT_OFF + (n % NST) * 1024) + half * 64;
       const float* dlt = lse2 + 128;
-      uint8_t* sPt = smem + L::PDS_OFF + pb * 65536;
-      uint8_t* sdSt = sPt + 32768;
+      uint8_t* rowp = smem + L::P_OFF + (n % NP) * 32768 + half * 16384 + r * 128;    // P^T row
+      uint8_t* rowd = smem + L::DS_OFF + (n % NDS) * 32768 + half * 16384 + r * 128;  // dS^T row
       mbar_wait(&qdo_full[n % QS], (n / QS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
       mbar_wait(sdp_full, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
-      mbar_wait(&pds_free[pb], ((n / PB) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
       tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32], dp[32];
-        tmem_ld32(tm_St + lane_off + c * 32, s);
-        tmem_ld32(tm_dPt + lane_off + c * 32, dp);
-        tmem_ld_wait();
-        float pv[32], ds[32];
+      uint32_t s[64], dp[64];
+      tmem_ld32(tm_St + lane_off + half * 64, s);
+      tmem_ld32(tm_St + lane_off + half * 64 + 32, s + 32);
+      tmem_ld32(tm_dPt + lane_off + half * 64, dp);
+      tmem_ld32(tm_dPt + lane_off + half * 64 + 32, dp + 32);
+      tmem_ld_wait();
+      // the buffers written below were last read by dV (P^T) and by dK / dQ (dS^T)
+      mbar_wait(&p_free[n % NP], ((n / NP) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+      mbar_wait(&ds_free[n % NDS], ((n / NDS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+      if (qt == j) {  // diagonal tile: query column < kv row is masked
 #pragma unroll
-        for (int k4 = 0; k4 < 8; ++k4) {
-          const float4 l4 = reinterpret_cast<const float4*>(lse2 + c * 32)[k4];
-          const float4 d4 = reinterpret_cast<const float4*>(dlt + c * 32)[k4];
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
-          const float dv[4] = {d4.x, d4.y, d4.z, d4.w};
+        for (int k = 0; k < 64; ++k)
+          if (half * 64 + k < r) s[k] = 0xff800000u;  // -inf -> p = 0
+      }
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int k = k4 * 4 + e;
-            float pe = fast_exp2(__uint_as_float(s[k]) * p.scale_log2 - lv[e]);
-            if (diag && (c * 32 + k) < r) pe = 0.f;
-            pv[k] = pe;
-            ds[k] = pe * (__uint_as_float(dp[k]) - dv[e]);
-          }
+      for (int c = 0; c < 8; ++c) {   // 8 chunks of 8 columns = one 16-byte store per matrix
+        uint32_t pk[4], dk[4];
+        const float4 la = reinterpret_cast<const float4*>(lse2)[2 * c];
+        const float4 lb = reinterpret_cast<const float4*>(lse2)[2 * c + 1];
+        const float4 da = reinterpret_cast<const float4*>(dlt)[2 * c];
+        const float4 db = reinterpret_cast<const float4*>(dlt)[2 * c + 1];
+        const float lv[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+        const float dv[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+#pragma unroll
+        for (int q2 = 0; q2 < 4; ++q2) {
+          const int k = c * 8 + q2 * 2;
+          const uint64_t t = fma_f32x2(pack_f32x2(__uint_as_float(s[k]), __uint_as_float(s[k + 1])),
+                                       sl2x2, pack_f32x2(-lv[2 * q2], -lv[2 * q2 + 1]));
+          float t0, t1;
+          unpack_f32x2(t, t0, t1);
+          const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+          const uint64_t dd = add_f32x2(pack_f32x2(__uint_as_float(dp[k]), __uint_as_float(dp[k + 1])),
+                                        pack_f32x2(-dv[2 * q2], -dv[2 * q2 + 1]));
+          const uint64_t ds2 = mul_f32x2(pack_f32x2(p0, p1), dd);
+          float d0, d1;
+          unpack_f32x2(ds2, d0, d1);
+          pk[q2] = pack_bf16x2(p0, p1);
+          dk[q2] = pack_bf16x2(d0, d1);
         }
-        uint8_t* rowp = sPt + (c >> 1) * 16384 + r * 128;
-        uint8_t* rowd = sdSt + (c >> 1) * 16384 + r * 128;
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          uint4 u, w;
-          u.x = pack_bf16x2(pv[8 * jj + 0], pv[8 * jj + 1]);
-          u.y = pack_bf16x2(pv[8 * jj + 2], pv[8 * jj + 3]);
-          u.z = pack_bf16x2(pv[8 * jj + 4], pv[8 * jj + 5]);
-          u.w = pack_bf16x2(pv[8 * jj + 6], pv[8 * jj + 7]);
-          w.x = pack_bf16x2(ds[8 * jj + 0], ds[8 * jj + 1]);
-          w.y = pack_bf16x2(ds[8 * jj + 2], ds[8 * jj + 3]);
-          w.z = pack_bf16x2(ds[8 * jj + 4], ds[8 * jj + 5]);
-          w.w = pack_bf16x2(ds[8 * jj + 6], ds[8 * jj + 7]);
-          const int chunk = ((c & 1) * 4 + jj) ^ (r & 7);
-          *reinterpret_cast<uint4*>(rowp + (chunk << 4)) = u;
-          *reinterpret_cast<uint4*>(rowd + (chunk << 4)) = w;
-        }
+        const int chunk = (c ^ (r & 7)) << 4;
+        *reinterpret_cast<uint4*>(rowp + chunk) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4*>(rowd + chunk) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
       }
       tc_fence_before();
       fence_proxy_async_smem();
-      mbar_arrive(&pds_ready[pb]);
+      mbar_arrive(&pds_ready[n % NDS]);
     }
-    // ---------------- dK / dV epilogue ----------------
-    mbar_wait(dkv_full, 0, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
-    tc_fence_after();
-    float* acc_row = p.acc + static_cast<long>(row_base + j * FAB_BLK + r) * p.ld_acc;
-#pragma unroll 1
-    for (int c = 0; c < D / 32; ++c) {
-      uint32_t o[32];
-      tmem_ld32(tm_dV + lane_off + c * 32, o);
-      tmem_ld_wait();
-#pragma unroll
-      for (int k = 0; k < 8; ++k)
-        red_add_v4(acc_row + v_col + c * 32 + 4 * k, __uint_as_float(o[4 * k]),
-                   __uint_as_float(o[4 * k + 1]), __uint_as_float(o[4 * k + 2]),
-                   __uint_as_float(o[4 * k + 3]));
-      tmem_ld32(tm_dK + lane_off + c * 32, o);
-      tmem_ld_wait();
-#pragma unroll
-      for (int k = 0; k < 8; ++k)
-        red_add_v4(acc_row + k_col + c * 32 + 4 * k, __uint_as_float(o[4 * k]),
-                   __uint_as_float(o[4 * k + 1]), __uint_as_float(o[4 * k + 2]),
-                   __uint_as_float(o[4 * k + 3]));
-    }
-  } else if (warp >= 8) {
-    // ---------------- dQ drain warpgroup: thread r owns query row r ----------------
-    const int r = threadIdx.x - 256;
+  } else {
+    reg_dealloc<72>();
+    // ---------------- drain warpgroup: dQ every step (thread r owns query row r), dK / dV at
+    // the end (thread r owns kv row r) ----------------
+    const int r = threadIdx.x - 384;
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     for (int n = 0; n < N; ++n) {
       const int head = step_head(n), qt = step_qtile(n);
@@ -346,6 +345,27 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       }
       tc_fence_before();
       mbar_arrive(dq_drained);
+    }
+    mbar_wait(dkv_full, 0, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
+    tc_fence_after();
+    float* acc_row = p.acc + static_cast<long>(row_base + j * FAB_BLK + r) * p.ld_acc;
+#pragma unroll 1
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t o[32];
+      tmem_ld32(tm_dV + lane_off + c * 32, o);
+      tmem_ld_wait();
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        red_add_v4(acc_row + v_col + c * 32 + 4 * k, __uint_as_float(o[4 * k]),
+                   __uint_as_float(o[4 * k + 1]), __uint_as_float(o[4 * k + 2]),
+                   __uint_as_float(o[4 * k + 3]));
+      tmem_ld32(tm_dK + lane_off + c * 32, o);
+      tmem_ld_wait();
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        red_add_v4(acc_row + k_col + c * 32 + 4 * k, __uint_as_float(o[4 * k]),
+                   __uint_as_float(o[4 * k + 1]), __uint_as_float(o[4 * k + 2]),
+                   __uint_as_float(o[4 * k + 3]));
     }
   }
 
@@ -412,19 +432,19 @@ __global__ void fa_bwd_post_kernel(const float* __restrict__ acc, __nv_bfloat16*
   }
 }
 
-template <int D, int QS, int PB>
+template <int D, int QS, int NP, int NDS, int NST>
 static int launch_fa_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const FaBwdParams& p,
                          cudaStream_t st) {
-  using L = FaBwdSmem<D, QS, PB>;
+  using L = FaBwdSmem<D, QS, NP, NDS, NST>;
   static bool attr = false;
   if (!attr) {
-    if (cudaFuncSetAttribute(fa_bwd_kernel<D, QS, PB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(fa_bwd_kernel<D, QS, NP, NDS, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              L::TOTAL) != cudaSuccess)
       return -10;
     attr = true;
   }
   const int grid = (p.S / FAB_BLK) * p.batch * p.n_groups * (p.g / p.hpc);
-  fa_bwd_kernel<D, QS, PB><<<grid, FAB_THREADS, L::TOTAL, st>>>(tq, tdo, p);
+  fa_bwd_kernel<D, QS, NP, NDS, NST><<<grid, FAB_THREADS, L::TOTAL, st>>>(tq, tdo, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -476,7 +496,8 @@ extern "C" int ft_attn_bwd(const void* dout, const void* qkv, const void* out, c
   p.scale_log2 = scale * 1.4426950408889634f;
   p.lse2 = d_lse2; p.delta = d_delta; p.acc = static_cast<float*>(acc);
   p.status = status;
-  int rc = (D == 64) ? launch_fa_bwd<64, 2, 2>(tq, tdo, p, st) : launch_fa_bwd<128, 1, 1>(tq, tdo, p, st);
+  int rc = (D == 64) ? launch_fa_bwd<64, 2, 2, 2, 2>(tq, tdo, p, st)
+                     : launch_fa_bwd<128, 1, 1, 1, 1>(tq, tdo, p, st);
   if (rc) return rc;
   {
     const long total = T * (ncols / 8);

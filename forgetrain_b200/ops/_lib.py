@@ -15,7 +15,8 @@ import torch
 
 _LIB = None
 _LOCK = threading.Lock()
-LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libft_b200.so"
+LIB_PATH = Path(os.environ.get("FT_B200_LIB") or
+                Path(__file__).resolve().parent.parent / "lib" / "libft_b200.so")
 
 c_int = ctypes.c_int
 c_long = ctypes.c_int64
