@@ -66,6 +66,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--backend", choices=["nccl", "gloo"], default=None)
     p.add_argument("--tie-embeddings", action=argparse.BooleanOptionalAction, default=None)
     p.add_argument("--vocab-size", type=int, default=None)
+    p.add_argument("--num-layers", type=int, default=None, help="override the spec's layer count")
     hf = p.add_argument_group("HuggingFace dataset")
     hf.add_argument("--hf-dataset", default=None)
     hf.add_argument("--tokenizer-path", default=None)
@@ -104,7 +105,8 @@ def _resolve_local_microbatches(args, spec, dp_size: int, mbs: int) -> int:
 def main(argv: list[str] | None = None) -> int:
     args = build_parser().parse_args(argv)
     _validate_resume_save_dir_mutex(args)
-    spec = load_model_spec(args.model, tie_embeddings=args.tie_embeddings, vocab_size=args.vocab_size)
+    spec = load_model_spec(args.model, tie_embeddings=args.tie_embeddings, vocab_size=args.vocab_size,
+                           num_layers=args.num_layers)
     overrides = {k[4:]: v for k, v in vars(args).items() if k.startswith("cfg_") and v is not None}
     env_cfg = ec.from_env()
     base = ec.from_spec(spec)

@@ -149,7 +149,7 @@ def shard_for_tp(ps: ParamSpec, full: torch.Tensor, spec: ModelSpec, tp_rank: in
         vpr = vocab_shard_rows(spec.vocab_size, tp)
         lo = tp_rank * vpr
         hi = min(spec.vocab_size, lo + vpr)
-        out = torch.zeros(vpr, full.shape[1], dtype=full.dtype)
+        out = torch.zeros(vpr, full.shape[1], dtype=full.dtype, device=full.device)
         if hi > lo:
             out[:hi - lo] = full[lo:hi]
         return out
@@ -261,18 +261,22 @@ class ParamStore:
         return math.prod(self.shapes[name])
 
     def init_random(self, seed: int, scheme: str = "spec", init_std: float | None = None) -> None:
-        """Seeded init: every rank draws the full tensor on CPU and keeps its shard."""
+        """Seeded init, independent of the tensor-parallel degree: every rank draws the FULL
+        tensor of each parameter from a generator keyed by (seed, parameter index) and keeps
+        its shard. The draw happens on the store's device (large models initialise in seconds
+        on a GPU), so CPU and GPU stores see different random streams."""
         std0 = self.spec.init_method_std if init_std is None else init_std
-        gen = torch.Generator(device="cpu")
-        gen.manual_seed(seed)
-        for ps in self.specs:  # registration order => layout-independent stream of draws
+        gen = torch.Generator(device=self.device)
+        for idx, ps in enumerate(self.specs):
             if ps.init == "ones":
                 self.params[ps.name].fill_(1.0)
                 continue
             std = init_std_for(ps, self.spec, scheme, std0)
-            full = torch.randn(ps.shape, dtype=torch.float32, generator=gen).mul_(std)
+            gen.manual_seed(seed * 1000003 + idx)
+            full = torch.randn(ps.shape, dtype=torch.float32, generator=gen, device=self.device).mul_(std)
             shard = shard_for_tp(ps, full, self.spec, self.tp_rank, self.tp_size)
             self.params[ps.name].copy_(shard.to(self.dtype))
+            del full, shard
 
     def load_named(self, tensors: dict[str, torch.Tensor], full_tensors: bool = True) -> None:
         for ps in self.specs:
