@@ -29,6 +29,11 @@ __device__ __forceinline__ bf16x8 pack8(const float* f) {
   for (int i = 0; i < 4; ++i) p.v[i] = pack_bf16x2(f[2 * i], f[2 * i + 1]);
   return p;
 }
+// Stops the compiler from keeping the unpacked fp32 copies of a packed vector alive across
+// this point (it would rather spend 16 registers than unpack twice).
+__device__ __forceinline__ void opaque(bf16x8& p) {
+  asm volatile("" : "+r"(p.v[0]), "+r"(p.v[1]), "+r"(p.v[2]), "+r"(p.v[3]));
+}
 __device__ __forceinline__ float round_bf16(float x) {
   return __bfloat162float(__float2bfloat16_rn(x));
 }
@@ -162,11 +167,11 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   const int tr = threadIdx.x % TPR;
   const int warp = threadIdx.x >> 5;
   const bf16x8* wv = reinterpret_cast<const bf16x8*>(w);
-  float wf[NV][8];
+  bf16x8 wp[NV];        // weights stay packed: they are unpacked where they are used
   float acc[NV][8];
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    unpack8(wv[tr + i * TPR], wf[i]);
+    wp[i] = wv[tr + i * TPR];
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[i][k] = 0.f;
   }
@@ -176,34 +181,52 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
     const long r = live ? row : (T - 1);
     const bf16x8* dyv = reinterpret_cast<const bf16x8*>(dy + r * H);
     const bf16x8* hv = reinterpret_cast<const bf16x8*>(h + r * H);
+    const bf16x8* rv = (dres && live) ? reinterpret_cast<const bf16x8*>(dres + row * H) : nullptr;
+    // issue every load of the row first (packed, 4 registers per 8 values) ...
+    bf16x8 dp[NV], hp[NV], rp[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      dp[i] = dyv[tr + i * TPR];
+      hp[i] = hv[tr + i * TPR];
+      if (rv) rp[i] = rv[tr + i * TPR];
+    }
     const float rstd = rstd_in[r];
-    float g[NV][8], xh[NV][8];
+    // ... then pass 1: c = mean(dy * w * xhat), weight-gradient partials
     float c = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      float d[8], hh[8];
-      unpack8(dyv[tr + i * TPR], d);
-      unpack8(hv[tr + i * TPR], hh);
+      float d[8], hh[8], wf[8];
+      unpack8(dp[i], d);
+      unpack8(hp[i], hh);
+      unpack8(wp[i], wf);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        xh[i][k] = hh[k] * rstd;
-        g[i][k] = d[k] * wf[i][k];
-        c += g[i][k] * xh[i][k];
-        if (live) acc[i][k] += d[k] * xh[i][k];
+        const float xh = hh[k] * rstd;
+        c += d[k] * wf[k] * xh;
+        if (live) acc[i][k] += d[k] * xh;
       }
     }
     c = row_sum<TPR>(c, red, warp) / (float)H;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      opaque(dp[i]);
+      opaque(hp[i]);
+      opaque(wp[i]);
+    }
+    // pass 2: dx = rstd * (dy*w - xhat*c) (+ dres), recomputed from the packed registers
     if (live) {
-      const bf16x8* rv = dres ? reinterpret_cast<const bf16x8*>(dres + row * H) : nullptr;
       bf16x8* ov = reinterpret_cast<bf16x8*>(dx_out + row * H);
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
-        float o[8];
+        float d[8], hh[8], wf[8], o[8];
+        unpack8(dp[i], d);
+        unpack8(hp[i], hh);
+        unpack8(wp[i], wf);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) o[k] = rstd * (g[i][k] - xh[i][k] * c);
+        for (int k = 0; k < 8; ++k) o[k] = rstd * (d[k] * wf[k] - hh[k] * rstd * c);
         if (rv) {
           float rf[8];
-          unpack8(rv[tr + i * TPR], rf);
+          unpack8(rp[i], rf);
 #pragma unroll
           for (int k = 0; k < 8; ++k) o[k] += rf[k];
         }
@@ -638,7 +661,7 @@ extern "C" int ft_rmsnorm_bwd_partials(int T, int H) {
   int nv, tpr;
   if (!norm_cfg(H, &nv, &tpr)) return -1;
   const int rows_per_cta = 128 / tpr;
-  return grid_for((long)(T + rows_per_cta - 1) / rows_per_cta, 1, tpr == 32 ? 6 : 8);
+  return grid_for((long)(T + rows_per_cta - 1) / rows_per_cta, 1, 3);
 }
 
 extern "C" int ft_rmsnorm_bwd(const void* dy, const void* h, const void* w, const void* rstd,

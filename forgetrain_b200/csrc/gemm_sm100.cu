@@ -26,7 +26,8 @@ namespace ft {
 
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
-constexpr int GEMM_THREADS = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int GEMM_THREADS = 320;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue
+constexpr int GEMM_EPI_WARPS = 8;    // two warps per TMEM lane quarter, each takes half the columns
 constexpr int GEMM_GROUP_M = 16;
 
 enum : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ADD = 2 };
@@ -47,7 +48,7 @@ struct GemmSmem {
   static constexpr int B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_BUF_BYTES = 4096;                 // 32 rows x 128 B
-  static constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;    // 4 warps x 2 buffers
+  static constexpr int EPI_BYTES = GEMM_EPI_WARPS * EPI_BUF_BYTES;  // one buffer per warp
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES + EPI_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;      // + barriers + alignment slack
 };
@@ -96,7 +97,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
-      mbar_init(&tempty_bar[b], 4);
+      mbar_init(&tempty_bar[b], GEMM_EPI_WARPS);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -190,8 +191,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else {
     // ------------------------------ epilogue ------------------------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may access
-    uint8_t* my_epi = epi_base + q * 2 * L::EPI_BUF_BYTES;
+    const int q = warp & 3;             // TMEM lane quarter this warp may access
+    const int chalf = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
+    uint8_t* my_epi = epi_base + (warp - 2) * L::EPI_BUF_BYTES;
     int it = 0;
     int nstores = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
@@ -206,16 +208,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const bool rows_live = row0 < p.M;
       if (p.out_mode == OUT_BF16) {
 #pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
+        for (int c = chalf * (BN / 128); c < (chalf + 1) * (BN / 128); ++c) {
           const int col0 = nt * BN + c * 64;
           if (col0 >= p.N || !rows_live) break;
           uint32_t r[64];
           tmem_ld32(taddr + c * 64, r);
           tmem_ld32(taddr + c * 64 + 32, r + 32);
           tmem_ld_wait();
-          uint8_t* sbuf = my_epi + (nstores & 1) * L::EPI_BUF_BYTES;
-          if (nstores >= 2) {
-            if (lane == 0) tma_wait_group_read<1>();
+          uint8_t* sbuf = my_epi;
+          if (nstores >= 1) {
+            if (lane == 0) tma_wait_group_read<0>();
             __syncwarp();
           }
 #pragma unroll
@@ -241,15 +243,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       } else {
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
           const int col0 = nt * BN + c * 32;
           if (col0 >= p.N || !rows_live) break;
           uint32_t r[32];
           tmem_ld32(taddr + c * 32, r);
           tmem_ld_wait();
-          uint8_t* sbuf = my_epi + (nstores & 1) * L::EPI_BUF_BYTES;
-          if (nstores >= 2) {
-            if (lane == 0) tma_wait_group_read<1>();
+          uint8_t* sbuf = my_epi;
+          if (nstores >= 1) {
+            if (lane == 0) tma_wait_group_read<0>();
             __syncwarp();
           }
 #pragma unroll
