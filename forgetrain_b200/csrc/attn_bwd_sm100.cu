@@ -45,7 +45,8 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
-// QS: Q/dO stages, NP: P^T buffers, NDS: dS^T buffers, NST: (lse2, delta) buffers
+// QS: Q/dO stages, NP: P^T buffers in shared memory (0: P^T is kept in TMEM as packed bf16 and
+// feeds the dV product as a TMEM operand), NDS: dS^T buffers, NST: (lse2, delta) buffers
 template <int D, int QS, int NP, int NDS, int NST>
 struct FaBwdSmem {
   static constexpr int TILE = FAB_BLK * D * 2;
@@ -73,16 +74,16 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* kv_full = bars;          // 1
-  uint64_t* qdo_full = bars + 1;     // 3
-  uint64_t* qdo_empty = bars + 4;    // 3
-  uint64_t* sdp_full = bars + 7;     // 1
-  uint64_t* pds_ready = bars + 8;    // 2 (count 256): P^T and dS^T of a step are written
-  uint64_t* ds_free = bars + 10;     // 2: dS^T buffer consumed by dK and dQ
-  uint64_t* p_free = bars + 12;      // 2: P^T buffer consumed by dV
-  uint64_t* dq_full = bars + 14;     // 1
-  uint64_t* dq_drained = bars + 15;  // 1 (count 128)
-  uint64_t* dkv_full = bars + 16;    // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  uint64_t* qdo_full = bars + 1;     // 4
+  uint64_t* qdo_empty = bars + 5;    // 4
+  uint64_t* sdp_full = bars + 9;     // 1
+  uint64_t* pds_ready = bars + 10;   // 2 (count 256): P^T and dS^T of a step are written
+  uint64_t* ds_free = bars + 12;     // 2: dS^T buffer consumed by dK and dQ
+  uint64_t* p_free = bars + 14;      // 2: P^T buffer consumed by dV
+  uint64_t* dq_full = bars + 16;     // 1
+  uint64_t* dq_drained = bars + 17;  // 1 (count 128)
+  uint64_t* dkv_full = bars + 18;    // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -104,7 +105,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 3; ++s) {
+    for (int s = 0; s < 4; ++s) {
       mbar_init(&qdo_full[s], 1);
       mbar_init(&qdo_empty[s], 1);
     }
@@ -135,6 +136,9 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   const uint32_t tm_dV = tmem_base + 256;
   const uint32_t tm_dK = tmem_base + 256 + D;
   const uint32_t tm_dQ = ALIAS ? tmem_base : tmem_base + 256 + 2 * D;
+  constexpr bool P_TMEM = (NP == 0);
+  constexpr int NPB = P_TMEM ? 1 : NP;           // ring length of the P^T hand-over barriers
+  const uint32_t tm_Pt = tmem_base + 448;        // 64 columns of packed bf16 (P_TMEM only)
 
   // step n -> (head, query tile)
   auto step_head = [&](int n) { return grp * p.g + hc * p.hpc + n / n_q; };
@@ -216,17 +220,28 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
         const int s = n % QS;
         mbar_wait(&pds_ready[n % NDS], (n / NDS) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
         tc_fence_after();
-        if (!ALIAS && n + 1 < N) issue_sdp(n + 1);
+        // With the single P^T buffer in TMEM, dV(n) goes first: it frees P^T before the softmax
+        // of step n+1 (which needs S^T(n+1), issued right behind it) wants to write it.
+        if (!ALIAS && !P_TMEM && n + 1 < N) issue_sdp(n + 1);
         const uint32_t q = sQDO + s * 2 * L::TILE, dO = q + L::TILE;
-        const uint32_t pT = sP + (n % NP) * 32768, dsT = sDS + (n % NDS) * 32768;
+        const uint32_t dsT = sDS + (n % NDS) * 32768;
+        if (P_TMEM) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t aoff = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_ss(tm_dV, make_smem_desc(pT + aoff, 16, 1024),
-                  make_smem_desc(dO + kk * 2048, 16384, 1024), idesc_dkv,
-                  (n > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 8; ++kk)   // 16 bf16 of the reduction index = 8 TMEM columns
+            umma_ts(tm_dV, tm_Pt + kk * 8, make_smem_desc(dO + kk * 2048, 16384, 1024), idesc_dkv,
+                    (n > 0 || kk > 0) ? 1u : 0u);
+        } else {
+          const uint32_t pT = sP + (n % NPB) * 32768;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t aoff = (kk / 4) * 16384 + (kk % 4) * 32;
+            umma_ss(tm_dV, make_smem_desc(pT + aoff, 16, 1024),
+                    make_smem_desc(dO + kk * 2048, 16384, 1024), idesc_dkv,
+                    (n > 0 || kk > 0) ? 1u : 0u);
+          }
         }
-        umma_commit(&p_free[n % NP]);
+        umma_commit(&p_free[n % NPB]);
+        if (!ALIAS && P_TMEM && n + 1 < N) issue_sdp(n + 1);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t aoff = (kk / 4) * 16384 + (kk % 4) * 32;
@@ -268,53 +283,66 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       const int qt = step_qtile(n);
       const float* lse2 = reinterpret_cast<const float*>(smem + L::STAT_OFF + (n % NST) * 1024) + half * 64;
       const float* dlt = lse2 + 128;
-      uint8_t* rowp = smem + L::P_OFF + (n % NP) * 32768 + half * 16384 + r * 128;    // P^T row
+      uint8_t* rowp = smem + L::P_OFF + (n % NPB) * 32768 + half * 16384 + r * 128;   // P^T row
       uint8_t* rowd = smem + L::DS_OFF + (n % NDS) * 32768 + half * 16384 + r * 128;  // dS^T row
       mbar_wait(&qdo_full[n % QS], (n / QS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
       mbar_wait(sdp_full, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
-      uint32_t s[64], dp[64];
+      alignas(8) uint32_t s[64];
+      alignas(8) uint32_t dp[64];
       tmem_ld32(tm_St + lane_off + half * 64, s);
       tmem_ld32(tm_St + lane_off + half * 64 + 32, s + 32);
       tmem_ld32(tm_dPt + lane_off + half * 64, dp);
       tmem_ld32(tm_dPt + lane_off + half * 64 + 32, dp + 32);
       tmem_ld_wait();
       // the buffers written below were last read by dV (P^T) and by dK / dQ (dS^T)
-      mbar_wait(&p_free[n % NP], ((n / NP) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+      mbar_wait(&p_free[n % NPB], ((n / NPB) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+      tc_fence_after();
+      uint32_t pt[32];   // this thread's 64 P values as packed bf16 (P_TMEM)
       mbar_wait(&ds_free[n % NDS], ((n / NDS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
       if (qt == j) {  // diagonal tile: query column < kv row is masked
 #pragma unroll
         for (int k = 0; k < 64; ++k)
           if (half * 64 + k < r) s[k] = 0xff800000u;  // -inf -> p = 0
       }
+      // Staged over the whole 64-column slice so that every stage is 32-64 independent
+      // instructions (the per-element chain fma -> ex2 -> mul -> cvt is long and serial).
+      uint64_t* s2 = reinterpret_cast<uint64_t*>(s);    // pairs of scores / probabilities
+      uint64_t* d2 = reinterpret_cast<uint64_t*>(dp);   // pairs of dP / dS
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {   // 8 chunks of 8 columns = one 16-byte store per matrix
+      for (int i = 0; i < 16; ++i) {                    // t = s * scale - lse2 ; dd = dP - delta
+        const float4 l4 = reinterpret_cast<const float4*>(lse2)[i];
+        const float4 e4 = reinterpret_cast<const float4*>(dlt)[i];
+        s2[2 * i] = fma_f32x2(s2[2 * i], sl2x2, pack_f32x2(-l4.x, -l4.y));
+        s2[2 * i + 1] = fma_f32x2(s2[2 * i + 1], sl2x2, pack_f32x2(-l4.z, -l4.w));
+        d2[2 * i] = add_f32x2(d2[2 * i], pack_f32x2(-e4.x, -e4.y));
+        d2[2 * i + 1] = add_f32x2(d2[2 * i + 1], pack_f32x2(-e4.z, -e4.w));
+      }
+#pragma unroll
+      for (int k = 0; k < 64; ++k) s[k] = __float_as_uint(fast_exp2(__uint_as_float(s[k])));
+#pragma unroll
+      for (int i = 0; i < 32; ++i) d2[i] = mul_f32x2(s2[i], d2[i]);   // dS = P * (dP - delta)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
         uint32_t pk[4], dk[4];
-        const float4 la = reinterpret_cast<const float4*>(lse2)[2 * c];
-        const float4 lb = reinterpret_cast<const float4*>(lse2)[2 * c + 1];
-        const float4 da = reinterpret_cast<const float4*>(dlt)[2 * c];
-        const float4 db = reinterpret_cast<const float4*>(dlt)[2 * c + 1];
-        const float lv[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
-        const float dv[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
 #pragma unroll
         for (int q2 = 0; q2 < 4; ++q2) {
           const int k = c * 8 + q2 * 2;
-          const uint64_t t = fma_f32x2(pack_f32x2(__uint_as_float(s[k]), __uint_as_float(s[k + 1])),
-                                       sl2x2, pack_f32x2(-lv[2 * q2], -lv[2 * q2 + 1]));
-          float t0, t1;
-          unpack_f32x2(t, t0, t1);
-          const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
-          const uint64_t dd = add_f32x2(pack_f32x2(__uint_as_float(dp[k]), __uint_as_float(dp[k + 1])),
-                                        pack_f32x2(-dv[2 * q2], -dv[2 * q2 + 1]));
-          const uint64_t ds2 = mul_f32x2(pack_f32x2(p0, p1), dd);
-          float d0, d1;
-          unpack_f32x2(ds2, d0, d1);
-          pk[q2] = pack_bf16x2(p0, p1);
-          dk[q2] = pack_bf16x2(d0, d1);
+          pk[q2] = pack_bf16x2(__uint_as_float(s[k]), __uint_as_float(s[k + 1]));
+          dk[q2] = pack_bf16x2(__uint_as_float(dp[k]), __uint_as_float(dp[k + 1]));
         }
         const int chunk = (c ^ (r & 7)) << 4;
-        *reinterpret_cast<uint4*>(rowp + chunk) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        if (P_TMEM) {
+#pragma unroll
+          for (int q2 = 0; q2 < 4; ++q2) pt[c * 4 + q2] = pk[q2];
+        } else {
+          *reinterpret_cast<uint4*>(rowp + chunk) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
         *reinterpret_cast<uint4*>(rowd + chunk) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
+      }
+      if (P_TMEM) {
+        tmem_st32(tm_Pt + lane_off + half * 32, pt);
+        tmem_st_wait();
       }
       tc_fence_before();
       fence_proxy_async_smem();
