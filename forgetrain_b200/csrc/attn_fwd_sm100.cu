@@ -214,7 +214,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       mbar_wait(&s_full[w], j & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
       // one pass over TMEM: the whole score row (128 fp32) lives in registers
-      uint32_t s[128];
+      alignas(8) uint32_t s[128];
       tmem_ld32(tmem_S[w] + lane_off, s);
       tmem_ld32(tmem_S[w] + lane_off + 32, s + 32);
       tmem_ld32(tmem_S[w] + lane_off + 64, s + 64);
@@ -256,23 +256,30 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
         }
       }
       const uint64_t negm2 = pack_f32x2(-m_ref, -m_ref);
+      // staged so that each stage is a long run of independent instructions
+      uint64_t* s2 = reinterpret_cast<uint64_t*>(s);
+#pragma unroll
+      for (int i = 0; i < 64; ++i) s2[i] = fma_f32x2(s2[i], sl2x2, negm2);
+#pragma unroll
+      for (int k = 0; k < 128; ++k) s[k] = __float_as_uint(fast_exp2(__uint_as_float(s[k])));
+      uint64_t acc0 = s2[0], acc1 = s2[1], acc2 = s2[2], acc3 = s2[3];
+#pragma unroll
+      for (int i = 4; i < 64; i += 4) {
+        acc0 = add_f32x2(acc0, s2[i]);
+        acc1 = add_f32x2(acc1, s2[i + 1]);
+        acc2 = add_f32x2(acc2, s2[i + 2]);
+        acc3 = add_f32x2(acc3, s2[i + 3]);
+      }
+      lsum2 = add_f32x2(lsum2, add_f32x2(add_f32x2(acc0, acc1), add_f32x2(acc2, acc3)));
 #pragma unroll
       for (int c = 0; c < 16; ++c) {  // 16 chunks of 8 columns = one 16-byte store each
-        uint32_t packed[4];
-#pragma unroll
-        for (int q2 = 0; q2 < 4; ++q2) {
-          const int k = c * 8 + q2 * 2;
-          const uint64_t t = fma_f32x2(pack_f32x2(__uint_as_float(s[k]), __uint_as_float(s[k + 1])),
-                                       sl2x2, negm2);
-          float t0, t1;
-          unpack_f32x2(t, t0, t1);
-          const float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
-          lsum2 = add_f32x2(lsum2, pack_f32x2(p0, p1));
-          packed[q2] = pack_bf16x2(p0, p1);
-        }
+        uint4 u;
+        u.x = pack_bf16x2(__uint_as_float(s[c * 8 + 0]), __uint_as_float(s[c * 8 + 1]));
+        u.y = pack_bf16x2(__uint_as_float(s[c * 8 + 2]), __uint_as_float(s[c * 8 + 3]));
+        u.z = pack_bf16x2(__uint_as_float(s[c * 8 + 4]), __uint_as_float(s[c * 8 + 5]));
+        u.w = pack_bf16x2(__uint_as_float(s[c * 8 + 6]), __uint_as_float(s[c * 8 + 7]));
         uint8_t* rowp = sP + (c >> 3) * 16384 + r * 128;
-        *reinterpret_cast<uint4*>(rowp + (((c & 7) ^ (r & 7)) << 4)) =
-            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        *reinterpret_cast<uint4*>(rowp + (((c & 7) ^ (r & 7)) << 4)) = u;
       }
       tc_fence_before();
       fence_proxy_async_smem();
