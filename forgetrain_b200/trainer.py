@@ -93,6 +93,14 @@ class Trainer:
                 if ps.is_norm:
                     o = self.store.offsets[ps.name]
                     norm_exclude.append((o, o + self.store.numel(ps.name)))
+        if topo.replica_size > 1 and topo.tp_rank % topo.replica_size != 0:
+            # k / v rows of wqkv are replicated inside a KV group: count them on one rank only
+            D = spec.head_dim
+            for ps in self.store.order:
+                if ps.name.endswith("attention.wqkv.weight"):
+                    o = self.store.offsets[ps.name]
+                    rows, cols = self.store.shapes[ps.name]
+                    norm_exclude.append((o + (rows - 2 * D) * cols, o + rows * cols))
         if want_fused:
             from .parallel import fused_dp
             self.fused_dp = fused_dp.FusedDPComm(self.symm)

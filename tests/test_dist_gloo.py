@@ -76,12 +76,12 @@ def test_dp2_matches_gradient_accumulation_and_loss_decreases():
 
 
 # ------------------------------------------------------------------------------------------
-def _tp_worker(rank, world, sp, steps):
+def _tp_worker(rank, world, sp, steps, tp=2, heads=4):
     from forgetrain_b200.parallel.topology import init_topology
     from forgetrain_b200.trainer import Trainer
-    spec = _spec(tie_embeddings=False)
-    topo = init_topology(2, device="cpu", num_kv_groups=spec.num_query_groups)
-    tr = Trainer(spec, _cfg(spec, tensor_parallel_size=2, sequence_parallel=sp), topo, seq_length=64,
+    spec = _spec(tie_embeddings=False, num_attention_heads=heads)
+    topo = init_topology(tp, device="cpu", num_kv_groups=spec.num_query_groups)
+    tr = Trainer(spec, _cfg(spec, tensor_parallel_size=tp, sequence_parallel=sp), topo, seq_length=64,
                  micro_batch_size=2, seed=0)
     data = _batches(7, 1, 2, 64, spec.vocab_size)
     losses, norms = [], []
@@ -128,3 +128,18 @@ def test_dp2_checkpoint_resume_continues_the_run(tmp_path):
     full, resumed = res[0]
     assert (tmp_path / "full" / "step_0000002" / "training_state.pt").exists()
     assert resumed == pytest.approx(full[2:], abs=1e-5)
+
+
+def test_tp4_with_replicated_kv_heads_matches_tp1():
+    """TP degree above the number of KV groups: q heads are split, k / v are replicated inside
+    a group and their gradients summed over the replicas."""
+    from forgetrain_b200.parallel.topology import Topology
+    from forgetrain_b200.trainer import Trainer
+    res = run_ranks(_tp_worker, 4, True, 3, 4, 8)
+    spec = _spec(tie_embeddings=False, num_attention_heads=8)
+    tr = Trainer(spec, _cfg(spec), Topology(), seq_length=64, micro_batch_size=2, seed=0)
+    data = _batches(7, 1, 2, 64, spec.vocab_size)
+    for i in range(3):
+        out = tr.train_step(data)
+        assert float(out["loss"]) == pytest.approx(res[0][0][i], abs=3e-4)
+        assert float(out["grad_norm"]) == pytest.approx(res[0][1][i], rel=2e-3)
