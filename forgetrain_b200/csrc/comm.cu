@@ -284,6 +284,60 @@ small_all_reduce_kernel(CommPeers c, long scratch_off, float* __restrict__ vals,
   wait_peers(c, 4, epoch, limit_ns, status);
 }
 
+// ---------------------------------------------------------------------------------------
+// Vocab-parallel cross-entropy: exchange of the per-row statistics between tensor-parallel ranks
+// inside one kernel. Every rank has written (row max, sum-exp relative to that max, target
+// logit or 0) for its vocabulary shard as stats[3][T] at float offset `off` of its symmetric
+// buffer. After an entry barrier each rank reads every peer's three vectors with plain peer
+// loads and combines them: gmax = max_r m_r, gsum = sum_r s_r * exp(m_r - gmax),
+// gtarget = sum_r t_r; writes the combined [3][T] to `combined` (local) and the masked row
+// loss log(gsum) + gmax - gtarget to `row_loss`. An exit barrier keeps peers from rewriting
+// their statistics before everyone has read them. Replaces the MAX + SUM all-reduce pair of
+// exports/train_engine_8b/src/training_engine_tensor/backward.py:203-346.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+ce_stats_exchange_kernel(CommPeers c, long off, int T, const float* __restrict__ mask,
+                         float* __restrict__ combined, float* __restrict__ row_loss,
+                         uint32_t epoch, uint64_t limit_ns, unsigned int* __restrict__ done_ctr,
+                         int* status) {
+  if (blockIdx.x == 0) signal_peers(c, 5, epoch);
+  const bool ok = wait_peers(c, 5, epoch, limit_ns, status);
+  if (ok) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < T; i += gridDim.x * blockDim.x) {
+      float m[COMM_MAX_RANKS], sx[COMM_MAX_RANKS];
+      float gmax = -INFINITY, gt = 0.f;
+      for (int r = 0; r < c.world; ++r) {
+        const float* st = static_cast<const float*>(c.buf[r]) + off;
+        float t;
+        asm volatile("ld.global.relaxed.sys.f32 %0, [%1];" : "=f"(m[r]) : "l"(st + i) : "memory");
+        asm volatile("ld.global.relaxed.sys.f32 %0, [%1];" : "=f"(sx[r]) : "l"(st + T + i) : "memory");
+        asm volatile("ld.global.relaxed.sys.f32 %0, [%1];" : "=f"(t) : "l"(st + 2 * T + i) : "memory");
+        gmax = fmaxf(gmax, m[r]);
+        gt += t;
+      }
+      float gs = 0.f;
+      for (int r = 0; r < c.world; ++r) gs += sx[r] * __expf(m[r] - gmax);
+      combined[i] = gmax;
+      combined[T + i] = gs;
+      combined[2 * T + i] = gt;
+      if (row_loss) row_loss[i] = (logf(gs) + gmax - gt) * (mask ? mask[i] : 1.f);
+    }
+  }
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int prev = atomicAdd(done_ctr, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+    if (s_last) *done_ctr = 0;
+  }
+  __syncthreads();
+  if (s_last) {
+    signal_peers(c, 6, epoch);
+    wait_peers(c, 6, epoch, limit_ns, status);
+  }
+}
+
 }  // namespace ft
 
 using namespace ft;
@@ -353,5 +407,24 @@ extern "C" int ft_small_all_reduce(const void* const* bufs, const void* const* f
   fill_peers(c, bufs, flags, nullptr, rank, world);
   small_all_reduce_kernel<<<1, COMM_THREADS, 0, st>>>(c, scratch_off, static_cast<float*>(vals), n,
                                                       epoch, limit_ns, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+// stats: peer mappings of the symmetric buffer that holds every rank's [3][T] statistics at
+// float offset `off`; combined / row_loss: local outputs ([3][T] and [T] floats).
+extern "C" int ft_ce_stats_exchange(const void* const* bufs, const void* const* flags, int rank,
+                                    int world, long off, int T, const void* mask, void* combined,
+                                    void* row_loss, unsigned int epoch,
+                                    unsigned long long limit_ns, void* done_ctr, int* status,
+                                    cudaStream_t st) {
+  if (world > COMM_MAX_RANKS || T < 1) return -1;
+  CommPeers c;
+  fill_peers(c, bufs, flags, nullptr, rank, world);
+  int grid = (T + 255) / 256;
+  if (grid > 64) grid = 64;
+  ce_stats_exchange_kernel<<<grid, 256, 0, st>>>(c, off, T, static_cast<const float*>(mask),
+                                                 static_cast<float*>(combined),
+                                                 static_cast<float*>(row_loss), epoch, limit_ns,
+                                                 static_cast<unsigned int*>(done_ctr), status);
   return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }

@@ -129,7 +129,8 @@ class MiniCPM4:
         tp = self.tp
         return ops.cross_entropy_fwd_bwd(
             logits, labels, loss_mask, loss_scale, vocab_start=self.vocab_start,
-            stats_reduce=tp.stats_reduce if tp.enabled else None)
+            stats_reduce=tp.stats_reduce if tp.enabled else None,
+            tp_exchange=tp if (tp.enabled and hasattr(tp, "ce_exchange")) else None)
 
     # ----------------------------------------------------------------------------- backward
     def head_backward(self, dlogits, accumulate: bool, emit, dnf_extra=None, emit_output=True,

@@ -82,9 +82,12 @@ def linear_wgrad(dy, x, out, accumulate: bool, alpha: float = 1.0):
 
 
 def cross_entropy_fwd_bwd(logits, labels, mask, loss_scale, valid=None, vocab_start=0,
-                          stats_reduce=None):
-    return _pick(logits).cross_entropy_fwd_bwd(logits, labels, mask, loss_scale, valid,
-                                               vocab_start, stats_reduce)
+                          stats_reduce=None, tp_exchange=None):
+    if logits.is_cuda:
+        return _cuda().cross_entropy_fwd_bwd(logits, labels, mask, loss_scale, valid, vocab_start,
+                                             stats_reduce, tp_exchange)
+    return _ref.cross_entropy_fwd_bwd(logits, labels, mask, loss_scale, valid, vocab_start,
+                                      stats_reduce)
 
 
 def rope_tables(seq_len, head_dim, base, device=None):

@@ -132,8 +132,10 @@ def linear_wgrad(dy, x, out, accumulate, alpha=1.0):
 
 # ------------------------------------------------------------------------- cross-entropy
 def cross_entropy_fwd_bwd(logits, labels, mask, loss_scale, valid=None, vocab_start=0,
-                          stats_reduce=None):
-    """In place: ``logits`` is overwritten by its gradient (returned as ``dlogits``)."""
+                          stats_reduce=None, tp_exchange=None):
+    """In place: ``logits`` is overwritten by its gradient (returned as ``dlogits``).
+    ``tp_exchange`` (an object with ``ce_stats_buffer`` / ``ce_exchange``) combines the
+    vocabulary-shard statistics in one peer-memory kernel instead of two all-reduces."""
     _bf16(logits, "logits")
     T, V = logits.shape
     dev = logits.device
@@ -152,11 +154,22 @@ def cross_entropy_fwd_bwd(logits, labels, mask, loss_scale, valid=None, vocab_st
     loss = torch.empty(1, dtype=torch.float32, device=dev)
     L = _L()
     st = _lib.stream()
-    if stats_reduce is None:
+    sym = tp_exchange.ce_stats_buffer(T) if tp_exchange is not None else None
+    if stats_reduce is None and sym is None:
         rc = L.ft_cross_entropy(P(logits), P(labels), P(mask), P(valid_t), P(stats), P(row_loss),
                                 c_int(T), c_int(V), c_long(logits.stride(0)), c_int(vocab_start),
                                 c_float(loss_scale), c_int(3), st)
         _lib.check_rc(rc, "ft_cross_entropy")
+    elif sym is not None:
+        rc = L.ft_cross_entropy(P(logits), P(labels), P(mask), P(valid_t), P(sym), P(row_loss),
+                                c_int(T), c_int(V), c_long(logits.stride(0)), c_int(vocab_start),
+                                c_float(loss_scale), c_int(1), st)
+        _lib.check_rc(rc, "ft_cross_entropy(stats)")
+        tp_exchange.ce_exchange(T, mask, stats, row_loss)
+        rc = L.ft_cross_entropy(P(logits), P(labels), P(mask), P(valid_t), P(stats), P(row_loss),
+                                c_int(T), c_int(V), c_long(logits.stride(0)), c_int(vocab_start),
+                                c_float(loss_scale), c_int(2), st)
+        _lib.check_rc(rc, "ft_cross_entropy(grad)")
     else:
         rc = L.ft_cross_entropy(P(logits), P(labels), P(mask), P(valid_t), P(stats), P(row_loss),
                                 c_int(T), c_int(V), c_long(logits.stride(0)), c_int(vocab_start),

@@ -42,13 +42,18 @@ class FusedTPContext(TPContext):
         self.pool = symm_mem.empty(n_gather_slots * tokens * hidden, dtype=torch.bfloat16, device=device)
         self.partials = symm_mem.empty(2 * tokens * hidden, dtype=torch.bfloat16, device=device)
         self.flags = symm_mem.empty(8 * 16, dtype=torch.int32, device=device)
+        self.ce_stats = symm_mem.empty(3 * tokens, dtype=torch.float32, device=device)
         self.pool.zero_()
         self.partials.zero_()
         self.flags.zero_()
+        self.ce_stats.zero_()
         torch.cuda.synchronize(device)
         self.h_pool = symm_mem.rendezvous(self.pool, gname)
         self.h_part = symm_mem.rendezvous(self.partials, gname)
         self.h_flags = symm_mem.rendezvous(self.flags, gname)
+        self.h_ce = symm_mem.rendezvous(self.ce_stats, gname)
+        self.p_ce = (ctypes.c_void_p * size)(*[int(p) for p in self.h_ce.buffer_ptrs])
+        self.epoch_ce = 0
         self.pool_ptrs = [int(p) for p in self.h_pool.buffer_ptrs]
         self.part_ptrs = [int(p) for p in self.h_part.buffer_ptrs]
         VP = ctypes.c_void_p * size
@@ -160,3 +165,21 @@ class FusedTPContext(TPContext):
     def dgrad_scatter(self, dy, w, alpha: float = 1.0):
         r = self._gemm_rs(dy, w, alpha, b_mn=True) if dy.is_cuda else None
         return r if r is not None else super().dgrad_scatter(dy, w, alpha)
+
+    # ------------------------------------------------------------------ vocab-parallel CE
+    def ce_stats_buffer(self, T: int):
+        """[3][T] fp32 view in symmetric memory that the local statistics kernel writes."""
+        if T > self.T:
+            return None
+        return self.ce_stats[:3 * T].view(3, T)
+
+    def ce_exchange(self, T: int, mask, combined: torch.Tensor, row_loss: torch.Tensor) -> None:
+        """One kernel: entry barrier, peer loads of every rank's statistics, combination,
+        masked row loss, exit barrier."""
+        self.epoch_ce = (self.epoch_ce + 1) & 0x7FFFFFFF
+        rc = _lib.lib().ft_ce_stats_exchange(
+            self.p_ce, self.p_flags, c_int(self.rank), c_int(self.size), ctypes.c_long(0), c_int(T),
+            _lib.ptr(mask), _lib.ptr(combined), _lib.ptr(row_loss), c_uint(self.epoch_ce),
+            c_ull(self.limit_ns), _lib.c_void_p(self.done_ctr.data_ptr() + 8),
+            _lib.ptr(self.status), _lib.stream())
+        _lib.check_rc(rc, "ft_ce_stats_exchange")
