@@ -1,6 +1,7 @@
 // Persistent, warp-specialised bf16 GEMM for sm_100a:
 //   D[M,N] (=|+=) alpha * sum_k A[m,k] * B[n,k]
-// * operands are staged by TMA (128-byte swizzle, one CTA per load) into a multi-stage ring,
+// * operands are staged by TMA (128-byte swizzle, one CTA per load) into a multi-stage ring
+//   by two producer warps, several lanes each (one box per lane),
 // * one thread issues tcgen05.mma (128 x BN x 16 per instruction) into TMEM accumulators,
 // * two accumulator buffers in TMEM let the epilogue of tile i overlap the main loop of
 //   tile i+1,
@@ -18,6 +19,7 @@
 #include <unordered_map>
 #include <string>
 #include <string.h>
+#include <stdlib.h>
 
 #include "ptx.cuh"
 #include "tma_host.h"
@@ -26,7 +28,13 @@ namespace ft {
 
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
-constexpr int GEMM_THREADS = 320;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue
+// warps 0 and 10: TMA producers (even / odd stages), warp 1: MMA + TMEM owner, warps 2-9: epilogue.
+// A thread that issues a tiled TMA load is held for roughly 400 cycles per instruction whatever
+// the box size, so one issuing thread cannot feed a 500-cycle k-step that needs two or more
+// boxes; the boxes of a stage are therefore issued by different lanes of one instruction and
+// alternate stages by different warps.
+constexpr int GEMM_THREADS = 352;
+constexpr int GEMM_PRODUCER_WARP2 = 10;
 constexpr int GEMM_EPI_WARPS = 8;    // two warps per TMEM lane quarter, each takes half the columns
 constexpr int GEMM_GROUP_M = 16;
 
@@ -68,6 +76,84 @@ __device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int& 
   const int base = p.k_iters / p.splitk, rem = p.k_iters % p.splitk;
   kb = ks * base + min(ks, rem);
   kn = base + (ks < rem ? 1 : 0);
+}
+
+// Epilogue of one 128 x BN accumulator for one warp: its 32 TMEM lanes (rows row0..row0+31),
+// column half `chalf`. TMEM -> registers -> (alpha, convert) -> swizzled staging buffer ->
+// TMA store / reduce-add. `nstores` counts this warp's bulk groups so the staging buffer is
+// only rewritten after the previous store has read it.
+template <int BN>
+__device__ __forceinline__ void drain_tile(const GemmParams& p, const CUtensorMap* tmD,
+                                           uint32_t taddr, int row0, int colbase, int chalf,
+                                           uint8_t* sbuf, int lane, int& nstores) {
+  const bool rows_live = row0 < p.M;
+  if (p.out_mode == OUT_BF16) {
+#pragma unroll 1
+    for (int c = chalf * (BN / 128); c < (chalf + 1) * (BN / 128); ++c) {
+      const int col0 = colbase + c * 64;
+      if (col0 >= p.N || !rows_live) break;
+      uint32_t r[64];
+      tmem_ld32(taddr + c * 64, r);
+      tmem_ld32(taddr + c * 64 + 32, r + 32);
+      tmem_ld_wait();
+      if (nstores >= 1) {
+        if (lane == 0) tma_wait_group_read<0>();
+        __syncwarp();
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint4 v;
+        v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]) * p.alpha,
+                          __uint_as_float(r[8 * j + 1]) * p.alpha);
+        v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * p.alpha,
+                          __uint_as_float(r[8 * j + 3]) * p.alpha);
+        v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * p.alpha,
+                          __uint_as_float(r[8 * j + 5]) * p.alpha);
+        v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * p.alpha,
+                          __uint_as_float(r[8 * j + 7]) * p.alpha);
+        *reinterpret_cast<uint4*>(sbuf + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(tmD, sbuf, col0, row0);
+        tma_commit_group();
+      }
+      ++nstores;
+    }
+  } else {
+#pragma unroll 1
+    for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
+      const int col0 = colbase + c * 32;
+      if (col0 >= p.N || !rows_live) break;
+      uint32_t r[32];
+      tmem_ld32(taddr + c * 32, r);
+      tmem_ld_wait();
+      if (nstores >= 1) {
+        if (lane == 0) tma_wait_group_read<0>();
+        __syncwarp();
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 v;
+        v.x = __uint_as_float(r[4 * j + 0]) * p.alpha;
+        v.y = __uint_as_float(r[4 * j + 1]) * p.alpha;
+        v.z = __uint_as_float(r[4 * j + 2]) * p.alpha;
+        v.w = __uint_as_float(r[4 * j + 3]) * p.alpha;
+        *reinterpret_cast<float4*>(sbuf + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (p.out_mode == OUT_F32_ADD)
+          tma_reduce_add_2d(tmD, sbuf, col0, row0);
+        else
+          tma_store_2d(tmD, sbuf, col0, row0);
+        tma_commit_group();
+      }
+      ++nstores;
+    }
+  }
 }
 
 template <int BN, int STAGES>
@@ -116,38 +202,45 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int total_tiles = p.m_tiles * p.n_tiles * p.splitk;
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
+  if (warp == 0 || warp == GEMM_PRODUCER_WARP2) {
+    // ------------------------------ TMA producers ------------------------------
+    // Lane l issues box l of a stage: A is one 128-row box (K-major) or two 64 x 64 boxes
+    // (MN-major); B is BN/128 boxes of 128 rows or BN/64 boxes of 64 x 64.
+    const int pid = warp == 0 ? 0 : 1;
+    const int nA = p.a_mn ? GEMM_BM / 64 : 1;
+    const int nB = p.b_mn ? BN / 64 : BN / 128;
+    if (lane < nA + nB) {
       int stage = 0;
       uint32_t phase = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         int mt, nt, kb, kn;
         decode_tile(p, tile, mt, nt, kb, kn);
         for (int ki = kb; ki < kb + kn; ++ki) {
-          mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
-          uint8_t* sA = smem + stage * L::STAGE_BYTES;
-          uint8_t* sB = sA + L::A_BYTES;
-          mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
-          if (!p.a_mn) {
-            tma_load_2d(sA, &tmA, &full_bar[stage], ki * GEMM_BK, mt * GEMM_BM);
-          } else {
-#pragma unroll
-            for (int c = 0; c < GEMM_BM / 64; ++c)
-              tma_load_2d(sA + c * 8192, &tmA, &full_bar[stage], mt * GEMM_BM + c * 64,
-                          ki * GEMM_BK);
-          }
-          if (!p.b_mn) {
-            tma_load_2d(sB, &tmB, &full_bar[stage], ki * GEMM_BK, nt * BN);
-          } else {
-#pragma unroll
-            for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sB + c * 8192, &tmB, &full_bar[stage], nt * BN + c * 64, ki * GEMM_BK);
+          if ((stage & 1) == pid) {
+            mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
+            uint8_t* sA = smem + stage * L::STAGE_BYTES;
+            uint8_t* sB = sA + L::A_BYTES;
+            if (lane == 0) mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+            if (lane < nA) {
+              if (!p.a_mn)
+                tma_load_2d(sA, &tmA, &full_bar[stage], ki * GEMM_BK, mt * GEMM_BM);
+              else
+                tma_load_2d(sA + lane * 8192, &tmA, &full_bar[stage], mt * GEMM_BM + lane * 64,
+                            ki * GEMM_BK);
+            } else {
+              const int j = lane - nA;
+              if (!p.b_mn)
+                tma_load_2d(sB + j * 16384, &tmB, &full_bar[stage], ki * GEMM_BK,
+                            nt * BN + j * 128);
+              else
+                tma_load_2d(sB + j * 8192, &tmB, &full_bar[stage], nt * BN + j * 64,
+                            ki * GEMM_BK);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
-      if (*abort_flag) {
+      if (lane == 0 && *abort_flag) {
         // Give copies still in flight time to land before the CTA's shared memory goes away.
         const uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -205,76 +298,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
       const int row0 = mt * GEMM_BM + q * 32;
-      const bool rows_live = row0 < p.M;
-      if (p.out_mode == OUT_BF16) {
-#pragma unroll 1
-        for (int c = chalf * (BN / 128); c < (chalf + 1) * (BN / 128); ++c) {
-          const int col0 = nt * BN + c * 64;
-          if (col0 >= p.N || !rows_live) break;
-          uint32_t r[64];
-          tmem_ld32(taddr + c * 64, r);
-          tmem_ld32(taddr + c * 64 + 32, r + 32);
-          tmem_ld_wait();
-          uint8_t* sbuf = my_epi;
-          if (nstores >= 1) {
-            if (lane == 0) tma_wait_group_read<0>();
-            __syncwarp();
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]) * p.alpha,
-                              __uint_as_float(r[8 * j + 1]) * p.alpha);
-            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]) * p.alpha,
-                              __uint_as_float(r[8 * j + 3]) * p.alpha);
-            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]) * p.alpha,
-                              __uint_as_float(r[8 * j + 5]) * p.alpha);
-            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]) * p.alpha,
-                              __uint_as_float(r[8 * j + 7]) * p.alpha);
-            *reinterpret_cast<uint4*>(sbuf + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(&tmD, sbuf, col0, row0);
-            tma_commit_group();
-          }
-          ++nstores;
-        }
-      } else {
-#pragma unroll 1
-        for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
-          const int col0 = nt * BN + c * 32;
-          if (col0 >= p.N || !rows_live) break;
-          uint32_t r[32];
-          tmem_ld32(taddr + c * 32, r);
-          tmem_ld_wait();
-          uint8_t* sbuf = my_epi;
-          if (nstores >= 1) {
-            if (lane == 0) tma_wait_group_read<0>();
-            __syncwarp();
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float4 v;
-            v.x = __uint_as_float(r[4 * j + 0]) * p.alpha;
-            v.y = __uint_as_float(r[4 * j + 1]) * p.alpha;
-            v.z = __uint_as_float(r[4 * j + 2]) * p.alpha;
-            v.w = __uint_as_float(r[4 * j + 3]) * p.alpha;
-            *reinterpret_cast<float4*>(sbuf + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            if (p.out_mode == OUT_F32_ADD)
-              tma_reduce_add_2d(&tmD, sbuf, col0, row0);
-            else
-              tma_store_2d(&tmD, sbuf, col0, row0);
-            tma_commit_group();
-          }
-          ++nstores;
-        }
-      }
+      drain_tile<BN>(p, &tmD, taddr, row0, nt * BN, chalf, my_epi, lane, nstores);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
@@ -288,6 +312,200 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs owns a 256 x 256 output tile. Each CTA stages 128
+// rows of A and 128 columns' worth of B per k-step (32 KB instead of 48 KB for 128 x 256 of
+// output), so shared-memory write (TMA) plus read (tensor core) traffic per SM drops by a
+// third and six stages fit. The even CTA issues every MMA (`cta_group::2`, M = 256); each CTA
+// drains the 128 accumulator rows that live in its own TMEM.
+//   full[s]   (even CTA)  : armed by the even CTA's producer with both CTAs' bytes; both CTAs'
+//                           loads report to it.
+//   empty[s]  (each CTA)  : one commit from the issuing thread signals the barrier of both
+//                           CTAs (a second commit instruction per stage, or a relayed
+//                           arrive, measurably stalls the pipe).
+//   tfull[b]  (each CTA)  : same, at the end of a tile.
+//   tempty[b] (even CTA)  : 16 arrivals, one per epilogue warp of both CTAs.
+// ---------------------------------------------------------------------------------------
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_BN = 256;
+struct PairSmem {
+  static constexpr int A_BYTES = 128 * GEMM_BK * 2;
+  static constexpr int B_BYTES = 128 * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int EPI_BUF_BYTES = 4096;
+  static constexpr int EPI_BYTES = GEMM_EPI_WARPS * EPI_BUF_BYTES;
+  static constexpr int BAR_OFFSET = PAIR_STAGES * STAGE_BYTES + EPI_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
+                      const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
+  using L = PairSmem;
+  constexpr int STAGES = PAIR_STAGES;
+  constexpr int BN = PAIR_BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* epi_base = smem + STAGES * L::STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull_bar[b], 1);
+      mbar_init(&tempty_bar[b], 2 * GEMM_EPI_WARPS);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    prefetch_tmap(&tmD);
+  }
+  __syncwarp();
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers are initialised before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = p.m_tiles * p.n_tiles * p.splitk;
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+  if (warp == 0 || warp == GEMM_PRODUCER_WARP2) {
+    // ------------------------------ TMA producers (both CTAs) ------------------------------
+    const int pid = warp == 0 ? 0 : 1;
+    const int nA = p.a_mn ? 2 : 1;
+    const int nB = p.b_mn ? 2 : 1;
+    if (lane < nA + nB) {
+      const uint32_t full0 = mapa_u32(smem_u32(&full_bar[0]), 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = pair; tile < total_tiles; tile += npairs) {
+        int mt, nt, kb, kn;
+        decode_tile(p, tile, mt, nt, kb, kn);
+        const int arow = mt * 256 + static_cast<int>(rank) * 128;
+        const int brow = nt * BN + static_cast<int>(rank) * 128;
+        for (int ki = kb; ki < kb + kn; ++ki) {
+          if ((stage & 1) == pid) {
+            mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
+            uint8_t* sA = smem + stage * L::STAGE_BYTES;
+            uint8_t* sB = sA + L::A_BYTES;
+            if (leader && lane == 0) mbar_expect_tx(&full_bar[stage], 2 * L::STAGE_BYTES);
+            const uint32_t bar = full0 + stage * 8;
+            if (lane < nA) {
+              if (!p.a_mn)
+                tma_load_2d_pair(sA, &tmA, bar, ki * GEMM_BK, arow);
+              else
+                tma_load_2d_pair(sA + lane * 8192, &tmA, bar, arow + lane * 64, ki * GEMM_BK);
+            } else {
+              const int j = lane - nA;
+              if (!p.b_mn)
+                tma_load_2d_pair(sB, &tmB, bar, ki * GEMM_BK, brow);
+              else
+                tma_load_2d_pair(sB + j * 8192, &tmB, bar, brow + j * 64, ki * GEMM_BK);
+            }
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (lane == 0 && *abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (even CTA only) ------------------------------
+    if (lane == 0 && leader) {
+      const uint32_t idesc = make_idesc_bf16(256, BN, p.a_mn, p.b_mn);
+      const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
+      const uint32_t a_kstep = p.a_mn ? (2048u >> 4) : (32u >> 4);
+      const uint32_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      for (int tile = pair; tile < total_tiles; tile += npairs, ++it) {
+        int mt, nt, kb, kn;
+        decode_tile(p, tile, mt, nt, kb, kn);
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        mbar_wait(&tempty_bar[buf], acc_phase ^ 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int ki = 0; ki < kn; ++ki) {
+          mbar_wait(&full_bar[stage], phase, abort_flag, p.status, FT_ERR_WAIT_FULL);
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + stage * L::STAGE_BYTES);
+          const uint32_t sB = sA + L::A_BYTES;
+          const uint64_t adesc = make_smem_desc(sA, a_lbo, 1024);
+          const uint64_t bdesc = make_smem_desc(sB, b_lbo, 1024);
+#pragma unroll
+          for (int kk = 0; kk < GEMM_BK / 16; ++kk) {
+            umma_ss_pair(tmem_d, adesc + kk * a_kstep, bdesc + kk * b_kstep, idesc,
+                         (ki > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit_both(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        umma_commit_both(&tfull_bar[buf]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) ------------------------------
+    const int q = warp & 3;
+    const int chalf = (warp - 2) >> 2;
+    uint8_t* my_epi = epi_base + (warp - 2) * L::EPI_BUF_BYTES;
+    const uint32_t tempty0 = mapa_u32(smem_u32(&tempty_bar[0]), 0);
+    int it = 0;
+    int nstores = 0;
+    for (int tile = pair; tile < total_tiles; tile += npairs, ++it) {
+      int mt, nt, kb, kn;
+      decode_tile(p, tile, mt, nt, kb, kn);
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      mbar_wait(&tfull_bar[buf], acc_phase, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+      const int row0 = mt * 256 + static_cast<int>(rank) * 128 + q * 32;
+      drain_tile<BN>(p, &tmD, taddr, row0, nt * BN, chalf, my_epi, lane, nstores);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty0 + buf * 8);
+    }
+    if (lane == 0) tma_wait_group<0>();
+    __syncwarp();
+  }
+
+  // Neither CTA may leave (or free its TMEM) while the other can still signal its barriers
+  // or the issuing thread can still write its accumulators.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
 }
 
@@ -364,13 +582,44 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
+static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB,
+                            const CUtensorMap& tmD, const GemmParams& p, int max_ctas,
+                            cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_bf16_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         PairSmem::TOTAL);
+    if (e != cudaSuccess) return -10;
+    attr_set = true;
+  }
+  const int total = p.m_tiles * p.n_tiles * p.splitk;
+  int pairs = max_ctas / 2;
+  if (pairs > total) pairs = total;
+  if (pairs < 1) pairs = 1;
+  gemm_pair_bf16_kernel<<<2 * pairs, GEMM_THREADS, PairSmem::TOTAL, stream>>>(tmA, tmB, tmD, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Process-wide default for the tile shape when the caller passes bn = 0: 1 selects the
+// CTA-pair kernel wherever it applies. FT_GEMM_PAIR=0 in the environment turns it off.
+static int pair_default() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("FT_GEMM_PAIR");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v;
+}
+
 }  // namespace ft
 
 // D[M,N] (=|+=) alpha * A * B^T with bf16 operands.
 //   a_mn == 0: A is stored [M][lda] (reduction index contiguous); a_mn == 1: A is stored
 //   [K][lda] (row index contiguous). Same for B with N. out_dtype: 0 bf16, 1 fp32.
 //   accumulate != 0 (fp32 only): D += result. splitk <= 0 picks a split automatically
-//   (fp32 only); bn in {0 (auto), 128, 256}. All leading dimensions in elements; every base
+//   (fp32 only); bn in {0 (auto), 128, 256, 512 (256 x 256 tile on a CTA pair)}. All leading
+//   dimensions in elements; every base
 //   pointer 16-byte aligned and every leading dimension a multiple of 8 (bf16) / 4 (fp32).
 extern "C" int ft_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int lda,
                             int ldb, int ldd, int a_mn, int b_mn, int out_dtype, int accumulate,
@@ -381,16 +630,22 @@ extern "C" int ft_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   if (out_dtype == 0 && accumulate) return -2;
   const int sms = num_sms();
   if (max_ctas <= 0 || max_ctas > sms) max_ctas = sms;
-  const int m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
   const int k_iters = (K + GEMM_BK - 1) / GEMM_BK;
-  if (bn != 128 && bn != 256) bn = (N <= 128) ? 128 : 256;  // 256-wide tiles measured faster at every N > 128
+  // bn: 128 / 256 = one CTA per 128 x bn tile; 512 = a CTA pair per 256 x 256 tile.
+  if (bn != 128 && bn != 256 && bn != 512)
+    bn = (N <= 128) ? 128 : ((pair_default() && M > 128 && max_ctas >= 2) ? 512 : 256);
+  const bool pair = bn == 512;
+  if (pair) bn = 256;
+  const int bm = pair ? 256 : GEMM_BM;
+  const int m_tiles = (M + bm - 1) / bm;
   const int n_tiles = (N + bn - 1) / bn;
   if (out_dtype == 0) splitk = 1;
   if (splitk <= 0) {
     const int tiles = m_tiles * n_tiles;
     splitk = 1;
-    if (tiles < max_ctas) {
-      splitk = max_ctas / tiles;
+    const int units = pair ? max_ctas / 2 : max_ctas;
+    if (tiles < units) {
+      splitk = units / tiles;
       const int max_by_k = k_iters / 8 > 0 ? k_iters / 8 : 1;
       if (splitk > max_by_k) splitk = max_by_k;
       if (splitk > 16) splitk = 16;
@@ -419,13 +674,14 @@ extern "C" int ft_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   if (!a_mn) rc = get_tmap_2d(&tmA, A, 2, M, K, lda, GEMM_BM, GEMM_BK);
   else       rc = get_tmap_2d(&tmA, A, 2, K, M, lda, GEMM_BK, 64);
   if (rc) return -4;
-  if (!b_mn) rc = get_tmap_2d(&tmB, B, 2, N, K, ldb, bn, GEMM_BK);
+  if (!b_mn) rc = get_tmap_2d(&tmB, B, 2, N, K, ldb, 128, GEMM_BK);
   else       rc = get_tmap_2d(&tmB, B, 2, K, N, ldb, GEMM_BK, 64);
   if (rc) return -5;
   if (out_dtype == 0) rc = get_tmap_2d(&tmD, D, 2, M, N, ldd, 32, 64);
   else                rc = get_tmap_2d(&tmD, D, 4, M, N, ldd, 32, 32);
   if (rc) return -6;
 
+  if (pair) return launch_gemm_pair(tmA, tmB, tmD, p, max_ctas, stream);
   if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, tmD, p, max_ctas, stream);
   return launch_gemm<128, 6>(tmA, tmB, tmD, p, max_ctas, stream);
 }

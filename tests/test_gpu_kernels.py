@@ -45,6 +45,23 @@ def test_gemm_fwd_dgrad_wgrad(T, N, K):
     assert rel(dw1, ref) < 1e-3 and rel(dw4, ref) < 1e-3
 
 
+@pytest.mark.parametrize("bn", [128, 256, 512])
+@pytest.mark.parametrize("T,N,K", [(256, 256, 64), (640, 1280, 320), (1000, 1032, 1024), (2048, 4096, 512)])
+def test_gemm_tile_shapes(T, N, K, bn):
+    """Every tile shape (one CTA per 128 x 128 / 128 x 256 tile, a CTA pair per 256 x 256 tile)
+    against fp32 matmul, for all three operand-major combinations and the reduce-add epilogue."""
+    x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    dy = torch.randn(T, N, device="cuda").to(torch.bfloat16)
+    assert rel(gemm.linear_fwd(x, w, bn=bn), x.float() @ w.float().t()) < 0.01
+    assert rel(gemm.linear_dgrad(dy, w, bn=bn), dy.float() @ w.float()) < 0.01
+    ref = dy.float().t() @ x.float()
+    dw = gemm.linear_wgrad(dy, x, bn=bn)
+    assert rel(dw, ref) < 1e-3
+    gemm.linear_wgrad(dy, x, out=dw, accumulate=True, bn=bn, splitk=3)
+    assert rel(dw, 2 * ref) < 1e-3
+
+
 def test_gemm_strided_views():
     """Operands that are column slices of a wider buffer (row pitch != width)."""
     big = torch.randn(512, 3 * 256, device="cuda").to(torch.bfloat16)
