@@ -5,6 +5,9 @@ Every ``csrc/*.cu`` file is compiled for sm_100a only
 C ABI that :mod:`forgetrain_b200.ops._lib` loads through ``ctypes``. nvcc cross-compiles, so
 the build needs no GPU. Objects are rebuilt only when their source (or a header) changed.
 
+The host C++ reference ops of ``csrc/ref_cpu`` are built with g++ into
+``forgetrain_b200/lib/libft_ref_cpu.so`` by the same command.
+
 Usage: ``python -m forgetrain_b200.build [--force] [--verbose]``
 """
 from __future__ import annotations
@@ -22,6 +25,8 @@ CSRC = PKG_DIR / "csrc"
 OBJ_DIR = CSRC / "build"
 LIB_DIR = PKG_DIR / "lib"
 LIB_PATH = LIB_DIR / "libft_b200.so"
+REF_SRC = CSRC / "ref_cpu" / "ref_ops.cpp"
+REF_LIB_PATH = LIB_DIR / "libft_ref_cpu.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -95,10 +100,32 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+def build_ref_cpu(force: bool = False) -> Path:
+    """Compile the host C++ reference ops (``csrc/ref_cpu``) with g++ and OpenMP."""
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    tag = REF_LIB_PATH.with_suffix(".tag")
+    want = hashlib.sha256(REF_SRC.read_bytes()).hexdigest()
+    if not force and REF_LIB_PATH.exists() and tag.exists() and tag.read_text() == want:
+        return REF_LIB_PATH
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if cxx is None:
+        raise RuntimeError("g++ not found; the host reference library cannot be built")
+    tmp = REF_LIB_PATH.with_suffix(".so.tmp")
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-fopenmp", str(REF_SRC), "-o", str(tmp)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"g++ failed for {REF_SRC.name}:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp, REF_LIB_PATH)
+    tag.write_text(want)
+    return REF_LIB_PATH
+
+
 def main() -> None:
     force = "--force" in sys.argv
     verbose = "--verbose" in sys.argv
     path = build(force=force, verbose=verbose)
+    ref = build_ref_cpu(force=force)
+    print(f"built {ref}")
     print(f"built {path} ({path.stat().st_size / 1e6:.1f} MB) from {len(sources())} sources")
 
 
