@@ -37,6 +37,11 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
 __device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const void* mc_addr) {
   float4 v;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
@@ -252,6 +257,96 @@ bucket_all_gather_kernel(CommPeers c, long start, long n_per_rank, uint32_t epoc
 }
 
 // ---------------------------------------------------------------------------------------
+// AdamW shard update fused with the parameter all-gather: every thread updates eight master
+// weights (fp32 p / m / v, decoupled weight decay, bias correction, clip from hyper[6]) and
+// stores the eight bf16 results straight into EVERY rank's parameter buffer, by one
+// `multimem.st` through the switch or by one 16-byte store per peer, so the updated shard is
+// never re-read for a separate gather. Exit barrier on slot 2 as in the plain all-gather.
+//   shard = elements [start + rank*n_per_rank, +n_per_rank); n_per_rank % 8 == 0.
+//   hyper = {lr, beta1, beta2, eps, bias_corr1, bias_corr2, clip, _} in device memory;
+//   seg_end[s] = exclusive end offset of segment s within the shard, seg_wd, seg_lr_mult.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(COMM_THREADS)
+adamw_all_gather_kernel(CommPeers c, long start, long n_per_rank, float* __restrict__ p32,
+                        float* __restrict__ m, float* __restrict__ v,
+                        const float* __restrict__ g, const float* __restrict__ hyper,
+                        const long* __restrict__ seg_end, const float* __restrict__ seg_wd,
+                        const float* __restrict__ seg_lr_mult, int nseg, uint32_t epoch,
+                        uint64_t limit_ns, unsigned int* __restrict__ done_ctr, int* status) {
+  const float lr = hyper[0], b1 = hyper[1], b2 = hyper[2], eps = hyper[3];
+  const float inv_bc1 = 1.f / hyper[4], inv_bc2 = 1.f / hyper[5], clip = hyper[6];
+  const long base = start + static_cast<long>(c.rank) * n_per_rank;  // in elements
+  const long nvec = n_per_rank / 8;
+  for (long i = static_cast<long>(blockIdx.x) * COMM_THREADS + threadIdx.x; i < nvec;
+       i += static_cast<long>(gridDim.x) * COMM_THREADS) {
+    const long e0 = i * 8;
+    int lo = 0, hi = nseg - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (seg_end[mid] > e0) hi = mid; else lo = mid + 1;
+    }
+    int seg = lo;
+    float pp[8], mm[8], vv[8], gg[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float4 a = reinterpret_cast<const float4*>(p32)[2 * i + h];
+      const float4 b = reinterpret_cast<const float4*>(m)[2 * i + h];
+      const float4 d = reinterpret_cast<const float4*>(v)[2 * i + h];
+      const float4 e = reinterpret_cast<const float4*>(g)[2 * i + h];
+      pp[4 * h] = a.x; pp[4 * h + 1] = a.y; pp[4 * h + 2] = a.z; pp[4 * h + 3] = a.w;
+      mm[4 * h] = b.x; mm[4 * h + 1] = b.y; mm[4 * h + 2] = b.z; mm[4 * h + 3] = b.w;
+      vv[4 * h] = d.x; vv[4 * h + 1] = d.y; vv[4 * h + 2] = d.z; vv[4 * h + 3] = d.w;
+      gg[4 * h] = e.x; gg[4 * h + 1] = e.y; gg[4 * h + 2] = e.z; gg[4 * h + 3] = e.w;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      while (seg < nseg - 1 && seg_end[seg] <= e0 + k) ++seg;
+      const float wd = seg_wd[seg], lrm = seg_lr_mult[seg];
+      const float gr = gg[k] * clip;
+      mm[k] = b1 * mm[k] + (1.f - b1) * gr;
+      vv[k] = b2 * vv[k] + (1.f - b2) * gr * gr;
+      const float upd = (mm[k] * inv_bc1) / (sqrtf(vv[k] * inv_bc2) + eps) + wd * pp[k];
+      pp[k] -= lr * lrm * upd;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      reinterpret_cast<float4*>(p32)[2 * i + h] =
+          make_float4(pp[4 * h], pp[4 * h + 1], pp[4 * h + 2], pp[4 * h + 3]);
+      reinterpret_cast<float4*>(m)[2 * i + h] =
+          make_float4(mm[4 * h], mm[4 * h + 1], mm[4 * h + 2], mm[4 * h + 3]);
+      reinterpret_cast<float4*>(v)[2 * i + h] =
+          make_float4(vv[4 * h], vv[4 * h + 1], vv[4 * h + 2], vv[4 * h + 3]);
+    }
+    uint4 o;
+    o.x = pack2_bf16(pp[0], pp[1]);
+    o.y = pack2_bf16(pp[2], pp[3]);
+    o.z = pack2_bf16(pp[4], pp[5]);
+    o.w = pack2_bf16(pp[6], pp[7]);
+    if (c.mc) {
+      multimem_st_b32x4(reinterpret_cast<uint4*>(static_cast<uint16_t*>(c.mc) + base) + i, o);
+    } else {
+      for (int p = 0; p < c.world; ++p) {
+        const int q = (c.rank + p) % c.world;
+        st_peer_b32x4(reinterpret_cast<uint4*>(static_cast<uint16_t*>(c.buf[q]) + base) + i, o);
+      }
+    }
+  }
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(done_ctr, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+    if (s_last) *done_ctr = 0;
+  }
+  __syncthreads();
+  if (s_last) {
+    signal_peers(c, 2, epoch);
+    wait_peers(c, 2, epoch, limit_ns, status);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // Small all-reduce (sum) of a few floats through the flag-protected symmetric scratch area:
 // every rank writes its values into its own slot of every peer, barrier, each rank sums.
 //   scratch layout per rank: [world][n] floats at float offset `scratch_off`. n <= 64.
@@ -395,6 +490,30 @@ extern "C" int ft_bucket_all_gather(const void* const* bufs, const void* const* 
   bucket_all_gather_kernel<<<ctas, COMM_THREADS, 0, st>>>(c, start, n_per_rank, epoch, limit_ns,
                                                           static_cast<unsigned int*>(done_ctr),
                                                           status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
+// Fused AdamW + parameter all-gather of one bucket shard (see adamw_all_gather_kernel).
+// bufs: peer mappings of the bf16 parameter buffer; p32 / m / v / g: this rank's fp32 shard.
+extern "C" int ft_adamw_all_gather(const void* const* bufs, const void* const* flags, void* mc,
+                                   int rank, int world, long start, long n_per_rank, void* p32,
+                                   void* m, void* v, const void* g, const void* hyper,
+                                   const void* seg_end, const void* seg_wd,
+                                   const void* seg_lr_mult, int nseg, unsigned int epoch,
+                                   unsigned long long limit_ns, void* done_ctr, int ctas,
+                                   int* status, cudaStream_t st) {
+  if (world > COMM_MAX_RANKS || n_per_rank % 8 || nseg < 1) return -1;
+  CommPeers c;
+  fill_peers(c, bufs, flags, mc, rank, world);
+  if (ctas <= 0) ctas = 148 * 4;
+  const long need = (n_per_rank / 8 + COMM_THREADS - 1) / COMM_THREADS;
+  if (ctas > need) ctas = need < 1 ? 1 : static_cast<int>(need);
+  adamw_all_gather_kernel<<<ctas, COMM_THREADS, 0, st>>>(
+      c, start, n_per_rank, static_cast<float*>(p32), static_cast<float*>(m),
+      static_cast<float*>(v), static_cast<const float*>(g), static_cast<const float*>(hyper),
+      static_cast<const long*>(seg_end), static_cast<const float*>(seg_wd),
+      static_cast<const float*>(seg_lr_mult), nseg, epoch, limit_ns,
+      static_cast<unsigned int*>(done_ctr), status);
   return cudaGetLastError() == cudaSuccess ? 0 : -100;
 }
 

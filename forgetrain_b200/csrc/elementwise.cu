@@ -589,6 +589,39 @@ __global__ void clip_coef_kernel(const float* __restrict__ sumsq, float max_norm
   hyper_clip[0] = max_norm > 0.f ? fminf(1.f, max_norm / (nrm + 1e-6f)) : 1.f;
 }
 
+// One thread: advance the device-resident optimizer step counter and derive this step's
+// scalars, so that a replayed CUDA graph needs nothing from the host.
+//   sched = [max_lr, min_lr, warmup_iters, lr_decay_iters, wsd_decay_iters, beta1, beta2, eps]
+//   hyper[0..5] = lr, beta1, beta2, eps, 1 - beta1^t, 1 - beta2^t   (t = step after increment)
+// The learning rate is the warmup - stable - decay schedule evaluated at the step count
+// before the increment.
+__global__ void adam_hyper_kernel(int* __restrict__ step, const float* __restrict__ sched,
+                                  float* __restrict__ hyper) {
+  const int it = step[0];
+  const double max_lr = sched[0], min_lr = sched[1];
+  const int warmup = (int)sched[2], decay = (int)sched[3], wsd = (int)sched[4];
+  double lr;
+  if (warmup > 0 && it < warmup) {
+    lr = max_lr * it / warmup;
+  } else if (wsd <= 0) {
+    lr = it <= decay ? max_lr : min_lr;
+  } else {
+    const int stable_end = decay - wsd;
+    if (it <= stable_end) lr = max_lr;
+    else if (it > decay) lr = min_lr;
+    else lr = min_lr + (2.0 * pow(0.5, (double)(it - stable_end) / wsd) - 1.0) * (max_lr - min_lr);
+  }
+  const int t = it + 1;
+  step[0] = t;
+  const double b1 = sched[5], b2 = sched[6];
+  hyper[0] = (float)lr;
+  hyper[1] = sched[5];
+  hyper[2] = sched[6];
+  hyper[3] = sched[7];
+  hyper[4] = (float)(1.0 - pow(b1, (double)t));
+  hyper[5] = (float)(1.0 - pow(b2, (double)t));
+}
+
 static int grid_for(long work_items, int threads, int cap_mult = 8) {
   long b = (work_items + threads - 1) / threads;
   const long cap = 148L * cap_mult;
@@ -766,6 +799,11 @@ extern "C" int ft_clip_coef(const void* sumsq, float max_norm, void* hyper_clip,
                             cudaStream_t st) {
   clip_coef_kernel<<<1, 1, 0, st>>>((const float*)sumsq, max_norm, (float*)hyper_clip,
                                     (float*)norm_out);
+  return FT_LAUNCH_OK();
+}
+
+extern "C" int ft_adam_hyper(void* step, const void* sched, void* hyper, cudaStream_t st) {
+  adam_hyper_kernel<<<1, 1, 0, st>>>((int*)step, (const float*)sched, (float*)hyper);
   return FT_LAUNCH_OK();
 }
 

@@ -49,6 +49,7 @@ class EngineConfig:
     # ---- CUDA graphs ----
     forward_cuda_graph: bool = False
     step_cuda_graph: bool = False
+    full_step_cuda_graph: bool = False   # micro-batches + norm + clip + AdamW in ONE graph
     step_cuda_graph_warmup: int = 3
     step_cuda_graph_tol: float = 1e-3
     step_cuda_graph_sanity: bool = False
@@ -113,6 +114,7 @@ _ENV_MAP: dict[str, tuple[str, Callable[[str], Any]]] = {
     "SEQUENCE_PARALLEL": ("sequence_parallel", lambda v: v.lower() in _BOOL_TRUE),
     "FORWARD_CUDA_GRAPH": ("forward_cuda_graph", lambda v: v.lower() in _BOOL_TRUE),
     "STEP_CUDA_GRAPH": ("step_cuda_graph", lambda v: v.lower() in _BOOL_TRUE),
+    "FULL_STEP_CUDA_GRAPH": ("full_step_cuda_graph", lambda v: v.lower() in _BOOL_TRUE),
     "STEP_CUDA_GRAPH_WARMUP": ("step_cuda_graph_warmup", int),
     "STEP_CUDA_GRAPH_TOL": ("step_cuda_graph_tol", float),
     "STEP_CUDA_GRAPH_SANITY": ("step_cuda_graph_sanity", lambda v: v.lower() in _BOOL_TRUE),

@@ -76,3 +76,94 @@ class GraphedComputeStep:
         e["graph"].replay()
         self.replays += 1
         return e["loss"]
+
+
+class GraphedFullStep:
+    """A whole optimizer step in ONE CUDA graph: every micro-batch's forward + loss + backward,
+    the gradient-norm partials, the clip coefficient, the fused AdamW update of the master
+    weights and the bf16 parameter write-back.
+
+    What changes from step to step is either device state the graph itself advances (weights,
+    moments, gradients) or a handful of scalars (learning rate, bias corrections) that the host
+    stages in a pinned vector before the replay; the captured copy node reads them at replay
+    time. The first ``warmup`` calls run eagerly (they are real training steps and also warm
+    the allocator and the tensor-map cache); the next call captures (capture launches nothing)
+    and replays. One graph is kept per (number of micro-batches, input shape).
+
+    Plays the role of the reference's ``step_graph_full`` / ``step_graph_optimizer`` wrappers
+    (exports/train_engine_0.5B/src/training_engine_tensor/step_graph_full.py:147-482,
+    step_graph_optimizer.py:112-272) for one process per GPU.
+    """
+
+    def __init__(self, trainer, warmup: int = 3):
+        self.trainer = trainer
+        self.warmup = max(1, warmup)
+        self.calls = 0
+        self.replays = 0
+        self._graphs: dict = {}
+
+    @staticmethod
+    def _key(micro_batches):
+        return tuple((tuple(b["tokens"].shape), tuple(sorted(k for k, v in b.items()
+                                                             if torch.is_tensor(v))))
+                     for b in micro_batches)
+
+    def __call__(self, micro_batches: list[dict]) -> None:
+        tr = self.trainer
+        self.calls += 1
+        if self.calls <= self.warmup:
+            tr._device_step(micro_batches)
+            return
+        key = self._key(micro_batches)
+        e = self._graphs.get(key)
+        if e is None:
+            static = [{k: v.clone() for k, v in b.items() if torch.is_tensor(v)}
+                      for b in micro_batches]
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                tr._device_step(static)
+            e = {"graph": g, "static": static}
+            self._graphs[key] = e
+        for st, b in zip(e["static"], micro_batches):
+            for k, v in st.items():
+                v.copy_(b[k], non_blocking=True)
+        e["graph"].replay()
+        self.replays += 1
+
+
+class GraphedForward:
+    """Forward pass (logits) of a fixed input shape in a CUDA graph, for evaluation loops.
+    Counterpart of the reference's ``forward_graph`` wrapper
+    (exports/train_engine_0.5B/src/training_engine_tensor/forward_graph.py:66-272)."""
+
+    def __init__(self, model, warmup: int = 2):
+        self.model = model
+        self.warmup = max(1, warmup)
+        self._graphs: dict = {}
+        self.replays = 0
+
+    def __call__(self, tokens: torch.Tensor, position_ids: torch.Tensor | None = None):
+        key = (tuple(tokens.shape), position_ids is not None)
+        e = self._graphs.get(key)
+        if e is None:
+            st_tok = tokens.clone()
+            st_pos = None if position_ids is None else position_ids.clone()
+            side = torch.cuda.Stream(device=tokens.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(self.warmup):
+                    self.model.forward(st_tok, st_pos)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                logits = self.model.forward(st_tok, st_pos)
+            e = {"graph": g, "tokens": st_tok, "pos": st_pos, "logits": logits}
+            self._graphs[key] = e
+        e["tokens"].copy_(tokens, non_blocking=True)
+        if e["pos"] is not None:
+            e["pos"].copy_(position_ids, non_blocking=True)
+        e["graph"].replay()
+        self.replays += 1
+        return e["logits"]

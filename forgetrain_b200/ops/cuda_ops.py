@@ -216,6 +216,14 @@ def clip_coef(sumsq_t, max_norm, hyper, norm_out) -> None:
     _lib.check_rc(rc, "ft_clip_coef")
 
 
+def adam_hyper_step(step_dev, sched, hyper) -> None:
+    """Device-side schedule: ``step_dev[0] += 1`` and ``hyper[0:6]`` = this step's learning
+    rate (warmup - stable - decay), betas, eps and bias corrections."""
+    assert step_dev.dtype == torch.int32 and sched.dtype == torch.float32 and sched.numel() >= 8
+    rc = _L().ft_adam_hyper(P(step_dev), P(sched), P(hyper), _lib.stream())
+    _lib.check_rc(rc, "ft_adam_hyper")
+
+
 def c_void_off(t: torch.Tensor, elem_off: int):
     return _lib.c_void_p(t.data_ptr() + elem_off * t.element_size())
 

@@ -5,7 +5,9 @@ gradient bucket. One fused kernel launch per bucket applies clip * grad, the mom
 bias correction, decoupled weight decay and the per-parameter muP learning-rate multiplier
 (from a small segment table), and writes the new bf16 value directly at the shard's position in
 the flat parameter buffer, which is the all-gather destination, so the all-gather runs in
-place with no packing. Every per-step scalar (lr, bias corrections, clip coefficient) lives in
+place with no packing; with the peer-memory collectives the update kernel itself stores the
+bf16 results into every rank's parameter buffer (``multimem.st`` or peer stores), so update and
+all-gather are one launch. Every per-step scalar (lr, bias corrections, clip coefficient) lives in
 a device vector, which keeps the launches graph-capturable.
 
 Numerics follow the reference's fused kernel
@@ -14,6 +16,8 @@ sharded driver (optimizer.py:633-748): beta = (0.9, 0.95), eps 1e-8, weight deca
 matrices, hidden matrices at lr / (hidden / 256) under muP.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 import torch.distributed as dist
@@ -76,10 +80,30 @@ class ShardedAdamW:
         self.hyper_host = torch.zeros(8, dtype=torch.float32)
         if self.is_cuda:
             self.hyper_host = self.hyper_host.pin_memory()
+        # fused peer-memory path: update + all-gather in one kernel (FT_FUSE_ADAM_AG=0: two)
+        self.fuse_update_gather = os.environ.get("FT_FUSE_ADAM_AG", "1") != "0"
+        self.sched = None        # device schedule vector, see set_schedule()
+        self.step_dev = None
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self.sumsq_total = torch.zeros(1, dtype=torch.float32, device=dev)
         self.ag_events: list = [None] * len(buckets)
         self.sync_master_from_params()
+
+    def set_schedule(self, max_lr: float, min_lr: float, warmup_iters: int, lr_decay_iters: int,
+                     wsd_decay_iters: int) -> None:
+        """Keep the step counter and the learning-rate schedule on the device (CUDA only): each
+        :meth:`apply` then derives its own scalars in a one-thread kernel instead of copying
+        them from the host, which is what lets a captured step be replayed without any
+        per-step host data and keeps a host that runs ahead from overwriting scalars the
+        device has not consumed yet. The ``lr`` passed to :meth:`step` must be the same
+        schedule evaluated at ``step_count`` (it is only used for reporting then)."""
+        if not self.is_cuda:
+            return
+        dev = self.hyper.device
+        self.sched = torch.tensor([max_lr, min_lr, warmup_iters, lr_decay_iters, wsd_decay_iters,
+                                   self.beta1, self.beta2, self.eps], dtype=torch.float32,
+                                  device=dev)
+        self.step_dev = torch.tensor([self.step_count], dtype=torch.int32, device=dev)
 
     # ------------------------------------------------------------------ state plumbing
     def master_view(self, i: int) -> torch.Tensor:
@@ -120,17 +144,39 @@ class ShardedAdamW:
 
     def step(self, lr: float) -> None:
         """Update this rank's shard of every bucket, then all-gather the bf16 parameters."""
+        self.prepare_host(lr)
+        self.apply()
+
+    def prepare_host(self, lr: float) -> None:
+        """Host half of a step: advance the step count and stage this step's scalars in the
+        pinned hyper-parameter vector. Nothing is launched, so a captured :meth:`apply` can be
+        replayed after it."""
         self.step_count += 1
         t = self.step_count
+        self._lr = lr
         h = self.hyper_host
         h[0], h[1], h[2], h[3] = lr, self.beta1, self.beta2, self.eps
         h[4], h[5] = 1.0 - self.beta1 ** t, 1.0 - self.beta2 ** t
-        # slots 6 (clip) and 7 are device-owned: copy only the first six
-        self.hyper[:6].copy_(h[:6], non_blocking=True)
+
+    def apply(self) -> None:
+        """Device half of a step (capturable in a CUDA graph): copy the staged scalars and run
+        the fused AdamW kernel and the parameter all-gather bucket by bucket."""
+        lr, t = self._lr, self.step_count
+        if self.sched is not None:
+            from ..ops import cuda_ops
+            cuda_ops.adam_hyper_step(self.step_dev, self.sched, self.hyper)
+        else:
+            # slots 6 (clip) and 7 are device-owned: copy only the first six
+            self.hyper[:6].copy_(self.hyper_host[:6], non_blocking=True)
         flat_g, flat_p = self.store.flat_grads, self.store.flat_params
         for i, b in enumerate(self.buckets):
             lo, hi = b.shard_range(self.rank, self.world)
             p32, m, v = self._views(i)
+            if self.is_cuda and self.fused is not None and self.world > 1 and self.fuse_update_gather \
+                    and (hi - lo) % 8 == 0:
+                se, sw, sl = self.seg_dev[i]
+                self.fused.adamw_all_gather(b, p32, m, v, flat_g[lo:hi], self.hyper, se, sw, sl)
+                continue
             if self.is_cuda:
                 from ..ops import cuda_ops
                 se, sw, sl = self.seg_dev[i]
@@ -224,3 +270,5 @@ class ShardedAdamW:
                     t = src[name].reshape(-1)[a - p_lo:z - p_lo]
                     flat[base + a - s_lo:base + z - s_lo].copy_(t.to(flat.device))
         self.step_count = int(step_count)
+        if self.step_dev is not None:
+            self.step_dev.fill_(self.step_count)

@@ -110,6 +110,21 @@ class FusedDPComm:
             _lib.ptr(self.status), _lib.stream())
         _lib.check_rc(rc, "ft_bucket_all_gather")
 
+    def adamw_all_gather(self, b, p32, m, v, g, hyper, seg_end, seg_wd, seg_lr_mult) -> None:
+        """AdamW on this rank's shard of bucket ``b`` with the bf16 results stored straight
+        into every rank's parameter buffer (one kernel instead of update + all-gather)."""
+        s = self.s
+        ep = s.next_epoch(2)
+        rc = _lib.lib().ft_adamw_all_gather(
+            s.p_params, s.p_flags, ctypes.c_void_p(s.mc_params), ctypes.c_int(s.rank),
+            ctypes.c_int(s.world), ctypes.c_long(b.start), ctypes.c_long(b.size // s.world),
+            _lib.ptr(p32), _lib.ptr(m), _lib.ptr(v), _lib.ptr(g), _lib.ptr(hyper),
+            _lib.ptr(seg_end), _lib.ptr(seg_wd), _lib.ptr(seg_lr_mult),
+            ctypes.c_int(seg_end.numel()), ctypes.c_uint(ep), ctypes.c_ulonglong(self.limit_ns),
+            _lib.c_void_p(s.done_ctr.data_ptr() + 4), ctypes.c_int(0), _lib.ptr(self.status),
+            _lib.stream())
+        _lib.check_rc(rc, "ft_adamw_all_gather")
+
     def wait_all_gathers(self) -> None:
         return  # the kernels run on the caller's stream; stream order is the dependency
 

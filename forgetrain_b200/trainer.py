@@ -122,10 +122,18 @@ class Trainer:
             mup_lr_scaling=cfg.mup_lr_scaling, norm_reduce=norm_reduce,
             comm_stream=self.reducer.comm_stream if cfg.opt_allgather_overlap else None,
             fused=self.fused_dp)
+        self.opt.set_schedule(cfg.max_lr, cfg.min_lr, cfg.warmup_iters, cfg.lr_decay_iters,
+                              cfg.wsd_decay_iters)
         self.num_samples = 0
         self.loss_buf = torch.zeros(1, dtype=torch.float32, device=dev)
         self.graph = None
-        if cfg.step_cuda_graph and dev.type == "cuda" and self.mtp is None:
+        self.full_graph = None
+        self._fwd_graph = None
+        if cfg.full_step_cuda_graph and dev.type == "cuda" and topo.world == 1:
+            from .graph.step_graph import GraphedFullStep
+            self.full_graph = GraphedFullStep(self, cfg.step_cuda_graph_warmup)
+        elif (cfg.step_cuda_graph or cfg.full_step_cuda_graph) and dev.type == "cuda" \
+                and self.mtp is None:
             from .graph.step_graph import GraphedComputeStep
             self.graph = GraphedComputeStep(self.model, cfg.step_cuda_graph_warmup,
                                             cfg.step_cuda_graph_sanity, cfg.step_cuda_graph_tol)
@@ -136,6 +144,17 @@ class Trainer:
         if ps is not None and ps.is_norm and self.tp_ctx.sequence_parallel:
             self.tp_ctx.all_reduce_(self.store.grads[name])
         self.reducer.on_grad_ready(name)
+
+    @torch.no_grad()
+    def forward_logits(self, tokens: torch.Tensor, position_ids=None) -> torch.Tensor:
+        """Forward pass only (evaluation); replayed from a CUDA graph per input shape when
+        ``forward_cuda_graph`` is set."""
+        if self.cfg.forward_cuda_graph and tokens.is_cuda:
+            if self._fwd_graph is None:
+                from .graph.step_graph import GraphedForward
+                self._fwd_graph = GraphedForward(self.model)
+            return self._fwd_graph(tokens, position_ids)
+        return self.model.forward(tokens, position_ids)
 
     def current_lr(self) -> float:
         c = self.cfg
@@ -162,8 +181,21 @@ class Trainer:
     def train_step(self, micro_batches: list[dict], profiler: StepProfiler | None = None) -> dict:
         """One optimizer step over ``micro_batches`` (device tensors). Returns device-side
         ``loss`` (mean over micro-batches and DP ranks) and ``grad_norm`` plus the ``lr`` used."""
+        lr = self.current_lr()
+        self.opt.prepare_host(lr)
+        for batch in micro_batches:
+            self.num_samples += batch["tokens"].shape[0] * self.topo.dp_size
+        if self.full_graph is not None and profiler is None:
+            self.full_graph(micro_batches)
+        else:
+            self._device_step(micro_batches, profiler)
+        return {"loss": self.loss_buf, "grad_norm": self.opt.grad_norm, "lr": lr}
+
+    def _device_step(self, micro_batches: list[dict], prof: StepProfiler | None = None) -> None:
+        """Everything of a step that runs on the device: micro-batches, bucket reductions,
+        gradient norm and clip coefficient, AdamW, parameter all-gather, loss average. With one
+        process (or device-side collectives) it issues no host synchronisation."""
         n = len(micro_batches)
-        prof = profiler
         if prof:
             prof.mark("step_start")
         self.opt.wait_all_gathers()
@@ -172,7 +204,6 @@ class Trainer:
         for i, batch in enumerate(micro_batches):
             loss = self._micro_batch(batch, 1.0 / n, accumulate=i > 0, last=(i == n - 1))
             self.loss_buf += loss.detach().reshape(1) / n
-            self.num_samples += batch["tokens"].shape[0] * self.topo.dp_size
         if prof:
             prof.mark("microbatches")
         self.reducer.wait_all()
@@ -181,8 +212,7 @@ class Trainer:
         self.opt.compute_clip(self.reducer.local_sumsq())
         if prof:
             prof.mark("grad_norm")
-        lr = self.current_lr()
-        self.opt.step(lr)
+        self.opt.apply()
         if prof:
             prof.mark("optimizer")
         if self.topo.dp_size > 1:
@@ -193,7 +223,6 @@ class Trainer:
             self.loss_buf /= self.topo.dp_size
         if prof:
             prof.mark("loss_allreduce")
-        return {"loss": self.loss_buf, "grad_norm": self.opt.grad_norm, "lr": lr}
 
     # ------------------------------------------------------------------ checkpoint
     def save(self, save_dir, step: int, dataloader_state=None, async_io=True):

@@ -100,3 +100,34 @@ def test_cuda_graph_step_matches_eager():
             assert tr.graph.replays == 8 and len(tr.graph._graphs) == 2
     assert out[True] == pytest.approx(out[False], rel=2e-3)
     assert out[True][-1] < out[True][0]
+
+
+def test_full_step_graph_matches_eager_and_forward_graph():
+    """Whole optimizer step (two micro-batches + norm + clip + AdamW) replayed from one CUDA
+    graph tracks the eager run step for step, including the learning-rate schedule the host
+    stages per step; the forward-only graph returns the eager logits."""
+    from forgetrain_b200.engine_config import from_spec
+    from forgetrain_b200.parallel.topology import Topology
+    from forgetrain_b200.trainer import Trainer
+    spec = _spec()
+    tok, lab = _batch(spec)
+    batch = {"tokens": tok.cuda(), "labels": lab.cuda(), "loss_mask": torch.ones(2, 256, device="cuda")}
+    out, norms = {}, {}
+    for graph in (False, True):
+        cfg = from_spec(spec, dtype="bf16", comm="nccl", warmup_iters=4, max_lr=2e-3,
+                        full_step_cuda_graph=graph, step_cuda_graph_warmup=2,
+                        forward_cuda_graph=graph)
+        tr = Trainer(spec, cfg, Topology(device=torch.device("cuda", 0)), seq_length=256,
+                     micro_batch_size=2, seed=0)
+        res = [tr.train_step([batch, batch]) for _ in range(6)]
+        out[graph] = [float(r["loss"]) for r in res[-1:]] + [float(tr.train_step([batch, batch])["loss"])]
+        norms[graph] = float(tr.opt.grad_norm)
+        if graph:
+            assert tr.full_graph.replays == 5 and len(tr.full_graph._graphs) == 1
+            assert tr.opt.step_count == 7
+        a = tr.forward_logits(batch["tokens"]).float().clone()
+        b = tr.forward_logits(batch["tokens"]).float().clone()
+        assert torch.equal(a, b)
+        assert (a - tr.model.forward(batch["tokens"]).float()).abs().max() == 0
+    assert out[True] == pytest.approx(out[False], rel=5e-3)
+    assert norms[True] == pytest.approx(norms[False], rel=5e-2)

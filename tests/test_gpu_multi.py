@@ -103,6 +103,31 @@ def _collectives(rank, world, use_multimem):
     torch.cuda.synchronize()
     want = torch.cat([torch.full((n // world,), float(r + 1)) for r in range(world)]).cuda()
     out["ag_err"] = float((symm.params[:n].float() - want).abs().max())
+    # AdamW fused with the all-gather: every rank ends up with every rank's updated shard
+    from forgetrain_b200.ops import reference as R
+    ns = n // world
+    gen = torch.Generator(device="cuda").manual_seed(500 + rank)
+    p32 = torch.randn(ns, device="cuda", generator=gen)
+    gsh = torch.randn(ns, device="cuda", generator=gen)
+    m, vv = torch.zeros(ns, device="cuda"), torch.zeros(ns, device="cuda")
+    rp, rm, rv = p32.clone(), m.clone(), vv.clone()
+    hyper = torch.tensor([1e-2, 0.9, 0.95, 1e-8, 1 - 0.9, 1 - 0.95, 0.5, 0], device="cuda")
+    half = (ns // 2) // 8 * 8 + 3          # segment boundary inside a vector of eight
+    se = torch.tensor([half, ns], device="cuda", dtype=torch.int64)
+    sw = torch.tensor([0.1, 0.0], device="cuda")
+    sl = torch.tensor([1.0, 0.25], device="cuda")
+    symm.params.zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
+    comm.adamw_all_gather(b, p32, m, vv, gsh, hyper, se, sw, sl)
+    torch.cuda.synchronize()
+    exp = torch.empty(ns, device="cuda", dtype=torch.bfloat16)
+    R.adamw_step(rp[:half], rm[:half], rv[:half], gsh[:half], exp[:half], 1e-2, 0.9, 0.95, 1e-8, 0.1, 1, 0.5)
+    R.adamw_step(rp[half:], rm[half:], rv[half:], gsh[half:], exp[half:], 0.25e-2, 0.9, 0.95, 1e-8, 0.0, 1, 0.5)
+    allexp = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    dist.all_gather_into_tensor(allexp, exp)
+    out["adam_ag_err"] = float((symm.params[:n].float() - allexp.float()).abs().max())
+    out["adam_master_err"] = float((p32 - rp).abs().max())
     v = torch.tensor([1.0 + rank, 10.0], device="cuda")
     comm.all_reduce_small(v)
     comm.all_reduce_small(v)
@@ -121,6 +146,7 @@ def test_fused_collectives_match_nccl(use_multimem):
         assert o["rs_err0"] < 1e-6 and o["rs_err1"] < 1e-6, o
         assert o["ss_err0"] < 1e-4 and o["guard0"] == 0.0 and o["guard1"] == 0.0, o
         assert o["ag_err"] == 0.0, o
+        assert o["adam_ag_err"] <= 1e-2 and o["adam_master_err"] < 1e-5, o
         # two chained all-reduces over 2 ranks: (1+2)*2 = 6 and 10*2*2 = 40
         assert o["small"] == [6.0, 40.0], o
 
