@@ -4,13 +4,15 @@
 //   1. preprocess : delta[b,h,s] = sum_d out*dout, lse2 = lse * log2(e)
 //   2. main       : one CTA per (kv tile of 128 rows, batch, kv group, chunk of query heads);
 //                   it keeps K_j and V_j resident in shared memory and walks the query tiles
-//                   i >= j of its heads. Per step, with everything transposed so that one
-//                   thread owns one kv row:
-//                     S^T = K Q^T, dP^T = V dO^T                      (tcgen05 -> TMEM)
-//                     P^T = exp2(S^T*c - lse2), dS^T = P^T*(dP^T - delta)   (softmax warpgroup)
+//                   i >= j of its heads. Per step, with one softmax thread per QUERY row (its
+//                   lse2 and delta are then two scalars, not a vector re-read per element):
+//                     S = Q K^T, dP = dO V^T                          (tcgen05 -> TMEM)
+//                     P = exp2(S*c - lse2), dS = P*(dP - delta)       (softmax warpgroups)
 //                     dV += P^T dO, dK += dS^T Q, dQ = dS K           (tcgen05 -> TMEM)
-//                   The same shared-memory tiles serve as K-major operands of the first two
-//                   products and as MN-major operands of the last three, so nothing is
+//                   P and dS are stored once, as [query][kv] tiles; the transposed products
+//                   read them as MN-major A operands and dQ reads dS as a K-major one, and the
+//                   Q / dO / K tiles likewise serve as K-major operands of the first two
+//                   products and as MN-major B operands of the last three, so nothing is
 //                   transposed or copied. dQ tiles (every step) and dK/dV (once per CTA) are
 //                   reduced into an fp32 accumulator laid out like the qkv buffer with vector
 //                   reductions (red.global.add.v4.f32).
@@ -18,6 +20,8 @@
 //
 // Replaces the reference's three-kernel Hopper backward
 // (ops/attention/flash_attn_dsl/flash_bwd.py:243-3373).
+#include <stdlib.h>
+
 #include "ptx.cuh"
 #include "tma_host.h"
 
@@ -39,14 +43,16 @@ struct FaBwdParams {
   int* status;
 };
 
+__device__ __forceinline__ void red_add_v2(float* addr, float a, float b) {
+  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
+}
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b),
                "f"(c), "f"(d)
                : "memory");
 }
 
-// QS: Q/dO stages, NP: P^T buffers in shared memory (0: P^T is kept in TMEM as packed bf16 and
-// feeds the dV product as a TMEM operand), NDS: dS^T buffers, NST: (lse2, delta) buffers
+// QS: Q/dO stages, NP: P buffers in shared memory, NDS: dS buffers, NST: (lse2, delta) buffers
 template <int D, int QS, int NP, int NDS, int NST>
 struct FaBwdSmem {
   static constexpr int TILE = FAB_BLK * D * 2;
@@ -83,6 +89,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   uint64_t* dq_full = bars + 16;     // 1
   uint64_t* dq_drained = bars + 17;  // 1 (count 128)
   uint64_t* dkv_full = bars + 18;    // 1
+  uint64_t* sdp_free = bars + 19;    // 1 (count 256): S^T / dP^T of a step are in registers
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -116,8 +123,9 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
     }
     mbar_init(sdp_full, 1);
     mbar_init(dq_full, 1);
-    mbar_init(dq_drained, 128);
+    mbar_init(dq_drained, ALIAS ? 384 : 128);
     mbar_init(dkv_full, 1);
+    mbar_init(sdp_free, 256);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tm_qkv);
@@ -136,9 +144,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   const uint32_t tm_dV = tmem_base + 256;
   const uint32_t tm_dK = tmem_base + 256 + D;
   const uint32_t tm_dQ = ALIAS ? tmem_base : tmem_base + 256 + 2 * D;
-  constexpr bool P_TMEM = (NP == 0);
-  constexpr int NPB = P_TMEM ? 1 : NP;           // ring length of the P^T hand-over barriers
-  const uint32_t tm_Pt = tmem_base + 448;        // 64 columns of packed bf16 (P_TMEM only)
+  static_assert(NP >= 1 && NDS >= 1, "P and dS are handed over through shared memory");
+  constexpr int NPB = NP;                        // ring length of the P hand-over barriers
 
   // step n -> (head, query tile)
   auto step_head = [&](int n) { return grp * p.g + hc * p.hpc + n / n_q; };
@@ -147,41 +154,50 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   if (warp < 4) {
   reg_dealloc<88>();
   if (warp == 0) {
-    if (lane == 0) {
-      // ---------------- producer ----------------
-      mbar_expect_tx(kv_full, 2 * L::TILE);
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        tma_load_2d(smem + L::K_OFF + c * 16384, &tm_qkv, kv_full, k_col + c * 64,
-                    row_base + j * FAB_BLK);
-        tma_load_2d(smem + L::V_OFF + c * 16384, &tm_qkv, kv_full, v_col + c * 64,
-                    row_base + j * FAB_BLK);
+    // ---------------- producer ----------------
+    // A thread that issues a TMA load is held for several hundred cycles per instruction, so
+    // the loads of a step (Q and dO boxes, lse2 and delta rows) are spread over lanes: one
+    // instruction issues them all.
+    constexpr int NBOX = D / 64;            // 64-column boxes per tile
+    constexpr int NL = 2 * NBOX + 2;
+    if (lane < NL) {
+      if (lane == 0) mbar_expect_tx(kv_full, 2 * L::TILE);
+      if (lane < 2 * NBOX) {
+        const int c = lane % NBOX;
+        if (lane < NBOX)
+          tma_load_2d(smem + L::K_OFF + c * 16384, &tm_qkv, kv_full, k_col + c * 64,
+                      row_base + j * FAB_BLK);
+        else
+          tma_load_2d(smem + L::V_OFF + c * 16384, &tm_qkv, kv_full, v_col + c * 64,
+                      row_base + j * FAB_BLK);
       }
       for (int n = 0; n < N; ++n) {
         const int s = n % QS;
         const int head = step_head(n), qt = step_qtile(n);
         const int q_col = (grp * (p.g + 2) + head % p.g) * D;
-        mbar_wait(&qdo_empty[s], ((n / QS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
-        mbar_expect_tx(&qdo_full[s], 2 * L::TILE + 1024);
+        mbar_wait_relaxed(&qdo_empty[s], ((n / QS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
+        if (lane == 0) mbar_expect_tx(&qdo_full[s], 2 * L::TILE + 1024);
         uint8_t* dst = smem + L::QDO_OFF + s * 2 * L::TILE;
-        {
-          const long soff = (static_cast<long>(b) * p.Hq + head) * p.S + qt * FAB_BLK;
-          if (n >= NST)   // the (lse2, delta) slot is free once the softmax of step n-NST is done
-            mbar_wait(&pds_ready[(n - NST) % NDS], ((n - NST) / NDS) & 1, abort_flag, p.status,
-                      FT_ERR_WAIT_MISC);
-          float* st = reinterpret_cast<float*>(smem + L::STAT_OFF + (n % NST) * 1024);
-          bulk_load_1d(st, p.lse2 + soff, 512, &qdo_full[s]);
-          bulk_load_1d(st + 128, p.delta + soff, 512, &qdo_full[s]);
-        }
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-          tma_load_2d(dst + c * 16384, &tm_qkv, &qdo_full[s], q_col + c * 64,
+        if (lane < NBOX) {
+          tma_load_2d(dst + lane * 16384, &tm_qkv, &qdo_full[s], q_col + lane * 64,
                       row_base + qt * FAB_BLK);
+        } else if (lane < 2 * NBOX) {
+          const int c = lane - NBOX;
           tma_load_2d(dst + L::TILE + c * 16384, &tm_do, &qdo_full[s], head * D + c * 64,
                       row_base + qt * FAB_BLK);
+        } else {
+          const long soff = (static_cast<long>(b) * p.Hq + head) * p.S + qt * FAB_BLK;
+          if (n >= NST)   // the (lse2, delta) slot is free once the softmax of step n-NST is done
+            mbar_wait_relaxed(&pds_ready[(n - NST) % NDS], ((n - NST) / NDS) & 1, abort_flag,
+                              p.status, FT_ERR_WAIT_MISC);
+          float* st = reinterpret_cast<float*>(smem + L::STAT_OFF + (n % NST) * 1024);
+          if (lane == 2 * NBOX)
+            bulk_load_1d(st, p.lse2 + soff, 512, &qdo_full[s]);
+          else
+            bulk_load_1d(st + 128, p.delta + soff, 512, &qdo_full[s]);
         }
       }
-      if (*abort_flag) {
+      if (lane == 0 && *abort_flag) {
         const uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
       }
@@ -190,76 +206,74 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
     if (lane == 0) {
       // ---------------- MMA issuer ----------------
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
-      const uint32_t idesc_dkv = make_idesc_bf16(128, D, 0, 1);
-      const uint32_t idesc_dq = make_idesc_bf16(128, D, 1, 1);
+      const uint32_t idesc_dkv = make_idesc_bf16(128, D, 1, 1);   // P^T / dS^T: MN-major A
+      const uint32_t idesc_dq = make_idesc_bf16(128, D, 0, 1);    // dS: K-major A
       const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
       const uint32_t sQDO = smem_u32(smem + L::QDO_OFF);
       const uint32_t sP = smem_u32(smem + L::P_OFF), sDS = smem_u32(smem + L::DS_OFF);
+      // Descriptor low words of the resident tiles; per-step tiles add their stage offset.
+      // K-major operand, reduction step kk (16 elements): +(kk/4)*16384 + (kk%4)*32 bytes;
+      // MN-major operand, reduction step kk (16 rows of 128 B): + kk*2048 bytes.
+      const uint32_t kK = smem_desc_lo(sK, 16), vK = smem_desc_lo(sV, 16);
+      const uint32_t kMN = smem_desc_lo(sK, 16384);
+      const uint32_t qK0 = smem_desc_lo(sQDO, 16), qMN0 = smem_desc_lo(sQDO, 16384);
+      const uint32_t pMN0 = smem_desc_lo(sP, 16384);
+      const uint32_t dsK0 = smem_desc_lo(sDS, 16), dsMN0 = smem_desc_lo(sDS, 16384);
+      constexpr uint32_t STG = (2 * L::TILE) >> 4, TL = L::TILE >> 4, BUF = 32768 >> 4;
+#define FT_KOFF(kk) ((((kk) / 4) * 16384 + ((kk) % 4) * 32) >> 4)
+#define FT_MNOFF(kk) (((kk) * 2048) >> 4)
       auto issue_sdp = [&](int n) {
         const int s = n % QS;
         mbar_wait(&qdo_full[s], (n / QS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
         tc_fence_after();
-        const uint32_t q = sQDO + s * 2 * L::TILE, dO = q + L::TILE;
+        const uint32_t qK = qK0 + s * STG, doK = qK + TL;
+        umma_ss_lo<0>(tm_St, qK, kK, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_ss(tm_St, make_smem_desc(sK + off, 16, 1024), make_smem_desc(q + off, 16, 1024),
-                  idesc_s, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 1; kk < D / 16; ++kk)
+          umma_ss_lo<1>(tm_St, qK + FT_KOFF(kk), kK + FT_KOFF(kk), idesc_s);
+        umma_ss_lo<0>(tm_dPt, doK, vK, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_ss(tm_dPt, make_smem_desc(sV + off, 16, 1024), make_smem_desc(dO + off, 16, 1024),
-                  idesc_s, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 1; kk < D / 16; ++kk)
+          umma_ss_lo<1>(tm_dPt, doK + FT_KOFF(kk), vK + FT_KOFF(kk), idesc_s);
         umma_commit(sdp_full);
       };
       mbar_wait(kv_full, 0, abort_flag, p.status, FT_ERR_WAIT_FULL);
       issue_sdp(0);
       for (int n = 0; n < N; ++n) {
         const int s = n % QS;
+        // S^T / dP^T of step n+1 go to the tensor pipe as soon as the softmax warpgroups hold
+        // step n's scores in registers, i.e. while they are still computing P^T / dS^T of
+        // step n: the next softmax then starts without waiting for these products.
+        if (!ALIAS && n + 1 < N) {
+          mbar_wait(sdp_free, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
+          tc_fence_after();
+          issue_sdp(n + 1);
+        }
         mbar_wait(&pds_ready[n % NDS], (n / NDS) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
         tc_fence_after();
-        // With the single P^T buffer in TMEM, dV(n) goes first: it frees P^T before the softmax
-        // of step n+1 (which needs S^T(n+1), issued right behind it) wants to write it.
-        if (!ALIAS && !P_TMEM && n + 1 < N) issue_sdp(n + 1);
-        const uint32_t q = sQDO + s * 2 * L::TILE, dO = q + L::TILE;
-        const uint32_t dsT = sDS + (n % NDS) * 32768;
-        if (P_TMEM) {
+        const uint32_t qMN = qMN0 + s * STG, doMN = qMN + TL;
+        const uint32_t dsK = dsK0 + (n % NDS) * BUF, dsMN = dsMN0 + (n % NDS) * BUF;
+        const uint32_t acc0 = n > 0 ? 1u : 0u;
+        const uint32_t pMN = pMN0 + (n % NPB) * BUF;
+        umma_ss_lo_dyn(tm_dV, pMN, doMN, idesc_dkv, acc0);
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)   // 16 bf16 of the reduction index = 8 TMEM columns
-            umma_ts(tm_dV, tm_Pt + kk * 8, make_smem_desc(dO + kk * 2048, 16384, 1024), idesc_dkv,
-                    (n > 0 || kk > 0) ? 1u : 0u);
-        } else {
-          const uint32_t pT = sP + (n % NPB) * 32768;
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t aoff = (kk / 4) * 16384 + (kk % 4) * 32;
-            umma_ss(tm_dV, make_smem_desc(pT + aoff, 16, 1024),
-                    make_smem_desc(dO + kk * 2048, 16384, 1024), idesc_dkv,
-                    (n > 0 || kk > 0) ? 1u : 0u);
-          }
-        }
+        for (int kk = 1; kk < 8; ++kk)
+          umma_ss_lo<1>(tm_dV, pMN + FT_MNOFF(kk), doMN + FT_MNOFF(kk), idesc_dkv);
         umma_commit(&p_free[n % NPB]);
-        if (!ALIAS && P_TMEM && n + 1 < N) issue_sdp(n + 1);
+        umma_ss_lo_dyn(tm_dK, dsMN, qMN, idesc_dkv, acc0);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t aoff = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_ss(tm_dK, make_smem_desc(dsT + aoff, 16, 1024),
-                  make_smem_desc(q + kk * 2048, 16384, 1024), idesc_dkv,
-                  (n > 0 || kk > 0) ? 1u : 0u);
-        }
+        for (int kk = 1; kk < 8; ++kk)
+          umma_ss_lo<1>(tm_dK, dsMN + FT_MNOFF(kk), qMN + FT_MNOFF(kk), idesc_dkv);
         // Q_n / dO_n are last read by dK / dV: hand the stage back to the producer now
         umma_commit(&qdo_empty[s]);
         if (n > 0) {
           mbar_wait(dq_drained, (n - 1) & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
           tc_fence_after();
         }
+        umma_ss_lo<0>(tm_dQ, dsK, kMN, idesc_dq);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          umma_ss(tm_dQ, make_smem_desc(dsT + kk * 2048, 16384, 1024),
-                  make_smem_desc(sK + kk * 2048, 16384, 1024), idesc_dq, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 1; kk < 8; ++kk)
+          umma_ss_lo<1>(tm_dQ, dsK + FT_KOFF(kk), kMN + FT_MNOFF(kk), idesc_dq);
         umma_commit(dq_full);
         umma_commit(&ds_free[n % NDS]);
         if (ALIAS && n + 1 < N) {
@@ -268,12 +282,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
           issue_sdp(n + 1);
         }
       }
+#undef FT_KOFF
+#undef FT_MNOFF
       umma_commit(dkv_full);
     }
   }
   } else if (warp < 12) {
     reg_alloc<176>();
-    // ---------------- two softmax warpgroups: thread owns kv row r and 64 of the 128 query
+    // ---------------- two softmax warpgroups: thread owns query row r and 64 of the 128 kv
     // columns (warpgroup 1: columns 0-63, warpgroup 2: columns 64-127) ----------------
     const int half = (warp - 4) >> 2;
     const int r = (threadIdx.x - 128) & 127;
@@ -281,11 +297,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
     const uint64_t sl2x2 = pack_f32x2(p.scale_log2, p.scale_log2);
     for (int n = 0; n < N; ++n) {
       const int qt = step_qtile(n);
-      const float* lse2 = reinterpret_cast<const float*>(smem + L::STAT_OFF + (n % NST) * 1024) + half * 64;
-      const float* dlt = lse2 + 128;
-      uint8_t* rowp = smem + L::P_OFF + (n % NPB) * 32768 + half * 16384 + r * 128;   // P^T row
-      uint8_t* rowd = smem + L::DS_OFF + (n % NDS) * 32768 + half * 16384 + r * 128;  // dS^T row
+      const float* stat = reinterpret_cast<const float*>(smem + L::STAT_OFF + (n % NST) * 1024);
+      uint8_t* rowp = smem + L::P_OFF + (n % NPB) * 32768 + half * 16384 + r * 128;   // P row
+      uint8_t* rowd = smem + L::DS_OFF + (n % NDS) * 32768 + half * 16384 + r * 128;  // dS row
       mbar_wait(&qdo_full[n % QS], (n / QS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
+      const float nl = -stat[r], nd = -stat[128 + r];
+      const uint64_t nl2 = pack_f32x2(nl, nl), nd2 = pack_f32x2(nd, nd);
       mbar_wait(sdp_full, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
       alignas(8) uint32_t s[64];
@@ -295,58 +312,71 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       tmem_ld32(tm_dPt + lane_off + half * 64, dp);
       tmem_ld32(tm_dPt + lane_off + half * 64 + 32, dp + 32);
       tmem_ld_wait();
-      // the buffers written below were last read by dV (P^T) and by dK / dQ (dS^T)
-      mbar_wait(&p_free[n % NPB], ((n / NPB) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
-      tc_fence_after();
-      uint32_t pt[32];   // this thread's 64 P values as packed bf16 (P_TMEM)
-      mbar_wait(&ds_free[n % NDS], ((n / NDS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
-      if (qt == j) {  // diagonal tile: query column < kv row is masked
+      tc_fence_before();
+      mbar_arrive(sdp_free);
+      if (qt == j) {  // diagonal tile: kv column > query row is masked
 #pragma unroll
         for (int k = 0; k < 64; ++k)
-          if (half * 64 + k < r) s[k] = 0xff800000u;  // -inf -> p = 0
+          if (half * 64 + k > r) s[k] = 0xff800000u;  // -inf -> p = 0
       }
       // Staged over the whole 64-column slice so that every stage is 32-64 independent
       // instructions (the per-element chain fma -> ex2 -> mul -> cvt is long and serial).
       uint64_t* s2 = reinterpret_cast<uint64_t*>(s);    // pairs of scores / probabilities
       uint64_t* d2 = reinterpret_cast<uint64_t*>(dp);   // pairs of dP / dS
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {                    // t = s * scale - lse2 ; dd = dP - delta
-        const float4 l4 = reinterpret_cast<const float4*>(lse2)[i];
-        const float4 e4 = reinterpret_cast<const float4*>(dlt)[i];
-        s2[2 * i] = fma_f32x2(s2[2 * i], sl2x2, pack_f32x2(-l4.x, -l4.y));
-        s2[2 * i + 1] = fma_f32x2(s2[2 * i + 1], sl2x2, pack_f32x2(-l4.z, -l4.w));
-        d2[2 * i] = add_f32x2(d2[2 * i], pack_f32x2(-e4.x, -e4.y));
-        d2[2 * i + 1] = add_f32x2(d2[2 * i + 1], pack_f32x2(-e4.z, -e4.w));
+      for (int i = 0; i < 32; ++i) {                    // t = s * scale - lse2 ; dd = dP - delta
+        s2[i] = fma_f32x2(s2[i], sl2x2, nl2);
+        d2[i] = add_f32x2(d2[i], nd2);
       }
 #pragma unroll
       for (int k = 0; k < 64; ++k) s[k] = __float_as_uint(fast_exp2(__uint_as_float(s[k])));
 #pragma unroll
       for (int i = 0; i < 32; ++i) d2[i] = mul_f32x2(s2[i], d2[i]);   // dS = P * (dP - delta)
+      // the buffers written below were last read by dV (P) and by dK / dQ (dS)
+      mbar_wait(&p_free[n % NPB], ((n / NPB) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+      mbar_wait(&ds_free[n % NDS], ((n / NDS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         uint32_t pk[4], dk[4];
 #pragma unroll
         for (int q2 = 0; q2 < 4; ++q2) {
           const int k = c * 8 + q2 * 2;
-          pk[q2] = pack_bf16x2(__uint_as_float(s[k]), __uint_as_float(s[k + 1]));
-          dk[q2] = pack_bf16x2(__uint_as_float(dp[k]), __uint_as_float(dp[k + 1]));
+          pk[q2] = pack_bf16x2_int(__uint_as_float(s[k]), __uint_as_float(s[k + 1]));
+          dk[q2] = pack_bf16x2_int(__uint_as_float(dp[k]), __uint_as_float(dp[k + 1]));
         }
         const int chunk = (c ^ (r & 7)) << 4;
-        if (P_TMEM) {
-#pragma unroll
-          for (int q2 = 0; q2 < 4; ++q2) pt[c * 4 + q2] = pk[q2];
-        } else {
-          *reinterpret_cast<uint4*>(rowp + chunk) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-        }
+        *reinterpret_cast<uint4*>(rowp + chunk) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         *reinterpret_cast<uint4*>(rowd + chunk) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
-      }
-      if (P_TMEM) {
-        tmem_st32(tm_Pt + lane_off + half * 32, pt);
-        tmem_st_wait();
       }
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(&pds_ready[n % NDS]);
+      if (ALIAS) {
+        // head_dim 128: dQ lives in the columns of S, so the next S / dP cannot be issued (and
+        // these warpgroups have nothing to do) until dQ of this step is drained: take the upper
+        // half of its columns, one 32-column chunk per warpgroup.
+        const int head = step_head(n);
+        const int q_col = (grp * (p.g + 2) + head % p.g) * D;
+        float* acc_tile = p.acc + static_cast<long>(row_base + qt * FAB_BLK + (warp & 3) * 32) * p.ld_acc + q_col;
+        mbar_wait(dq_full, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
+        tc_fence_after();
+        const int c = D / 64 + half;   // 32-column chunk
+#pragma unroll 1
+        for (int hrow = 0; hrow < 2; ++hrow) {
+          uint32_t o[16];
+          tmem_ld_16x256b_x4(tm_dQ + lane_off + (static_cast<uint32_t>(hrow * 16) << 16) + c * 32, o);
+          tmem_ld_wait();
+          float* a0 = acc_tile + static_cast<long>(hrow * 16 + (lane >> 2)) * p.ld_acc + c * 32 + 2 * (lane & 3);
+          float* a1 = a0 + 8L * p.ld_acc;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            red_add_v2(a0 + 8 * i, __uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]));
+            red_add_v2(a1 + 8 * i, __uint_as_float(o[4 * i + 2]), __uint_as_float(o[4 * i + 3]));
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(dq_drained);
+      }
     }
   } else {
     reg_dealloc<72>();
@@ -358,23 +388,31 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       const int head = step_head(n), qt = step_qtile(n);
       const int q_col = (grp * (p.g + 2) + head % p.g) * D;
       float* acc_row = p.acc + static_cast<long>(row_base + qt * FAB_BLK + r) * p.ld_acc + q_col;
-      mbar_wait(dq_full, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
+      mbar_wait_relaxed(dq_full, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
+      // 16 x 256-bit loads: four lanes hold one aligned 32-byte piece of a row, so every
+      // reduction instruction of the warp updates whole sectors.
+      float* acc_tile = p.acc + static_cast<long>(row_base + qt * FAB_BLK + (warp & 3) * 32) * p.ld_acc + q_col;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t o[32];
-        tmem_ld32(tm_dQ + lane_off + c * 32, o);
-        tmem_ld_wait();
+      for (int c = 0; c < (ALIAS ? D / 128 : D / 64); ++c) {
+#pragma unroll 1
+        for (int hrow = 0; hrow < 2; ++hrow) {
+          uint32_t o[32];
+          tmem_ld_16x256b_x8(tm_dQ + lane_off + (static_cast<uint32_t>(hrow * 16) << 16) + c * 64, o);
+          tmem_ld_wait();
+          float* a0 = acc_tile + static_cast<long>(hrow * 16 + (lane >> 2)) * p.ld_acc + c * 64 + 2 * (lane & 3);
+          float* a1 = a0 + 8L * p.ld_acc;
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          red_add_v4(acc_row + c * 32 + 4 * k, __uint_as_float(o[4 * k]),
-                     __uint_as_float(o[4 * k + 1]), __uint_as_float(o[4 * k + 2]),
-                     __uint_as_float(o[4 * k + 3]));
+          for (int i = 0; i < 8; ++i) {
+            red_add_v2(a0 + 8 * i, __uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]));
+            red_add_v2(a1 + 8 * i, __uint_as_float(o[4 * i + 2]), __uint_as_float(o[4 * i + 3]));
+          }
+        }
       }
       tc_fence_before();
       mbar_arrive(dq_drained);
     }
-    mbar_wait(dkv_full, 0, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
+    mbar_wait_relaxed(dkv_full, 0, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL, 256);
     tc_fence_after();
     float* acc_row = p.acc + static_cast<long>(row_base + j * FAB_BLK + r) * p.ld_acc;
 #pragma unroll 1
@@ -524,7 +562,7 @@ extern "C" int ft_attn_bwd(const void* dout, const void* qkv, const void* out, c
   p.scale_log2 = scale * 1.4426950408889634f;
   p.lse2 = d_lse2; p.delta = d_delta; p.acc = static_cast<float*>(acc);
   p.status = status;
-  int rc = (D == 64) ? launch_fa_bwd<64, 2, 2, 2, 2>(tq, tdo, p, st)
+  int rc = (D == 64) ? launch_fa_bwd<64, 3, 1, 2, 2>(tq, tdo, p, st)
                      : launch_fa_bwd<128, 1, 1, 1, 1>(tq, tdo, p, st);
   if (rc) return rc;
   {
