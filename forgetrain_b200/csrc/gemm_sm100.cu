@@ -601,13 +601,15 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB,
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
-// Process-wide default for the tile shape when the caller passes bn = 0: 1 selects the
-// CTA-pair kernel wherever it applies. FT_GEMM_PAIR=0 in the environment turns it off.
+// Process-wide default for the tile shape when the caller passes bn = 0. The CTA-pair kernel is
+// opt-in (FT_GEMM_PAIR=1): it is correct and faster when it has the GPU to itself, but stopped
+// making progress in a test that runs it next to library GEMMs, copies and small kernels from
+// other streams of the same process, and the cause has not been found.
 static int pair_default() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("FT_GEMM_PAIR");
-    v = (e && e[0] == '0') ? 0 : 1;
+    v = (e && e[0] == '1') ? 1 : 0;
   }
   return v;
 }

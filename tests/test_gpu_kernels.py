@@ -45,11 +45,10 @@ def test_gemm_fwd_dgrad_wgrad(T, N, K):
     assert rel(dw1, ref) < 1e-3 and rel(dw4, ref) < 1e-3
 
 
-@pytest.mark.parametrize("bn", [128, 256, 512])
+@pytest.mark.parametrize("bn", [128, 256])
 @pytest.mark.parametrize("T,N,K", [(256, 256, 64), (640, 1280, 320), (1000, 1032, 1024), (2048, 4096, 512)])
 def test_gemm_tile_shapes(T, N, K, bn):
-    """Every tile shape (one CTA per 128 x 128 / 128 x 256 tile, a CTA pair per 256 x 256 tile)
-    against fp32 matmul, for all three operand-major combinations and the reduce-add epilogue."""
+    """Both single-CTA tile shapes (128 x 128, 128 x 256) against fp32 matmul, for all three operand-major combinations and the reduce-add epilogue."""
     x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
     w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
     dy = torch.randn(T, N, device="cuda").to(torch.bfloat16)

@@ -26,7 +26,7 @@ def bf(*shape, scale=1.0):
     return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
 
 
-@pytest.mark.parametrize("bn", [256, 512])
+@pytest.mark.parametrize("bn", [128, 256])
 def test_gemm_against_cpp(bn):
     x, w, dy = bf(384, 192), bf(320, 192, scale=0.05), bf(384, 320)
     assert rel(gemm.linear_fwd(x, w, alpha=0.5, bn=bn), C.linear_fwd(x, w, 0.5)) < 0.01
