@@ -24,6 +24,9 @@ int get_tmap_2d(CUtensorMap* out, const void* base, int elt, uint64_t rows, uint
 
 constexpr int FA_THREADS = 384;
 constexpr int FA_BLK = 128;
+#ifndef FA_POLY
+#define FA_POLY 1   // pairs out of every 4 whose 2^x is evaluated by polynomial
+#endif
 
 struct FaFwdParams {
   int S, Hq, g, n_groups, batch;
@@ -60,7 +63,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   uint64_t* s_full = bars + 9;        // 2
   uint64_t* p_ready = bars + 11;      // 2
   uint64_t* o_done = bars + 13;       // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* s_free = bars + 15;       // 2 (count 128): the score row of a step is in registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -90,6 +94,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       mbar_init(&s_full[s], 1);
       mbar_init(&p_ready[s], 128);
       mbar_init(&o_done[s], 1);
+      mbar_init(&s_free[s], 128);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -110,30 +115,36 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   if (warp < 4) {
   reg_dealloc<96>();   // TMA / MMA warps need few registers, the softmax warps a whole score row
   if (warp == 0) {
-    if (lane == 0) {
-      // ---------------- producer ----------------
-      mbar_expect_tx(q_full, 2 * L::TILE);
-      for (int w = 0; w < 2; ++w)
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c)
-          tma_load_2d(smem + L::Q_OFF + w * L::TILE + c * 16384, &tm_qkv, q_full, q_col + c * 64,
-                      row_base + (2 * pair + w) * FA_BLK);
+    // ---------------- producer: lanes [0, NBOX) load K, lanes [NBOX, 2 NBOX) load V, one
+    // 64-column box each (a thread that issues a TMA load is held for several hundred cycles
+    // per instruction, so the boxes of a step go out from different lanes) ----------------
+    constexpr int NBOX = D / 64;
+    if (lane < 2 * NBOX) {
+      const int c = lane % NBOX;
+      const bool is_v = lane >= NBOX;
+      if (lane == 0) mbar_expect_tx(q_full, 2 * L::TILE);
+      // Q tiles: 2 * NBOX boxes, one per lane
+      {
+        const int w = lane / NBOX;
+        tma_load_2d(smem + L::Q_OFF + w * L::TILE + c * 16384, &tm_qkv, q_full, q_col + c * 64,
+                    row_base + (2 * pair + w) * FA_BLK);
+      }
       for (int j = 0; j < n_total; ++j) {
-        const int ks = j % KS, vs = j % VS;
-        mbar_wait(&k_empty[ks], ((j / KS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
-        mbar_expect_tx(&k_full[ks], L::TILE);
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c)
+        if (!is_v) {
+          const int ks = j % KS;
+          mbar_wait(&k_empty[ks], ((j / KS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
+          if (c == 0) mbar_expect_tx(&k_full[ks], L::TILE);
           tma_load_2d(smem + L::K_OFF + ks * L::TILE + c * 16384, &tm_qkv, &k_full[ks],
                       k_col + c * 64, row_base + j * FA_BLK);
-        mbar_wait(&v_empty[vs], ((j / VS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
-        mbar_expect_tx(&v_full[vs], L::TILE);
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c)
+        } else {
+          const int vs = j % VS;
+          mbar_wait(&v_empty[vs], ((j / VS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
+          if (c == 0) mbar_expect_tx(&v_full[vs], L::TILE);
           tma_load_2d(smem + L::V_OFF + vs * L::TILE + c * 16384, &tm_qkv, &v_full[vs],
                       v_col + c * 64, row_base + j * FA_BLK);
+        }
       }
-      if (*abort_flag) {
+      if (lane == 0 && *abort_flag) {
         const uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
       }
@@ -145,26 +156,26 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       const uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);
       const uint32_t sQ = smem_u32(smem + L::Q_OFF), sK = smem_u32(smem + L::K_OFF);
       const uint32_t sV = smem_u32(smem + L::V_OFF), sP = smem_u32(smem + L::P_OFF);
+      // descriptor low words: K-major step kk: +(kk/4)*16384 + (kk%4)*32 bytes; MN-major: + kk*2048
+      const uint32_t qK0 = smem_desc_lo(sQ, 16), kK0 = smem_desc_lo(sK, 16);
+      const uint32_t pK0 = smem_desc_lo(sP, 16), vMN0 = smem_desc_lo(sV, 16384);
+      constexpr uint32_t TL = L::TILE >> 4, PB = 32768 >> 4;
+#define FT_KOFF(kk) ((((kk) / 4) * 16384 + ((kk) % 4) * 32) >> 4)
+#define FT_MNOFF(kk) (((kk) * 2048) >> 4)
       auto issue_S = [&](int w, int j) {
-        const int ks = j % KS;
-        const uint32_t qa = sQ + w * L::TILE, ka = sK + ks * L::TILE;
+        const uint32_t qa = qK0 + w * TL, ka = kK0 + (j % KS) * TL;
+        umma_ss_lo<0>(tmem_S[w], qa, ka, idesc_s);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_ss(tmem_S[w], make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024),
-                  idesc_s, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 1; kk < D / 16; ++kk)
+          umma_ss_lo<1>(tmem_S[w], qa + FT_KOFF(kk), ka + FT_KOFF(kk), idesc_s);
         umma_commit(&s_full[w]);
       };
       auto issue_PV = [&](int w, int j) {
-        const int vs = j % VS;
-        const uint32_t pa = sP + w * 32768, va = sV + vs * L::TILE;
+        const uint32_t pa = pK0 + w * PB, va = vMN0 + (j % VS) * TL;
+        umma_ss_lo_dyn(tmem_O[w], pa, va, idesc_o, j > 0 ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t poff = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_ss(tmem_O[w], make_smem_desc(pa + poff, 16, 1024),
-                  make_smem_desc(va + kk * 2048, 16384, 1024), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-        }
+        for (int kk = 1; kk < 8; ++kk)
+          umma_ss_lo<1>(tmem_O[w], pa + FT_KOFF(kk), va + FT_MNOFF(kk), idesc_o);
         umma_commit(&o_done[w]);
       };
       mbar_wait(q_full, 0, abort_flag, p.status, FT_ERR_WAIT_FULL);
@@ -175,28 +186,34 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       umma_commit(&k_empty[0]);
       for (int j = 0; j < n_total; ++j) {
         const int vs = j % VS;
-        mbar_wait(&v_full[vs], (j / VS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
+        // S of step j+1 goes to the tensor pipe as soon as the softmax warpgroup holds the
+        // score row of step j in registers, i.e. while it is still exponentiating it.
         bool next_k_ready = false;
+        for (int w = 0; w < 2; ++w) {
+          if (j + 1 >= n_kv[w]) continue;
+          mbar_wait(&s_free[w], j & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
+          if (!next_k_ready) {
+            mbar_wait(&k_full[(j + 1) % KS], ((j + 1) / KS) & 1, abort_flag, p.status,
+                      FT_ERR_WAIT_FULL);
+            next_k_ready = true;
+          }
+          tc_fence_after();
+          issue_S(w, j + 1);
+          if (w == 1) umma_commit(&k_empty[(j + 1) % KS]);
+        }
+        mbar_wait(&v_full[vs], (j / VS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
         for (int w = 0; w < 2; ++w) {
           if (j >= n_kv[w]) continue;
           mbar_wait(&p_ready[w], j & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
           tc_fence_after();
           issue_PV(w, j);
           if (w == 1) umma_commit(&v_empty[vs]);
-          if (j + 1 < n_kv[w]) {
-            if (!next_k_ready) {
-              mbar_wait(&k_full[(j + 1) % KS], ((j + 1) / KS) & 1, abort_flag, p.status,
-                        FT_ERR_WAIT_FULL);
-              tc_fence_after();
-              next_k_ready = true;
-            }
-            issue_S(w, j + 1);
-            if (w == 1) umma_commit(&k_empty[(j + 1) % KS]);
-          }
         }
       }
     }
   }
+#undef FT_KOFF
+#undef FT_MNOFF
   } else {
     reg_alloc<200>();
     // ---------------- softmax warpgroups ----------------
@@ -220,6 +237,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       tmem_ld32(tmem_S[w] + lane_off + 64, s + 64);
       tmem_ld32(tmem_S[w] + lane_off + 96, s + 96);
       tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&s_free[w]);
       if (j == qt) {  // diagonal tile: columns beyond the row are masked
 #pragma unroll
         for (int k = 0; k < 128; ++k)
@@ -234,11 +253,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       const float mx = fmaxf(mx0, mx1);
       const float m_new = fmaxf(m_ref, mx * p.scale_log2);
       const bool need = (m_new - m_ref) > 8.0f;  // also true while m_ref is still -inf
-      if (j > 0) {
-        mbar_wait(&o_done[w], (j - 1) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
-        tc_fence_after();
-      }
+      bool o_waited = false;
       if (__any_sync(0xffffffffu, need)) {
+        if (j > 0) {   // the rescale touches O: the previous P V product must have landed
+          mbar_wait(&o_done[w], (j - 1) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+          tc_fence_after();
+          o_waited = true;
+        }
         const float alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
         m_ref = m_new;
         lsum2 = mul_f32x2(lsum2, pack_f32x2(alpha, alpha));
@@ -260,8 +281,17 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       uint64_t* s2 = reinterpret_cast<uint64_t*>(s);
 #pragma unroll
       for (int i = 0; i < 64; ++i) s2[i] = fma_f32x2(s2[i], sl2x2, negm2);
+      // FA_POLY of every 4 pairs take the polynomial path: the transcendental unit is the
+      // scarce pipe of this loop (8 cycles per warp instruction), the FMA pipe has room.
 #pragma unroll
-      for (int k = 0; k < 128; ++k) s[k] = __float_as_uint(fast_exp2(__uint_as_float(s[k])));
+      for (int i = 0; i < 64; ++i) {
+        if ((i & 3) < FA_POLY) {
+          s2[i] = exp2_poly_f32x2(s2[i]);
+        } else {
+          s[2 * i] = __float_as_uint(fast_exp2(__uint_as_float(s[2 * i])));
+          s[2 * i + 1] = __float_as_uint(fast_exp2(__uint_as_float(s[2 * i + 1])));
+        }
+      }
       uint64_t acc0 = s2[0], acc1 = s2[1], acc2 = s2[2], acc3 = s2[3];
 #pragma unroll
       for (int i = 4; i < 64; i += 4) {
@@ -271,13 +301,17 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
         acc3 = add_f32x2(acc3, s2[i + 3]);
       }
       lsum2 = add_f32x2(lsum2, add_f32x2(add_f32x2(acc0, acc1), add_f32x2(acc2, acc3)));
+      if (j > 0 && !o_waited) {   // the P buffer is still read by the previous P V product
+        mbar_wait(&o_done[w], (j - 1) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+        tc_fence_after();
+      }
 #pragma unroll
       for (int c = 0; c < 16; ++c) {  // 16 chunks of 8 columns = one 16-byte store each
         uint4 u;
-        u.x = pack_bf16x2(__uint_as_float(s[c * 8 + 0]), __uint_as_float(s[c * 8 + 1]));
-        u.y = pack_bf16x2(__uint_as_float(s[c * 8 + 2]), __uint_as_float(s[c * 8 + 3]));
-        u.z = pack_bf16x2(__uint_as_float(s[c * 8 + 4]), __uint_as_float(s[c * 8 + 5]));
-        u.w = pack_bf16x2(__uint_as_float(s[c * 8 + 6]), __uint_as_float(s[c * 8 + 7]));
+        u.x = pack_bf16x2_int(__uint_as_float(s[c * 8 + 0]), __uint_as_float(s[c * 8 + 1]));
+        u.y = pack_bf16x2_int(__uint_as_float(s[c * 8 + 2]), __uint_as_float(s[c * 8 + 3]));
+        u.z = pack_bf16x2_int(__uint_as_float(s[c * 8 + 4]), __uint_as_float(s[c * 8 + 5]));
+        u.w = pack_bf16x2_int(__uint_as_float(s[c * 8 + 6]), __uint_as_float(s[c * 8 + 7]));
         uint8_t* rowp = sP + (c >> 3) * 16384 + r * 128;
         *reinterpret_cast<uint4*>(rowp + (((c & 7) ^ (r & 7)) << 4)) = u;
       }

@@ -148,6 +148,10 @@ __device__ __forceinline__ void reg_alloc() {
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+// Non-blocking arrival on a named barrier that other warps wait on with named_bar_sync.
+__device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 
 // ---------------------------------------------------------------------------------------
 // TMA (tiled). Loads complete on an mbarrier; stores / reduces use bulk groups.
@@ -511,6 +515,28 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// 2^t for a packed pair on the FMA / integer pipes instead of the transcendental unit:
+// clamp to -126, split t = j + f with j = rn(t) by the 1.5 * 2^23 trick (the integer j ends up
+// in the low mantissa bits), 2^f by a degree-3 polynomial on [-0.5, 0.5] (max relative error
+// 1.0e-4, below bf16 resolution), then j is added into the exponent field.
+__device__ __forceinline__ uint64_t exp2_poly_f32x2(uint64_t t2) {
+  float a, b;
+  unpack_f32x2(t2, a, b);
+  t2 = pack_f32x2(fmaxf(a, -126.f), fmaxf(b, -126.f));
+  const uint64_t tt = add_f32x2(t2, pack_f32x2(12582912.f, 12582912.f));
+  const uint64_t jf = add_f32x2(tt, pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t fr = fma_f32x2(jf, pack_f32x2(-1.f, -1.f), t2);
+  uint64_t p = fma_f32x2(pack_f32x2(0.05500871f, 0.05500871f), fr,
+                         pack_f32x2(0.24221068f, 0.24221068f));
+  p = fma_f32x2(p, fr, pack_f32x2(0.69328292f, 0.69328292f));
+  p = fma_f32x2(p, fr, pack_f32x2(1.f, 1.f));
+  float p0, p1, j0, j1;
+  unpack_f32x2(p, p0, p1);
+  unpack_f32x2(tt, j0, j1);
+  const uint32_t r0 = __float_as_uint(p0) + (__float_as_uint(j0) << 23);
+  const uint32_t r1 = __float_as_uint(p1) + (__float_as_uint(j1) << 23);
+  return pack_f32x2(__uint_as_float(r0), __uint_as_float(r1));
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
