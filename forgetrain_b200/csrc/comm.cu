@@ -26,6 +26,10 @@ struct CommPeers {
   void* buf[COMM_MAX_RANKS];         // peer base pointers of the data buffer
   uint32_t* flags[COMM_MAX_RANKS];   // peer base pointers of the flag arrays [slots][world]
   void* mc;                          // multicast mapping of the data buffer (nullptr: none)
+  // Per-slot epoch base in device memory (nullptr: none). The epoch a kernel signals / waits for
+  // is its launch argument plus this base, so a captured CUDA graph can be replayed: its
+  // launch arguments stay fixed while a kernel at the end of the graph advances the base.
+  const uint32_t* ebase;
   int rank, world;
 };
 
@@ -73,6 +77,7 @@ __device__ __forceinline__ void st_peer_b32x4(void* p, uint4 v) {
 // Signal `epoch` into slot [slot][rank] of every peer (threads 0..world-1 of the calling CTA).
 __device__ __forceinline__ void signal_peers(const CommPeers& c, int slot, uint32_t epoch) {
   if (threadIdx.x < c.world) {
+    if (c.ebase) epoch += c.ebase[slot];
     __threadfence_system();
     st_release_sys(c.flags[threadIdx.x] + slot * c.world + c.rank, epoch);
   }
@@ -86,6 +91,7 @@ __device__ __forceinline__ bool wait_peers(const CommPeers& c, int slot, uint32_
   if (threadIdx.x == 0) s_fail = 0;
   __syncthreads();
   if (threadIdx.x < c.world) {
+    if (c.ebase) epoch += c.ebase[slot];
     const uint32_t* f = c.flags[c.rank] + slot * c.world + threadIdx.x;
     const uint64_t t0 = globaltimer_ns();
     while (true) {
@@ -433,12 +439,46 @@ ce_stats_exchange_kernel(CommPeers c, long off, int T, const float* __restrict__
   }
 }
 
+// base[slot] += add[slot] for the eight flag slots; the last node of a captured step.
+__global__ void epoch_advance_kernel(uint32_t* base, uint32_t a0, uint32_t a1, uint32_t a2,
+                                     uint32_t a3, uint32_t a4, uint32_t a5, uint32_t a6,
+                                     uint32_t a7) {
+  const uint32_t add[8] = {a0, a1, a2, a3, a4, a5, a6, a7};
+  if (threadIdx.x < 8) base[threadIdx.x] += add[threadIdx.x];
+}
+
 }  // namespace ft
 
 using namespace ft;
 
+#include <mutex>
+#include <unordered_map>
+// epoch-base registry: this rank's flag array -> device array of 8 per-slot bases
+static std::mutex g_ebase_mu;
+static std::unordered_map<const void*, const uint32_t*> g_ebase;
+
+// Every later launch whose flag array (own rank's mapping) is `self_flags` adds ebase[slot] to
+// its epoch argument. ebase == nullptr removes the entry.
+extern "C" int ft_comm_set_epoch_base(const void* self_flags, const void* ebase) {
+  std::lock_guard<std::mutex> g(g_ebase_mu);
+  if (ebase) g_ebase[self_flags] = static_cast<const uint32_t*>(ebase);
+  else g_ebase.erase(self_flags);
+  return 0;
+}
+
+extern "C" int ft_comm_epoch_advance(void* ebase, const unsigned int* add8, cudaStream_t st) {
+  epoch_advance_kernel<<<1, 32, 0, st>>>(static_cast<uint32_t*>(ebase), add8[0], add8[1], add8[2],
+                                         add8[3], add8[4], add8[5], add8[6], add8[7]);
+  return cudaGetLastError() == cudaSuccess ? 0 : -100;
+}
+
 static void fill_peers(CommPeers& c, const void* const* bufs, const void* const* flags, void* mc,
                        int rank, int world) {
+  {
+    std::lock_guard<std::mutex> g(g_ebase_mu);
+    auto it = g_ebase.find(flags[rank]);
+    c.ebase = it == g_ebase.end() ? nullptr : it->second;
+  }
   for (int i = 0; i < COMM_MAX_RANKS; ++i) {
     c.buf[i] = i < world ? const_cast<void*>(bufs[i]) : nullptr;
     c.flags[i] = i < world ? static_cast<uint32_t*>(const_cast<void*>(flags[i])) : nullptr;

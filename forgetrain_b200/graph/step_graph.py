@@ -92,7 +92,11 @@ class GraphedFullStep:
 
     Plays the role of the reference's ``step_graph_full`` / ``step_graph_optimizer`` wrappers
     (exports/train_engine_0.5B/src/training_engine_tensor/step_graph_full.py:147-482,
-    step_graph_optimizer.py:112-272) for one process per GPU.
+    step_graph_nccl_opt.py:116-261, step_graph_optimizer.py:112-272). With data parallelism over
+    the peer-memory collectives (bucket reduce-scatter, fused AdamW + all-gather, small
+    all-reduces) those kernels are part of the graph: their barrier epochs are relative launch
+    arguments plus a device-side base that the last node of the graph advances, and every rank
+    replays the same graph in the same step.
     """
 
     def __init__(self, trainer, warmup: int = 3):
@@ -120,9 +124,14 @@ class GraphedFullStep:
             static = [{k: v.clone() for k, v in b.items() if torch.is_tensor(v)}
                       for b in micro_batches]
             torch.cuda.synchronize()
+            symm = getattr(tr, "symm", None)   # peer-memory collectives: epochs go device-side
+            if symm is not None:
+                symm.begin_capture()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 tr._device_step(static)
+                if symm is not None:
+                    symm.end_capture()
             e = {"graph": g, "static": static}
             self._graphs[key] = e
         for st, b in zip(e["static"], micro_batches):

@@ -67,11 +67,59 @@ class SymmetricBuffers:
         self.p_scratch = VP(*[int(p) for p in self.h_scratch.buffer_ptrs])
         self.done_ctr = torch.zeros(4, dtype=torch.int32, device=device)
         self.epoch = [0] * NUM_FLAG_SLOTS
+        # Device-side epoch base (see begin_capture): zero in eager mode, where the host passes
+        # absolute epochs; registered once so that every launch on these flags adds it.
+        self.epoch_base = torch.zeros(NUM_FLAG_SLOTS, dtype=torch.int32, device=device)
+        self._capturing = False
+        self._graph_mode = False
+        self._used = [0] * NUM_FLAG_SLOTS
+        _lib.lib().ft_comm_set_epoch_base(ctypes.c_void_p(int(self.h_flags.buffer_ptrs[rank])),
+                                          _lib.ptr(self.epoch_base))
         dist.barrier(group=group)
 
     def next_epoch(self, slot: int) -> int:
+        if self._capturing:
+            # relative numbering inside a captured step: the device base supplies the rest
+            self._used[slot] += 1
+            return self._used[slot]
+        if self._graph_mode:
+            raise RuntimeError("peer-memory collectives were captured in a CUDA graph; call "
+                               "resync_epochs() before launching them eagerly again")
         self.epoch[slot] = (self.epoch[slot] + 1) & 0x7FFFFFFF
         return self.epoch[slot]
+
+    def set_epoch(self, slot: int, value: int) -> None:
+        """Mirror ``value`` (the epoch another slot just took) into ``slot``."""
+        if self._capturing:
+            self._used[slot] = value
+        else:
+            self.epoch[slot] = value
+
+    # -- CUDA-graph support ---------------------------------------------------------------
+    def begin_capture(self) -> None:
+        """Call right before capturing a step that launches these collectives. From here on the
+        launch arguments are epochs relative to the device-side base, which is set to the epochs
+        used so far; :meth:`end_capture` (inside the capture) appends the kernel that advances
+        the base by what one replay consumes. Every rank must capture the same sequence."""
+        if self._graph_mode:
+            self.resync_epochs()
+        self.epoch_base.copy_(torch.tensor(self.epoch, dtype=torch.int32))
+        self._used = [0] * NUM_FLAG_SLOTS
+        self._capturing = True
+
+    def end_capture(self) -> None:
+        add = (ctypes.c_uint * NUM_FLAG_SLOTS)(*self._used)
+        rc = _lib.lib().ft_comm_epoch_advance(_lib.ptr(self.epoch_base), add, _lib.stream())
+        _lib.check_rc(rc, "ft_comm_epoch_advance")
+        self._capturing = False
+        self._graph_mode = True
+
+    def resync_epochs(self) -> None:
+        """Back to eager launches after graph replays: read the base back (synchronises)."""
+        base = self.epoch_base.cpu().tolist()
+        self.epoch = [int(b) & 0x7FFFFFFF for b in base]
+        self.epoch_base.zero_()
+        self._graph_mode = False
 
 
 class FusedDPComm:
@@ -89,7 +137,7 @@ class FusedDPComm:
     def reduce_scatter_bucket(self, b, sumsq: torch.Tensor, scale: float | None = None) -> None:
         s = self.s
         ep = s.next_epoch(0)
-        s.epoch[1] = ep
+        s.set_epoch(1, ep)
         rc = _lib.lib().ft_bucket_reduce_scatter(
             s.p_grads, s.p_flags, ctypes.c_void_p(s.mc_grads), ctypes.c_int(s.rank),
             ctypes.c_int(s.world), ctypes.c_long(b.start), ctypes.c_long(b.size // s.world),
@@ -134,7 +182,7 @@ class FusedDPComm:
         s = self.s
         assert vals.dtype == torch.float32 and vals.numel() <= 64
         ep = s.next_epoch(3)
-        s.epoch[4] = ep
+        s.set_epoch(4, ep)
         rc = _lib.lib().ft_small_all_reduce(
             s.p_scratch, s.p_flags, ctypes.c_int(s.rank), ctypes.c_int(s.world), ctypes.c_long(0),
             _lib.ptr(vals), ctypes.c_int(vals.numel()), ctypes.c_uint(ep),

@@ -129,7 +129,8 @@ class Trainer:
         self.graph = None
         self.full_graph = None
         self._fwd_graph = None
-        if cfg.full_step_cuda_graph and dev.type == "cuda" and topo.world == 1:
+        graphable_comm = topo.world == 1 or (self.fused_dp is not None and tp == 1)
+        if cfg.full_step_cuda_graph and dev.type == "cuda" and graphable_comm:
             from .graph.step_graph import GraphedFullStep
             self.full_graph = GraphedFullStep(self, cfg.step_cuda_graph_warmup)
         elif (cfg.step_cuda_graph or cfg.full_step_cuda_graph) and dev.type == "cuda" \

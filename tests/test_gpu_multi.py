@@ -188,7 +188,7 @@ def test_bounded_wait_reports_status_instead_of_hanging():
 
 
 # ------------------------------------------------------------------------------------------
-def _train(rank, world, comm):
+def _train(rank, world, comm, full_graph=False, steps=5):
     from forgetrain_b200.config import load_model_spec
     from forgetrain_b200.engine_config import from_spec
     from forgetrain_b200.ops import _lib
@@ -196,7 +196,8 @@ def _train(rank, world, comm):
     from forgetrain_b200.trainer import Trainer
     spec = load_model_spec("0.5b", num_layers=2, vocab_size=4096, seq_length=256, max_position_embeddings=256)
     cfg = from_spec(spec, dtype="bf16", comm=comm, warmup_iters=0, max_lr=2e-3,
-                    wgrad_bucket_target_elems=3_000_000)
+                    wgrad_bucket_target_elems=3_000_000, full_step_cuda_graph=full_graph,
+                    step_cuda_graph_warmup=2)
     topo = init_topology(1)
     tr = Trainer(spec, cfg, topo, seq_length=256, micro_batch_size=2, seed=0)
     g = torch.Generator().manual_seed(5 + rank)
@@ -204,12 +205,20 @@ def _train(rank, world, comm):
     batch = {"tokens": c[:, :-1].contiguous().cuda(), "labels": c[:, 1:].contiguous().cuda(),
              "loss_mask": torch.ones(2, 256, device="cuda")}
     losses, norms = [], []
-    for _ in range(5):
+    for _ in range(steps):
         out = tr.train_step([batch])
         losses.append(float(out["loss"]))
         norms.append(float(out["grad_norm"]))
     torch.cuda.synchronize()
     _lib.check_status()
+    if full_graph:
+        assert tr.full_graph is not None and tr.full_graph.replays == steps - 2
+        tr.symm.resync_epochs()                  # eager collectives still line up afterwards
+        v = torch.ones(1, device="cuda")
+        tr.fused_dp.all_reduce_small(v)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        assert float(v) == world
     return losses, norms, len(tr.reducer.buckets)
 
 
@@ -222,6 +231,18 @@ def test_dp2_fused_matches_nccl_training():
     assert fused[0][0][-1] < fused[0][0][0]
     assert fused[0][0] == pytest.approx(nccl[0][0], rel=2e-3)
     assert fused[0][1] == pytest.approx(nccl[0][1], rel=2e-2)
+
+
+@needs2
+def test_dp2_whole_step_graph_with_peer_memory_collectives():
+    """The whole step (backward-overlapped bucket reduce-scatter kernels, norm, clip, fused
+    AdamW + all-gather, loss all-reduce) replayed from one CUDA graph per rank tracks the
+    eager run."""
+    eager = run_gpus(_train, 2, "fused", False, 6)
+    graph = run_gpus(_train, 2, "fused", True, 6)
+    assert graph[0][0] == graph[1][0]
+    assert graph[0][0] == pytest.approx(eager[0][0], rel=5e-3)
+    assert graph[0][1] == pytest.approx(eager[0][1], rel=5e-2)
 
 
 # ------------------------------------------------------------------------------------------
