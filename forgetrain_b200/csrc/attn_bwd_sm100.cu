@@ -71,7 +71,11 @@ __global__ void __launch_bounds__(FAB_THREADS, 1)
 fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
               const FaBwdParams p) {
   using L = FaBwdSmem<D, QS, NP, NDS, NST>;
-  constexpr bool ALIAS = (D == 128);  // dQ shares the TMEM columns of S^T
+  // head_dim 128 fills all 512 TMEM columns with S, dP, dV and dK, so dQ has to share the
+  // columns of dP. The step is then split: S of step n+1 is issued as soon as S of step n is in
+  // registers and the softmax warpgroups exponentiate it (and dV starts) while dQ of step n is
+  // still being drained; only dP of step n+1 waits for the drain.
+  constexpr bool ALIAS = (D == 128);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (smem_u32(smem) & 1023u) {  // swizzled tiles need a 1024-byte aligned base
@@ -89,8 +93,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   uint64_t* dq_full = bars + 16;     // 1
   uint64_t* dq_drained = bars + 17;  // 1 (count 128)
   uint64_t* dkv_full = bars + 18;    // 1
-  uint64_t* sdp_free = bars + 19;    // 1 (count 256): S^T / dP^T of a step are in registers
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  uint64_t* sdp_free = bars + 19;    // 1 (count 256): S (and dP) of a step are in registers
+  uint64_t* dp_full = bars + 20;     // 1: dP of a step is in TMEM (head_dim 128 only)
+  uint64_t* p_ready = bars + 21;     // 2 (count 256): P of a step is written (head_dim 128 only)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -123,7 +129,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
     }
     mbar_init(sdp_full, 1);
     mbar_init(dq_full, 1);
-    mbar_init(dq_drained, ALIAS ? 384 : 128);
+    mbar_init(dq_drained, 128);
+    mbar_init(dp_full, 1);
+    mbar_init(&p_ready[0], 256);
+    mbar_init(&p_ready[1], 256);
     mbar_init(dkv_full, 1);
     mbar_init(sdp_free, 256);
     *abort_flag = 0;
@@ -143,7 +152,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   const uint32_t tm_dPt = tmem_base + 128;
   const uint32_t tm_dV = tmem_base + 256;
   const uint32_t tm_dK = tmem_base + 256 + D;
-  const uint32_t tm_dQ = ALIAS ? tmem_base : tmem_base + 256 + 2 * D;
+  const uint32_t tm_dQ = ALIAS ? tm_dPt : tmem_base + 256 + 2 * D;
   static_assert(NP >= 1 && NDS >= 1, "P and dS are handed over through shared memory");
   constexpr int NPB = NP;                        // ring length of the P hand-over barriers
 
@@ -222,64 +231,92 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       constexpr uint32_t STG = (2 * L::TILE) >> 4, TL = L::TILE >> 4, BUF = 32768 >> 4;
 #define FT_KOFF(kk) ((((kk) / 4) * 16384 + ((kk) % 4) * 32) >> 4)
 #define FT_MNOFF(kk) (((kk) * 2048) >> 4)
-      auto issue_sdp = [&](int n) {
+      auto issue_s = [&](int n) {
         const int s = n % QS;
         mbar_wait(&qdo_full[s], (n / QS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
         tc_fence_after();
-        const uint32_t qK = qK0 + s * STG, doK = qK + TL;
+        const uint32_t qK = qK0 + s * STG;
         umma_ss_lo<0>(tm_St, qK, kK, idesc_s);
 #pragma unroll
         for (int kk = 1; kk < D / 16; ++kk)
           umma_ss_lo<1>(tm_St, qK + FT_KOFF(kk), kK + FT_KOFF(kk), idesc_s);
+        if (ALIAS) umma_commit(sdp_full);
+      };
+      auto issue_dp = [&](int n) {   // after issue_s(n): Q/dO of the step are known to be loaded
+        const uint32_t doK = qK0 + (n % QS) * STG + TL;
         umma_ss_lo<0>(tm_dPt, doK, vK, idesc_s);
 #pragma unroll
         for (int kk = 1; kk < D / 16; ++kk)
           umma_ss_lo<1>(tm_dPt, doK + FT_KOFF(kk), vK + FT_KOFF(kk), idesc_s);
-        umma_commit(sdp_full);
+        umma_commit(ALIAS ? dp_full : sdp_full);
       };
-      mbar_wait(kv_full, 0, abort_flag, p.status, FT_ERR_WAIT_FULL);
-      issue_sdp(0);
-      for (int n = 0; n < N; ++n) {
-        const int s = n % QS;
-        // S^T / dP^T of step n+1 go to the tensor pipe as soon as the softmax warpgroups hold
-        // step n's scores in registers, i.e. while they are still computing P^T / dS^T of
-        // step n: the next softmax then starts without waiting for these products.
-        if (!ALIAS && n + 1 < N) {
-          mbar_wait(sdp_free, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
-          tc_fence_after();
-          issue_sdp(n + 1);
-        }
-        mbar_wait(&pds_ready[n % NDS], (n / NDS) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
-        tc_fence_after();
-        const uint32_t qMN = qMN0 + s * STG, doMN = qMN + TL;
-        const uint32_t dsK = dsK0 + (n % NDS) * BUF, dsMN = dsMN0 + (n % NDS) * BUF;
-        const uint32_t acc0 = n > 0 ? 1u : 0u;
+      auto issue_dv = [&](int n) {
+        const uint32_t doMN = qMN0 + (n % QS) * STG + TL;
         const uint32_t pMN = pMN0 + (n % NPB) * BUF;
-        umma_ss_lo_dyn(tm_dV, pMN, doMN, idesc_dkv, acc0);
+        umma_ss_lo_dyn(tm_dV, pMN, doMN, idesc_dkv, n > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 1; kk < 8; ++kk)
           umma_ss_lo<1>(tm_dV, pMN + FT_MNOFF(kk), doMN + FT_MNOFF(kk), idesc_dkv);
         umma_commit(&p_free[n % NPB]);
-        umma_ss_lo_dyn(tm_dK, dsMN, qMN, idesc_dkv, acc0);
+      };
+      auto issue_dk = [&](int n) {
+        const uint32_t qMN = qMN0 + (n % QS) * STG;
+        const uint32_t dsMN = dsMN0 + (n % NDS) * BUF;
+        umma_ss_lo_dyn(tm_dK, dsMN, qMN, idesc_dkv, n > 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 1; kk < 8; ++kk)
           umma_ss_lo<1>(tm_dK, dsMN + FT_MNOFF(kk), qMN + FT_MNOFF(kk), idesc_dkv);
         // Q_n / dO_n are last read by dK / dV: hand the stage back to the producer now
-        umma_commit(&qdo_empty[s]);
-        if (n > 0) {
-          mbar_wait(dq_drained, (n - 1) & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
-          tc_fence_after();
-        }
+        umma_commit(&qdo_empty[n % QS]);
+      };
+      auto issue_dq = [&](int n) {
+        const uint32_t dsK = dsK0 + (n % NDS) * BUF;
         umma_ss_lo<0>(tm_dQ, dsK, kMN, idesc_dq);
 #pragma unroll
         for (int kk = 1; kk < 8; ++kk)
           umma_ss_lo<1>(tm_dQ, dsK + FT_KOFF(kk), kMN + FT_MNOFF(kk), idesc_dq);
         umma_commit(dq_full);
         umma_commit(&ds_free[n % NDS]);
-        if (ALIAS && n + 1 < N) {
-          mbar_wait(dq_drained, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
+      };
+      mbar_wait(kv_full, 0, abort_flag, p.status, FT_ERR_WAIT_FULL);
+      issue_s(0);
+      issue_dp(0);
+      for (int n = 0; n < N; ++n) {
+        if (!ALIAS) {
+          // S / dP of step n+1 go to the tensor pipe as soon as the softmax warpgroups hold
+          // step n's scores in registers, i.e. while they are still computing P / dS of step
+          // n: the next softmax then starts without waiting for these products.
+          if (n + 1 < N) {
+            mbar_wait(sdp_free, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
+            tc_fence_after();
+            issue_s(n + 1);
+            issue_dp(n + 1);
+          }
+          mbar_wait(&pds_ready[n % NDS], (n / NDS) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
           tc_fence_after();
-          issue_sdp(n + 1);
+          issue_dv(n);
+          issue_dk(n);
+          if (n > 0) {
+            mbar_wait(dq_drained, (n - 1) & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
+            tc_fence_after();
+          }
+          issue_dq(n);
+        } else {
+          mbar_wait(&p_ready[n % NPB], (n / NPB) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+          tc_fence_after();
+          issue_dv(n);
+          mbar_wait(&pds_ready[n % NDS], (n / NDS) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+          tc_fence_after();
+          issue_dk(n);
+          issue_dq(n);   // into the columns of dP(n), which the softmax has read by now
+          if (n + 1 < N) {
+            mbar_wait(sdp_free, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
+            tc_fence_after();
+            issue_s(n + 1);
+            mbar_wait(dq_drained, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
+            tc_fence_after();
+            issue_dp(n + 1);
+          }
         }
       }
 #undef FT_KOFF
@@ -309,8 +346,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       alignas(8) uint32_t dp[64];
       tmem_ld32(tm_St + lane_off + half * 64, s);
       tmem_ld32(tm_St + lane_off + half * 64 + 32, s + 32);
-      tmem_ld32(tm_dPt + lane_off + half * 64, dp);
-      tmem_ld32(tm_dPt + lane_off + half * 64 + 32, dp + 32);
+      if (!ALIAS) {
+        tmem_ld32(tm_dPt + lane_off + half * 64, dp);
+        tmem_ld32(tm_dPt + lane_off + half * 64 + 32, dp + 32);
+      }
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(sdp_free);
@@ -324,16 +363,39 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       uint64_t* s2 = reinterpret_cast<uint64_t*>(s);    // pairs of scores / probabilities
       uint64_t* d2 = reinterpret_cast<uint64_t*>(dp);   // pairs of dP / dS
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {                    // t = s * scale - lse2 ; dd = dP - delta
-        s2[i] = fma_f32x2(s2[i], sl2x2, nl2);
-        d2[i] = add_f32x2(d2[i], nd2);
-      }
+      for (int i = 0; i < 32; ++i) s2[i] = fma_f32x2(s2[i], sl2x2, nl2);   // t = s * scale - lse2
 #pragma unroll
       for (int k = 0; k < 64; ++k) s[k] = __float_as_uint(fast_exp2(__uint_as_float(s[k])));
+      if (ALIAS) {
+        // P goes out first (dV can start); dP of this step arrives once dQ of the previous
+        // step has left the columns the two share.
+        mbar_wait(&p_free[n % NPB], ((n / NPB) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) d2[i] = mul_f32x2(s2[i], d2[i]);   // dS = P * (dP - delta)
+        for (int c = 0; c < 8; ++c) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int q2 = 0; q2 < 4; ++q2) {
+            const int k = c * 8 + q2 * 2;
+            pk[q2] = pack_bf16x2_int(__uint_as_float(s[k]), __uint_as_float(s[k + 1]));
+          }
+          *reinterpret_cast<uint4*>(rowp + ((c ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+        tc_fence_before();
+        fence_proxy_async_smem();
+        mbar_arrive(&p_ready[n % NPB]);
+        mbar_wait(dp_full, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
+        tc_fence_after();
+        tmem_ld32(tm_dPt + lane_off + half * 64, dp);
+        tmem_ld32(tm_dPt + lane_off + half * 64 + 32, dp + 32);
+        tmem_ld_wait();
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) d2[i] = add_f32x2(d2[i], nd2);          // dd = dP - delta
+#pragma unroll
+      for (int i = 0; i < 32; ++i) d2[i] = mul_f32x2(s2[i], d2[i]);        // dS = P * dd
       // the buffers written below were last read by dV (P) and by dK / dQ (dS)
-      mbar_wait(&p_free[n % NPB], ((n / NPB) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+      if (!ALIAS)
+        mbar_wait(&p_free[n % NPB], ((n / NPB) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
       mbar_wait(&ds_free[n % NDS], ((n / NDS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -341,42 +403,16 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
 #pragma unroll
         for (int q2 = 0; q2 < 4; ++q2) {
           const int k = c * 8 + q2 * 2;
-          pk[q2] = pack_bf16x2_int(__uint_as_float(s[k]), __uint_as_float(s[k + 1]));
+          if (!ALIAS) pk[q2] = pack_bf16x2_int(__uint_as_float(s[k]), __uint_as_float(s[k + 1]));
           dk[q2] = pack_bf16x2_int(__uint_as_float(dp[k]), __uint_as_float(dp[k + 1]));
         }
         const int chunk = (c ^ (r & 7)) << 4;
-        *reinterpret_cast<uint4*>(rowp + chunk) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        if (!ALIAS) *reinterpret_cast<uint4*>(rowp + chunk) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         *reinterpret_cast<uint4*>(rowd + chunk) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
       }
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive(&pds_ready[n % NDS]);
-      if (ALIAS) {
-        // head_dim 128: dQ lives in the columns of S, so the next S / dP cannot be issued (and
-        // these warpgroups have nothing to do) until dQ of this step is drained: take the upper
-        // half of its columns, one 32-column chunk per warpgroup.
-        const int head = step_head(n);
-        const int q_col = (grp * (p.g + 2) + head % p.g) * D;
-        float* acc_tile = p.acc + static_cast<long>(row_base + qt * FAB_BLK + (warp & 3) * 32) * p.ld_acc + q_col;
-        mbar_wait(dq_full, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
-        tc_fence_after();
-        const int c = D / 64 + half;   // 32-column chunk
-#pragma unroll 1
-        for (int hrow = 0; hrow < 2; ++hrow) {
-          uint32_t o[16];
-          tmem_ld_16x256b_x4(tm_dQ + lane_off + (static_cast<uint32_t>(hrow * 16) << 16) + c * 32, o);
-          tmem_ld_wait();
-          float* a0 = acc_tile + static_cast<long>(hrow * 16 + (lane >> 2)) * p.ld_acc + c * 32 + 2 * (lane & 3);
-          float* a1 = a0 + 8L * p.ld_acc;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            red_add_v2(a0 + 8 * i, __uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]));
-            red_add_v2(a1 + 8 * i, __uint_as_float(o[4 * i + 2]), __uint_as_float(o[4 * i + 3]));
-          }
-        }
-        tc_fence_before();
-        mbar_arrive(dq_drained);
-      }
     }
   } else {
     reg_dealloc<72>();
@@ -394,7 +430,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       // reduction instruction of the warp updates whole sectors.
       float* acc_tile = p.acc + static_cast<long>(row_base + qt * FAB_BLK + (warp & 3) * 32) * p.ld_acc + q_col;
 #pragma unroll 1
-      for (int c = 0; c < (ALIAS ? D / 128 : D / 64); ++c) {
+      for (int c = 0; c < D / 64; ++c) {
 #pragma unroll 1
         for (int hrow = 0; hrow < 2; ++hrow) {
           uint32_t o[32];
