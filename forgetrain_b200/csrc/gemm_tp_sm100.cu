@@ -176,13 +176,16 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
+    // One box per lane (lane 0: A, lanes 1..: B): a thread that issues a tiled TMA load is held
+    // for several hundred cycles per instruction, so the boxes of a stage leave together.
+    const int nB = p.b_mn ? BN / 64 : 1;
+    if (lane < 1 + nB) {
       int stage = 0;
       uint32_t phase = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         int mt, nt;
         tp_decode_tile(p, tile, rot, mt, nt);
-        if (p.mode == 1) {
+        if (p.mode == 1 && lane == 0) {
           const int owner = mt / p.tiles_per_slot;
           if (owner != p.rank) {
             // wait until the CTAs that share this 128-row chunk have copied their slices
@@ -205,19 +208,20 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
           uint8_t* sA = smem + stage * L::STAGE_BYTES;
           uint8_t* sB = sA + L::A_BYTES;
-          mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
-          tma_load_2d(sA, &tmA, &full_bar[stage], ki * TP_BK, mt * TP_BM);
-          if (!p.b_mn) {
+          if (lane == 0) {
+            // only this lane reads the gathered A operand, after its wait above
+            mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+            tma_load_2d(sA, &tmA, &full_bar[stage], ki * TP_BK, mt * TP_BM);
+          } else if (!p.b_mn) {
             tma_load_2d(sB, &tmB, &full_bar[stage], ki * TP_BK, nt * BN);
           } else {
-#pragma unroll
-            for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sB + c * 8192, &tmB, &full_bar[stage], nt * BN + c * 64, ki * TP_BK);
+            const int c = lane - 1;
+            tma_load_2d(sB + c * 8192, &tmB, &full_bar[stage], nt * BN + c * 64, ki * TP_BK);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
-      if (*abort_flag) {
+      if (lane == 0 && *abort_flag) {
         const uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
       }
