@@ -232,3 +232,30 @@ def test_native_library_is_the_cuda_path():
     ops.linear_fwd(x, w)
     ops.swiglu_fwd(x)
     assert _lib.launch_count() == before + 2
+
+
+def test_device_side_schedule_matches_host_schedule():
+    """The one-thread schedule kernel (step counter, warmup - stable - decay learning rate, bias
+    corrections) against the host formulas, across every region of the schedule."""
+    from forgetrain_b200.optim.lr import compute_lr
+    max_lr, min_lr, warm, decay, wsd = 3e-3, 1e-4, 5, 40, 12
+    b1, b2, eps = 0.9, 0.95, 1e-8
+    sched = torch.tensor([max_lr, min_lr, warm, decay, wsd, b1, b2, eps], device="cuda")
+    step = torch.zeros(1, dtype=torch.int32, device="cuda")
+    hyper = torch.zeros(8, device="cuda")
+    hyper[6] = 0.5                                   # the clip slot belongs to another kernel
+    for it in range(50):
+        K.adam_hyper_step(step, sched, hyper)
+        h = hyper.cpu().double()
+        t = it + 1
+        assert int(step) == t
+        assert h[0] == pytest.approx(compute_lr(it, max_lr, min_lr, warm, decay, wsd), rel=1e-6, abs=1e-12)
+        assert h[1] == pytest.approx(b1, rel=1e-7) and h[2] == pytest.approx(b2, rel=1e-7)
+        assert h[4] == pytest.approx(1 - b1 ** t, rel=1e-5) and h[5] == pytest.approx(1 - b2 ** t, rel=1e-5)
+        assert h[6] == 0.5
+    # warmup-then-constant (the 8B engine's schedule): wsd == 0
+    sched[4] = 0
+    step.zero_()
+    for it in range(8):
+        K.adam_hyper_step(step, sched, hyper)
+        assert float(hyper[0]) == pytest.approx(compute_lr(it, max_lr, min_lr, warm, decay, 0), rel=1e-6)
