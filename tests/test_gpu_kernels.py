@@ -245,7 +245,7 @@ def test_device_side_schedule_matches_host_schedule():
     hyper = torch.zeros(8, device="cuda")
     hyper[6] = 0.5                                   # the clip slot belongs to another kernel
     for it in range(50):
-        K.adam_hyper_step(step, sched, hyper)
+        C.adam_hyper_step(step, sched, hyper)
         h = hyper.cpu().double()
         t = it + 1
         assert int(step) == t
@@ -257,5 +257,5 @@ def test_device_side_schedule_matches_host_schedule():
     sched[4] = 0
     step.zero_()
     for it in range(8):
-        K.adam_hyper_step(step, sched, hyper)
+        C.adam_hyper_step(step, sched, hyper)
         assert float(hyper[0]) == pytest.approx(compute_lr(it, max_lr, min_lr, warm, decay, 0), rel=1e-6)
