@@ -240,6 +240,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
+      // Tail: observe the release of every stage once more, so that no asynchronous arrival of
+      // the tensor pipe is still on its way when the CTA exits.
+      for (int i = 0; i < STAGES; ++i) {
+        if ((stage & 1) == pid)
+          mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
       if (lane == 0 && *abort_flag) {
         // Give copies still in flight time to land before the CTA's shared memory goes away.
         const uint64_t t0 = globaltimer_ns();
@@ -431,6 +438,15 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
+      // Tail: one more trip round the ring, waiting only. The releases of the last stages are
+      // asynchronous arrivals sent by the other CTA's tensor pipe; each of them has to be
+      // observed here before this CTA may exit, or it would land in the shared memory of
+      // whatever CTA (of any kernel) gets this SM next.
+      for (int i = 0; i < STAGES; ++i) {
+        if ((stage & 1) == pid)
+          mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
       if (lane == 0 && *abort_flag) {
         const uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -470,6 +486,12 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         umma_commit_both(&tfull_bar[buf]);
+      }
+      // Tail: both accumulator buffers released, i.e. every epilogue warp of BOTH CTAs has sent
+      // its (remote) arrival and it has landed here, before this CTA leaves.
+      for (int i = 0; i < 2; ++i, ++it) {
+        mbar_wait(&tempty_bar[it & 1], ((it >> 1) & 1) ^ 1, abort_flag, p.status,
+                  FT_ERR_WAIT_TMEM_EMPTY);
       }
     }
   } else {
@@ -604,7 +626,9 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB,
 // Process-wide default for the tile shape when the caller passes bn = 0. The CTA-pair kernel is
 // opt-in (FT_GEMM_PAIR=1): it is correct and faster when it has the GPU to itself, but stopped
 // making progress in a test that runs it next to library GEMMs, copies and small kernels from
-// other streams of the same process, and the cause has not been found.
+// other streams of the same process. Draining every cross-CTA barrier arrival before exit (the
+// tails in the kernel) made a 2-second run of that test pass (16 k launches) but not the
+// 4-second one, so a second cause is still unknown.
 static int pair_default() {
   static int v = -1;
   if (v < 0) {
