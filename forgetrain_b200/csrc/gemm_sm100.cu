@@ -529,6 +529,11 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
+  // Neither CTA leaves before BOTH have issued the pair-wide free: a CTA of another kernel that
+  // got the first SM in between would otherwise have its fresh TMEM allocation there hit by
+  // the second CTA's free.
+  __syncwarp();
+  cluster_sync_all();
 }
 
 // ---------------------------------------------------------------------------------------
