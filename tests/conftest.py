@@ -10,6 +10,17 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
 
 
+def pytest_collection_modifyitems(config, items):
+    """Every GPU test gets a hard time limit (when pytest-timeout is installed): a device-side
+    wait that never ends blocks the host inside the CUDA runtime, where only a watchdog thread
+    that ends the process can still act."""
+    if not config.pluginmanager.hasplugin("timeout"):
+        return
+    for item in items:
+        if item.get_closest_marker("gpu") and not item.get_closest_marker("timeout"):
+            item.add_marker(pytest.mark.timeout(240, method="thread"))
+
+
 @pytest.fixture(autouse=True)
 def _reset_engine_config():
     from forgetrain_b200 import engine_config
