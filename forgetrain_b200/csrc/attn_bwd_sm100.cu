@@ -556,7 +556,9 @@ static int launch_fa_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const Fa
 // layout; lse: [batch][Hq][S] fp32 from the forward. Scratch (caller-provided, fp32):
 //   acc   [batch*S][ncols]  zero-filled by this call,  ncols = n_groups*(g+2)*D
 //   delta [2][batch][Hq][S] (second half holds lse*log2(e))
-// heads_per_cta <= 0 picks a value that keeps the grid well above the SM count.
+// heads_per_cta <= 0 picks the largest value that keeps the grid at three CTAs per SM or more
+// (measured optimum: longer CTAs amortise the K/V load and the dK/dV drain, but the causal
+// triangle needs a few waves to balance).
 extern "C" int ft_attn_bwd(const void* dout, const void* qkv, const void* out, const void* lse,
                            void* dqkv, void* acc, void* delta, int batch, int S, int n_groups,
                            int g, int D, int ld_qkv, int ld_out, int ld_dout, float scale,
@@ -569,7 +571,7 @@ extern "C" int ft_attn_bwd(const void* dout, const void* qkv, const void* out, c
   if (heads_per_cta <= 0) {
     heads_per_cta = g;
     while (heads_per_cta > 1 &&
-           static_cast<long>(S / FAB_BLK) * batch * n_groups * (g / heads_per_cta) < 148 * 6)
+           static_cast<long>(S / FAB_BLK) * batch * n_groups * (g / heads_per_cta) < 148 * 3)
       heads_per_cta /= 2;
   }
   if (g % heads_per_cta) return -4;
