@@ -7,7 +7,9 @@ exports/train_engine_8b/src/training_engine_tensor/__main__.py:57-224):
 
 * ``pretrain``               random-init (or ``--resume``) training; synthetic uniform tokens
                              unless ``--hf-dataset`` is given
-* ``train``                  continue from ``--checkpoint-root`` (a checkpoint to import)
+* ``train``                  start from ``--checkpoint-root``: a Megatron export
+                             (``canonical_state_fp32.pt`` + optional optimizer state) or one of
+                             this engine's own checkpoints
 * ``checkpoint-train-loop``  train with periodic checkpoints (defaults to 200 steps)
 
 Every :class:`~forgetrain_b200.engine_config.EngineConfig` field is also exposed as

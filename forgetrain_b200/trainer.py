@@ -248,6 +248,24 @@ class Trainer:
 
     def load(self, path) -> dict:
         p = Path(path)
+        from .ckpt import megatron_import as mg
+        if mg.is_megatron_root(p):
+            # a Megatron export: full tensors by Megatron names (+ optional Adam state); every
+            # rank reads the file and keeps its tensor-parallel shard
+            log = print if self.topo.rank == 0 else (lambda *_: None)
+            n_mtp = self.cfg.mtp_num_layers
+            tensors = mg.load_megatron_checkpoint(p, self.spec, n_mtp, log=log)
+            self.store.load_named(tensors, full_tensors=True)
+            ost = mg.load_megatron_optimizer_state(p, log=log)
+            if ost is not None and self.topo.tp_size == 1:
+                L = self.spec.num_layers
+                for k in ("master_weights", "exp_avg", "exp_avg_sq"):
+                    ost[k] = mg.rename_state(ost[k], L, n_mtp)
+                self.opt.load_full_state(ost, ost["step_count"])
+                self.num_samples = ost["num_samples"]
+            else:
+                self.opt.sync_master_from_params()
+            return {"step": 0, "num_samples": self.num_samples, "dataloader_state": None}
         if self.topo.tp_size > 1:
             if p.is_dir() and not (p / f"rank_{self.topo.tp_rank}.pt").exists():
                 cands = sorted(q for q in p.glob("step_*") if (q / f"rank_{self.topo.tp_rank}.pt").exists())
