@@ -74,7 +74,9 @@ class EngineConfig:
     mup_lr_scaling: bool = True          # hidden matrices use lr / (hidden / base width)
     # ---- init ----
     random_init: bool = True
-    init_scheme: str = "spec"            # "spec": muP-aware std from the model spec; "normal": N(0, init_std)
+    # "spec": muP-aware std from the model spec; "normal": N(0, init_std); "mcore": N(0, init_std)
+    # with the residual-stream projections at init_std / sqrt(2 * layers) (the 8B engine's)
+    init_scheme: str = "spec"
     init_std: float = 0.02
     # ---- profiling ----
     profile_range: str = ""              # "start,end" (step indices, end exclusive)

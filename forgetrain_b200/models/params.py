@@ -182,9 +182,17 @@ def local_shape(ps: ParamSpec, spec: ModelSpec, tp: int) -> tuple[int, ...]:
 
 def init_std_for(ps: ParamSpec, spec: ModelSpec, scheme: str, init_std: float) -> float:
     """``spec`` scheme: embeddings / head use init_std, hidden matrices init_std/sqrt(width
-    multiplier) under muP (reference parameters.py:181-262); ``normal``: N(0, init_std)."""
+    multiplier) under muP (reference parameters.py:181-262); ``normal``: N(0, init_std);
+    ``mcore``: N(0, init_std) with the residual-stream projections scaled down by depth."""
     if ps.init == "ones":
         return 0.0
+    if scheme == "mcore":
+        # Megatron-core's scaled init of the 8B engine: the two projections that write into the
+        # residual stream (attention output, FFN down) use init_std / sqrt(2 * num_layers)
+        # (reference: exports/train_engine_8b/src/training_engine_tensor/parameters.py:253-358)
+        if ps.name.endswith("attention.wo.weight") or ps.name.endswith("feed_forward.w2.weight"):
+            return init_std / math.sqrt(2.0 * spec.num_layers)
+        return init_std
     if scheme == "normal" or not spec.mup_enabled or ps.init == "normal":
         return init_std
     return init_std / math.sqrt(spec.mup_width_scale)

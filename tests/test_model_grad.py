@@ -82,3 +82,27 @@ def test_rope_inverse_is_transpose():
     # v columns untouched
     v = x.view(64, 2, 4, 16)[:, :, 3]
     assert torch.equal(y.view(64, 2, 4, 16)[:, :, 3], v)
+
+
+def test_init_schemes():
+    """muP-aware, plain and depth-scaled initial standard deviations."""
+    import math
+    from forgetrain_b200.config import load_model_spec
+    from forgetrain_b200.models.params import ParamStore
+    spec = load_model_spec("tiny")
+    stds = {}
+    for scheme in ("spec", "normal", "mcore"):
+        st = ParamStore(spec, "cpu", torch.float32)
+        st.init_random(0, scheme, 0.1)
+        stds[scheme] = {n: float(st.params[n].std()) for n in
+                        ("tok_embeddings.weight", "layers.0.attention.wqkv.weight",
+                         "layers.0.attention.wo.weight", "layers.1.feed_forward.w2.weight")}
+        assert torch.all(st.params["layers.0.ffn_norm.weight"] == 1)
+    w = math.sqrt(spec.mup_width_scale) if spec.mup_enabled else 1.0
+    assert stds["spec"]["tok_embeddings.weight"] == pytest.approx(0.1, rel=0.05)
+    assert stds["spec"]["layers.0.attention.wqkv.weight"] == pytest.approx(0.1 / w, rel=0.05)
+    assert all(v == pytest.approx(0.1, rel=0.05) for v in stds["normal"].values())
+    d = math.sqrt(2 * spec.num_layers)
+    assert stds["mcore"]["layers.0.attention.wqkv.weight"] == pytest.approx(0.1, rel=0.05)
+    assert stds["mcore"]["layers.0.attention.wo.weight"] == pytest.approx(0.1 / d, rel=0.05)
+    assert stds["mcore"]["layers.1.feed_forward.w2.weight"] == pytest.approx(0.1 / d, rel=0.05)
