@@ -162,8 +162,19 @@ class Trainer:
         return compute_lr(self.opt.step_count, c.max_lr, c.min_lr, c.warmup_iters, c.lr_decay_iters,
                           c.wsd_decay_iters)
 
+    def _grad_norm_diag(self) -> None:
+        """``GRAD_NORM_DIAG``: this rank's full gradient norm before any reduction and the
+        twelve largest per-parameter norms (reference train_loop.py:829-856). Synchronises."""
+        rows = sorted(((float(self.store.grads[ps.name].float().norm()), ps.name)
+                       for ps in self.store.specs), reverse=True)
+        total = sum(g * g for g, _ in rows) ** 0.5
+        print(f"[grad-norm-diag] pre_reduce_rank{self.topo.rank}_full={total:.10f}", flush=True)
+        print("[grad-norm-top] " + " | ".join(f"{g:.6f}:{n}" for g, n in rows[:12]), flush=True)
+
     def _micro_batch(self, batch, loss_scale: float, accumulate: bool, last: bool):
-        grad_ready = self._grad_ready if last else None
+        diag = self.cfg.grad_norm_diag and last and self.topo.dp_rank == 0
+        hold = self.cfg.grad_norm_diag and last   # every rank holds its buckets back alike
+        grad_ready = self._grad_ready if (last and not hold) else None
         tokens, labels = batch["tokens"], batch["labels"]
         mask = batch.get("loss_mask")
         pos = batch.get("position_ids")
@@ -175,8 +186,16 @@ class Trainer:
                     self._grad_ready(ps.name)
             return loss
         if self.mtp is None:
-            return m.forward_backward(tokens, labels, mask, loss_scale, accumulate, grad_ready, pos)
-        return self.mtp.forward_backward(tokens, labels, mask, loss_scale, accumulate, grad_ready, pos)
+            loss = m.forward_backward(tokens, labels, mask, loss_scale, accumulate, grad_ready, pos)
+        else:
+            loss = self.mtp.forward_backward(tokens, labels, mask, loss_scale, accumulate,
+                                             grad_ready, pos)
+        if hold:   # diagnostics look at the local gradients, so the buckets are released after
+            if diag:
+                self._grad_norm_diag()
+            for ps in self.store.order:
+                self._grad_ready(ps.name)
+        return loss
 
     # ------------------------------------------------------------------ the step
     def train_step(self, micro_batches: list[dict], profiler: StepProfiler | None = None) -> dict:

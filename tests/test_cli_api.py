@@ -79,3 +79,29 @@ def test_cli_pretrain_tiny_cpu_writes_report_and_checkpoint(tmp_path):
     assert (tmp_path / "out" / "3step" / "ours_results.jsonl").exists()
     assert (tmp_path / "ck" / "step_0000002" / "training_state.pt").exists()
     assert (tmp_path / "ck" / "step_0000003" / "training_state.pt").exists()
+
+
+def test_grad_norm_diag_prints_local_norms(capsys):
+    """GRAD_NORM_DIAG: full pre-reduce norm and top per-parameter norms; the step itself is
+    unchanged."""
+    import torch
+    from forgetrain_b200.config import load_model_spec
+    from forgetrain_b200.engine_config import from_spec
+    from forgetrain_b200.parallel.topology import Topology
+    from forgetrain_b200.trainer import Trainer
+    spec = load_model_spec("tiny")
+    tok = torch.randint(0, spec.vocab_size, (2, 33), generator=torch.Generator().manual_seed(0))
+    batch = {"tokens": tok[:, :-1].contiguous(), "labels": tok[:, 1:].contiguous()}
+    out = {}
+    for diag in (False, True):
+        cfg = from_spec(spec, dtype="fp32", comm="nccl", warmup_iters=0, grad_norm_diag=diag,
+                        no_grad_clip=True)
+        tr = Trainer(spec, cfg, Topology(device=torch.device("cpu")), seq_length=32,
+                     micro_batch_size=2, seed=0)
+        r = tr.train_step([batch, batch])
+        out[diag] = (float(r["loss"]), float(r["grad_norm"]))
+    text = capsys.readouterr().out
+    assert "[grad-norm-diag] pre_reduce_rank0_full=" in text and "[grad-norm-top]" in text
+    full = float(text.split("pre_reduce_rank0_full=")[1].split()[0])
+    assert full == pytest.approx(out[True][1], rel=1e-4)      # one rank: local norm == global
+    assert out[True] == pytest.approx(out[False], rel=1e-6)
