@@ -56,6 +56,8 @@ class MiniCPM4:
         self.vocab_start = tp.rank * self.vocab_rows if tpn > 1 else 0
         self._saved: list[LayerSaved] = []
         self._head_saved = None
+        # set to a dict to have the backward record a few intermediate gradients in it
+        self.diagnostics: dict | None = None
         self._ensure_rope(S)
 
     def _ensure_rope(self, S: int) -> None:
@@ -147,8 +149,13 @@ class MiniCPM4:
         dnf = tp.dgrad_scatter(dlogits, p["output.weight"], alpha=a)
         if dnf_extra is not None:
             dnf = dnf + dnf_extra
+        diag = self.diagnostics
+        if diag is not None:
+            diag["d_normed_final"] = dnf.detach().clone()
         dh = ops.rmsnorm_bwd(dnf, h_fin, p["norm.weight"], rsf, None, g["norm.weight"], accumulate)
         emit("norm.weight")
+        if diag is not None:
+            diag["d_hidden_after_norm"] = dh.detach().clone()
         self._head_saved = None
         return dh
 
@@ -161,11 +168,19 @@ class MiniCPM4:
         n_w2, n_fc1 = f"{prefix}.feed_forward.w2.weight", f"{prefix}.feed_forward.wfc1.weight"
         n_qkv, n_wo = f"{prefix}.attention.wqkv.weight", f"{prefix}.attention.wo.weight"
         n_fn, n_an = f"{prefix}.ffn_norm.weight", f"{prefix}.attention_norm.weight"
+        # gradients of the LAST block are what a numerical comparison with another engine looks
+        # at first (reference backward.py:211-252: the ``diagnostics`` dict)
+        diag = self.diagnostics if prefix == f"layers.{sp.num_layers - 1}" else None
+        if diag is not None:
+            diag["d_hidden_into_last_layer"] = dh.detach().clone()
         # ---- feed-forward branch
         dact, dh_full = tp.dgrad_gather(dh, p[n_w2], alpha=r, key="bwd.ffn")
         ops.linear_wgrad(dh_full, sv.act, g[n_w2], accumulate, alpha=r)
         emit(n_w2)
         dy1 = ops.swiglu_bwd(dact, sv.y1)
+        if diag is not None:
+            diag["d_intermediate_last"] = dact.detach().clone()
+            diag["d_fc1_last"] = dy1.detach().clone()
         del dact
         ops.linear_wgrad(dy1, sv.n2_full, g[n_fc1], accumulate)
         emit(n_fc1)

@@ -106,3 +106,27 @@ def test_init_schemes():
     assert stds["mcore"]["layers.0.attention.wqkv.weight"] == pytest.approx(0.1, rel=0.05)
     assert stds["mcore"]["layers.0.attention.wo.weight"] == pytest.approx(0.1 / d, rel=0.05)
     assert stds["mcore"]["layers.1.feed_forward.w2.weight"] == pytest.approx(0.1 / d, rel=0.05)
+
+
+def test_backward_diagnostics_hook():
+    """``model.diagnostics = {}`` collects the gradients a cross-engine comparison starts from;
+    leaving it None changes nothing."""
+    spec = load_model_spec("tiny")
+    store = ParamStore(spec, "cpu", torch.float32)
+    store.init_random(0, "normal", 0.05)
+    model = MiniCPM4(spec, store)
+    tok = torch.randint(0, spec.vocab_size, (2, 33), generator=torch.Generator().manual_seed(1))
+    x, y = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    model.forward_backward(x, y)
+    ref = store.flat_grads.clone()
+    model.diagnostics = {}
+    model.forward_backward(x, y)
+    assert torch.equal(store.flat_grads, ref)
+    d = model.diagnostics
+    T, H, F = 64, spec.hidden_size, spec.ffn_hidden_size
+    assert set(d) == {"d_normed_final", "d_hidden_after_norm", "d_hidden_into_last_layer",
+                      "d_intermediate_last", "d_fc1_last"}
+    assert d["d_normed_final"].shape == (T, H) and d["d_intermediate_last"].shape == (T, F)
+    assert d["d_fc1_last"].shape == (T, 2 * F)
+    assert torch.equal(d["d_hidden_after_norm"], d["d_hidden_into_last_layer"])
+    assert float(d["d_fc1_last"].abs().sum()) > 0
