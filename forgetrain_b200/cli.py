@@ -40,6 +40,24 @@ def _add_engine_config_args(p: argparse.ArgumentParser) -> None:
         else:
             typ = {"int": int, "float": float, "str": str}.get(str(f.type), str)
             grp.add_argument(flag, dest=f"cfg_{f.name}", type=typ, default=None)
+    # the reference engines' own spellings: renamed fields translate, path selectors that
+    # have no counterpart here are accepted and reported as having no effect
+    old = p.add_argument_group("reference-engine spellings")
+    own = {f.name for f in dataclasses.fields(ec.EngineConfig)}
+    for name, (fld, conv) in sorted(ec.LEGACY_FIELD_ALIASES.items()):
+        flag = "--" + name.replace("_", "-")
+        if conv is bool or name == "fp32_mode":
+            old.add_argument(flag, dest=f"legacy_{name}", action=argparse.BooleanOptionalAction,
+                             default=None, help=f"same as --{fld.replace('_', '-')}")
+        else:
+            old.add_argument(flag, dest=f"legacy_{name}", type=conv, default=None,
+                             help=f"same as --{fld.replace('_', '-')}")
+    for name in sorted(ec.LEGACY_NOOP_FIELDS - own):
+        flag = "--" + name.replace("_", "-")
+        if flag in p._option_string_actions:
+            continue
+        old.add_argument(flag, "--no-" + name.replace("_", "-"), dest=f"noop_{name}", nargs="?",
+                         const=True, default=None, help=argparse.SUPPRESS)
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -110,6 +128,14 @@ def main(argv: list[str] | None = None) -> int:
     spec = load_model_spec(args.model, tie_embeddings=args.tie_embeddings, vocab_size=args.vocab_size,
                            num_layers=args.num_layers)
     overrides = {k[4:]: v for k, v in vars(args).items() if k.startswith("cfg_") and v is not None}
+    for k, v in vars(args).items():
+        if k.startswith("legacy_") and v is not None:
+            fld, conv = ec.LEGACY_FIELD_ALIASES[k[7:]]
+            overrides.setdefault(fld, conv(v))
+    ignored = sorted(k[5:] for k, v in vars(args).items() if k.startswith("noop_") and v is not None)
+    if ignored:
+        print("[CONFIG] no effect here (the fused kernels are the only path): " + " ".join(ignored),
+              file=sys.stderr)
     env_cfg = ec.from_env()
     base = ec.from_spec(spec)
     # precedence: CLI > environment > model spec defaults

@@ -117,6 +117,11 @@ _ENV_MAP: dict[str, tuple[str, Callable[[str], Any]]] = {
     "FORWARD_CUDA_GRAPH": ("forward_cuda_graph", lambda v: v.lower() in _BOOL_TRUE),
     "STEP_CUDA_GRAPH": ("step_cuda_graph", lambda v: v.lower() in _BOOL_TRUE),
     "FULL_STEP_CUDA_GRAPH": ("full_step_cuda_graph", lambda v: v.lower() in _BOOL_TRUE),
+    "STEP_CUDA_GRAPH_FULL": ("full_step_cuda_graph", lambda v: v.lower() in _BOOL_TRUE),
+    "FP32_MODE": ("dtype", lambda v: "fp32" if v.lower() in _BOOL_TRUE else "bf16"),
+    "LR_WARMUP_ITERS": ("warmup_iters", int),
+    "LR_WSD_DECAY_ITERS": ("wsd_decay_iters", int),
+    "CLIP_GRAD": ("max_grad_norm", float),
     "STEP_CUDA_GRAPH_WARMUP": ("step_cuda_graph_warmup", int),
     "STEP_CUDA_GRAPH_TOL": ("step_cuda_graph_tol", float),
     "STEP_CUDA_GRAPH_SANITY": ("step_cuda_graph_sanity", lambda v: v.lower() in _BOOL_TRUE),
@@ -155,6 +160,62 @@ def from_env(env: dict | None = None, **overrides: Any) -> EngineConfig:
     cfg = EngineConfig(**kw)
     validate_config(cfg)
     return cfg
+
+
+# Field names of the reference's two engines that differ from the names here
+# (0.5B engine_config.py:141-277, 8B engine_config.py:117-192): old name -> (field, converter).
+LEGACY_FIELD_ALIASES: dict[str, tuple[str, Callable[[Any], Any]]] = {
+    "lr_warmup_iters": ("warmup_iters", int),
+    "lr_wsd_decay_iters": ("wsd_decay_iters", int),
+    "clip_grad": ("max_grad_norm", float),
+    "step_cuda_graph_full": ("full_step_cuda_graph", bool),
+    "fp32_mode": ("dtype", lambda on: "fp32" if on else "bf16"),
+}
+
+# Switches of the reference that select between a fused and an unfused code path, a library
+# and a custom kernel, or a stream layout. Here the fused kernels are the only path, so the
+# names are accepted (a config file written for the reference loads) and have no effect.
+LEGACY_NOOP_FIELDS = frozenset({
+    "fused_ops", "fuse_ce", "fuse_swiglu", "fuse_rmsnorm_residual", "fuse_rope",
+    "fuse_rope_doc_aware", "fuse_adam_sync", "fuse_gemm_pad", "fuse_direct_attn",
+    "fuse_inplace_residual", "fuse_index_add_emb_bwd", "use_span_based_attn", "unfused_mode",
+    "te_rope", "fp32_allreduce", "fp32_grad_accum", "accum_stream_overlap", "multi_tensor_adam",
+    "custom_gemm", "use_fused_norm_bwd", "norm_bwd_nan_diag", "step_cuda_graph_accum",
+    "step_cuda_graph_reducer", "step_cuda_graph_nccl_opt", "step_cuda_graph_optimizer",
+    "forward_cuda_graph_warmup", "forward_cuda_graph_tol", "forward_cuda_graph_sanity",
+    "forward_cuda_graph_sample_stride",
+    "fused_rope", "fused_rope_pack", "fused_residual_rmsnorm", "fused_rope_qkv",
+    "fused_attn_rmsnorm_bwd", "fused_mlp_residual_rmsnorm", "fused_dw_reduce",
+    "fused_rope_fp32cos", "ag_fwd_overlap", "adam_ag_pipeline", "gpu_norm_clip", "fused_ce",
+    "defer_wgrad_sync", "fused_swiglu", "dw_reduce_rows_per_block", "direct_attn",
+    "dsl_attn_fwd", "rope_bhsd", "padded_vocab_size", "vocab_size",
+})
+
+
+def from_legacy(fields: dict, **overrides: Any) -> tuple[EngineConfig, list[str]]:
+    """Build a config from a dict keyed by the reference engines' field names.
+
+    Names that exist here pass through, renamed ones are translated, path selectors that
+    have no counterpart are dropped. Returns the config and the list of dropped names so
+    the caller can tell the user; an unknown name raises.
+    """
+    own = {f.name for f in dataclasses.fields(EngineConfig)}
+    kw: dict[str, Any] = {}
+    dropped: list[str] = []
+    for name, value in fields.items():
+        if name in own:
+            kw[name] = value
+        elif name in LEGACY_FIELD_ALIASES:
+            fld, conv = LEGACY_FIELD_ALIASES[name]
+            kw[fld] = conv(value)
+        elif name in LEGACY_NOOP_FIELDS:
+            dropped.append(name)
+        else:
+            raise KeyError(f"unknown engine config field {name!r}")
+    kw.update({k: v for k, v in overrides.items() if v is not None})
+    cfg = EngineConfig(**kw)
+    validate_config(cfg)
+    return cfg, sorted(dropped)
 
 
 def from_spec(spec, **overrides: Any) -> EngineConfig:

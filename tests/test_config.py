@@ -81,3 +81,25 @@ def test_from_spec_takes_training_defaults():
     s = C.load_model_spec("8b")
     cfg = ec.from_spec(s)
     assert cfg.max_lr == s.lr and cfg.tensor_parallel_size == 2 and cfg.wsd_decay_iters == 0
+
+
+def test_legacy_field_names_translate_or_drop():
+    """Names of the reference engines (0.5B engine_config.py:141-277, 8B engine_config.py:117-192)."""
+    cfg, dropped = ec.from_legacy({"lr_warmup_iters": 10, "clip_grad": 0.5, "fp32_mode": True,
+                                   "step_cuda_graph_full": True, "fused_ce": True, "custom_gemm": False,
+                                   "max_lr": 1e-3})
+    assert (cfg.warmup_iters, cfg.max_grad_norm, cfg.dtype) == (10, 0.5, "fp32")
+    assert cfg.full_step_cuda_graph and cfg.max_lr == 1e-3
+    assert dropped == ["custom_gemm", "fused_ce"]
+    with pytest.raises(KeyError):
+        ec.from_legacy({"no_such_field": 1})
+    env = ec.from_env({"CLIP_GRAD": "2.0", "STEP_CUDA_GRAPH_FULL": "1", "LR_WARMUP_ITERS": "7"})
+    assert (env.max_grad_norm, env.full_step_cuda_graph, env.warmup_iters) == (2.0, True, 7)
+
+
+def test_cli_accepts_reference_spellings(capsys):
+    from forgetrain_b200.cli import build_parser
+    a = build_parser().parse_args(["pretrain", "--clip-grad", "0.25", "--lr-warmup-iters", "5",
+                                   "--no-fused-ce", "--custom-gemm", "--rs-buckets", "4"])
+    assert a.legacy_clip_grad == 0.25 and a.legacy_lr_warmup_iters == 5
+    assert a.noop_fused_ce is True and a.noop_custom_gemm is True and a.cfg_rs_buckets == 4
