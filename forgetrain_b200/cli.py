@@ -92,7 +92,8 @@ def build_parser() -> argparse.ArgumentParser:
     hf.add_argument("--tokenizer-path", default=None)
     hf.add_argument("--hf-dataset-config", default=None)
     hf.add_argument("--hf-dataset-split", default="train")
-    hf.add_argument("--hf-text-field", default="text")
+    hf.add_argument("--hf-text-field", nargs="+", default=None,
+                    help="text column name(s); auto-detected when omitted")
     hf.add_argument("--hf-text-template", default=None)
     hf.add_argument("--hf-data-format", default=None)
     hf.add_argument("--hf-data-files", default=None)

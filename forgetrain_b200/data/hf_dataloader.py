@@ -67,8 +67,40 @@ class PackedTokenLoader:
             self.cursor = (self.batches_drawn * self.mbs) % n
 
 
-def render_text(example: dict, text_field: str, template: str | None) -> str:
-    return template.format(**example) if template else str(example[text_field])
+_COMMON_TEXT_COLUMNS = ("text", "content", "input", "sentence", "document")
+
+
+def detect_text_fields(dataset) -> list[str]:
+    """Pick the text column(s) of a dataset when ``--hf-text-field`` is not given: the first
+    conventional name that exists, else every string-typed column, else an error that names the
+    columns (reference: 0.5B hf_dataloader.py:76-103)."""
+    cols = getattr(dataset, "column_names", None)
+    if isinstance(cols, dict):                       # DatasetDict: columns of the first split
+        cols = next(iter(cols.values()))
+    if cols is None:                                 # plain iterable of dicts
+        first = next(iter(dataset))
+        cols = list(first)
+        strings = [c for c in cols if isinstance(first[c], str)]
+    else:
+        feats = getattr(dataset, "features", None) or {}
+        strings = [c for c in cols if getattr(feats.get(c), "dtype", None) == "string"]
+    for name in _COMMON_TEXT_COLUMNS:
+        if name in cols:
+            return [name]
+    if strings:
+        return strings
+    raise ValueError(f"no text column found among {list(cols)}; pass --hf-text-field")
+
+
+def render_text(example: dict, text_field, template: str | None) -> str:
+    """One document's text: the template filled from the row, else the non-empty named columns
+    joined by newlines (a single name gives that column)."""
+    if template:
+        return template.format(**example)
+    fields = [text_field] if isinstance(text_field, str) else list(text_field)
+    if len(fields) == 1:
+        return str(example[fields[0]])
+    return "\n".join(str(example[f]) for f in fields if example.get(f))
 
 
 def build_hf_dataloader(args, spec, micro_batch_size: int, seq_length: int, topo,
@@ -98,11 +130,17 @@ def build_hf_dataloader(args, spec, micro_batch_size: int, seq_length: int, topo
         eos = 2
     vocab = spec.vocab_size
 
+    fields = args.hf_text_field
+    if fields is None and not args.hf_text_template:
+        fields = detect_text_fields(dataset)
+        if topo.rank == 0:
+            print(f"[hf_dataloader] text_fields={fields}", flush=True)
+
     def docs():
         for i, ex in enumerate(dataset):
             if i % topo.dp_size != topo.dp_rank:
                 continue
-            ids = tokenizer(render_text(ex, args.hf_text_field, args.hf_text_template),
+            ids = tokenizer(render_text(ex, fields, args.hf_text_template),
                             add_special_tokens=False)["input_ids"]
             yield [t if t < vocab else vocab - 1 for t in ids]
 

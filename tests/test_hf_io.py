@@ -88,3 +88,19 @@ def test_build_loader_with_injected_tokenizer_and_rank_sharding():
     b = build_hf_dataloader(args, spec, 1, 16, Topology(dp_size=2, dp_rank=1), tokenizer=Tok(), dataset=data)
     assert a.rows.shape[1] == 17 and a.rows.shape[0] == b.rows.shape[0] > 0
     assert int(a.rows.max()) < spec.vocab_size
+
+
+def test_text_field_detection_and_multi_column_rendering():
+    from forgetrain_b200.data.hf_dataloader import detect_text_fields, render_text
+
+    class DS(list):
+        column_names = ["id", "content", "title"]
+    assert detect_text_fields(DS()) == ["content"]
+    rows = [{"id": 3, "question": "q?", "answer": "a."}]
+    assert detect_text_fields(rows) == ["question", "answer"]
+    with pytest.raises(ValueError, match="hf-text-field"):
+        detect_text_fields([{"id": 1, "n": 2}])
+    assert render_text(rows[0], ["question", "answer"], None) == "q?\na."
+    assert render_text({"question": "q?", "answer": ""}, ["question", "answer"], None) == "q?"
+    assert render_text(rows[0], "question", None) == "q?"
+    assert render_text(rows[0], None, "Q: {question} A: {answer}") == "Q: q? A: a."
