@@ -48,6 +48,7 @@ struct GemmParams {
   int splitk;
   int m_tiles, n_tiles, k_iters;
   int* status;
+  int swiglu_F;       // > 0 (SWIGLU kernel only): B is [2F][K] = [gate rows ; up rows]
 };
 
 template <int BN, int STAGES>
@@ -156,10 +157,72 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const CUtensorMa
   }
 }
 
-template <int BN, int STAGES>
+// Epilogue of the fused FC1 + SwiGLU tile. The accumulator's columns 0..127 are gate columns
+// n0..n0+127 and its columns 128..255 the up columns F+n0..F+n0+127 of the same rows. A warp
+// takes 64 gate columns and the matching 64 up columns, writes both (bf16) into Y, which the
+// backward pass reads, and act = silu(gate) * up into ACT. The activation is computed from the
+// ROUNDED bf16 gate / up values with the arithmetic of swiglu_fwd_kernel, so it is bitwise the
+// result of running that kernel on Y.
+__device__ __forceinline__ void drain_tile_swiglu(const GemmParams& p, const CUtensorMap* tmY,
+                                                  const CUtensorMap* tmAct, uint32_t taddr,
+                                                  int row0, int n0, int chalf, uint8_t* sbuf,
+                                                  int lane, int& nstores) {
+  if (row0 >= p.M) return;
+  const int gcol = n0 + chalf * 64;
+  if (gcol >= p.swiglu_F) return;
+  // Three 64-column stores go through the warp's one staging buffer, each waiting until the
+  // previous store has read it. The TMEM load of the up half and the activation arithmetic are
+  // placed between the stores so that they run during those reads.
+  uint32_t g[32], u[32];   // 64 gate and 64 up values of this thread's row, packed bf16x2
+  uint32_t r[64];
+  auto put = [&](const uint32_t* w, const CUtensorMap* tm, int col) {
+    if (nstores >= 1) {
+      if (lane == 0) tma_wait_group_read<0>();
+      __syncwarp();
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      *reinterpret_cast<uint4*>(sbuf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+          make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tm, sbuf, col, row0);
+      tma_commit_group();
+    }
+    ++nstores;
+  };
+  tmem_ld32(taddr + chalf * 64, r);
+  tmem_ld32(taddr + chalf * 64 + 32, r + 32);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i)
+    g[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * p.alpha, __uint_as_float(r[2 * i + 1]) * p.alpha);
+  tmem_ld32(taddr + 128 + chalf * 64, r);
+  tmem_ld32(taddr + 128 + chalf * 64 + 32, r + 32);
+  put(g, tmY, gcol);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i)
+    u[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * p.alpha, __uint_as_float(r[2 * i + 1]) * p.alpha);
+  put(u, tmY, p.swiglu_F + gcol);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const uint32_t gw = g[i], uw = u[i];
+    const float g0 = __uint_as_float(gw << 16), g1 = __uint_as_float(gw & 0xffff0000u);
+    const float u0 = __uint_as_float(uw << 16), u1 = __uint_as_float(uw & 0xffff0000u);
+    const float s0 = 1.f / (1.f + __expf(-g0)), s1 = 1.f / (1.f + __expf(-g1));
+    g[i] = pack_bf16x2(g0 * s0 * u0, g1 * s1 * u1);
+  }
+  put(g, tmAct, gcol);
+}
+
+template <int BN, int STAGES, bool SWIGLU = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmD2,
+                 const GemmParams p) {
+  static_assert(!SWIGLU || BN == 256, "the fused SwiGLU epilogue needs a 128 + 128 column tile");
   using L = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -190,6 +253,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
     prefetch_tmap(&tmD);
+    if (SWIGLU) prefetch_tmap(&tmD2);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -229,7 +293,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                             ki * GEMM_BK);
             } else {
               const int j = lane - nA;
-              if (!p.b_mn)
+              if (SWIGLU)   // box 0: 128 gate rows, box 1: the 128 up rows of the same columns
+                tma_load_2d(sB + j * 16384, &tmB, &full_bar[stage], ki * GEMM_BK,
+                            nt * 128 + j * p.swiglu_F);
+              else if (!p.b_mn)
                 tma_load_2d(sB + j * 16384, &tmB, &full_bar[stage], ki * GEMM_BK,
                             nt * BN + j * 128);
               else
@@ -305,7 +372,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
       const int row0 = mt * GEMM_BM + q * 32;
-      drain_tile<BN>(p, &tmD, taddr, row0, nt * BN, chalf, my_epi, lane, nstores);
+      if (SWIGLU)
+        drain_tile_swiglu(p, &tmD, &tmD2, taddr, row0, nt * 128, chalf, my_epi, lane, nstores);
+      else
+        drain_tile<BN>(p, &tmD, taddr, row0, nt * BN, chalf, my_epi, lane, nstores);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
@@ -591,13 +661,14 @@ static int num_sms() {
   return g_num_sms;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool SWIGLU = false>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD,
-                       const GemmParams& p, int max_ctas, cudaStream_t stream) {
+                       const CUtensorMap& tmD2, const GemmParams& p, int max_ctas,
+                       cudaStream_t stream) {
   using L = GemmSmem<BN, STAGES>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES, SWIGLU>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return -10;
     attr_set = true;
@@ -605,7 +676,8 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   const int total = p.m_tiles * p.n_tiles * p.splitk;
   int grid = total < max_ctas ? total : max_ctas;
   if (grid < 1) grid = 1;
-  gemm_bf16_kernel<BN, STAGES><<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmD, p);
+  gemm_bf16_kernel<BN, STAGES, SWIGLU>
+      <<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmD, tmD2, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -692,6 +764,7 @@ extern "C" int ft_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   p.splitk = splitk;
   p.m_tiles = m_tiles; p.n_tiles = n_tiles; p.k_iters = k_iters;
   p.status = status;
+  p.swiglu_F = 0;
   if (out_dtype == 0) p.out_mode = OUT_BF16;
   else p.out_mode = (accumulate || splitk > 1) ? OUT_F32_ADD : OUT_F32;
   if (out_dtype == 1 && !accumulate && splitk > 1) {
@@ -713,8 +786,39 @@ extern "C" int ft_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   if (rc) return -6;
 
   if (pair) return launch_gemm_pair(tmA, tmB, tmD, p, max_ctas, stream);
-  if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, tmD, p, max_ctas, stream);
-  return launch_gemm<128, 6>(tmA, tmB, tmD, p, max_ctas, stream);
+  if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, tmD, tmD, p, max_ctas, stream);
+  return launch_gemm<128, 6>(tmA, tmB, tmD, tmD, p, max_ctas, stream);
+}
+
+// FC1 with the SwiGLU activation in the epilogue. A is [M][lda] activations, W is [2F][ldw] =
+// [gate rows ; up rows] (both with the reduction index contiguous). Writes Y[M][2F] = alpha * A W^T
+// (bf16, what the backward pass needs) and ACT[M][F] = silu(Y[:, :F]) * Y[:, F:] in one pass.
+// F must be a multiple of 128 (a tile holds 128 gate columns and the matching 128 up columns).
+extern "C" int ft_gemm_swiglu_bf16(const void* A, const void* W, void* Y, void* ACT, int M, int F,
+                                   int K, int lda, int ldw, int ldy, int ldact, float alpha,
+                                   int max_ctas, int* status, cudaStream_t stream) {
+  using namespace ft;
+  if (M <= 0 || F <= 0 || K <= 0) return -1;
+  if (F % 128) return -2;
+  const int sms = num_sms();
+  if (max_ctas <= 0 || max_ctas > sms) max_ctas = sms;
+  GemmParams p;
+  p.M = M; p.N = 2 * F; p.K = K;
+  p.a_mn = 0; p.b_mn = 0;
+  p.out_mode = OUT_BF16;
+  p.alpha = alpha;
+  p.splitk = 1;
+  p.m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
+  p.n_tiles = F / 128;
+  p.k_iters = (K + GEMM_BK - 1) / GEMM_BK;
+  p.status = status;
+  p.swiglu_F = F;
+  CUtensorMap tmA, tmB, tmY, tmAct;
+  if (get_tmap_2d(&tmA, A, 2, M, K, lda, GEMM_BM, GEMM_BK)) return -4;
+  if (get_tmap_2d(&tmB, W, 2, 2 * static_cast<uint64_t>(F), K, ldw, 128, GEMM_BK)) return -5;
+  if (get_tmap_2d(&tmY, Y, 2, M, 2 * static_cast<uint64_t>(F), ldy, 32, 64)) return -6;
+  if (get_tmap_2d(&tmAct, ACT, 2, M, F, ldact, 32, 64)) return -6;
+  return launch_gemm<256, 4, true>(tmA, tmB, tmY, tmAct, p, max_ctas, stream);
 }
 
 extern "C" void ft_tmap_cache_clear() {

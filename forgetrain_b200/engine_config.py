@@ -22,7 +22,7 @@ EXTERNAL_ENV_WHITELIST = frozenset({
     "NCCL_PROTO", "NCCL_MIN_NCHANNELS", "NCCL_NVLS_ENABLE", "NCCL_IB_QPS",
     "TORCH_NCCL_HEARTBEAT_TIMEOUT_SEC", "OUTPUT_DIR", "HF_HOME", "TOKENIZERS_PARALLELISM",
     "FT_PEAK_TFLOPS", "FT_B200_NO_AUTOBUILD", "FT_COMM_MULTIMEM", "FT_COMM_TIMEOUT_MS",
-    "FT_COMM_CTAS", "FT_B200_LIB", "FT_FUSE_ADAM_AG", "FT_GEMM_PAIR",
+    "FT_COMM_CTAS", "FT_B200_LIB", "FT_FUSE_ADAM_AG", "FT_GEMM_PAIR", "FT_FUSE_FC1_SWIGLU",
 })
 
 

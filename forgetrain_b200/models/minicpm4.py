@@ -16,6 +16,8 @@ with r = depth_scale/sqrt(L); embedding * emb_scale; logits = Wout·(rmsnorm(h) 
 """
 from __future__ import annotations
 
+import os
+
 from typing import Callable
 
 import torch
@@ -58,6 +60,8 @@ class MiniCPM4:
         self._head_saved = None
         # set to a dict to have the backward record a few intermediate gradients in it
         self.diagnostics: dict | None = None
+        # FC1 + SwiGLU in one kernel where FC1 is a plain local GEMM (no tensor parallelism)
+        self.fuse_fc1_swiglu = tpn == 1 and os.environ.get("FT_FUSE_FC1_SWIGLU", "1") != "0"
         self._ensure_rope(S)
 
     def _ensure_rope(self, S: int) -> None:
@@ -95,9 +99,14 @@ class MiniCPM4:
         sv.h_mid, n2, sv.rs2 = ops.add_rmsnorm_fwd(
             h_in, o, p[f"{prefix}.ffn_norm.weight"], sp.norm_epsilon,
             tp.gather_dest(f"{prefix}.n2", o.shape[0], o.shape[1]))
-        sv.y1, sv.n2_full = tp.linear_gather(n2, p[f"{prefix}.feed_forward.wfc1.weight"],
-                                             key=f"{prefix}.n2")
-        sv.act = ops.swiglu_fwd(sv.y1)
+        if self.fuse_fc1_swiglu:
+            # one kernel: FC1 with silu(gate) * up computed in its epilogue
+            sv.n2_full = n2
+            sv.y1, sv.act = ops.linear_swiglu_fwd(n2, p[f"{prefix}.feed_forward.wfc1.weight"])
+        else:
+            sv.y1, sv.n2_full = tp.linear_gather(n2, p[f"{prefix}.feed_forward.wfc1.weight"],
+                                                 key=f"{prefix}.n2")
+            sv.act = ops.swiglu_fwd(sv.y1)
         f = tp.linear_scatter(sv.act, p[f"{prefix}.feed_forward.w2.weight"], alpha=r)
         return sv.h_mid, f, sv
 

@@ -73,6 +73,11 @@ def linear_fwd(x, w, alpha: float = 1.0):
     return _pick(x).linear_fwd(x, w, alpha)
 
 
+def linear_swiglu_fwd(x, w, alpha: float = 1.0):
+    """``(y, act)``: FC1 output and ``silu(gate) * up`` of it, fused into one kernel on CUDA."""
+    return _pick(x).linear_swiglu_fwd(x, w, alpha)
+
+
 def linear_dgrad(dy, w, alpha: float = 1.0):
     return _pick(dy).linear_dgrad(dy, w, alpha)
 

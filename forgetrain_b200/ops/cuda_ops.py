@@ -122,6 +122,13 @@ def linear_fwd(x, w, alpha=1.0):
     return gemm.linear_fwd(x, w, alpha=alpha)
 
 
+def linear_swiglu_fwd(x, w, alpha=1.0):
+    if (w.shape[0] // 2) % 128:
+        y = gemm.linear_fwd(x, w, alpha=alpha)
+        return y, swiglu_fwd(y)
+    return gemm.linear_swiglu_fwd(x, w, alpha=alpha)
+
+
 def linear_dgrad(dy, w, alpha=1.0):
     return gemm.linear_dgrad(dy, w, alpha=alpha)
 

@@ -6,6 +6,7 @@ operand majors, so no transposed copies are made:
 * :func:`linear_fwd`   ``y = alpha * x @ w.T``            (bf16 out)
 * :func:`linear_dgrad` ``dx = alpha * dy @ w``            (bf16 out)
 * :func:`linear_wgrad` ``dw (+)= dy.T @ x``               (fp32 out, optional accumulate)
+* :func:`linear_swiglu_fwd` FC1 forward with ``silu(gate) * up`` computed in the epilogue
 
 Plays the role of the reference's ``custom_gemm_<op>_{fwd,dgrad,wgrad}`` shims
 (exports/train_engine_8b/src/training_engine_tensor/custom_gemm.py:81-225) for all five
@@ -56,6 +57,26 @@ def linear_fwd(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None
     _check2d(out, "out", torch.bfloat16)
     gemm_raw(x, w, out, T, N, K, 0, 0, alpha=alpha, **kw)
     return out
+
+
+def linear_swiglu_fwd(x: torch.Tensor, w: torch.Tensor, alpha: float = 1.0,
+                      max_ctas: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+    """FC1 with the activation in the GEMM epilogue: ``y = alpha * x @ w.T`` with
+    ``w = [gate rows ; up rows]`` (``[2F, K]``) and ``act = silu(y[:, :F]) * y[:, F:]``, one kernel.
+    ``act`` is bitwise what ``swiglu_fwd(y)`` returns. ``F`` must be a multiple of 128."""
+    _check2d(x, "x", torch.bfloat16)
+    _check2d(w, "w", torch.bfloat16)
+    T, K = x.shape
+    F = w.shape[0] // 2
+    assert w.shape[1] == K and w.shape[0] == 2 * F and F % 128 == 0
+    y = torch.empty(T, 2 * F, dtype=torch.bfloat16, device=x.device)
+    act = torch.empty(T, F, dtype=torch.bfloat16, device=x.device)
+    rc = _lib.lib().ft_gemm_swiglu_bf16(
+        _lib.ptr(x), _lib.ptr(w), _lib.ptr(y), _lib.ptr(act), c_int(T), c_int(F), c_int(K),
+        c_int(x.stride(0)), c_int(w.stride(0)), c_int(y.stride(0)), c_int(act.stride(0)),
+        c_float(alpha), c_int(max_ctas), _lib.ptr(_lib.status_word(x.device)), _lib.stream())
+    _lib.check_rc(rc, "ft_gemm_swiglu_bf16")
+    return y, act
 
 
 def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,

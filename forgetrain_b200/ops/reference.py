@@ -194,6 +194,11 @@ def linear_fwd(x: torch.Tensor, w: torch.Tensor, alpha: float = 1.0) -> torch.Te
     return (y * alpha).to(x.dtype) if alpha != 1.0 else y.to(x.dtype)
 
 
+def linear_swiglu_fwd(x: torch.Tensor, w: torch.Tensor, alpha: float = 1.0):
+    y = linear_fwd(x, w, alpha)
+    return y, swiglu_fwd(y)
+
+
 def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, alpha: float = 1.0) -> torch.Tensor:
     dx = dy.float() @ w.float()
     return (dx * alpha).to(dy.dtype) if alpha != 1.0 else dx.to(dy.dtype)

@@ -137,6 +137,13 @@ def bench_gemm(args):
             lib["fwd"] = time_ms(lambda: torch.mm(x, w.t(), out=y), args.iters)
             lib["dgrad"] = time_ms(lambda: torch.mm(dy, w, out=dx), args.iters)
             lib["wgrad"] = time_ms(lambda: torch.mm(dy.t(), x), args.iters)
+        if name == "fc1" and (N // 2) % 128 == 0:
+            from forgetrain_b200.ops import cuda_ops as C
+            t_two = time_ms(lambda: C.swiglu_fwd(gemm.linear_fwd(x, w, out=y)), args.iters, args.once)
+            t_one = time_ms(lambda: gemm.linear_swiglu_fwd(x, w), args.iters, args.once)
+            _lib.check_status()
+            emit(kernel="fc1_fwd_plus_swiglu_two_kernels", M=T, N=N, K=K, ms=t_two)
+            emit(kernel="fc1_fwd_swiglu_epilogue", M=T, N=N, K=K, ms=t_one, tflops=fl / t_one / 1e9)
         for k, t in res.items():
             emit(kernel=f"gemm_{name}_{k}", M=T, N=N, K=K, ms=t, tflops=fl / t / 1e9,
                  frac_of_peak=fl / t / 1e9 / pk["bf16_tflops"], peak_kind=pk["kind"],

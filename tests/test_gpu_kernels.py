@@ -61,6 +61,29 @@ def test_gemm_tile_shapes(T, N, K, bn):
     assert rel(dw, 2 * ref) < 1e-3
 
 
+@pytest.mark.parametrize("T,F,K", [(128, 128, 64), (300, 256, 200), (1000, 1024, 256), (4096, 4096, 1024)])
+def test_fc1_with_swiglu_in_the_epilogue(T, F, K):
+    """One kernel writes y = x w^T and act = silu(gate) * up; both must be BITWISE what the plain
+    GEMM followed by the SwiGLU kernel give, and close to the fp32 statement."""
+    x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(2 * F, K, device="cuda") * 0.08).to(torch.bfloat16)
+    y, act = gemm.linear_swiglu_fwd(x, w)
+    y_ref = gemm.linear_fwd(x, w)
+    act_ref = C.swiglu_fwd(y_ref)
+    assert torch.equal(y, y_ref)
+    assert torch.equal(act, act_ref)
+    yf = x.float() @ w.float().t()
+    assert rel(y, yf) < 0.01
+    assert rel(act, torch.nn.functional.silu(yf[:, :F]) * yf[:, F:]) < 0.02
+    y2, act2 = gemm.linear_swiglu_fwd(x, w, alpha=0.5)
+    assert torch.equal(y2, gemm.linear_fwd(x, w, alpha=0.5))
+    assert torch.equal(act2, C.swiglu_fwd(y2))
+    # a width that is not a multiple of 128 takes the two-kernel route through the same front end
+    w3 = w[: 2 * 64].contiguous()
+    y3, act3 = C.linear_swiglu_fwd(x, w3)
+    assert torch.equal(act3, C.swiglu_fwd(gemm.linear_fwd(x, w3)))
+
+
 def test_gemm_strided_views():
     """Operands that are column slices of a wider buffer (row pitch != width)."""
     big = torch.randn(512, 3 * 256, device="cuda").to(torch.bfloat16)

@@ -131,3 +131,26 @@ def test_full_step_graph_matches_eager_and_forward_graph():
         assert (a - tr.model.forward(batch["tokens"]).float()).abs().max() == 0
     assert out[True] == pytest.approx(out[False], rel=5e-3)
     assert norms[True] == pytest.approx(norms[False], rel=5e-2)
+
+
+def test_fused_fc1_swiglu_step_is_bitwise_the_two_kernel_step(monkeypatch):
+    """FC1 with the activation in its epilogue writes the same bits as GEMM + SwiGLU kernel, so the
+    loss and every gradient of a step agree exactly except for the attention backward's atomics."""
+    from forgetrain_b200.models.minicpm4 import MiniCPM4
+    from forgetrain_b200.models.params import ParamStore
+    spec = _spec()
+    tok, lab = _batch(spec)
+    out = []
+    for flag in ("0", "1"):
+        monkeypatch.setenv("FT_FUSE_FC1_SWIGLU", flag)
+        st = ParamStore(spec, "cuda", torch.bfloat16)
+        st.init_random(0, "normal", 0.02)
+        m = MiniCPM4(spec, st)
+        assert m.fuse_fc1_swiglu == (flag == "1")
+        loss = m.forward_backward(tok.cuda(), lab.cuda(), None, 1.0)
+        torch.cuda.synchronize()
+        out.append((float(loss), st.grads["output.weight"].clone(),
+                    st.grads["layers.1.feed_forward.w2.weight"].clone()))
+    assert out[0][0] == out[1][0]                      # forward is bitwise identical
+    assert torch.equal(out[0][1], out[1][1])           # head gradient depends on the forward only
+    assert torch.equal(out[0][2], out[1][2])           # last layer's W2 gradient: act and dy only
