@@ -1,6 +1,6 @@
 """Job launcher: environment variables of a cluster job -> one ``torch.distributed.run`` command.
 
-``python -m forgetrain_b200.launch [--dry-run] [--nproc-per-node N] [-- extra CLI args]``
+``python -m forgetrain_b200.launch [--dry-run] [--job-spec FILE] [--nproc-per-node N] [-- extra CLI args]``
 
 The reference drives its production runs through shell entry scripts that read the job's
 environment, pick a training *stage* and exec ``torchrun -m training_engine_tensor <cmd> ...``
@@ -171,6 +171,26 @@ def plan_from_env(env: dict, nproc_per_node: int | None = None,
                       cli_args=tuple(args), child_env=child)
 
 
+def env_from_job_spec(path: str, base_env: dict | None = None) -> dict:
+    """Environment of a scheduler job spec (``task.envVars`` = list of ``{name, value}``) laid over
+    ``base_env``; ``${VAR}`` references in values are expanded from the combined environment.
+    Spec files for an 8-GPU node live in ``forgetrain_b200/job_specs/`` (the counterpart of the
+    reference's ``job_specs/smoke/*.json``)."""
+    import json
+    import re
+    with open(path) as f:
+        task = json.load(f)["task"]
+    env = dict(base_env or {})
+    for item in task.get("envVars", []):
+        env[item["name"]] = str(item["value"])
+    expand = lambda v: re.sub(r"\$\{(\w+)\}", lambda m: env.get(m.group(1), m.group(0)), v)
+    out = {k: expand(v) for k, v in env.items()}
+    gpus = task.get("resources", {}).get("gpuCount")
+    if gpus and "NPROC_PER_NODE" not in out:
+        out["NPROC_PER_NODE"] = str(gpus)
+    return out
+
+
 def _visible_gpus() -> int:
     import torch
     n = torch.cuda.device_count() if torch.cuda.is_available() else 0
@@ -190,18 +210,21 @@ def main(argv: list[str] | None = None) -> int:
     p = argparse.ArgumentParser(prog="forgetrain_b200.launch", description=__doc__.split("\n\n")[0])
     p.add_argument("--dry-run", action="store_true", help="print the plan and exit")
     p.add_argument("--nproc-per-node", type=int, default=None)
+    p.add_argument("--job-spec", default=None,
+                   help="scheduler job spec (JSON) whose task.envVars are laid over the environment")
     p.add_argument("extra", nargs=argparse.REMAINDER, help="after --: flags passed to the training CLI")
     a = p.parse_args(argv)
     extra = tuple(x for x in a.extra if x != "--")
     try:
-        plan = plan_from_env(dict(os.environ), a.nproc_per_node, extra)
+        job_env = env_from_job_spec(a.job_spec, dict(os.environ)) if a.job_spec else dict(os.environ)
+        plan = plan_from_env(job_env, a.nproc_per_node, extra)
     except LaunchError as e:
         print(f"ERROR: {e}", file=sys.stderr)
         return 2
     print(describe(plan), flush=True)
     if a.dry_run:
         return 0
-    env = dict(os.environ)
+    env = job_env
     env.update(plan.child_env)
     # the launcher's own RANK / WORLD_SIZE are node-level; workers get theirs from the launcher
     env.pop("RANK", None)

@@ -89,3 +89,30 @@ def test_dry_run_exit_codes():
     r = subprocess.run([sys.executable, "-m", "forgetrain_b200.launch", "--dry-run"],
                        env={**env, "STAGE": "stable_2", "HF_DATASET": "x"}, capture_output=True, text=True)
     assert r.returncode == 2 and "RESUME_DIR" in r.stderr
+
+
+def test_bundled_job_specs_give_valid_plans():
+    """Every spec under forgetrain_b200/job_specs launches: its variables pass the stage validation
+    and every flag the plan emits is one the training CLI parses (the reference checks its own
+    specs in tests/test_job_specs.py)."""
+    import json
+    from pathlib import Path
+    from forgetrain_b200.cli import build_parser
+    root = Path(launch.__file__).parent / "job_specs"
+    files = sorted(root.glob("*.json"))
+    assert len(files) >= 4
+    for f in files:
+        task = json.loads(f.read_text())["task"]
+        assert task["resources"]["gpuCount"] == 8 and task["resources"]["gpuModel"] == "b200"
+        assert "replicas" not in task                    # single-node examples
+        env = launch.env_from_job_spec(str(f), {"HOME": "/home/u"})
+        assert all("${HOME}" not in v for v in env.values())
+        plan = launch.plan_from_env(env, repo_root="/job")
+        assert plan.nproc_per_node == 8
+        ns = build_parser().parse_args([plan.subcommand, *plan.cli_args])
+        assert ns.global_batch_size % ns.micro_batch_size == 0
+        if "8b" in f.name:
+            assert ns.cfg_tensor_parallel_size == 2 and ns.grad_accum_steps == 8
+        if "gsm8k" in f.name:
+            assert ns.hf_text_template == "Question: {question}\nAnswer: {answer}"
+            assert "--save-dir" not in plan.cli_args
