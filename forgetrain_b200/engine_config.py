@@ -294,3 +294,42 @@ def print_config_summary(cfg: EngineConfig, prefix: str = "[CONFIG]") -> str:
     line = f"{prefix} " + " ".join(parts)
     print(line, flush=True)
     return line
+
+
+# What the package's own switches outside EngineConfig do (kept next to the whitelist so that the
+# generated table cannot drift from the code that reads them).
+_SWITCH_NOTES = {
+    "FT_PEAK_TFLOPS": "peak used for the MFU lines instead of the measured / nominal one",
+    "FT_B200_NO_AUTOBUILD": "1: never build the native library on import",
+    "FT_B200_LIB": "path of the native library to load instead of the in-tree one",
+    "FT_COMM_MULTIMEM": "0: peer loads instead of multimem (NVSwitch) in the fused collectives",
+    "FT_COMM_TIMEOUT_MS": "limit (ms, default 30000) of every wait on a peer flag in the fused collectives",
+    "FT_COMM_CTAS": "CTAs per fused data-parallel collective launch (default 96)",
+    "FT_FUSE_ADAM_AG": "0: AdamW and the parameter all-gather as two kernels instead of one",
+    "FT_GEMM_PAIR": "1: CTA-pair (cta_group::2) GEMM where the shape allows it",
+    "FT_FUSE_FC1_SWIGLU": "0: FC1 and SwiGLU as two kernels instead of one",
+}
+
+
+def env_table_markdown() -> str:
+    """The declared environment variables as a markdown document (the counterpart of the
+    reference's ENV_WHITELIST.md; ``python -m forgetrain_b200.engine_config`` prints it and
+    ``forgetrain_b200/ENV_VARS.md`` is its committed output)."""
+    d = EngineConfig()
+    lines = ["# Environment variables", "",
+             "Generated by `python -m forgetrain_b200.engine_config`; a test keeps this file in step",
+             "with the code. Anything else read from the environment fails the whitelist test.", "",
+             "## EngineConfig bridge (`engine_config.from_env`; the CLI flag of the same field wins)", "",
+             "| variable | field | default |", "|---|---|---|"]
+    for name, (fld, _) in _ENV_MAP.items():
+        lines.append(f"| `{name}` | `{fld}` | `{getattr(d, fld)!r}` |")
+    lines += ["", "## Switches read where they are used", "", "| variable | effect |", "|---|---|"]
+    for name in sorted(_SWITCH_NOTES):
+        lines.append(f"| `{name}` | {_SWITCH_NOTES[name]} |")
+    lines += ["", "## From the launcher and the libraries (read, never set)", "",
+              ", ".join(f"`{n}`" for n in sorted(EXTERNAL_ENV_WHITELIST - set(_SWITCH_NOTES))), ""]
+    return "\n".join(lines)
+
+
+if __name__ == "__main__":
+    print(env_table_markdown(), end="")

@@ -103,3 +103,12 @@ def test_cli_accepts_reference_spellings(capsys):
                                    "--no-fused-ce", "--custom-gemm", "--rs-buckets", "4"])
     assert a.legacy_clip_grad == 0.25 and a.legacy_lr_warmup_iters == 5
     assert a.noop_fused_ce is True and a.noop_custom_gemm is True and a.cfg_rs_buckets == 4
+
+
+def test_env_table_is_in_step_with_the_code():
+    from pathlib import Path
+    doc = Path(ec.__file__).with_name("ENV_VARS.md").read_text()
+    assert doc == ec.env_table_markdown()
+    # every package switch in the whitelist is explained
+    own = {n for n in ec.EXTERNAL_ENV_WHITELIST if n.startswith("FT_")}
+    assert own == set(ec._SWITCH_NOTES)
