@@ -1,0 +1,96 @@
+"""Properties of the epoch-flag protocol of the peer-memory collectives, checked on a host model
+(threads as ranks): late signals, a missing rank, wrap-around of the 32-bit epoch, buffer reuse
+across consecutive buckets, and the device-side epoch base that a captured graph relies on."""
+import numpy as np
+import pytest
+
+from flag_protocol_model import ERR_WAIT_PEER, FlagBoards, reduce_scatter, run_ranks
+
+
+def _bufs(world, n, seed=0):
+    rng = np.random.default_rng(seed)
+    return [rng.standard_normal(n * world).astype(np.float32) for _ in range(world)]
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_reduce_scatter_with_a_late_rank(world):
+    boards = FlagBoards(world)
+    bufs = _bufs(world, 64)
+    want = sum(b.copy() for b in bufs) / world
+    ss = run_ranks(world, lambda r: reduce_scatter(boards, bufs, r, epoch=1,
+                                                   delay_s=0.05 if r == world - 1 else 0.0))
+    for r in range(world):
+        assert np.allclose(bufs[r][r * 64:(r + 1) * 64], want[r * 64:(r + 1) * 64], atol=1e-6)
+    assert sum(ss) == pytest.approx(float((want ** 2).sum()), rel=1e-5)
+    assert boards.status == [0] * world
+
+
+def test_a_rank_that_never_signals_gives_a_status_not_a_hang():
+    world = 3
+    boards = FlagBoards(world)
+    bufs = _bufs(world, 16)
+    before = [b.copy() for b in bufs]
+    run_ranks(world, lambda r: reduce_scatter(boards, bufs, r, epoch=1, limit_s=0.05,
+                                              skip_signal=(r == 2)))
+    assert all(s == ERR_WAIT_PEER for s in boards.status)
+    for a, b in zip(bufs, before):          # nobody reduced from a buffer that was not ready
+        assert np.array_equal(a, b)
+
+
+def test_consecutive_buckets_reuse_the_flags_with_growing_epochs():
+    """The exit barrier keeps a fast rank from starting bucket k+1 (and overwriting data a slow
+    rank still reads) before everybody has left bucket k."""
+    world = 4
+    boards = FlagBoards(world)
+    data = [_bufs(world, 32, seed=k) for k in range(5)]
+    want = [sum(b.copy() for b in d) / world for d in data]
+
+    def rank_main(r):
+        for k in range(5):
+            reduce_scatter(boards, data[k], r, epoch=k + 1, delay_s=0.002 * ((r + k) % world))
+
+    run_ranks(world, rank_main)
+    for k in range(5):
+        for r in range(world):
+            assert np.allclose(data[k][r][r * 32:(r + 1) * 32], want[k][r * 32:(r + 1) * 32], atol=1e-6)
+    assert boards.status == [0] * world
+
+
+def test_epoch_comparison_survives_wrap_around():
+    world = 2
+    boards = FlagBoards(world)
+    # flags sit just below 2^32 from earlier launches; the next epochs wrap to small numbers
+    boards.flags[:] = 0xFFFFFFFE
+    for epoch in (0xFFFFFFFF, 0x00000000, 0x00000001):
+        bufs = _bufs(world, 8, seed=epoch & 7)
+        want = (bufs[0] + bufs[1]) / 2
+        run_ranks(world, lambda r: reduce_scatter(boards, bufs, r, epoch=epoch))
+        assert np.allclose(bufs[0][:8], want[:8], atol=1e-6) and np.allclose(bufs[1][8:], want[8:], atol=1e-6)
+    assert boards.status == [0, 0]
+    # a stale flag from BEFORE the wrap must not satisfy a wait for an epoch after it
+    boards.flags[0, 0, 1] = 0xFFFFFFF0
+    assert boards.wait(0, 0, 5, limit_s=0.02) is False
+
+
+def test_device_side_base_makes_relative_epochs_replayable():
+    """A captured graph always launches with the same (relative) epochs; the base that its last
+    node advances turns them into fresh absolute ones on every replay."""
+    world = 2
+    boards = FlagBoards(world)
+    per_replay = 3                       # collectives inside the captured step
+    for replay in range(4):
+        for k in range(per_replay):
+            bufs = _bufs(world, 8, seed=10 * replay + k)
+            want = (bufs[0] + bufs[1]) / 2
+            run_ranks(world, lambda r: reduce_scatter(boards, bufs, r, epoch=k + 1))
+            assert np.allclose(bufs[0][:8], want[:8], atol=1e-6)
+        boards.base[:, 0] += per_replay   # what the epoch-advance node does, on every rank
+        boards.base[:, 1] += per_replay
+    assert int(boards.flags[0, 0, 1]) == 4 * per_replay
+    # without the advance a replay would find its epochs already satisfied and skip the wait:
+    stale = FlagBoards(world)
+    stale.signal(1, 0, 1)
+    assert stale.wait(0, 0, 1, limit_s=0.01) is False      # rank 0 itself has not signalled
+    stale.signal(0, 0, 1)
+    assert stale.wait(0, 0, 1, limit_s=0.01) is True
+    assert stale.wait(0, 0, 1, limit_s=0.01) is True       # ... and stays true: epochs must grow
