@@ -110,3 +110,68 @@ def test_reducer_norm_exclusion():
         red.on_grad_ready(ps.name)
     red.wait_all()
     assert float(red.local_sumsq()) == float(store.grads["output.weight"].numel())
+
+
+# ---------------------------------------------------------------------------------------------
+# layout invariants for arbitrary parameter lists (property-based)
+# ---------------------------------------------------------------------------------------------
+from hypothesis import given, settings, strategies as hst
+
+
+@settings(max_examples=200, deadline=None)
+@given(world=hst.integers(1, 16), units=hst.lists(hst.integers(1, 40), min_size=1, max_size=30),
+       target_units=hst.integers(1, 120))
+def test_bucket_layout_invariants(world, units, target_units):
+    sizes = [u * world for u in units]               # the store pads every parameter like this
+    entries = _entries(sizes)
+    target = target_units * world
+    buckets = compute_grad_buckets(entries, world, target)
+    # buckets tile the flat buffer in order, without holes or overlap
+    assert buckets[0].start == 0
+    for a, b in zip(buckets, buckets[1:]):
+        assert b.start == a.start + a.size and b.index == a.index + 1
+    assert buckets[-1].start + buckets[-1].size == sum(sizes)
+    # whole parameters, in flat order, each in exactly one bucket
+    assert [n for b in buckets for n in b.params] == [e[0] for e in entries]
+    for b in buckets:
+        assert b.size == sum(b.param_sizes.values()) and b.size % world == 0
+        off = 0
+        for n in b.params:
+            assert b.param_offsets[n] == off
+            off += b.param_sizes[n]
+        # greedy close: a bucket reaches the target only with its last parameter
+        if b is not buckets[-1]:
+            assert b.size >= target and b.size - b.param_sizes[b.params[-1]] < target
+        # rank shards partition the bucket
+        r = [b.shard_range(k, world) for k in range(world)]
+        assert r[0][0] == b.start and r[-1][1] == b.start + b.size
+        assert all(x[1] == y[0] for x, y in zip(r, r[1:]))
+        assert all(hi - lo == b.shard_size(world) for lo, hi in r)
+
+
+def test_reducer_runs_many_steps_and_resets_its_state():
+    store, red = _reducer()
+    for step in range(3):
+        store.flat_grads.fill_(float(step + 1))
+        for name, off, n in store.entries():
+            store.flat_grads[off + store.numel(name):off + n] = 0
+        red.start_step()
+        for ps in reversed(store.order):              # any arrival order is fine
+            red.on_grad_ready(ps.name)
+        red.wait_all()
+        real = sum(store.numel(p.name) for p in store.order)
+        assert float(red.local_sumsq()) == pytest.approx(real * (step + 1) ** 2, rel=1e-6)
+    red.wait_all()                                    # idempotent outside a step
+    with pytest.raises(RuntimeError):
+        red.on_grad_ready("norm.weight")
+
+
+def test_single_rank_reduction_leaves_gradients_untouched():
+    store, red = _reducer()
+    store.flat_grads.normal_()
+    before = store.flat_grads.clone()
+    red.start_step()
+    for ps in store.order:
+        red.on_grad_ready(ps.name)
+    red.wait_all()
+    assert torch.equal(store.flat_grads, before)
