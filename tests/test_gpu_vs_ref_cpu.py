@@ -34,6 +34,14 @@ def test_gemm_against_cpp(bn):
     assert rel(gemm.linear_wgrad(dy, x, bn=bn), C.linear_wgrad(dy, x)) < 1e-3
 
 
+def test_fc1_swiglu_epilogue_against_cpp():
+    x, w = bf(384, 192), bf(2 * 256, 192, scale=0.08)
+    y, act = gemm.linear_swiglu_fwd(x, w)
+    cy = C.linear_fwd(x, w, 1.0)
+    assert rel(y, cy) < 0.01
+    assert rel(act, C.swiglu_fwd(cy)) < 0.02
+
+
 def test_embedding_norm_rope_swiglu_against_cpp():
     w = bf(512, 256)
     ids = torch.randint(0, 512, (300,), device="cuda")
