@@ -10,7 +10,7 @@ exports/train_engine_8b/src/training_engine_tensor/hf_dataloader.py:42-469.
 """
 from __future__ import annotations
 
-from typing import Callable, Iterable, Iterator
+from typing import Iterable, Iterator
 
 import torch
 

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import dataclasses
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Callable
 
 # Environment variables that come from the launcher / libraries, not from this package.

@@ -7,8 +7,6 @@ optimizer state), contiguous in the last dimension and 16-byte aligned.
 """
 from __future__ import annotations
 
-import math
-
 import torch
 
 from . import _lib, gemm

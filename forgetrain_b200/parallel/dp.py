@@ -105,7 +105,6 @@ class BucketedGradReducer:
                 self.done_events[b.index] = done
 
     def _accumulate_norm(self, b: Bucket) -> None:
-        from .. import ops  # noqa: F401  (keeps import order simple)
         sh = self.shard_view(b)
         if self.is_cuda:
             from ..ops import cuda_ops
