@@ -143,3 +143,39 @@ def test_tp4_with_replicated_kv_heads_matches_tp1():
         out = tr.train_step(data)
         assert float(out["loss"]) == pytest.approx(res[0][0][i], abs=3e-4)
         assert float(out["grad_norm"]) == pytest.approx(res[0][1][i], rel=2e-3)
+
+
+# ------------------------------------------------------------------------------------------
+def _tp_dp_worker(rank, world, steps):
+    """World 4 = TP 2 x DP 2 (consecutive ranks form a TP group): the 8B topology in miniature."""
+    from forgetrain_b200.parallel.topology import init_topology
+    from forgetrain_b200.trainer import Trainer
+    spec = _spec(tie_embeddings=False)
+    topo = init_topology(2, device="cpu", num_kv_groups=spec.num_query_groups)
+    assert (topo.tp_size, topo.dp_size) == (2, 2) and topo.dp_rank == rank // 2
+    tr = Trainer(spec, _cfg(spec, tensor_parallel_size=2, sequence_parallel=True), topo,
+                 seq_length=64, micro_batch_size=2, seed=0)
+    data = _batches(100 + topo.dp_rank, 1, 2, 64, spec.vocab_size)   # one batch per DP replica
+    losses, norms = [], []
+    for _ in range(steps):
+        out = tr.train_step(data)
+        losses.append(float(out["loss"]))
+        norms.append(float(out["grad_norm"]))
+    return losses, norms
+
+
+def test_tp2_x_dp2_matches_one_process_with_two_microbatches():
+    from forgetrain_b200.parallel.topology import Topology
+    from forgetrain_b200.trainer import Trainer
+    res = run_ranks(_tp_dp_worker, 4, 3)
+    for r in range(1, 4):                      # the loss is the global mean on every rank
+        assert res[r][0] == pytest.approx(res[0][0], abs=1e-6)
+        assert res[r][1] == pytest.approx(res[0][1], rel=1e-6)
+    spec = _spec(tie_embeddings=False)
+    tr = Trainer(spec, _cfg(spec), Topology(), seq_length=64, micro_batch_size=2, seed=0)
+    data = _batches(100, 1, 2, 64, spec.vocab_size) + _batches(101, 1, 2, 64, spec.vocab_size)
+    for i in range(3):
+        out = tr.train_step(data)
+        assert float(out["loss"]) == pytest.approx(res[0][0][i], abs=3e-4)
+        # TP-duplicated norm gradients are counted once, sharded ones on every TP rank
+        assert float(out["grad_norm"]) == pytest.approx(res[0][1][i], rel=2e-3)
