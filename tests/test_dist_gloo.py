@@ -179,3 +179,34 @@ def test_tp2_x_dp2_matches_one_process_with_two_microbatches():
         assert float(out["loss"]) == pytest.approx(res[0][0][i], abs=3e-4)
         # TP-duplicated norm gradients are counted once, sharded ones on every TP rank
         assert float(out["grad_norm"]) == pytest.approx(res[0][1][i], rel=2e-3)
+
+
+def _tp_ckpt_worker(rank, world, root):
+    from forgetrain_b200.parallel.topology import init_topology
+    from forgetrain_b200.trainer import run_training_loop
+    spec = _spec(tie_embeddings=False)
+    topo = init_topology(2, device="cpu", num_kv_groups=spec.num_query_groups)
+    cfg = _cfg(spec, tensor_parallel_size=2, sequence_parallel=True)
+    a = run_training_loop(spec=spec, cfg=cfg, topo=topo, num_steps=4, micro_batch_size=1, seq_length=64,
+                          seed=3, save_dir=os.path.join(root, "full"), save_interval=2)
+    b = run_training_loop(spec=spec, cfg=cfg, topo=topo, num_steps=2, micro_batch_size=1, seq_length=64,
+                          seed=3, resume=os.path.join(root, "full", "step_0000002"))
+    return [s["loss"] for s in a["steps"]], [s["loss"] for s in b["steps"]]
+
+
+def test_tp2_x_dp2_per_rank_shards_resume(tmp_path):
+    """With tensor parallelism every TP rank of the first DP replica writes ``rank_<R>.pt`` (its
+    parameter shard plus the DP-gathered optimizer state of that shard); a resumed run continues
+    the loss curve (reference: 8B parameters.py:375-449)."""
+    res = run_ranks(_tp_ckpt_worker, 4, str(tmp_path))
+    d = tmp_path / "full" / "step_0000002"
+    assert sorted(p.name for p in d.iterdir()) == ["rank_0.pt", "rank_1.pt"]
+    st = torch.load(d / "rank_1.pt", map_location="cpu", weights_only=False)
+    assert st["tp_size"] == 2 and st["tp_rank"] == 1 and st["format_version"] == 1
+    # column-parallel weights hold half of the rows, row-parallel ones half of the columns
+    assert st["params"]["layers.0.feed_forward.wfc1.weight"].shape == (256, 128)
+    assert st["params"]["layers.0.feed_forward.w2.weight"].shape == (128, 128)
+    full, resumed = res[0]
+    assert resumed == pytest.approx(full[2:], abs=1e-5)
+    for r in range(1, 4):
+        assert res[r][1] == pytest.approx(resumed, abs=1e-6)
