@@ -4,7 +4,8 @@
     python -m forgetrain_b200.ckpt.convert_to_hf --checkpoint <step dir | training_state.pt> \\
         --output <dir> [--model 0.5b] [--dtype bfloat16]
 
-Writes ``model.safetensors`` and ``config.json``. The fused projection weights are taken apart:
+``--checkpoint`` may also be a step directory of a tensor-parallel run (``rank_<R>.pt`` files):
+the shards are merged back into full tensors first. Writes ``model.safetensors`` and ``config.json``. The fused projection weights are taken apart:
 ``attention.wqkv`` is interleaved per KV group as ``[q_0..q_{g-1} | k | v]`` and becomes
 ``q_proj / k_proj / v_proj``; ``feed_forward.wfc1`` is ``[gate ; up]``. ``tie_word_embeddings``
 is decided by comparing the two tables. Same mapping as the reference's export script
@@ -91,10 +92,23 @@ def hf_config(spec: ModelSpec, tied: bool, dtype: str = "bfloat16") -> dict:
 
 def convert(checkpoint: str, output: str, model: str = "0.5b", dtype: str = "bfloat16") -> Path:
     from safetensors.torch import save_file
-    state = load_resume_checkpoint(checkpoint)
-    params = state["params"]
-    spec = load_model_spec(model, vocab_size=params["tok_embeddings.weight"].shape[0],
-                           tie_embeddings="output.weight" not in params)
+    ranks = sorted(Path(checkpoint).glob("rank_*.pt"), key=lambda q: int(q.stem.split("_")[1])) \
+        if Path(checkpoint).is_dir() else []
+    if ranks:
+        # tensor-parallel run: one parameter shard per TP rank, merged back into full tensors
+        from ..models.params import merge_tp_shards
+        shards = [torch.load(q, map_location="cpu", weights_only=False) for q in ranks]
+        if len(shards) != int(shards[0].get("tp_size", len(shards))):
+            raise ValueError(f"{checkpoint}: found {len(shards)} rank files for tp_size "
+                             f"{shards[0].get('tp_size')}")
+        tied = "output.weight" not in shards[0]["params"]
+        spec = load_model_spec(model, tie_embeddings=tied)
+        params = merge_tp_shards(spec, [sh["params"] for sh in shards])
+    else:
+        state = load_resume_checkpoint(checkpoint)
+        params = state["params"]
+        spec = load_model_spec(model, vocab_size=params["tok_embeddings.weight"].shape[0],
+                               tie_embeddings="output.weight" not in params)
     sd, tied = to_hf_state_dict(params, spec, getattr(torch, dtype))
     out = Path(output)
     out.mkdir(parents=True, exist_ok=True)

@@ -157,6 +157,46 @@ def shard_for_tp(ps: ParamSpec, full: torch.Tensor, spec: ModelSpec, tp_rank: in
     return full.narrow(ps.tp_axis, tp_rank * size, size)
 
 
+def unshard_from_tp(ps: ParamSpec, parts: list[torch.Tensor], spec: ModelSpec) -> torch.Tensor:
+    """Inverse of :func:`shard_for_tp`: the full parameter from the shards of all ``tp`` ranks
+    (in rank order). Replicated parameters come from rank 0."""
+    tp = len(parts)
+    if tp == 1 or ps.tp_axis is None:
+        return parts[0]
+    name = ps.name
+    G, g, D = spec.num_query_groups, spec.heads_per_group, spec.head_dim
+    if name.endswith("attention.wqkv.weight"):
+        if tp <= G:
+            return torch.cat(parts, dim=0)
+        rep = tp // G                      # q heads of a group are spread over `rep` ranks
+        qpr = g // rep
+        H = parts[0].shape[1]
+        groups = []
+        for grp in range(G):
+            mine = [parts[grp * rep + sub].view(qpr + 2, D, H) for sub in range(rep)]
+            groups.append(torch.cat([m[:qpr] for m in mine] + [mine[0][qpr:]], dim=0))
+        return torch.cat(groups, dim=0).reshape(-1, H)
+    if name.endswith("feed_forward.wfc1.weight"):
+        fpr = parts[0].shape[0] // 2
+        return torch.cat([x[:fpr] for x in parts] + [x[fpr:] for x in parts], dim=0)
+    if name in ("tok_embeddings.weight", "output.weight"):
+        return torch.cat(parts, dim=0)[:spec.vocab_size]
+    axis = 1 if name.endswith(("attention.wo.weight", "feed_forward.w2.weight")) else ps.tp_axis
+    return torch.cat(parts, dim=axis)
+
+
+def merge_tp_shards(spec: ModelSpec, shards: list[dict[str, torch.Tensor]],
+                    specs: list[ParamSpec] | None = None) -> dict[str, torch.Tensor]:
+    """Full (TP = 1) named tensors from the per-rank dictionaries of a tensor-parallel run, e.g.
+    the ``params`` / ``exp_avg`` entries of its ``rank_<R>.pt`` files in rank order."""
+    specs = specs or all_param_specs(spec)
+    out = {}
+    for ps in specs:
+        if ps.name in shards[0]:
+            out[ps.name] = unshard_from_tp(ps, [sh[ps.name] for sh in shards], spec)
+    return out
+
+
 def vocab_shard_rows(vocab: int, tp: int) -> int:
     """Rows per vocabulary shard (padded so every shard has the same, 8-aligned size)."""
     per = (vocab + tp - 1) // tp

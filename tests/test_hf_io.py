@@ -104,3 +104,50 @@ def test_text_field_detection_and_multi_column_rendering():
     assert render_text({"question": "q?", "answer": ""}, ["question", "answer"], None) == "q?"
     assert render_text(rows[0], "question", None) == "q?"
     assert render_text(rows[0], None, "Q: {question} A: {answer}") == "Q: q? A: a."
+
+
+@pytest.mark.parametrize("tp,heads", [(2, 4), (4, 8)])
+def test_tp_shards_merge_back_to_the_full_tensors(tp, heads):
+    """shard_for_tp / unshard_from_tp are inverses, also when the TP degree exceeds the number of
+    KV groups (q heads split, k / v replicated) and the vocabulary shards are padded."""
+    from forgetrain_b200.models.params import all_param_specs, merge_tp_shards, shard_for_tp
+    spec = load_model_spec("tiny", num_layers=1, vocab_size=130, hidden_size=128, ffn_hidden_size=256,
+                           num_attention_heads=heads, num_query_groups=2, head_dim=32, tie_embeddings=False)
+    g = torch.Generator().manual_seed(0)
+    full = {ps.name: torch.randn(ps.shape, generator=g) for ps in all_param_specs(spec)}
+    shards = [{ps.name: shard_for_tp(ps, full[ps.name], spec, r, tp) for ps in all_param_specs(spec)}
+              for r in range(tp)]
+    assert shards[0]["output.weight"].shape[0] * tp >= 130          # padded vocabulary rows
+    merged = merge_tp_shards(spec, shards)
+    assert set(merged) == set(full)
+    for name, t in full.items():
+        assert torch.equal(merged[name], t), name
+
+
+def test_export_from_tensor_parallel_rank_files(tmp_path):
+    """``rank_<R>.pt`` shards of a TP run export to the same HF weights as the unsharded model."""
+    from safetensors.torch import load_file
+    from forgetrain_b200.models.params import shard_for_tp
+    spec = _spec()
+    st = ParamStore(spec, "cpu", torch.float32)
+    st.init_random(0)
+    d = tmp_path / "step_0000003"
+    d.mkdir()
+    for r in range(2):
+        params = {ps.name: shard_for_tp(ps, st.params[ps.name], spec, r, 2).clone() for ps in st.specs}
+        torch.save({"format_version": 1, "step": 3, "params": params, "tp_size": 2, "tp_rank": r},
+                   d / f"rank_{r}.pt")
+    spec_path = tmp_path / "spec.toml"
+    spec_path.write_text(
+        "[model]\nname='t'\nvocab_size=128\nhidden_size=128\nnum_layers=2\nnum_attention_heads=4\n"
+        "num_query_groups=2\nhead_dim=32\nffn_hidden_size=256\nseq_length=64\n"
+        "max_position_embeddings=64\nnorm_epsilon=1e-6\nrotary_base=10000.0\ninit_method_std=0.02\n")
+    out = convert(str(d), str(tmp_path / "hf"), model=str(spec_path), dtype="float32")
+    sd = load_file(str(out / "model.safetensors"))
+    want, _ = to_hf_state_dict({n: st.params[n] for n in st.offsets}, spec, torch.float32)
+    assert set(sd) == set(want)
+    for k in want:
+        assert torch.equal(sd[k], want[k]), k
+    (d / "rank_1.pt").unlink()
+    with pytest.raises(ValueError, match="rank files"):
+        convert(str(d), str(tmp_path / "hf2"), model=str(spec_path), dtype="float32")
