@@ -285,15 +285,45 @@ class Trainer:
             else:
                 self.opt.sync_master_from_params()
             return {"step": 0, "num_samples": self.num_samples, "dataloader_state": None}
-        if self.topo.tp_size > 1:
-            if p.is_dir() and not (p / f"rank_{self.topo.tp_rank}.pt").exists():
-                cands = sorted(q for q in p.glob("step_*") if (q / f"rank_{self.topo.tp_rank}.pt").exists())
+        if p.is_dir() and not any(p.glob("rank_*.pt")) and not (p / "training_state.pt").exists():
+            cands = sorted(q for q in p.glob("step_*") if any(q.glob("rank_*.pt")))
+            if cands:
                 p = cands[-1]
-            state = torch.load(p / f"rank_{self.topo.tp_rank}.pt", map_location="cpu", weights_only=False)
+        rank_files = sorted(p.glob("rank_*.pt"), key=lambda q: int(q.stem.split("_")[1])) \
+            if p.is_dir() else []
+        tp, tpr = self.topo.tp_size, self.topo.tp_rank
+        if rank_files and len(rank_files) == tp and tp > 1:
+            # same tensor-parallel degree: every rank reads its own shard
+            state = torch.load(p / f"rank_{tpr}.pt", map_location="cpu", weights_only=False)
             self.store.load_named(state["params"], full_tensors=False)
         else:
-            state = ckpt.load_resume_checkpoint(p, expected_vocab=self.spec.vocab_size)
+            # a checkpoint of another tensor-parallel degree (or of none): rebuild the full
+            # tensors, then keep this rank's shard of parameters and optimizer state
+            from .models.params import merge_tp_shards, shard_for_tp
+            if rank_files:
+                shards = [torch.load(q, map_location="cpu", weights_only=False) for q in rank_files]
+                if len(shards) != int(shards[0].get("tp_size", len(shards))):
+                    raise ValueError(f"{p}: {len(shards)} rank files for tp_size {shards[0].get('tp_size')}")
+                state = dict(shards[0])
+                state["params"] = merge_tp_shards(self.spec, [sh["params"] for sh in shards],
+                                                  self.store.specs)
+                osts = [sh.get("optimizer_state") for sh in shards]
+                if all(osts):
+                    merged = dict(osts[0])
+                    for k in ("master_weights", "exp_avg", "exp_avg_sq"):
+                        merged[k] = merge_tp_shards(self.spec, [o[k] for o in osts], self.store.specs)
+                    state["optimizer_state"] = merged
+            else:
+                state = ckpt.load_resume_checkpoint(p, expected_vocab=self.spec.vocab_size)
             self.store.load_named(state["params"], full_tensors=True)
+            ost = state.get("optimizer_state")
+            if ost and tp > 1:
+                by_name = {ps.name: ps for ps in self.store.specs}
+                ost = dict(ost)
+                for k in ("master_weights", "exp_avg", "exp_avg_sq"):
+                    ost[k] = {n: shard_for_tp(by_name[n], t, self.spec, tpr, tp)
+                              for n, t in ost[k].items() if n in by_name}
+                state["optimizer_state"] = ost
         ost = state.get("optimizer_state")
         if ost:
             self.opt.load_full_state(ost, ost.get("step_count", state.get("step", 0)))

@@ -210,3 +210,36 @@ def test_tp2_x_dp2_per_rank_shards_resume(tmp_path):
     assert resumed == pytest.approx(full[2:], abs=1e-5)
     for r in range(1, 4):
         assert res[r][1] == pytest.approx(resumed, abs=1e-6)
+
+
+def _reshard_worker(rank, world, root, phase):
+    """phase 'save': TP2 run that saves at step 2 of 4. phase 'resume': TP2 run resumed from the
+    checkpoint that a single process (TP1) wrote."""
+    from forgetrain_b200.parallel.topology import init_topology
+    from forgetrain_b200.trainer import run_training_loop
+    spec = _spec(tie_embeddings=False)
+    topo = init_topology(2, device="cpu", num_kv_groups=spec.num_query_groups)
+    cfg = _cfg(spec, tensor_parallel_size=2, sequence_parallel=True)
+    if phase == "save":
+        a = run_training_loop(spec=spec, cfg=cfg, topo=topo, num_steps=4, micro_batch_size=1,
+                              seq_length=64, seed=3, save_dir=os.path.join(root, "tp2"), save_interval=2)
+    else:
+        a = run_training_loop(spec=spec, cfg=cfg, topo=topo, num_steps=2, micro_batch_size=1,
+                              seq_length=64, seed=3, resume=os.path.join(root, "tp1", "step_0000002"))
+    return [s["loss"] for s in a["steps"]]
+
+
+def test_checkpoints_move_between_tensor_parallel_degrees(tmp_path):
+    """A TP2 checkpoint resumes in one process and a one-process checkpoint resumes at TP2: shards
+    (parameters and Adam state) are merged to full tensors and cut again for the new degree."""
+    from forgetrain_b200.parallel.topology import Topology
+    from forgetrain_b200.trainer import run_training_loop
+    tp2 = run_ranks(_reshard_worker, 2, str(tmp_path), "save")[0]
+    spec = _spec(tie_embeddings=False)
+    one = run_training_loop(spec=spec, cfg=_cfg(spec), topo=Topology(), num_steps=2, micro_batch_size=1,
+                            seq_length=64, seed=3, resume=str(tmp_path / "tp2" / "step_0000002"))
+    assert [s["loss"] for s in one["steps"]] == pytest.approx(tp2[2:], abs=3e-4)
+    full = run_training_loop(spec=spec, cfg=_cfg(spec), topo=Topology(), num_steps=4, micro_batch_size=1,
+                             seq_length=64, seed=3, save_dir=str(tmp_path / "tp1"), save_interval=2)
+    back = run_ranks(_reshard_worker, 2, str(tmp_path), "resume")[0]
+    assert back == pytest.approx([s["loss"] for s in full["steps"]][2:], abs=3e-4)
