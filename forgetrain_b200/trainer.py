@@ -276,10 +276,16 @@ class Trainer:
             tensors = mg.load_megatron_checkpoint(p, self.spec, n_mtp, log=log)
             self.store.load_named(tensors, full_tensors=True)
             ost = mg.load_megatron_optimizer_state(p, log=log)
-            if ost is not None and self.topo.tp_size == 1:
+            if ost is not None:
+                from .models.params import shard_for_tp
                 L = self.spec.num_layers
+                by_name = {ps.name: ps for ps in self.store.specs}
+                tp, tpr = self.topo.tp_size, self.topo.tp_rank
                 for k in ("master_weights", "exp_avg", "exp_avg_sq"):
                     ost[k] = mg.rename_state(ost[k], L, n_mtp)
+                    if tp > 1:       # full tensors in the export: keep this rank's shard
+                        ost[k] = {n: shard_for_tp(by_name[n], t, self.spec, tpr, tp)
+                                  for n, t in ost[k].items() if n in by_name}
                 self.opt.load_full_state(ost, ost["step_count"])
                 self.num_samples = ost["num_samples"]
             else:

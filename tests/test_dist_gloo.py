@@ -243,3 +243,46 @@ def test_checkpoints_move_between_tensor_parallel_degrees(tmp_path):
                              seq_length=64, seed=3, save_dir=str(tmp_path / "tp1"), save_interval=2)
     back = run_ranks(_reshard_worker, 2, str(tmp_path), "resume")[0]
     assert back == pytest.approx([s["loss"] for s in full["steps"]][2:], abs=3e-4)
+
+
+def _megatron_tp_worker(rank, world, root):
+    from forgetrain_b200.parallel.topology import init_topology
+    from forgetrain_b200.trainer import Trainer
+    spec = _spec(tie_embeddings=False)
+    topo = init_topology(2, device="cpu", num_kv_groups=spec.num_query_groups)
+    tr = Trainer(spec, _cfg(spec, tensor_parallel_size=2, sequence_parallel=True), topo,
+                 seq_length=64, micro_batch_size=1, seed=0)
+    tr.load(root)
+    st = tr.opt.gather_full_state()
+    name = "layers.1.feed_forward.wfc1.weight"
+    out = tr.train_step(_batches(5, 1, 1, 64, spec.vocab_size))
+    return (tr.opt.step_count, tuple(st["exp_avg"][name].shape), st["exp_avg"][name].clone(),
+            st["master_weights"][name].clone(), tr.store.params[name].shape, float(out["loss"]))
+
+
+def test_megatron_export_with_adam_state_loads_at_tp2(tmp_path):
+    """Every TP rank reads the full Megatron tensors and keeps its shard of the parameters AND of
+    the Adam moments / master weights."""
+    from forgetrain_b200.ckpt import megatron_import as mg
+    from forgetrain_b200.models.params import all_param_specs, shard_for_tp
+    spec = _spec(tie_embeddings=False)
+    g = torch.Generator().manual_seed(1)
+    ours = {ps.name: torch.randn(ps.shape, generator=g) * 0.02 for ps in all_param_specs(spec)}
+    inv = {k: v for k, v in mg.megatron_name_map(spec.num_layers, 0).items()
+           if not (k.startswith("decoder.layers") and (k.endswith("input_layernorm.weight")
+                                                       or k.endswith("pre_mlp_layernorm.weight")))}
+    ck = {k: ours[v].clone() for k, v in inv.items() if v in ours}
+    mom = {k: torch.randn(v.shape, generator=g) * 1e-3 for k, v in ck.items()}
+    torch.save(ck, tmp_path / mg.PARAMS_FILE)
+    torch.save({"master_weights": ck, "exp_avg": mom, "exp_avg_sq": {k: v * v for k, v in mom.items()},
+                "step_count": 9, "num_samples": 18}, tmp_path / mg.OPTIM_FILE)
+    res = run_ranks(_megatron_tp_worker, 2, str(tmp_path))
+    name = "layers.1.feed_forward.wfc1.weight"
+    ps = next(p for p in all_param_specs(spec) if p.name == name)
+    mkey = next(k for k, v in inv.items() if v == name)
+    for r in range(2):
+        steps, shape, m, master, pshape, loss = res[r]
+        assert steps == 10 and shape == (256, 128) == tuple(pshape)
+        assert torch.allclose(m, shard_for_tp(ps, mom[mkey], spec, r, 2))
+        assert torch.allclose(master, shard_for_tp(ps, ours[name], spec, r, 2))
+    assert res[0][5] == pytest.approx(res[1][5], abs=1e-6)
