@@ -173,7 +173,7 @@ def main(argv: list[str] | None = None) -> int:
         if not args.checkpoint_root:
             raise SystemExit("train needs --checkpoint-root")
         resume = resume or args.checkpoint_root
-    save_dir = args.save_dir or args.export_checkpoint_root
+    save_dir = args.save_dir
     if args.command == "checkpoint-train-loop" and not save_dir:
         raise SystemExit("checkpoint-train-loop needs --save-dir")
     source = None
@@ -183,7 +183,13 @@ def main(argv: list[str] | None = None) -> int:
     elif topo.rank == 0:
         print("no --hf-dataset given: using synthetic uniform token ids", flush=True)
     out_dir = os.environ.get("OUTPUT_DIR")
-    report_path = args.export_report or (str(Path(out_dir) / "training_report.json") if out_dir else None)
+    # --export-checkpoint-root names the directory that receives training_report.json
+    # (reference: 0.5B __main__.py:520-530), --export-report a file; OUTPUT_DIR is the fallback
+    report_path = args.export_report
+    if report_path is None and args.export_checkpoint_root:
+        report_path = str(Path(args.export_checkpoint_root) / "training_report.json")
+    if report_path is None and out_dir:
+        report_path = str(Path(out_dir) / "training_report.json")
     rep = run_training_loop(spec=spec, cfg=cfg, topo=topo, num_steps=num_steps, micro_batch_size=mbs,
                             seq_length=seq, num_local_microbatches=n_mb, seed=args.seed,
                             save_dir=save_dir, save_interval=args.save_interval, resume=resume,

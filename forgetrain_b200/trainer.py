@@ -435,6 +435,7 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
     report = {"steps": results, "model": spec.name, "world": topo.world,
               "tokens_per_step": tokens_per_step}
     if report_path and topo.rank == 0:
+        Path(report_path).parent.mkdir(parents=True, exist_ok=True)
         tmp = Path(report_path).with_suffix(".tmp")
         tmp.write_text(json.dumps(report, indent=1))
         os.replace(tmp, report_path)

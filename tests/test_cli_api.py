@@ -105,3 +105,17 @@ def test_grad_norm_diag_prints_local_norms(capsys):
     full = float(text.split("pre_reduce_rank0_full=")[1].split()[0])
     assert full == pytest.approx(out[True][1], rel=1e-4)      # one rank: local norm == global
     assert out[True] == pytest.approx(out[False], rel=1e-6)
+
+
+def test_export_checkpoint_root_receives_the_report_not_checkpoints(tmp_path):
+    """--export-checkpoint-root is the directory of training_report.json (reference: 0.5B
+    __main__.py:520-530); it does not turn on checkpoint saving."""
+    from forgetrain_b200.cli import main
+    root = tmp_path / "export" / "run1"
+    rc = main(["pretrain", "--model", "tiny", "--num-steps", "2", "--device", "cpu",
+               "--micro-batch-size", "1", "--global-batch-size", "1", "--seq-length", "64",
+               "--export-checkpoint-root", str(root)])
+    assert rc == 0
+    rep = json.loads((root / "training_report.json").read_text())
+    assert len(rep["steps"]) == 2
+    assert not list(root.glob("step_*"))
