@@ -177,11 +177,24 @@ def main(argv: list[str] | None = None) -> int:
     if args.command == "checkpoint-train-loop" and not save_dir:
         raise SystemExit("checkpoint-train-loop needs --save-dir")
     source = None
+    # One process standing in for data-parallel rank R of N (no launcher): it reads the data
+    # shard that rank would read. Under a launcher the ranks come from the environment.
+    data_topo = topo
+    if topo.world == 1 and args.data_parallel_rank is not None:
+        n = args.data_parallel_ranks or args.data_parallel_rank + 1
+        if not 0 <= args.data_parallel_rank < n:
+            raise SystemExit(f"--data-parallel-rank {args.data_parallel_rank} outside 0..{n - 1}")
+        data_topo = dataclasses.replace(topo, dp_rank=args.data_parallel_rank, dp_size=n)
     if args.hf_dataset or args.hf_data_files:
         from .data.hf_dataloader import build_hf_dataloader
-        source = build_hf_dataloader(args, spec, mbs, seq, topo)
-    elif topo.rank == 0:
-        print("no --hf-dataset given: using synthetic uniform token ids", flush=True)
+        source = build_hf_dataloader(args, spec, mbs, seq, data_topo)
+    else:
+        if topo.rank == 0:
+            print("no --hf-dataset given: using synthetic uniform token ids", flush=True)
+        if data_topo is not topo:
+            from .data.synthetic import SyntheticTokenSource
+            source = SyntheticTokenSource(spec.vocab_size, mbs, seq, seed=args.seed,
+                                          dp_rank=data_topo.dp_rank, pin=topo.device.type == "cuda")
     out_dir = os.environ.get("OUTPUT_DIR")
     # --export-checkpoint-root names the directory that receives training_report.json
     # (reference: 0.5B __main__.py:520-530), --export-report a file; OUTPUT_DIR is the fallback

@@ -119,3 +119,21 @@ def test_export_checkpoint_root_receives_the_report_not_checkpoints(tmp_path):
     rep = json.loads((root / "training_report.json").read_text())
     assert len(rep["steps"]) == 2
     assert not list(root.glob("step_*"))
+
+
+def test_data_parallel_rank_flag_selects_that_ranks_data(tmp_path):
+    """Without a launcher, --data-parallel-rank R makes the single process read rank R's data
+    shard (the reference uses the flag as the RANK fallback, 0.5B __main__.py:288-305)."""
+    from forgetrain_b200.cli import main
+    losses = {}
+    for r in (0, 1):
+        root = tmp_path / f"r{r}"
+        main(["pretrain", "--model", "tiny", "--num-steps", "1", "--device", "cpu",
+              "--micro-batch-size", "1", "--global-batch-size", "1", "--seq-length", "64",
+              "--data-parallel-rank", str(r), "--data-parallel-ranks", "2",
+              "--export-checkpoint-root", str(root)])
+        losses[r] = json.loads((root / "training_report.json").read_text())["steps"][0]["loss"]
+    assert losses[0] != losses[1]            # same weights, different shard of the data
+    with pytest.raises(SystemExit):
+        main(["pretrain", "--model", "tiny", "--device", "cpu", "--data-parallel-rank", "3",
+              "--data-parallel-ranks", "2"])
