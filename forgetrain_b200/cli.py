@@ -66,6 +66,11 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("command", choices=["pretrain", "train", "checkpoint-train-loop"])
     p.add_argument("--model", default="0.5b", help="built-in spec (tiny, 0.5b, 8b) or a model_spec.toml")
     p.add_argument("--num-steps", type=int, default=None)
+    p.add_argument("--step-indices", nargs="+", type=int, default=None,
+                   help="run len(STEP_INDICES) steps (alternative to --num-steps)")
+    p.add_argument("--tokenized-inputs", default=None,
+                   help=".pt file of pre-tokenised rows (tokens, labels, loss_mask[, position_ids]); "
+                        "the same rows are replayed every step")
     p.add_argument("--global-batch-size", type=int, default=None)
     p.add_argument("--micro-batch-size", type=int, default=None)
     p.add_argument("--grad-accum-steps", type=int, default=None)
@@ -167,15 +172,22 @@ def main(argv: list[str] | None = None) -> int:
     mbs = args.micro_batch_size or spec.micro_batch_size
     seq = args.seq_length or spec.seq_length
     n_mb = _resolve_local_microbatches(args, spec, topo.dp_size, mbs)
-    num_steps = args.num_steps or (200 if args.command == "checkpoint-train-loop" else 1)
+    num_steps = args.num_steps or (len(args.step_indices) if args.step_indices else
+                                   (200 if args.command == "checkpoint-train-loop" else 1))
     resume = args.resume
     if args.command == "train":
         if not args.checkpoint_root:
             raise SystemExit("train needs --checkpoint-root")
         resume = resume or args.checkpoint_root
     save_dir = args.save_dir
-    if args.command == "checkpoint-train-loop" and not save_dir:
-        raise SystemExit("checkpoint-train-loop needs --save-dir")
+    if args.command == "checkpoint-train-loop":
+        # two forms: from a checkpoint on pre-tokenised inputs (the reference's gate run), or a
+        # long run that writes periodic checkpoints
+        if args.tokenized_inputs:
+            resume = resume or args.checkpoint_root
+        elif not save_dir:
+            raise SystemExit("checkpoint-train-loop needs --tokenized-inputs (with --checkpoint-root) "
+                             "or --save-dir")
     source = None
     # One process standing in for data-parallel rank R of N (no launcher): it reads the data
     # shard that rank would read. Under a launcher the ranks come from the environment.
@@ -185,7 +197,16 @@ def main(argv: list[str] | None = None) -> int:
         if not 0 <= args.data_parallel_rank < n:
             raise SystemExit(f"--data-parallel-rank {args.data_parallel_rank} outside 0..{n - 1}")
         data_topo = dataclasses.replace(topo, dp_rank=args.data_parallel_rank, dp_size=n)
-    if args.hf_dataset or args.hf_data_files:
+    if args.tokenized_inputs:
+        from .data.tokenized import FixedBatchSource
+        source = FixedBatchSource(args.tokenized_inputs, mbs, data_topo.dp_rank, data_topo.dp_size,
+                                  n_mb, pin=topo.device.type == "cuda")
+        if args.seq_length is None:
+            seq = source.seq_length
+        elif seq != source.seq_length:
+            raise SystemExit(f"--seq-length {seq} but the tokenised inputs have rows of "
+                             f"{source.seq_length}")
+    elif args.hf_dataset or args.hf_data_files:
         from .data.hf_dataloader import build_hf_dataloader
         source = build_hf_dataloader(args, spec, mbs, seq, data_topo)
     else:

@@ -137,3 +137,33 @@ def test_data_parallel_rank_flag_selects_that_ranks_data(tmp_path):
     with pytest.raises(SystemExit):
         main(["pretrain", "--model", "tiny", "--device", "cpu", "--data-parallel-rank", "3",
               "--data-parallel-ranks", "2"])
+
+
+def test_checkpoint_train_loop_on_pretokenized_inputs(tmp_path):
+    """The reference's gate run: start from a checkpoint, replay one pre-tokenised batch for the
+    requested steps (0.5B __main__.py:140-146, train_loop.py:487-505). The dump of step 0 of a run
+    is a valid --tokenized-inputs file, and replaying it gives that run's first loss."""
+    import torch
+    from forgetrain_b200.cli import main
+    from forgetrain_b200.data.tokenized import FixedBatchSource
+    common = ["--model", "tiny", "--device", "cpu", "--micro-batch-size", "2", "--global-batch-size", "2",
+              "--seq-length", "64"]
+    main(["pretrain", *common, "--num-steps", "2", "--save-dir", str(tmp_path / "ck"), "--save-interval", "1",
+          "--dump-inputs-dir", str(tmp_path / "dump"), "--export-checkpoint-root", str(tmp_path / "a")])
+    first = json.loads((tmp_path / "a" / "training_report.json").read_text())["steps"]
+    inputs = tmp_path / "dump" / "inputs_step0000001.pt"
+    assert inputs.exists()
+    main(["checkpoint-train-loop", "--model", "tiny", "--device", "cpu", "--micro-batch-size", "2",
+          "--checkpoint-root", str(tmp_path / "ck" / "step_0000001"), "--tokenized-inputs", str(inputs),
+          "--step-indices", "1", "2", "3", "--export-checkpoint-root", str(tmp_path / "b")])
+    rep = json.loads((tmp_path / "b" / "training_report.json").read_text())["steps"]
+    assert len(rep) == 3
+    assert rep[0]["loss"] == pytest.approx(first[1]["loss"], abs=1e-6)     # same weights, same rows
+    assert rep[2]["loss"] < rep[0]["loss"]                                  # one batch, memorised
+    # row selection per rank and micro-batch, and the size check
+    data = {"tokens": torch.arange(8 * 4).view(8, 4), "labels": torch.arange(8 * 4).view(8, 4)}
+    src = FixedBatchSource(data, 2, dp_rank=1, dp_size=2, num_local_microbatches=2)
+    assert next(src)["tokens"][:, 0].tolist() == [16, 20] and next(src)["tokens"][:, 0].tolist() == [24, 28]
+    assert next(src)["tokens"][:, 0].tolist() == [16, 20] and float(next(src)["loss_mask"].sum()) == 8.0
+    with pytest.raises(ValueError, match="rows"):
+        FixedBatchSource(data, 4, dp_rank=0, dp_size=2, num_local_microbatches=2)
