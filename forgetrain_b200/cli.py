@@ -169,6 +169,14 @@ def main(argv: list[str] | None = None) -> int:
                          num_kv_groups=spec.num_query_groups)
     if topo.rank == 0:
         ec.print_config_summary(cfg)
+        if cfg.mup_emb_scale > 0 or cfg.mup_depth_scale > 0:
+            res = cfg.mup_depth_scale / spec.num_layers ** 0.5 if cfg.mup_depth_scale > 0 else 1.0
+            print(f"[muP] emb_scale={cfg.mup_emb_scale} depth_scale={cfg.mup_depth_scale} "
+                  f"residual_scale={res:.6f} width_scale={spec.mup_width_scale:.1f}", flush=True)
+        if cfg.mtp_num_layers > 0:
+            print(f"[MTP] num_layers={cfg.mtp_num_layers} "
+                  f"loss_scaling_factor={cfg.mtp_loss_scaling_factor} "
+                  f"per_layer_scale={cfg.mtp_loss_scaling_factor / cfg.mtp_num_layers:.6f}", flush=True)
     mbs = args.micro_batch_size or spec.micro_batch_size
     seq = args.seq_length or spec.seq_length
     n_mb = _resolve_local_microbatches(args, spec, topo.dp_size, mbs)
