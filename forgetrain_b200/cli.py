@@ -243,7 +243,9 @@ def main(argv: list[str] | None = None) -> int:
             d.mkdir(parents=True, exist_ok=True)
             with open(d / "ours_results.jsonl", "w") as f:
                 for s in rep["steps"]:
-                    f.write(json.dumps(s) + "\n")
+                    # `step_time` is the 8B engine's name of the same figure
+                    f.write(json.dumps({**s, "step_time": s.get("total_step_time")}) + "\n")
+            (d / "DONE").write_text("ok\n")           # tombstone a job watcher polls for
         print("DONE", flush=True)
     shutdown()
     return 0

@@ -76,7 +76,9 @@ def test_cli_pretrain_tiny_cpu_writes_report_and_checkpoint(tmp_path):
     rep = json.loads((tmp_path / "out" / "training_report.json").read_text())
     assert len(rep["steps"]) == 3 and {"loss", "grad_norm", "lr", "total_step_time", "mfu_e2e",
                                        "mfu_e2e_standard"} <= set(rep["steps"][0])
-    assert (tmp_path / "out" / "3step" / "ours_results.jsonl").exists()
+    lines = (tmp_path / "out" / "3step" / "ours_results.jsonl").read_text().splitlines()
+    assert len(lines) == 3 and json.loads(lines[0])["step_time"] > 0
+    assert (tmp_path / "out" / "3step" / "DONE").read_text() == "ok\n"
     assert (tmp_path / "ck" / "step_0000002" / "training_state.pt").exists()
     assert (tmp_path / "ck" / "step_0000003" / "training_state.pt").exists()
 
