@@ -127,7 +127,9 @@ def main() -> int:
     ap.add_argument("--model", default="0.5b")
     ap.add_argument("--seq", type=int, default=SEQ)
     ap.add_argument("--mbs", type=int, default=MBS)
-    ap.add_argument("--graph", type=int, default=int(os.environ.get("FT_BENCH_GRAPH", "0")))
+    ap.add_argument("--graph", type=int, default=int(os.environ.get("FT_BENCH_GRAPH", "0")),
+                    help="0: eager; 1: CUDA graph of fwd + loss + bwd per micro-batch; "
+                         "2: one graph for the whole optimizer step")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -155,7 +157,8 @@ def main() -> int:
     K = args.steps
     spec = load_model_spec(args.model)
     cfg = from_spec(spec, dtype="bf16", comm=args.comm, tensor_parallel_size=1,
-                    init_scheme="normal", init_std=0.02, step_cuda_graph=bool(args.graph))
+                    init_scheme="normal", init_std=0.02, step_cuda_graph=args.graph == 1,
+                    full_step_cuda_graph=args.graph == 2)
     topo = init_topology(1)
     trainer = Trainer(spec, cfg, topo, seq_length=args.seq, micro_batch_size=args.mbs, seed=1234)
     source = SyntheticTokenSource(spec.vocab_size, args.mbs, args.seq, seed=1234, dp_rank=topo.dp_rank,
@@ -224,7 +227,7 @@ def main() -> int:
             "config": {"model": MODEL if args.model == "0.5b" else args.model,
                        "global_batch": args.mbs * topo.world, "micro_batch_per_gpu": args.mbs,
                        "seq_len": args.seq, "parallelism": f"dp{topo.world}", "comm": args.comm,
-                       "optimizer": "adamw fp32 master, zero-1", "cuda_graph": bool(args.graph),
+                       "optimizer": "adamw fp32 master, zero-1", "cuda_graph": {0: False, 1: "compute step", 2: "whole step"}.get(args.graph, False),
                        "l2": "inputs larger than L2 (multi-GB activations per step)"},
             "tokens_per_sec_per_gpu": value / topo.world,
             "mfu_standard": flops_std / step_s / peak, "mfu_hardware": flops_hw / step_s / peak,
