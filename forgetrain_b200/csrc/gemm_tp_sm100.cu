@@ -351,7 +351,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int j = c % p.tiles_per_slot;
       const int src = (p.rank + hop) % p.tp;
       if (src != waited_src) {
-        // one thread waits for the peer's "slot written" flag and publishes the verdict, so
+        // one thread waits for the peer's "slot written" flag and publishes the outcome, so
         // that all copy threads take the same branch around the named barriers below
         if (ct == 0) {
           const bool ok = tp_wait_flag(p.flags[p.rank] + 0 * p.tp + src, p.epoch, p.limit_ns,
