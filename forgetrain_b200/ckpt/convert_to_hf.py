@@ -119,7 +119,8 @@ def convert(checkpoint: str, output: str, model: str = "0.5b", dtype: str = "bfl
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
-    ap.add_argument("--checkpoint", required=True)
+    ap.add_argument("--checkpoint", "--input", dest="checkpoint", required=True,
+                    help="step directory, training_state.pt, or a directory of rank_<R>.pt shards")
     ap.add_argument("--output", required=True)
     ap.add_argument("--model", default="0.5b")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16", "float32"])

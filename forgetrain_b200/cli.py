@@ -110,9 +110,11 @@ def build_parser() -> argparse.ArgumentParser:
 def _validate_resume_save_dir_mutex(args) -> None:
     if args.resume and args.save_dir:
         a, b = Path(args.resume).resolve(), Path(args.save_dir).resolve()
-        if a == b or b in a.parents:
-            raise SystemExit("--resume and --save-dir must not point into the same directory: a "
-                             "resumed run would overwrite the checkpoints it was started from")
+        # equal paths only: resuming from <run>/step_N while saving later steps into <run> is
+        # the normal way to continue a run (each step has its own sub-directory)
+        if a == b:
+            raise SystemExit("--resume and --save-dir point at the same directory: a resumed run "
+                             "would overwrite the checkpoint it was started from")
 
 
 def _resolve_local_microbatches(args, spec, dp_size: int, mbs: int) -> int:
@@ -184,8 +186,10 @@ def main(argv: list[str] | None = None) -> int:
                                    (200 if args.command == "checkpoint-train-loop" else 1))
     resume = args.resume
     if args.command == "train":
-        if not args.checkpoint_root:
-            raise SystemExit("train needs --checkpoint-root")
+        # continues a run: from a save directory of this engine (--resume) or from an initial
+        # checkpoint such as a Megatron export (--checkpoint-root); --resume wins when both are given
+        if not args.checkpoint_root and not resume:
+            raise SystemExit("train needs --checkpoint-root or --resume")
         resume = resume or args.checkpoint_root
     save_dir = args.save_dir
     if args.command == "checkpoint-train-loop":

@@ -35,6 +35,16 @@ class Topology:
         return self.world > 1
 
 
+def node_layout(world: int, ranks_per_node: int | None, tp_size: int) -> tuple[bool, bool]:
+    """``(multi_node, tp_groups_inside_a_node)`` for ``world`` ranks launched ``ranks_per_node`` to
+    a node. Tensor-parallel groups are runs of consecutive ranks, so they stay inside a node iff
+    the TP degree divides the ranks per node; data-parallel groups are strided and span nodes as
+    soon as there is more than one. Peer-memory kernels are only used inside a node."""
+    per = ranks_per_node or world
+    multi = per < world
+    return multi, (not multi) or (tp_size <= per and per % tp_size == 0)
+
+
 def resolve_env() -> tuple[int, int, int]:
     return (int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
             int(os.environ.get("LOCAL_RANK", "0")))

@@ -53,7 +53,18 @@ class Trainer:
         if dev.type == "cuda" and self.dtype != torch.bfloat16:
             raise ValueError("the CUDA path is bf16-only; use --dtype bf16 on GPUs")
         dp, tp = topo.dp_size, topo.tp_size
+        # Peer memory only reaches the GPUs of this node. On several nodes the tensor-parallel
+        # groups (consecutive ranks) stay inside a node when the TP degree divides the ranks per
+        # node, so their fused kernels stay; the data-parallel groups span nodes and fall back
+        # to the NCCL reducer / all-gather.
+        from .parallel.topology import node_layout
+        per_node = int(os.environ.get("LOCAL_WORLD_SIZE", "0") or 0) or topo.world
+        multi_node, tp_in_node = node_layout(topo.world, per_node, tp)
+        if multi_node and cfg.comm == "fused" and topo.rank == 0:
+            print(f"[engine] {topo.world} ranks on nodes of {per_node}: data-parallel collectives "
+                  f"use NCCL; tensor-parallel kernels stay fused: {tp_in_node and tp > 1}", flush=True)
         if (cfg.comm == "fused" and dev.type == "cuda" and tp > 1 and cfg.sequence_parallel
+                and tp_in_node
                 and (micro_batch_size * seq_length) % (128 * tp) == 0):
             from .parallel.fused_tp import FusedTPContext
             n_slots = 2 * (spec.num_layers + cfg.mtp_num_layers) + 4
@@ -67,7 +78,7 @@ class Trainer:
         self.fused_dp = None
         self.symm = None
         grad_buffer = param_buffer = None
-        want_fused = (cfg.comm == "fused" and dev.type == "cuda" and dp > 1)
+        want_fused = (cfg.comm == "fused" and dev.type == "cuda" and dp > 1 and not multi_node)
         pad = ALIGN_ELEMS * dp
         if want_fused:
             from .parallel import fused_dp

@@ -169,3 +169,20 @@ def test_checkpoint_train_loop_on_pretokenized_inputs(tmp_path):
     assert next(src)["tokens"][:, 0].tolist() == [16, 20] and float(next(src)["loss_mask"].sum()) == 8.0
     with pytest.raises(ValueError, match="rows"):
         FixedBatchSource(data, 4, dp_rank=0, dp_size=2, num_local_microbatches=2)
+
+
+def test_train_subcommand_needs_a_starting_point_and_accepts_resume_alone(tmp_path):
+    from forgetrain_b200.cli import main
+    from forgetrain_b200.ckpt.convert_to_hf import main as export_main
+    common = ["--model", "tiny", "--device", "cpu", "--micro-batch-size", "1", "--global-batch-size", "1",
+              "--seq-length", "64"]
+    with pytest.raises(SystemExit, match="checkpoint-root or --resume"):
+        main(["train", *common])
+    main(["pretrain", *common, "--num-steps", "1", "--save-dir", str(tmp_path / "run1")])
+    main(["train", *common, "--num-steps", "1", "--resume", str(tmp_path / "run1" / "step_0000001"),
+          "--save-dir", str(tmp_path / "run1")])
+    assert (tmp_path / "run1" / "step_0000002" / "training_state.pt").exists()
+    # the exporter takes the reference's --input spelling too
+    assert export_main(["--input", str(tmp_path / "run1" / "step_0000002"), "--output", str(tmp_path / "hf"),
+                        "--model", "tiny"]) == 0
+    assert (tmp_path / "hf" / "model.safetensors").exists() and (tmp_path / "hf" / "config.json").exists()

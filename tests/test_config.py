@@ -112,3 +112,13 @@ def test_env_table_is_in_step_with_the_code():
     # every package switch in the whitelist is explained
     own = {n for n in ec.EXTERNAL_ENV_WHITELIST if n.startswith("FT_")}
     assert own == set(ec._SWITCH_NOTES)
+
+
+def test_node_layout_decides_where_peer_memory_kernels_may_run():
+    from forgetrain_b200.parallel.topology import node_layout
+    assert node_layout(8, 8, 2) == (False, True)        # one node: everything may be fused
+    assert node_layout(8, None, 2) == (False, True)     # no launcher information: one node
+    assert node_layout(16, 8, 2) == (True, True)        # two nodes: TP pairs stay inside a node
+    assert node_layout(16, 8, 8) == (True, True)
+    assert node_layout(12, 6, 4) == (True, False)       # a TP group would straddle two nodes
+    assert node_layout(32, 8, 16) == (True, False)
