@@ -191,6 +191,10 @@ def main(argv: list[str] | None = None) -> int:
         if not args.checkpoint_root and not resume:
             raise SystemExit("train needs --checkpoint-root or --resume")
         resume = resume or args.checkpoint_root
+    elif args.command == "pretrain" and args.checkpoint_root and not resume:
+        # the 8B engine's `pretrain --checkpoint-root`: start from given weights instead of random
+        # ones (reference: 8B __main__.py:360-455)
+        resume = args.checkpoint_root
     save_dir = args.save_dir
     if args.command == "checkpoint-train-loop":
         # two forms: from a checkpoint on pre-tokenised inputs (the reference's gate run), or a
