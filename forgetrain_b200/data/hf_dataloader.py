@@ -35,30 +35,50 @@ def pack_token_stream(docs: Iterable[list[int]], eos_id: int, seq_length: int,
 
 
 class PackedTokenLoader:
-    """Cycles over pre-packed rows in micro-batches; the cursor is the only state."""
+    """Cycles over pre-packed rows in micro-batches. With ``shuffle`` every pass over the rows
+    uses its own permutation, drawn from ``seed`` and the pass number (the 8B engine shuffles
+    packed rows per epoch, hf_dataloader.py:93-118), so the position in the stream is a pure
+    function of the number of batches drawn and that number is the only state to checkpoint."""
 
-    def __init__(self, rows: torch.Tensor, micro_batch_size: int, pin: bool = False):
+    def __init__(self, rows: torch.Tensor, micro_batch_size: int, pin: bool = False,
+                 shuffle: bool = False, seed: int = 0):
         if rows.shape[0] < micro_batch_size:
             raise ValueError(f"only {rows.shape[0]} packed rows for micro-batch {micro_batch_size}")
         self.rows, self.mbs, self.pin = rows, micro_batch_size, pin
+        self.shuffle, self.seed = shuffle, seed
         self.cursor = 0
         self.batches_drawn = 0
+        self._perm_epoch = -1
+        self._perm: torch.Tensor | None = None
 
     def __iter__(self) -> Iterator[dict]:
         return self
 
+    def _row_index(self, k: int) -> int:
+        """Row of the ``k``-th sample of the stream."""
+        n = self.rows.shape[0]
+        if not self.shuffle:
+            return k % n
+        epoch, pos = divmod(k, n)
+        if epoch != self._perm_epoch:
+            g = torch.Generator().manual_seed(self.seed * 1_000_003 + epoch)
+            self._perm, self._perm_epoch = torch.randperm(n, generator=g), epoch
+        return int(self._perm[pos])
+
     def __next__(self) -> dict:
         n = self.rows.shape[0]
-        idx = [(self.cursor + i) % n for i in range(self.mbs)]
-        self.cursor = (self.cursor + self.mbs) % n
+        first = self.batches_drawn * self.mbs
+        idx = [self._row_index(first + i) for i in range(self.mbs)]
         self.batches_drawn += 1
+        self.cursor = (self.batches_drawn * self.mbs) % n
         chunk = self.rows[idx]
         b = {"tokens": chunk[:, :-1].contiguous(), "labels": chunk[:, 1:].contiguous(),
              "loss_mask": torch.ones(self.mbs, chunk.shape[1] - 1, dtype=torch.float32)}
         return {k: v.pin_memory() for k, v in b.items()} if self.pin else b
 
     def state_dict(self) -> dict:
-        return {"kind": "packed", "cursor": self.cursor, "batches_drawn": self.batches_drawn}
+        return {"kind": "packed", "cursor": self.cursor, "batches_drawn": self.batches_drawn,
+                "shuffle": self.shuffle, "seed": self.seed}
 
     def load_state_dict(self, st: dict) -> None:
         if st and st.get("kind") == "packed":
@@ -140,9 +160,13 @@ def build_hf_dataloader(args, spec, micro_batch_size: int, seq_length: int, topo
         for i, ex in enumerate(dataset):
             if i % topo.dp_size != topo.dp_rank:
                 continue
-            ids = tokenizer(render_text(ex, fields, args.hf_text_template),
-                            add_special_tokens=False)["input_ids"]
+            text = render_text(ex, fields, args.hf_text_template)
+            if not text.strip():
+                continue                                  # empty documents add nothing but an EOS
+            ids = tokenizer(text, add_special_tokens=False)["input_ids"]
             yield [t if t < vocab else vocab - 1 for t in ids]
 
     rows = pack_token_stream(docs(), eos, seq_length, getattr(args, "max_packed_rows", None))
-    return PackedTokenLoader(rows, micro_batch_size, pin=topo.device.type == "cuda")
+    return PackedTokenLoader(rows, micro_batch_size, pin=topo.device.type == "cuda",
+                             shuffle=bool(getattr(args, "hf_shuffle", False)),
+                             seed=int(getattr(args, "seed", 0)) + topo.dp_rank)

@@ -151,3 +151,29 @@ def test_export_from_tensor_parallel_rank_files(tmp_path):
     (d / "rank_1.pt").unlink()
     with pytest.raises(ValueError, match="rank files"):
         convert(str(d), str(tmp_path / "hf2"), model=str(spec_path), dtype="float32")
+
+
+def test_shuffled_loader_permutes_each_pass_and_resumes_from_the_batch_count():
+    rows = torch.arange(10).view(10, 1).repeat(1, 3)          # row i = [i, i, i]
+    ld = PackedTokenLoader(rows, 2, shuffle=True, seed=7)
+    first = [int(t) for _ in range(5) for t in next(ld)["tokens"][:, 0]]
+    second = [int(t) for _ in range(5) for t in next(ld)["tokens"][:, 0]]
+    assert sorted(first) == sorted(second) == list(range(10))     # every pass sees every row once
+    assert first != list(range(10)) and first != second           # ... in its own order
+    again = PackedTokenLoader(rows, 2, shuffle=True, seed=7)
+    assert [int(t) for _ in range(5) for t in next(again)["tokens"][:, 0]] == first
+    other = PackedTokenLoader(rows, 2, shuffle=True, seed=8)      # another rank: another order
+    assert [int(t) for _ in range(5) for t in next(other)["tokens"][:, 0]] != first
+    # resume in the middle of the second pass
+    st = None
+    ld = PackedTokenLoader(rows, 2, shuffle=True, seed=7)
+    for _ in range(7):
+        next(ld)
+    st = ld.state_dict()
+    want = next(ld)["tokens"]
+    ld2 = PackedTokenLoader(rows, 2, shuffle=True, seed=7)
+    ld2.load_state_dict(st)
+    assert torch.equal(next(ld2)["tokens"], want)
+    # unshuffled: sequential with wrap-around, as before
+    seq = PackedTokenLoader(rows, 4)
+    assert [int(t) for _ in range(3) for t in next(seq)["tokens"][:, 0]] == [0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 0, 1]
