@@ -17,21 +17,30 @@ import torch
 
 def pack_token_stream(docs: Iterable[list[int]], eos_id: int, seq_length: int,
                       max_rows: int | None = None) -> torch.Tensor:
-    """Join documents with EOS and cut the stream into rows of ``seq_length + 1`` tokens."""
+    """Join documents with EOS and cut the stream into rows of ``seq_length + 1`` tokens.
+
+    The whole slice is tokenised once, up front, into one int32 array (4 bytes per token), so that
+    drawing a batch is an index operation (the 8B engine's preload mode, hf_dataloader.py:159-237)."""
+    import numpy as np
     row = seq_length + 1
-    buf: list[int] = []
-    rows: list[list[int]] = []
+    want = max_rows * row if max_rows else None
+    parts: list = []
+    total = 0
     for d in docs:
-        buf.extend(d)
-        buf.append(eos_id)
-        while len(buf) >= row:
-            rows.append(buf[:row])
-            buf = buf[row:]
-            if max_rows and len(rows) >= max_rows:
-                return torch.tensor(rows, dtype=torch.int64)
-    if not rows:
+        a = np.empty(len(d) + 1, dtype=np.int32)
+        a[:-1] = d
+        a[-1] = eos_id
+        parts.append(a)
+        total += a.size
+        if want is not None and total >= want:
+            break
+    n_rows = total // row
+    if max_rows:
+        n_rows = min(n_rows, max_rows)
+    if n_rows == 0:
         raise ValueError("dataset too small: not a single full sequence could be packed")
-    return torch.tensor(rows, dtype=torch.int64)
+    flat = np.concatenate(parts)[:n_rows * row]
+    return torch.from_numpy(flat.reshape(n_rows, row).copy())
 
 
 class PackedTokenLoader:
@@ -71,7 +80,7 @@ class PackedTokenLoader:
         idx = [self._row_index(first + i) for i in range(self.mbs)]
         self.batches_drawn += 1
         self.cursor = (self.batches_drawn * self.mbs) % n
-        chunk = self.rows[idx]
+        chunk = self.rows[idx].long()
         b = {"tokens": chunk[:, :-1].contiguous(), "labels": chunk[:, 1:].contiguous(),
              "loss_mask": torch.ones(self.mbs, chunk.shape[1] - 1, dtype=torch.float32)}
         return {k: v.pin_memory() for k, v in b.items()} if self.pin else b
