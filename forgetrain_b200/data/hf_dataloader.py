@@ -43,6 +43,19 @@ def pack_token_stream(docs: Iterable[list[int]], eos_id: int, seq_length: int,
     return torch.from_numpy(flat.reshape(n_rows, row).copy())
 
 
+def doc_position_ids(tokens: torch.Tensor, eos_id: int) -> torch.Tensor:
+    """Positions that restart after every EOS of a packed row (``[rows, seq]`` int32): the input
+    of the document-aware RoPE (reference: ``position_ids`` in 0.5B data.py:93-107 and the
+    per-(s, b) rotary branch of forward.py:97-103)."""
+    S = tokens.shape[1]
+    idx = torch.arange(S, dtype=torch.int64).expand_as(tokens)
+    starts = torch.zeros_like(tokens, dtype=torch.bool)
+    starts[:, 0] = True
+    starts[:, 1:] = tokens[:, :-1] == eos_id
+    last_start = torch.where(starts, idx, torch.zeros_like(idx)).cummax(dim=1).values
+    return (idx - last_start).to(torch.int32)
+
+
 class PackedTokenLoader:
     """Cycles over pre-packed rows in micro-batches. With ``shuffle`` every pass over the rows
     uses its own permutation, drawn from ``seed`` and the pass number (the 8B engine shuffles
@@ -50,11 +63,12 @@ class PackedTokenLoader:
     function of the number of batches drawn and that number is the only state to checkpoint."""
 
     def __init__(self, rows: torch.Tensor, micro_batch_size: int, pin: bool = False,
-                 shuffle: bool = False, seed: int = 0):
+                 shuffle: bool = False, seed: int = 0, doc_positions_eos: int | None = None):
         if rows.shape[0] < micro_batch_size:
             raise ValueError(f"only {rows.shape[0]} packed rows for micro-batch {micro_batch_size}")
         self.rows, self.mbs, self.pin = rows, micro_batch_size, pin
         self.shuffle, self.seed = shuffle, seed
+        self.doc_positions_eos = doc_positions_eos     # not None: add document-relative positions
         self.cursor = 0
         self.batches_drawn = 0
         self._perm_epoch = -1
@@ -83,6 +97,8 @@ class PackedTokenLoader:
         chunk = self.rows[idx].long()
         b = {"tokens": chunk[:, :-1].contiguous(), "labels": chunk[:, 1:].contiguous(),
              "loss_mask": torch.ones(self.mbs, chunk.shape[1] - 1, dtype=torch.float32)}
+        if self.doc_positions_eos is not None:
+            b["position_ids"] = doc_position_ids(b["tokens"], self.doc_positions_eos)
         return {k: v.pin_memory() for k, v in b.items()} if self.pin else b
 
     def state_dict(self) -> dict:
@@ -177,5 +193,6 @@ def build_hf_dataloader(args, spec, micro_batch_size: int, seq_length: int, topo
 
     rows = pack_token_stream(docs(), eos, seq_length, getattr(args, "max_packed_rows", None))
     return PackedTokenLoader(rows, micro_batch_size, pin=topo.device.type == "cuda",
+                             doc_positions_eos=eos if getattr(args, "hf_doc_positions", False) else None,
                              shuffle=bool(getattr(args, "hf_shuffle", False)),
                              seed=int(getattr(args, "seed", 0)) + topo.dp_rank)

