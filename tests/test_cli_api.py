@@ -186,3 +186,27 @@ def test_train_subcommand_needs_a_starting_point_and_accepts_resume_alone(tmp_pa
     assert export_main(["--input", str(tmp_path / "run1" / "step_0000002"), "--output", str(tmp_path / "hf"),
                         "--model", "tiny"]) == 0
     assert (tmp_path / "hf" / "model.safetensors").exists() and (tmp_path / "hf" / "config.json").exists()
+
+
+def test_reference_module_names_resolve_to_this_engine():
+    """``training_engine_tensor.<module>`` exists for every module a user of the reference imports
+    from, each ``__all__`` is a literal list and every name in it is defined (the reference checks
+    its own ``__all__`` lists the same way, tests/test_public_api.py)."""
+    import importlib
+    pkg = ROOT / "training_engine_tensor"
+    names = {"engine_config", "config", "train_loop", "parameters", "optimizer", "nccl", "data",
+             "hf_dataloader", "profiling"}
+    assert names <= {p.stem for p in pkg.glob("*.py")}
+    for name in sorted(names):
+        tree = ast.parse((pkg / f"{name}.py").read_text())
+        alls = [n for n in tree.body if isinstance(n, ast.Assign)
+                and any(isinstance(t, ast.Name) and t.id == "__all__" for t in n.targets)]
+        assert len(alls) == 1
+        exported = ast.literal_eval(alls[0].value)
+        mod = importlib.import_module(f"training_engine_tensor.{name}")
+        assert exported and all(hasattr(mod, x) for x in exported), name
+    from training_engine_tensor.config import load_model_spec, mup_residual_scale, mup_width_scale
+    spec = load_model_spec("0.5b")
+    assert mup_width_scale(spec) == 4.0 and abs(mup_residual_scale(spec) - 1.4 / 24 ** 0.5) < 1e-9
+    from training_engine_tensor.optimizer import compute_lr
+    assert compute_lr(0, 1e-2, 0.0, 10, 100, 0) == 0.0
