@@ -163,6 +163,31 @@ void ftref_swiglu_fwd(const float* y1, float* act, int T, int F, int round_bf16)
     }
 }
 
+// FC1 with the activation folded in, the statement of the device kernel's fused epilogue: per
+// row, gate_j = alpha * <a, w_j>, up_j = alpha * <a, w_{F+j}>, both stored (rounded) into Y, and
+// act_j = silu(gate_j) * up_j computed FROM THE ROUNDED values, as the device epilogue does.
+void ftref_linear_swiglu(const float* A, const float* W, float* Y, float* act, int M, int F, int K,
+                         int lda, int ldw, float alpha, int round_bf16) {
+#pragma omp parallel for schedule(static)
+  for (int m = 0; m < M; ++m) {
+    const float* a = A + (size_t)m * lda;
+    for (int j = 0; j < F; ++j) {
+      double g = 0.0, u = 0.0;
+      const float* wg = W + (size_t)j * ldw;
+      const float* wu = W + (size_t)(F + j) * ldw;
+      for (int k = 0; k < K; ++k) {
+        g += (double)a[k] * wg[k];
+        u += (double)a[k] * wu[k];
+      }
+      const float gate = store(static_cast<float>(g) * alpha, round_bf16);
+      const float up = store(static_cast<float>(u) * alpha, round_bf16);
+      Y[(size_t)m * 2 * F + j] = gate;
+      Y[(size_t)m * 2 * F + F + j] = up;
+      act[(size_t)m * F + j] = store(gate / (1.f + std::exp(-gate)) * up, round_bf16);
+    }
+  }
+}
+
 void ftref_swiglu_bwd(const float* dact, const float* y1, float* dy1, int T, int F,
                       int round_bf16) {
 #pragma omp parallel for schedule(static)

@@ -122,6 +122,17 @@ def swiglu_fwd(y1):
     return _back(act, y1)
 
 
+def linear_swiglu_fwd(x, w, alpha=1.0):
+    """``(y, act)`` of FC1 with the activation folded in (one pass per row, no intermediate)."""
+    X, W = _f(x), _f(w)
+    T, K = X.shape
+    F = W.shape[0] // 2
+    y, act = torch.empty(T, 2 * F), torch.empty(T, F)
+    lib().ftref_linear_swiglu(_p(X), _p(W), _p(y), _p(act), c_int(T), c_int(F), c_int(K),
+                              c_int(X.stride(0)), c_int(W.stride(0)), c_float(alpha), c_int(_rnd(x)))
+    return _back(y, x), _back(act, x)
+
+
 def swiglu_bwd(dact, y1):
     D, Y = _f(dact), _f(y1)
     T, F2 = Y.shape

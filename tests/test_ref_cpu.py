@@ -114,3 +114,18 @@ def test_adamw_and_sumsq():
         R.adamw_step(pb, mb, vb, g, ob, 1e-2, 0.9, 0.95, 1e-8, 0.1, t, clip=0.7)
     assert rel(pa, pb) < 1e-6 and rel(va, vb) < 1e-6 and rel(oa, ob) < 1e-3
     assert math.isclose(float(C.sumsq(g)), float(R.sumsq(g)), rel_tol=1e-5)
+
+
+def test_fused_fc1_swiglu_reference_equals_the_two_op_composition():
+    """The one-pass C++ statement of the fused FC1 epilogue gives bitwise what GEMM followed by
+    SwiGLU gives (the activation is computed from the rounded FC1 output in both)."""
+    torch.manual_seed(0)
+    x = torch.randn(37, 48).to(torch.bfloat16)
+    w = (torch.randn(2 * 24, 48) * 0.2).to(torch.bfloat16)
+    y, act = C.linear_swiglu_fwd(x, w, 0.5)
+    y2 = C.linear_fwd(x, w, 0.5)
+    assert torch.equal(y, y2) and torch.equal(act, C.swiglu_fwd(y2))
+    ry, ract = R.linear_swiglu_fwd(x, w, 0.5)
+    assert rel(y, ry) < 1e-2 and rel(act, ract) < 2e-2
+    yf, actf = C.linear_swiglu_fwd(x.float(), w.float())          # fp32 storage: no rounding
+    assert rel(actf, torch.nn.functional.silu(yf[:, :24]) * yf[:, 24:]) < 1e-6
