@@ -195,7 +195,7 @@ def test_reference_module_names_resolve_to_this_engine():
     import importlib
     pkg = ROOT / "training_engine_tensor"
     names = {"engine_config", "config", "train_loop", "parameters", "optimizer", "nccl", "data",
-             "hf_dataloader", "profiling"}
+             "hf_dataloader", "profiling", "kernels", "forward", "backward"}
     assert names <= {p.stem for p in pkg.glob("*.py")}
     for name in sorted(names):
         tree = ast.parse((pkg / f"{name}.py").read_text())
@@ -210,3 +210,26 @@ def test_reference_module_names_resolve_to_this_engine():
     assert mup_width_scale(spec) == 4.0 and abs(mup_residual_scale(spec) - 1.4 / 24 ** 0.5) < 1e-9
     from training_engine_tensor.optimizer import compute_lr
     assert compute_lr(0, 1e-2, 0.0, 10, 100, 0) == 0.0
+
+
+def test_functional_forward_backward_aliases_drive_the_model():
+    import torch
+    from forgetrain_b200.config import load_model_spec
+    from forgetrain_b200.models.params import ParamStore
+    from training_engine_tensor.backward import backward_pass, cross_entropy_loss_backward
+    from training_engine_tensor.forward import MiniCPM4, forward_pass_with_save
+    spec = load_model_spec("tiny")
+    st = ParamStore(spec, "cpu", torch.float32)
+    st.init_random(0)
+    tok = torch.randint(0, spec.vocab_size, (2, 33), generator=torch.Generator().manual_seed(0))
+    a, b = MiniCPM4(spec, st), None
+    logits = forward_pass_with_save(a, tok[:, :-1].contiguous())
+    loss, dlogits = cross_entropy_loss_backward(a, logits, tok[:, 1:].contiguous())
+    seen = []
+    backward_pass(a, tok[:, :-1].contiguous(), dlogits, grad_sink=seen.append)
+    g1 = st.flat_grads.clone()
+    assert seen[0] == "output.weight" or seen[0] == "norm.weight"
+    assert seen[-1] == "tok_embeddings.weight" and float(g1.abs().sum()) > 0
+    st.flat_grads.zero_()
+    loss2 = MiniCPM4(spec, st).forward_backward(tok[:, :-1].contiguous(), tok[:, 1:].contiguous())
+    assert float(loss2) == float(loss) and torch.equal(st.flat_grads, g1)
