@@ -233,3 +233,14 @@ def test_functional_forward_backward_aliases_drive_the_model():
     st.flat_grads.zero_()
     loss2 = MiniCPM4(spec, st).forward_backward(tok[:, :-1].contiguous(), tok[:, 1:].contiguous())
     assert float(loss2) == float(loss) and torch.equal(st.flat_grads, g1)
+
+
+def test_doctor_reports_the_environment():
+    from forgetrain_b200 import doctor
+    info = doctor.collect()
+    assert {"python", "torch", "devices", "native_library", "peak_tflops_for_mfu", "problems",
+            "can_train_on_gpu", "can_train_on_cpu"} <= set(info)
+    assert info["backends"]["gloo"] is True and info["can_train_on_cpu"] is True
+    assert "gemm_sm100.cu" in info["native_library"]["sources"]
+    if not info["cuda_available"]:
+        assert info["can_train_on_gpu"] is False and doctor.main([]) == 0
