@@ -103,6 +103,8 @@ def build_parser() -> argparse.ArgumentParser:
     hf.add_argument("--hf-data-format", default=None)
     hf.add_argument("--hf-data-files", default=None)
     hf.add_argument("--max-packed-rows", type=int, default=None)
+    hf.add_argument("--hf-stream", action="store_true",
+                    help="tokenise on demand instead of packing the whole slice up front")
     hf.add_argument("--hf-doc-positions", action="store_true",
                     help="rotary positions restart at every document of a packed row")
     hf.add_argument("--hf-shuffle", action=argparse.BooleanOptionalAction, default=True,

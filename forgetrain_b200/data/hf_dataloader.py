@@ -112,6 +112,88 @@ class PackedTokenLoader:
             self.cursor = (self.batches_drawn * self.mbs) % n
 
 
+class StreamingTokenLoader:
+    """Tokenises on demand instead of packing the whole slice up front: for corpora whose token
+    array would not fit in host memory. Documents of this rank's strided slice are visited in a
+    new order on every pass (seed + pass number), joined with EOS and cut into rows of
+    ``seq_length + 1`` (the 0.5B engine's stream, hf_dataloader.py:148-170; the 8B engine keeps the
+    same mode as ``preload=False``). The state is (pass, position in the pass, tokens left over),
+    so a resumed run continues in the middle of a document."""
+
+    def __init__(self, n_docs: int, doc_tokens, eos_id: int, micro_batch_size: int, seq_length: int,
+                 dp_rank: int = 0, dp_size: int = 1, seed: int = 0, shuffle: bool = True,
+                 pin: bool = False):
+        self.doc_ids = list(range(dp_rank, n_docs, dp_size))
+        if not self.doc_ids:
+            raise ValueError(f"no documents for rank {dp_rank} of {dp_size}")
+        self.doc_tokens = doc_tokens          # callable: document index -> list of token ids
+        self.eos, self.mbs, self.row = eos_id, micro_batch_size, seq_length + 1
+        self.seed, self.shuffle, self.pin = seed, shuffle, pin
+        self.epoch, self.pos, self.buf = 0, 0, []
+        self.batches_drawn = 0
+        self._order_epoch, self._order = -1, None
+        self._history: dict[int, dict] = {}
+
+    def __iter__(self):
+        return self
+
+    def state_dict_at(self, batches_consumed: int) -> dict:
+        """State as it was when ``batches_consumed`` batches had been drawn (within the last 16):
+        what a checkpoint must record when a prefetcher has already drawn further."""
+        if batches_consumed == self.batches_drawn:
+            return self.state_dict()
+        return dict(self._history[batches_consumed])
+
+    def _order_of(self, epoch: int) -> list[int]:
+        if epoch != self._order_epoch:
+            order = list(self.doc_ids)
+            if self.shuffle:
+                g = torch.Generator().manual_seed(self.seed * 1_000_003 + epoch)
+                order = [order[i] for i in torch.randperm(len(order), generator=g).tolist()]
+            self._order, self._order_epoch = order, epoch
+        return self._order
+
+    def _fill(self, n_tokens: int) -> None:
+        empty_pass = 0
+        while len(self.buf) < n_tokens:
+            order = self._order_of(self.epoch)
+            if self.pos >= len(order):
+                self.epoch, self.pos = self.epoch + 1, 0
+                empty_pass += 1
+                if empty_pass > 1 and not self.buf:
+                    raise ValueError("the documents of this rank contain no tokens")
+                continue
+            ids = self.doc_tokens(order[self.pos])
+            self.pos += 1
+            if ids:
+                self.buf.extend(ids)
+                self.buf.append(self.eos)
+                empty_pass = 0
+
+    def __next__(self) -> dict:
+        need = self.mbs * self.row
+        # a prefetcher draws ahead of what the model has consumed: remember the last few states
+        self._history[self.batches_drawn] = self.state_dict()
+        self._history.pop(self.batches_drawn - 16, None)
+        self._fill(need)
+        chunk = torch.tensor(self.buf[:need], dtype=torch.int64).view(self.mbs, self.row)
+        self.buf = self.buf[need:]
+        self.batches_drawn += 1
+        b = {"tokens": chunk[:, :-1].contiguous(), "labels": chunk[:, 1:].contiguous(),
+             "loss_mask": torch.ones(self.mbs, self.row - 1, dtype=torch.float32)}
+        return {k: v.pin_memory() for k, v in b.items()} if self.pin else b
+
+    def state_dict(self) -> dict:
+        return {"kind": "stream", "epoch": self.epoch, "pos": self.pos, "buf": list(self.buf),
+                "batches_drawn": self.batches_drawn}
+
+    def load_state_dict(self, st: dict) -> None:
+        if st and st.get("kind") == "stream":
+            self.epoch, self.pos = int(st["epoch"]), int(st["pos"])
+            self.buf = list(st.get("buf", []))
+            self.batches_drawn = int(st.get("batches_drawn", 0))
+
+
 _COMMON_TEXT_COLUMNS = ("text", "content", "input", "sentence", "document")
 
 
@@ -180,6 +262,18 @@ def build_hf_dataloader(args, spec, micro_batch_size: int, seq_length: int, topo
         fields = detect_text_fields(dataset)
         if topo.rank == 0:
             print(f"[hf_dataloader] text_fields={fields}", flush=True)
+
+    if getattr(args, "hf_stream", False):
+        def doc_tokens(i: int) -> list[int]:
+            text = render_text(dataset[i], fields, args.hf_text_template)
+            if not text.strip():
+                return []
+            ids = tokenizer(text, add_special_tokens=False)["input_ids"]
+            return [t if t < vocab else vocab - 1 for t in ids]
+        return StreamingTokenLoader(len(dataset), doc_tokens, eos, micro_batch_size, seq_length,
+                                    topo.dp_rank, topo.dp_size, seed=int(getattr(args, "seed", 0)),
+                                    shuffle=bool(getattr(args, "hf_shuffle", True)),
+                                    pin=topo.device.type == "cuda")
 
     def docs():
         for i, ex in enumerate(dataset):

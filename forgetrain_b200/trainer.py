@@ -436,9 +436,12 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
         done = step + 1
         if save_dir and ckpt.should_save_after_step(done, start_step + num_steps, save_interval,
                                                     start_step):
-            ds = dict(getattr(source, "state_dict", dict)())
-            if "batches_drawn" in ds:   # the prefetcher reads ahead: record what was consumed
-                ds["batches_drawn"] = consumed
+            if hasattr(source, "state_dict_at"):   # a stream cannot be rewound by a count alone
+                ds = source.state_dict_at(consumed)
+            else:
+                ds = dict(getattr(source, "state_dict", dict)())
+                if "batches_drawn" in ds:   # the prefetcher reads ahead: record what was consumed
+                    ds["batches_drawn"] = consumed
             trainer.save(save_dir, done, dataloader_state=ds)
     ckpt.wait_for_async_save()
     if profiler:

@@ -189,3 +189,53 @@ def test_document_relative_positions():
     b = next(PackedTokenLoader(rows, 1, doc_positions_eos=0))
     assert b["position_ids"].dtype == torch.int32 and b["position_ids"].shape == b["tokens"].shape
     assert "position_ids" not in next(PackedTokenLoader(rows, 1))
+
+
+def test_streaming_loader_visits_every_document_each_pass_and_resumes_mid_document():
+    from forgetrain_b200.data.hf_dataloader import StreamingTokenLoader
+    docs = {i: [100 + i] * (3 + i % 4) for i in range(12)}          # doc i = its own id repeated
+    docs[5] = []                                                     # an empty document is skipped
+    mk = lambda **kw: StreamingTokenLoader(12, lambda i: docs[i], 0, 2, 7, seed=3, **kw)
+    ld = mk(dp_rank=1, dp_size=2)                                    # odd documents only
+    seen, stream = set(), []
+    for _ in range(6):
+        b = next(ld)
+        assert b["tokens"].shape == (2, 7) and torch.equal(b["labels"][:, :-1], b["tokens"][:, 1:])
+        stream += [int(t) for row in torch.cat([b["tokens"], b["labels"][:, -1:]], 1) for t in row]
+    seen = {t - 100 for t in stream if t >= 100}
+    assert seen == {1, 3, 7, 9, 11}                                  # rank's slice, 5 is empty
+    first_pass = [t for t in stream if t != 0][:sum(len(docs[i]) for i in (1, 3, 7, 9, 11))]
+    order = list(dict.fromkeys(first_pass))
+    assert sorted(order) == [101, 103, 107, 109, 111] and order != [101, 103, 107, 109, 111]
+    # resume: same continuation from the saved state, in the middle of a document
+    a = mk()
+    for _ in range(3):
+        next(a)
+    st = a.state_dict()
+    want = [next(a)["tokens"] for _ in range(3)]
+    b2 = mk()
+    b2.load_state_dict(st)
+    assert all(torch.equal(next(b2)["tokens"], w) for w in want)
+    with pytest.raises(ValueError, match="no tokens"):
+        next(StreamingTokenLoader(3, lambda i: [], 0, 1, 4))
+
+
+def test_streaming_loader_checkpoint_ignores_prefetch_read_ahead(tmp_path):
+    """A run on the streaming loader, saved while the prefetcher had drawn two batches ahead,
+    resumes on exactly the batch the model would have seen next."""
+    from forgetrain_b200.data.hf_dataloader import StreamingTokenLoader
+    from forgetrain_b200.engine_config import from_spec
+    from forgetrain_b200.trainer import run_training_loop
+    spec = load_model_spec("tiny")
+    g = torch.Generator().manual_seed(0)
+    docs = [torch.randint(1, spec.vocab_size, (int(n),), generator=g).tolist()
+            for n in torch.randint(20, 90, (40,), generator=g)]
+    mk = lambda: StreamingTokenLoader(len(docs), lambda i: docs[i], 0, 1, 32, seed=1)
+    cfg = from_spec(spec, dtype="fp32", comm="nccl", warmup_iters=0, data_prefetch_depth=2)
+    kw = dict(spec=spec, cfg=cfg, topo=Topology(), micro_batch_size=1, seq_length=32, seed=0)
+    full = run_training_loop(num_steps=4, data_source=mk(), save_dir=str(tmp_path / "ck"),
+                             save_interval=2, **kw)
+    rest = run_training_loop(num_steps=2, data_source=mk(), resume=str(tmp_path / "ck" / "step_0000002"),
+                             **kw)
+    assert [s["loss"] for s in rest["steps"]] == pytest.approx([s["loss"] for s in full["steps"]][2:],
+                                                               abs=1e-6)
