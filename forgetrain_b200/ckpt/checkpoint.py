@@ -82,7 +82,10 @@ def save_checkpoint(save_dir: str | os.PathLike, step: int, *, params: dict, par
         "step": int(step),
         "num_samples": int(num_samples),
         "param_names": list(param_names),
-        "params": {k: v.detach().to("cpu") for k, v in params.items()},
+        # a snapshot the writer thread owns: `.to("cpu")` copies device tensors but aliases host
+        # ones, which training would go on modifying while the file is written
+        "params": {k: (v.detach().to("cpu") if v.device.type != "cpu" else v.detach().clone())
+                   for k, v in params.items()},
         "optimizer_state": optimizer_state,
         "dataloader_state": dataloader_state or {},
     }

@@ -72,3 +72,27 @@ def test_save_boundary_policy():
     assert f(2, 10, 2) and not f(3, 10, 2) and f(10, 10, 0) and f(10, 10, 3)
     assert not f(5, 10, 0)
     assert not f(4, 10, 2, start_step=4)
+
+
+def test_async_save_snapshots_host_tensors(tmp_path, monkeypatch):
+    """The writer thread must own its data: parameters that already live on the host are cloned
+    on the caller's thread, so a training step that runs while the file is being written cannot
+    leak into the checkpoint."""
+    import threading
+    import torch
+    gate = threading.Event()
+    real = ck._write_atomic
+
+    def slow_write(payload, path):
+        gate.wait(10)                       # hold the writer until the caller has changed the tensor
+        real(payload, path)
+
+    monkeypatch.setattr(ck, "_write_atomic", slow_write)
+    w = torch.zeros(8)
+    ck.save_checkpoint(tmp_path, 1, params={"w": w}, param_names=["w"], optimizer_state=None,
+                       async_io=True)
+    w.fill_(7.0)                            # "the next training step"
+    gate.set()
+    ck.wait_for_async_save()
+    st = ck.load_resume_checkpoint(tmp_path / "step_0000001")
+    assert float(st["params"]["w"].sum()) == 0.0
