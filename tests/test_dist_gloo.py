@@ -286,3 +286,35 @@ def test_megatron_export_with_adam_state_loads_at_tp2(tmp_path):
         assert torch.allclose(m, shard_for_tp(ps, mom[mkey], spec, r, 2))
         assert torch.allclose(master, shard_for_tp(ps, ours[name], spec, r, 2))
     assert res[0][5] == pytest.approx(res[1][5], abs=1e-6)
+
+
+def _dp_save_worker(rank, world, root):
+    from forgetrain_b200.parallel.topology import init_topology
+    from forgetrain_b200.trainer import run_training_loop
+    spec = _spec()
+    topo = init_topology(1, device="cpu")
+    rep = run_training_loop(spec=spec, cfg=_cfg(spec), topo=topo, num_steps=2, micro_batch_size=1,
+                            seq_length=64, seed=3, save_dir=os.path.join(root, "dp2"), save_interval=2)
+    tr = rep["trainer"]
+    st = tr.opt.gather_full_state()
+    return tr.store.named_cpu_params(), st["exp_avg"]["norm.weight"], st["master_weights"]["norm.weight"]
+
+
+def test_a_dp2_checkpoint_loads_in_one_process(tmp_path):
+    """The checkpoint does not depend on the number of data-parallel ranks that wrote it: ZeRO-1
+    shards of the optimizer state are gathered before the write."""
+    from forgetrain_b200.parallel.topology import Topology
+    from forgetrain_b200.trainer import Trainer
+    res = run_ranks(_dp_save_worker, 2, str(tmp_path))
+    params, m_norm, master_norm = res[0]
+    spec = _spec()
+    tr = Trainer(spec, _cfg(spec), Topology(), seq_length=64, micro_batch_size=1, seed=99)
+    state = tr.load(str(tmp_path / "dp2" / "step_0000002"))
+    assert state["step"] == 2 and tr.opt.step_count == 2
+    for name, t in params.items():
+        assert torch.equal(tr.store.params[name], t), name
+    full = tr.opt.gather_full_state()
+    assert torch.equal(full["exp_avg"]["norm.weight"], m_norm)
+    assert torch.equal(full["master_weights"]["norm.weight"], master_norm)
+    out = tr.train_step(_batches(1, 1, 1, 64, spec.vocab_size))
+    assert torch.isfinite(out["loss"]).all() and tr.opt.step_count == 3
