@@ -31,7 +31,7 @@ class EngineConfig:
     # ---- precision / debug ----
     dtype: str = "bf16"                  # compute dtype: bf16 (GPU) or fp32 (CPU plumbing runs)
     no_grad_clip: bool = False
-    grad_diag: bool = False
+    grad_diag: bool = False              # accepted; the reference declares it and never reads it either
     grad_norm_diag: bool = False
     emit_loss_lines: bool = False
     serial_streams: bool = False         # force every side stream onto the main stream
@@ -40,8 +40,8 @@ class EngineConfig:
     wgrad_overlap: bool = True           # reduce buckets while backward is still running
     wgrad_bucket_target_elems: int = 100 * 1024 * 1024
     opt_allgather_overlap: bool = True
-    async_loss_ar: bool = True
-    sharded_optimizer: bool = True       # ZeRO-1
+    async_loss_ar: bool = True           # accepted; the loss all-reduce never blocks the host here
+    sharded_optimizer: bool = True       # ZeRO-1; False: all-reduced grads, full Adam state per rank
     data_prefetch_depth: int = 2
     rs_buckets: int = 32                 # 8B-style: number of layer-aligned buckets (0 = by size)
     tensor_parallel_size: int = 1

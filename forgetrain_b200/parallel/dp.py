@@ -28,7 +28,8 @@ from .buckets import Bucket, compute_grad_buckets
 class BucketedGradReducer:
     def __init__(self, flat_grads: torch.Tensor, entries, world: int, rank: int, group,
                  target_elems: int, backend: str = "nccl", overlap: bool = True,
-                 norm_exclude: list[tuple[int, int]] | None = None, fused=None):
+                 norm_exclude: list[tuple[int, int]] | None = None, fused=None,
+                 all_reduce: bool = False):
         self.flat = flat_grads
         self.world, self.rank, self.group = world, rank, group
         self.backend = backend
@@ -41,6 +42,9 @@ class BucketedGradReducer:
         self.pending = [0] * len(self.buckets)
         self.seen: set[str] = set()
         self.fused = fused
+        # True: every rank ends up with the WHOLE reduced bucket (unsharded optimizer); the norm
+        # is still accumulated over this rank's shard only, so the sum over ranks stays correct
+        self.all_reduce = all_reduce
         # ranges (absolute offsets) left out of the norm on this rank (TP-duplicated params)
         self.norm_exclude = norm_exclude or []
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=flat_grads.device)
@@ -94,7 +98,7 @@ class BucketedGradReducer:
             else:
                 view = self.bucket_view(b)
                 view.mul_(1.0 / self.world)
-                if self.is_cuda:
+                if self.is_cuda and not self.all_reduce:
                     dist.reduce_scatter_tensor(self.shard_view(b), view, group=self.group)
                 else:
                     dist.all_reduce(view, group=self.group)

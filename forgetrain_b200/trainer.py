@@ -78,7 +78,12 @@ class Trainer:
         self.fused_dp = None
         self.symm = None
         grad_buffer = param_buffer = None
-        want_fused = (cfg.comm == "fused" and dev.type == "cuda" and dp > 1 and not multi_node)
+        # SHARDED_OPTIMIZER=0: every rank keeps the whole optimizer state and updates every
+        # parameter itself; gradients are all-reduced by the library and nothing is gathered
+        # (the reference's non-ZeRO path, 0.5B optimizer.py:569-630). Costs dp x the state memory.
+        sharded = cfg.sharded_optimizer or dp == 1
+        want_fused = (cfg.comm == "fused" and dev.type == "cuda" and dp > 1 and not multi_node
+                      and sharded)
         pad = ALIGN_ELEMS * dp
         if want_fused:
             from .parallel import fused_dp
@@ -118,15 +123,19 @@ class Trainer:
         self.reducer = BucketedGradReducer(
             self.store.flat_grads, self.store.entries(), dp, topo.dp_rank, topo.dp_group, target,
             backend=cfg.comm, overlap=cfg.wgrad_overlap and not cfg.serial_streams,
-            norm_exclude=norm_exclude, fused=self.fused_dp)
+            norm_exclude=norm_exclude, fused=self.fused_dp, all_reduce=not sharded)
         norm_reduce = None
         if topo.world > 1:
             if self.fused_dp is not None and tp == 1:
                 norm_reduce = self.fused_dp.all_reduce_small
             else:
                 norm_reduce = (lambda t: dist.all_reduce(t))  # world: DP shards x TP shards
+        opt_buckets, opt_world, opt_rank = self.reducer.buckets, dp, topo.dp_rank
+        if not sharded:
+            from .parallel.buckets import compute_grad_buckets
+            opt_buckets, opt_world, opt_rank = compute_grad_buckets(self.store.entries(), 1, target), 1, 0
         self.opt = ShardedAdamW(
-            self.store, self.reducer.buckets, dp, topo.dp_rank, topo.dp_group,
+            self.store, opt_buckets, opt_world, opt_rank, topo.dp_group if sharded else None,
             beta1=cfg.adam_beta1, beta2=cfg.adam_beta2, eps=cfg.adam_eps,
             weight_decay=cfg.weight_decay,
             max_grad_norm=0.0 if cfg.no_grad_clip else cfg.max_grad_norm,

@@ -318,3 +318,28 @@ def test_a_dp2_checkpoint_loads_in_one_process(tmp_path):
     assert torch.equal(full["master_weights"]["norm.weight"], master_norm)
     out = tr.train_step(_batches(1, 1, 1, 64, spec.vocab_size))
     assert torch.isfinite(out["loss"]).all() and tr.opt.step_count == 3
+
+
+def _unsharded_worker(rank, world, sharded):
+    from forgetrain_b200.parallel.topology import init_topology
+    from forgetrain_b200.trainer import Trainer
+    spec = _spec()
+    topo = init_topology(1, device="cpu")
+    tr = Trainer(spec, _cfg(spec, sharded_optimizer=sharded), topo, seq_length=64, micro_batch_size=2,
+                 seed=0)
+    data = _batches(100 + rank, 1, 2, 64, spec.vocab_size)
+    losses = [float(tr.train_step(data)["loss"]) for _ in range(3)]
+    return losses, tr.store.named_cpu_params(), tr.opt.master.numel(), float(tr.opt.grad_norm)
+
+
+def test_unsharded_optimizer_matches_zero1():
+    """SHARDED_OPTIMIZER=0: all-reduced gradients and a full Adam state on every rank give the
+    same training as the ZeRO-1 path, at twice the optimizer memory on two ranks."""
+    z = run_ranks(_unsharded_worker, 2, True)
+    u = run_ranks(_unsharded_worker, 2, False)
+    assert u[0][0] == pytest.approx(z[0][0], abs=1e-6) and u[1][0] == pytest.approx(u[0][0], abs=1e-7)
+    assert u[0][3] == pytest.approx(z[0][3], rel=1e-6)
+    for name, t in z[0][1].items():
+        assert torch.allclose(u[0][1][name], t, atol=1e-6), name
+        assert torch.equal(u[0][1][name], u[1][1][name]), name       # replicas stay identical
+    assert u[0][2] == 2 * z[0][2]
