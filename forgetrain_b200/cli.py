@@ -133,7 +133,15 @@ def _resolve_local_microbatches(args, spec, dp_size: int, mbs: int) -> int:
         if gbs % (mbs * dp_size):
             raise SystemExit(f"global batch {gbs} is not a multiple of micro-batch {mbs} x DP {dp_size}")
         return gbs // (mbs * dp_size)
-    return max(1, spec.grad_accum_steps or 1)
+    if getattr(args, "command", None) == "checkpoint-train-loop" and getattr(args, "tokenized_inputs", None):
+        return 1              # the gate run replays one micro-batch per rank unless told otherwise
+    if spec.grad_accum_steps:
+        return spec.grad_accum_steps
+    # no flag: the model spec's global batch, as in the reference CLI (its defaults come from
+    # model_spec.toml); when this world cannot split it evenly, one micro-batch per step
+    if spec.global_batch_size and spec.global_batch_size % (mbs * dp_size) == 0:
+        return spec.global_batch_size // (mbs * dp_size)
+    return 1
 
 
 def main(argv: list[str] | None = None) -> int:

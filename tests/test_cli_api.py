@@ -244,3 +244,23 @@ def test_doctor_reports_the_environment():
     assert "gemm_sm100.cu" in info["native_library"]["sources"]
     if not info["cuda_available"]:
         assert info["can_train_on_gpu"] is False and doctor.main([]) == 0
+
+
+def test_batch_defaults_come_from_the_model_spec():
+    """No batch flags: micro-batch, sequence length and global batch are the model spec's
+    (the reference pins the same in tests/test_cli_defaults.py)."""
+    import types
+    from forgetrain_b200.cli import _resolve_local_microbatches, build_parser
+    from forgetrain_b200.config import load_model_spec
+    a = build_parser().parse_args(["pretrain"])
+    assert a.micro_batch_size is None and a.global_batch_size is None and a.seq_length is None
+    s05, s8 = load_model_spec("0.5b"), load_model_spec("8b")
+    assert (s05.micro_batch_size, s05.global_batch_size, s05.seq_length) == (10, 160, 4096)
+    assert _resolve_local_microbatches(a, s05, 1, s05.micro_batch_size) == 16
+    assert _resolve_local_microbatches(a, s05, 8, s05.micro_batch_size) == 2
+    assert _resolve_local_microbatches(a, s05, 3, s05.micro_batch_size) == 1      # 160 / 30: no
+    assert _resolve_local_microbatches(a, s8, 4, s8.micro_batch_size) == 8        # the spec's GAS
+    b = build_parser().parse_args(["pretrain", "--global-batch-size", "40"])
+    assert _resolve_local_microbatches(b, s05, 2, 10) == 2
+    with pytest.raises(SystemExit):
+        _resolve_local_microbatches(b, s05, 3, 10)
