@@ -99,7 +99,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = warp_idx_uniform();
   const int lane = threadIdx.x & 31;
 
   // work decomposition: kv tile ascending = heavy first
@@ -212,8 +212,9 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // ---------------- MMA issuer ----------------
+    {
+      // ---------------- MMA issuer: the whole warp runs the loop and the waits, one elected
+      // lane issues (descriptors and loop state stay warp-uniform) ----------------
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       const uint32_t idesc_dkv = make_idesc_bf16(128, D, 1, 1);   // P^T / dS^T: MN-major A
       const uint32_t idesc_dq = make_idesc_bf16(128, D, 0, 1);    // dS: K-major A
@@ -231,10 +232,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       constexpr uint32_t STG = (2 * L::TILE) >> 4, TL = L::TILE >> 4, BUF = 32768 >> 4;
 #define FT_KOFF(kk) ((((kk) / 4) * 16384 + ((kk) % 4) * 32) >> 4)
 #define FT_MNOFF(kk) (((kk) * 2048) >> 4)
+      auto wait_qdo = [&](int n) {
+        mbar_wait(&qdo_full[n % QS], (n / QS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
+        tc_fence_after();
+      };
       auto issue_s = [&](int n) {
         const int s = n % QS;
-        mbar_wait(&qdo_full[s], (n / QS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
-        tc_fence_after();
         const uint32_t qK = qK0 + s * STG;
         umma_ss_lo<0>(tm_St, qK, kK, idesc_s);
 #pragma unroll
@@ -279,8 +282,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
         umma_commit(&ds_free[n % NDS]);
       };
       mbar_wait(kv_full, 0, abort_flag, p.status, FT_ERR_WAIT_FULL);
-      issue_s(0);
-      issue_dp(0);
+      wait_qdo(0);
+      if (elect_one_sync()) {
+        issue_s(0);
+        issue_dp(0);
+      }
+      __syncwarp();
       for (int n = 0; n < N; ++n) {
         if (!ALIAS) {
           // S / dP of step n+1 go to the tensor pipe as soon as the softmax warpgroups hold
@@ -288,40 +295,56 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
           // n: the next softmax then starts without waiting for these products.
           if (n + 1 < N) {
             mbar_wait(sdp_free, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
-            tc_fence_after();
-            issue_s(n + 1);
-            issue_dp(n + 1);
+            wait_qdo(n + 1);
+            if (elect_one_sync()) {
+              issue_s(n + 1);
+              issue_dp(n + 1);
+            }
+            __syncwarp();
           }
           mbar_wait(&pds_ready[n % NDS], (n / NDS) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
           tc_fence_after();
-          issue_dv(n);
-          issue_dk(n);
+          if (elect_one_sync()) {
+            issue_dv(n);
+            issue_dk(n);
+          }
+          __syncwarp();
           if (n > 0) {
             mbar_wait(dq_drained, (n - 1) & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
             tc_fence_after();
           }
-          issue_dq(n);
+          if (elect_one_sync()) {
+            issue_dq(n);
+          }
+          __syncwarp();
         } else {
           mbar_wait(&p_ready[n % NPB], (n / NPB) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
           tc_fence_after();
-          issue_dv(n);
+          if (elect_one_sync()) issue_dv(n);
+          __syncwarp();
           mbar_wait(&pds_ready[n % NDS], (n / NDS) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
           tc_fence_after();
-          issue_dk(n);
-          issue_dq(n);   // into the columns of dP(n), which the softmax has read by now
+          if (elect_one_sync()) {
+            issue_dk(n);
+            issue_dq(n);   // into the columns of dP(n), which the softmax has read by now
+          }
+          __syncwarp();
           if (n + 1 < N) {
             mbar_wait(sdp_free, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
-            tc_fence_after();
-            issue_s(n + 1);
+            wait_qdo(n + 1);
+            if (elect_one_sync()) issue_s(n + 1);
+            __syncwarp();
             mbar_wait(dq_drained, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
             tc_fence_after();
-            issue_dp(n + 1);
+            if (elect_one_sync()) issue_dp(n + 1);
+            __syncwarp();
           }
         }
       }
 #undef FT_KOFF
 #undef FT_MNOFF
-      umma_commit(dkv_full);
+      if (elect_one_sync()) umma_commit(dkv_full);
+      __syncwarp();
     }
   }
   } else if (warp < 12) {

@@ -69,6 +69,20 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
   return ok;
 }
 
+// Non-blocking test (try_wait may suspend the thread for a while before it answers): for
+// threads that poll several barriers in turn.
+__device__ __forceinline__ uint32_t mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok;
+}
+
 // Bounded wait. `abort_flag` lives in shared memory and is shared by the whole CTA.
 // Returns false when the wait gave up (or an earlier one did); the caller carries on with
 // its (finite) loops so that the CTA drains and exits.
@@ -228,6 +242,27 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_ma
          | (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+// One lane of a converged warp. Code that issues tcgen05.mma should run its loops and barrier
+// waits on the WHOLE warp and put only the issue itself under `if (elect_one_sync())`: loop
+// counters, shared-memory descriptors and TMEM addresses then stay warp-uniform and the MMA
+// reads them from uniform registers. Under `if (lane == 0)` the same values are per-thread
+// and every operand of every MMA is first moved to a uniform register, which costs an
+// isolated M=128, N=64 MMA stream 45 instead of 32 cycles per instruction (measured) and far
+// more when other warps compete for the scheduler.
+__device__ __forceinline__ uint32_t elect_one_sync() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .b32 r;\n\t.reg .pred p;\n\t"
+      "elect.sync r|p, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred;
+}
+// Warp index as a value the compiler knows to be the same in every lane.
+__device__ __forceinline__ int warp_idx_uniform() {
+  return __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+}
+
 // D[tmem] (+)= A[smem] * B[smem]; one thread issues.
 __device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                         uint32_t idesc, uint32_t accumulate) {
@@ -267,6 +302,30 @@ __device__ __forceinline__ void umma_ss_lo_dyn(uint32_t tmem_d, uint32_t a_lo, u
       "setp.ne.b32 p, %5, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(tmem_d),
       "r"(a_lo), "r"(b_lo), "r"(SMEM_DESC_HI), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (M = 128 rows on the 128 lanes) is read from
+// TMEM, where 16 bf16 of a row occupy 8 consecutive 32-bit columns (element 2c in the low half
+// of column c). Successive k-steps advance `tmem_a` by 8 columns.
+template <int ACC>
+__device__ __forceinline__ void umma_ts_lo(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo,
+                                           uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "r"(b_lo), "r"(SMEM_DESC_HI), "r"(idesc), "n"(ACC)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts_lo_dyn(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "r"(b_lo), "r"(SMEM_DESC_HI), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // Arrive on an mbarrier once all MMAs issued so far by this thread have completed.

@@ -93,7 +93,8 @@ def test_gemm_strided_views():
 
 
 @pytest.mark.parametrize("B,S,G,g,D", [(1, 256, 1, 1, 64), (2, 512, 2, 2, 64), (1, 1024, 2, 8, 64),
-                                        (1, 512, 1, 2, 128), (2, 768, 2, 4, 128)])
+                                        (1, 512, 1, 2, 128), (2, 768, 2, 4, 128),
+                                        (1, 4096, 1, 2, 64), (1, 4096, 1, 1, 128)])
 def test_flash_attention_fwd_bwd(B, S, G, g, D):
     qkv = torch.randn(B * S, G * (g + 2) * D, device="cuda").to(torch.bfloat16)
     o, lse = A.attention_fwd(qkv, B, G, g, D)
