@@ -28,8 +28,8 @@ extern "C" {
 //   dx_out    : bf16 [T][H] (may alias dres)
 //   dw        : fp32 [H], overwritten (accumulate == 0) or added to (accumulate != 0)
 //
-// Returns 0 on success, -1 for an unsupported hidden size (H must be 256*k with k in
-// {1,2,4,8} up to 1024, or 1024*k with k in {2,4,8}), -2 when H exceeds FT_NOALLOC_MAX_HIDDEN,
+// Returns 0 on success, -1 for an unsupported hidden size (the kernels exist for H = 256, 512,
+// 1024, 2048, 4096 and 8192), -2 when H exceeds FT_NOALLOC_MAX_HIDDEN,
 // -3 when the address of the scratch array could not be obtained, -100 for a launch error.
 //
 // The first call on each device looks up the device address of the scratch array (with that

@@ -392,8 +392,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+#ifdef FT_BUILD_PAIR_GEMM
 // ---------------------------------------------------------------------------------------
-// CTA-pair variant: a cluster of two CTAs owns a 256 x 256 output tile. Each CTA stages 128
+// CTA-pair variant (NOT BUILT: kept for reading only, behind FT_BUILD_PAIR_GEMM, which the
+// build never defines; under neighbour load on a shared GPU this kernel stopped making progress
+// and the cause has not been found): a cluster of two CTAs owns a 256 x 256 output tile. Each CTA stages 128
 // rows of A and 128 columns' worth of B per k-step (32 KB instead of 48 KB for 128 x 256 of
 // output), so shared-memory write (TMA) plus read (tensor core) traffic per SM drops by a
 // third and six stages fit. The even CTA issues every MMA (`cta_group::2`, M = 256); each CTA
@@ -606,6 +609,8 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
   cluster_sync_all();
 }
 
+#endif  // FT_BUILD_PAIR_GEMM
+
 // ---------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------
@@ -681,6 +686,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
+#ifdef FT_BUILD_PAIR_GEMM
 static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB,
                             const CUtensorMap& tmD, const GemmParams& p, int max_ctas,
                             cudaStream_t stream) {
@@ -699,21 +705,7 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB,
   gemm_pair_bf16_kernel<<<2 * pairs, GEMM_THREADS, PairSmem::TOTAL, stream>>>(tmA, tmB, tmD, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
-
-// Process-wide default for the tile shape when the caller passes bn = 0. The CTA-pair kernel is
-// opt-in (FT_GEMM_PAIR=1): it is correct and faster when it has the GPU to itself, but stopped
-// making progress in a test that runs it next to library GEMMs, copies and small kernels from
-// other streams of the same process. Draining every cross-CTA barrier arrival before exit (the
-// tails in the kernel) made a 2-second run of that test pass (16 k launches) but not the
-// 4-second one, so a second cause is still unknown.
-static int pair_default() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("FT_GEMM_PAIR");
-    v = (e && e[0] == '1') ? 1 : 0;
-  }
-  return v;
-}
+#endif  // FT_BUILD_PAIR_GEMM
 
 }  // namespace ft
 
@@ -721,8 +713,7 @@ static int pair_default() {
 //   a_mn == 0: A is stored [M][lda] (reduction index contiguous); a_mn == 1: A is stored
 //   [K][lda] (row index contiguous). Same for B with N. out_dtype: 0 bf16, 1 fp32.
 //   accumulate != 0 (fp32 only): D += result. splitk <= 0 picks a split automatically
-//   (fp32 only); bn in {0 (auto), 128, 256, 512 (256 x 256 tile on a CTA pair)}. All leading
-//   dimensions in elements; every base
+//   (fp32 only); bn in {0 (auto), 128, 256}. All leading dimensions in elements; every base
 //   pointer 16-byte aligned and every leading dimension a multiple of 8 (bf16) / 4 (fp32).
 extern "C" int ft_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int lda,
                             int ldb, int ldd, int a_mn, int b_mn, int out_dtype, int accumulate,
@@ -734,12 +725,10 @@ extern "C" int ft_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   const int sms = num_sms();
   if (max_ctas <= 0 || max_ctas > sms) max_ctas = sms;
   const int k_iters = (K + GEMM_BK - 1) / GEMM_BK;
-  // bn: 128 / 256 = one CTA per 128 x bn tile; 512 = a CTA pair per 256 x 256 tile.
-  if (bn != 128 && bn != 256 && bn != 512)
-    bn = (N <= 128) ? 128 : ((pair_default() && M > 128 && max_ctas >= 2) ? 512 : 256);
-  const bool pair = bn == 512;
-  if (pair) bn = 256;
-  const int bm = pair ? 256 : GEMM_BM;
+  // bn: 128 / 256 = one CTA per 128 x bn tile.
+  if (bn != 128 && bn != 256) bn = (N <= 128) ? 128 : 256;
+  constexpr bool pair = false;
+  const int bm = GEMM_BM;
   const int m_tiles = (M + bm - 1) / bm;
   const int n_tiles = (N + bn - 1) / bn;
   if (out_dtype == 0) splitk = 1;
@@ -785,7 +774,6 @@ extern "C" int ft_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   else                rc = get_tmap_2d(&tmD, D, 4, M, N, ldd, 32, 32);
   if (rc) return -6;
 
-  if (pair) return launch_gemm_pair(tmA, tmB, tmD, p, max_ctas, stream);
   if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, tmD, tmD, p, max_ctas, stream);
   return launch_gemm<128, 6>(tmA, tmB, tmD, tmD, p, max_ctas, stream);
 }

@@ -2,7 +2,7 @@
 
 Keeps up to ``depth`` (1..4) batches in flight: each batch is copied with non-blocking
 transfers on the copy stream and carries an event; ``next()`` makes the compute stream wait
-for that event only. Batches whose loss mask is entirely zero are skipped. On CPU it degrades
+for that event only and records the consuming stream on every tensor it hands out. Batches whose loss mask is entirely zero are skipped. On CPU it degrades
 to a pass-through FIFO so the state machine can be unit-tested without a GPU. Behavioural
 spec: exports/train_engine_0.5B/src/training_engine_tensor/data.py:37-185.
 """
@@ -76,13 +76,29 @@ class DataPrefetcher:
         dev, ev, host, nbytes = self.queue.popleft()
         if ev is not None:
             if self.cuda:
-                torch.cuda.current_stream().wait_event(ev)
+                cur = torch.cuda.current_stream()
+                cur.wait_event(ev)
+                # The tensors were allocated on the copy stream and are consumed on the compute
+                # stream: tell the caching allocator, or it may hand a batch's block to the next
+                # host-to-device copy while a kernel of the consuming step (the embedding
+                # backward runs last) has not read it yet. Same discipline as the reference's
+                # reducer buffers (nccl.py:1077-1084).
+                for v in dev.values():
+                    if torch.is_tensor(v):
+                        v.record_stream(cur)
             else:
                 ev.wait()
+                self._record(dev)
         self.bytes_last = nbytes
         self._keepalive = host  # pinned source must outlive the async copy
         self._fill()
         return dev
+
+
+    def _record(self, dev: dict) -> None:
+        """CPU stand-in of the record_stream step (counted so the state machine is testable)."""
+        self.recorded_tensors = getattr(self, "recorded_tensors", 0) + sum(
+            1 for v in dev.values() if torch.is_tensor(v))
 
 
 class _Null:

@@ -22,7 +22,7 @@ EXTERNAL_ENV_WHITELIST = frozenset({
     "NCCL_PROTO", "NCCL_MIN_NCHANNELS", "NCCL_NVLS_ENABLE", "NCCL_IB_QPS",
     "TORCH_NCCL_HEARTBEAT_TIMEOUT_SEC", "OUTPUT_DIR", "HF_HOME", "TOKENIZERS_PARALLELISM",
     "FT_PEAK_TFLOPS", "FT_B200_NO_AUTOBUILD", "FT_COMM_MULTIMEM", "FT_COMM_TIMEOUT_MS",
-    "FT_COMM_CTAS", "FT_B200_LIB", "FT_FUSE_ADAM_AG", "FT_GEMM_PAIR", "FT_FUSE_FC1_SWIGLU",
+    "FT_COMM_CTAS", "FT_B200_LIB", "FT_FUSE_ADAM_AG", "FT_FUSE_FC1_SWIGLU",
 })
 
 
@@ -46,6 +46,9 @@ class EngineConfig:
     rs_buckets: int = 32                 # 8B-style: number of layer-aligned buckets (0 = by size)
     tensor_parallel_size: int = 1
     sequence_parallel: bool = True
+    # ---- activation recomputation (memory for time) ----
+    recompute_attn: bool = False         # attention output / log-sum-exp rebuilt in backward
+    recompute_mlp: bool = False          # FC1 output and SwiGLU activation rebuilt in backward
     # ---- CUDA graphs ----
     forward_cuda_graph: bool = False
     step_cuda_graph: bool = False
@@ -114,6 +117,8 @@ _ENV_MAP: dict[str, tuple[str, Callable[[str], Any]]] = {
     "RS_BUCKETS": ("rs_buckets", int),
     "TENSOR_PARALLEL_SIZE": ("tensor_parallel_size", int),
     "SEQUENCE_PARALLEL": ("sequence_parallel", lambda v: v.lower() in _BOOL_TRUE),
+    "RECOMPUTE_ATTN": ("recompute_attn", lambda v: v.lower() in _BOOL_TRUE),
+    "RECOMPUTE_MLP": ("recompute_mlp", lambda v: v.lower() in _BOOL_TRUE),
     "FORWARD_CUDA_GRAPH": ("forward_cuda_graph", lambda v: v.lower() in _BOOL_TRUE),
     "STEP_CUDA_GRAPH": ("step_cuda_graph", lambda v: v.lower() in _BOOL_TRUE),
     "FULL_STEP_CUDA_GRAPH": ("full_step_cuda_graph", lambda v: v.lower() in _BOOL_TRUE),
@@ -306,7 +311,6 @@ _SWITCH_NOTES = {
     "FT_COMM_TIMEOUT_MS": "limit (ms, default 30000) of every wait on a peer flag in the fused collectives",
     "FT_COMM_CTAS": "CTAs per fused data-parallel collective launch (default 96)",
     "FT_FUSE_ADAM_AG": "0: AdamW and the parameter all-gather as two kernels instead of one",
-    "FT_GEMM_PAIR": "1: CTA-pair (cta_group::2) GEMM where the shape allows it",
     "FT_FUSE_FC1_SWIGLU": "0: FC1 and SwiGLU as two kernels instead of one",
 }
 

@@ -32,11 +32,26 @@ class LayerSaved:
     __slots__ = ("h_in", "rs1", "n1_full", "qkv", "attn", "lse", "h_mid", "rs2", "n2_full", "y1",
                  "act")
 
+    def __init__(self):
+        self.attn = self.lse = self.y1 = self.act = None   # absent when they are recomputed
+
 
 class MiniCPM4:
     def __init__(self, spec: ModelSpec, store: ParamStore, tp: TPContext = NO_TP,
-                 max_seq_len: int | None = None, save_act: bool = True):
+                 max_seq_len: int | None = None, save_act: bool = True,
+                 recompute_attn: bool = False, recompute_mlp: bool = False):
+        """``recompute_attn`` / ``recompute_mlp``: activation recomputation, the reference's
+        switches of the same names (exports/train_engine_8b/src/training_engine_tensor/
+        forward.py:65-66,286-306). With ``recompute_attn`` the attention output and its
+        log-sum-exp are not kept between forward and backward; the backward runs the forward
+        kernel again on the saved (rotated) qkv buffer. With ``recompute_mlp`` the FC1 output
+        and the SwiGLU activation (3 * ffn_hidden values per token and layer, the largest
+        saved tensors) are dropped and rebuilt from the saved FFN-norm output. Both reruns use
+        the kernels of the forward pass on the same inputs, so gradients are bitwise those of
+        the saved-activation path."""
         self.spec = spec
+        self.recompute_attn = recompute_attn
+        self.recompute_mlp = recompute_mlp
         self.store = store
         self.tp = tp
         self.p = store.params
@@ -60,6 +75,10 @@ class MiniCPM4:
         self._head_saved = None
         # set to a dict to have the backward record a few intermediate gradients in it
         self.diagnostics: dict | None = None
+        # called with a parameter-name prefix ("tok_embeddings", "layers.3", "norm", "output")
+        # right before the forward first reads parameters under it: the trainer hangs the
+        # per-bucket "updated and gathered" events of the previous optimizer step on it
+        self.param_gate: Callable[[str], None] | None = None
         # FC1 + SwiGLU in one kernel where FC1 is a plain local GEMM (no tensor parallelism)
         self.fuse_fc1_swiglu = tpn == 1 and os.environ.get("FT_FUSE_FC1_SWIGLU", "1") != "0"
         self._ensure_rope(S)
@@ -72,6 +91,8 @@ class MiniCPM4:
     # ------------------------------------------------------------------------------ forward
     def embed(self, tokens: torch.Tensor) -> torch.Tensor:
         """Token embedding * emb_scale, returned on this rank's token shard."""
+        if self.param_gate is not None:
+            self.param_gate("tok_embeddings")
         w = self.p["tok_embeddings.weight"]
         e = ops.embedding_fwd(tokens, w, self.spec.emb_scale, self.vocab_start)
         if self.tp.enabled:
@@ -82,6 +103,8 @@ class MiniCPM4:
         """One decoder block. ``h_prev + branch`` is the block input (the add is fused into the
         first norm); returns ``(h_mid, ffn_branch, saved)`` with the output being their sum."""
         sp, p, tp = self.spec, self.p, self.tp
+        if self.param_gate is not None:
+            self.param_gate(prefix)
         r = sp.mup_residual_scale
         sv = LayerSaved()
         x_in = h_prev if h_prev is not None else branch
@@ -94,21 +117,35 @@ class MiniCPM4:
         ops.rope_(qkv, self.cos, self.sin, batch, self.local_groups, self.local_g, sp.head_dim,
                   position_ids=position_ids)
         sv.qkv = qkv
-        sv.attn, sv.lse = ops.attention_fwd(qkv, batch, self.local_groups, self.local_g, sp.head_dim)
-        o = tp.linear_scatter(sv.attn, p[f"{prefix}.attention.wo.weight"], alpha=r)
+        attn, lse = ops.attention_fwd(qkv, batch, self.local_groups, self.local_g, sp.head_dim)
+        if not self.recompute_attn:
+            sv.attn, sv.lse = attn, lse
+        o = tp.linear_scatter(attn, p[f"{prefix}.attention.wo.weight"], alpha=r)
+        del attn, lse
         sv.h_mid, n2, sv.rs2 = ops.add_rmsnorm_fwd(
             h_in, o, p[f"{prefix}.ffn_norm.weight"], sp.norm_epsilon,
             tp.gather_dest(f"{prefix}.n2", o.shape[0], o.shape[1]))
         if self.fuse_fc1_swiglu:
             # one kernel: FC1 with silu(gate) * up computed in its epilogue
             sv.n2_full = n2
-            sv.y1, sv.act = ops.linear_swiglu_fwd(n2, p[f"{prefix}.feed_forward.wfc1.weight"])
+            y1, act = ops.linear_swiglu_fwd(n2, p[f"{prefix}.feed_forward.wfc1.weight"])
         else:
-            sv.y1, sv.n2_full = tp.linear_gather(n2, p[f"{prefix}.feed_forward.wfc1.weight"],
-                                                 key=f"{prefix}.n2")
-            sv.act = ops.swiglu_fwd(sv.y1)
-        f = tp.linear_scatter(sv.act, p[f"{prefix}.feed_forward.w2.weight"], alpha=r)
+            y1, sv.n2_full = tp.linear_gather(n2, p[f"{prefix}.feed_forward.wfc1.weight"],
+                                              key=f"{prefix}.n2")
+            act = ops.swiglu_fwd(y1)
+        if not self.recompute_mlp:
+            sv.y1, sv.act = y1, act
+        f = tp.linear_scatter(act, p[f"{prefix}.feed_forward.w2.weight"], alpha=r)
         return sv.h_mid, f, sv
+
+    def _recompute_mlp(self, prefix: str, sv: LayerSaved):
+        """FC1 output and SwiGLU activation again, from the saved (gathered) FFN-norm output:
+        a local GEMM, no collective."""
+        w = self.p[f"{prefix}.feed_forward.wfc1.weight"]
+        if self.fuse_fc1_swiglu:
+            return ops.linear_swiglu_fwd(sv.n2_full, w)
+        y1 = ops.linear_fwd(sv.n2_full, w)
+        return y1, ops.swiglu_fwd(y1)
 
     def forward_hidden(self, tokens: torch.Tensor, position_ids=None):
         """Embedding + all blocks. Returns (h, branch): the final hidden state is h + branch."""
@@ -124,6 +161,9 @@ class MiniCPM4:
     def head_forward(self, h, branch):
         """Final norm, logit divisor, LM head. Returns logits of this rank's vocabulary shard."""
         sp, p = self.spec, self.p
+        if self.param_gate is not None:
+            self.param_gate("norm")
+            self.param_gate("output")
         h_fin, nf, rsf = ops.add_rmsnorm_fwd(
             h, branch, p["norm.weight"], sp.norm_epsilon,
             self.tp.gather_dest("head.nf", branch.shape[0], branch.shape[1]))
@@ -183,10 +223,14 @@ class MiniCPM4:
         if diag is not None:
             diag["d_hidden_into_last_layer"] = dh.detach().clone()
         # ---- feed-forward branch
+        y1, act = (sv.y1, sv.act) if sv.y1 is not None else self._recompute_mlp(prefix, sv)
+        sv.y1 = sv.act = None
         dact, dh_full = tp.dgrad_gather(dh, p[n_w2], alpha=r, key="bwd.ffn")
-        ops.linear_wgrad(dh_full, sv.act, g[n_w2], accumulate, alpha=r)
+        ops.linear_wgrad(dh_full, act, g[n_w2], accumulate, alpha=r)
+        del act
         emit(n_w2)
-        dy1 = ops.swiglu_bwd(dact, sv.y1)
+        dy1 = ops.swiglu_bwd(dact, y1)
+        del y1
         if diag is not None:
             diag["d_intermediate_last"] = dact.detach().clone()
             diag["d_fc1_last"] = dy1.detach().clone()
@@ -198,11 +242,15 @@ class MiniCPM4:
         dh = ops.rmsnorm_bwd(dn2, sv.h_mid, p[n_fn], sv.rs2, dh, g[n_fn], accumulate)
         emit(n_fn)
         # ---- attention branch
+        if sv.attn is None:   # recompute_attn: the forward kernel again, on the rotated qkv
+            sv.attn, sv.lse = ops.attention_fwd(sv.qkv, batch, self.local_groups, self.local_g,
+                                                sp.head_dim)
         dattn, dh_full = tp.dgrad_gather(dh, p[n_wo], alpha=r, key="bwd.attn")
         ops.linear_wgrad(dh_full, sv.attn, g[n_wo], accumulate, alpha=r)
         dqkv = ops.attention_bwd(dattn, sv.qkv, sv.attn, sv.lse, batch, self.local_groups,
                                  self.local_g, sp.head_dim)
         del dattn
+        sv.attn = sv.lse = None
         ops.rope_(dqkv, self.cos, self.sin, batch, self.local_groups, self.local_g, sp.head_dim,
                   inverse=True, position_ids=position_ids)
         ops.linear_wgrad(dqkv, sv.n1_full, g[n_qkv], accumulate)

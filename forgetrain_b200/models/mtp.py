@@ -54,6 +54,8 @@ class MTPHead:
         self.last_mtp_losses = []
         for k in range(self.K):
             pre = mtp_layer_prefix(k)
+            if m.param_gate is not None:
+                m.param_gate(pre)
             ids, lab, msk = roll_left_one(ids), roll_left_one(lab), roll_left_one(msk)
             e = ops.embedding_fwd(ids, p["tok_embeddings.weight"], sp.emb_scale)
             _, en, rse = ops.add_rmsnorm_fwd(None, e, p[f"{pre}.enorm.weight"], sp.norm_epsilon)

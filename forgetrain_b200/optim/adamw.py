@@ -10,6 +10,13 @@ bf16 results into every rank's parameter buffer (``multimem.st`` or peer stores)
 all-gather are one launch. Every per-step scalar (lr, bias corrections, clip coefficient) lives in
 a device vector, which keeps the launches graph-capturable.
 
+The buckets are updated and gathered in the order in which the next forward pass reads them
+(embedding first, head last: the reverse of the flat-buffer order), on a side stream, with one
+event per bucket; the next forward waits for a bucket's event only right before the first
+layer that reads a parameter of it, so the update and the gather of everything but the first
+bucket overlap the forward pass (the reference's per-bucket Adam -> all-gather pipeline,
+exports/train_engine_8b/src/training_engine_tensor/entry.py:681-710, forward.py:150-158).
+
 Numerics follow the reference's fused kernel
 (exports/train_engine_0.5B/src/training_engine_tensor/triton_kernels.py:414-607) and its
 sharded driver (optimizer.py:633-748): beta = (0.9, 0.95), eps 1e-8, weight decay only on
@@ -87,6 +94,10 @@ class ShardedAdamW:
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self.sumsq_total = torch.zeros(1, dtype=torch.float32, device=dev)
         self.ag_events: list = [None] * len(buckets)
+        # True: apply() leaves the per-bucket events pending for wait_bucket(); False: apply()
+        # joins the side stream before it returns (CUDA-graph capture, serial streams)
+        self.overlap_forward = False
+        self.opt_stream = comm_stream
         self.sync_master_from_params()
 
     def set_schedule(self, max_lr: float, min_lr: float, warmup_iters: int, lr_decay_iters: int,
@@ -159,39 +170,61 @@ class ShardedAdamW:
         h[4], h[5] = 1.0 - self.beta1 ** t, 1.0 - self.beta2 ** t
 
     def apply(self) -> None:
-        """Device half of a step (capturable in a CUDA graph): copy the staged scalars and run
-        the fused AdamW kernel and the parameter all-gather bucket by bucket."""
+        """Device half of a step (capturable in a CUDA graph): derive the step's scalars and run
+        the fused AdamW kernel and the parameter all-gather bucket by bucket, in forward-
+        consumption order, on the side stream when there is one."""
         lr, t = self._lr, self.step_count
-        if self.sched is not None:
-            from ..ops import cuda_ops
-            cuda_ops.adam_hyper_step(self.step_dev, self.sched, self.hyper)
+        side = self.opt_stream if (self.is_cuda and self.opt_stream is not None) else None
+        if side is not None:
+            ready = torch.cuda.Event()
+            ready.record()                 # gradients reduced, clip coefficient written
+            side.wait_event(ready)
+            ctx = torch.cuda.stream(side)
         else:
-            # slots 6 (clip) and 7 are device-owned: copy only the first six
-            self.hyper[:6].copy_(self.hyper_host[:6], non_blocking=True)
-        flat_g, flat_p = self.store.flat_grads, self.store.flat_params
-        for i, b in enumerate(self.buckets):
-            lo, hi = b.shard_range(self.rank, self.world)
-            p32, m, v = self._views(i)
-            if self.is_cuda and self.fused is not None and self.world > 1 and self.fuse_update_gather \
-                    and (hi - lo) % 8 == 0:
-                se, sw, sl = self.seg_dev[i]
-                self.fused.adamw_all_gather(b, p32, m, v, flat_g[lo:hi], self.hyper, se, sw, sl)
-                continue
-            if self.is_cuda:
+            ctx = _null_ctx()
+        with ctx:
+            if self.sched is not None:
                 from ..ops import cuda_ops
-                se, sw, sl = self.seg_dev[i]
-                cuda_ops.adamw_flat(p32, m, v, flat_g[lo:hi], flat_p[lo:hi], self.hyper, se, sw, sl)
+                cuda_ops.adam_hyper_step(self.step_dev, self.sched, self.hyper)
             else:
-                clip = float(self.hyper[6])
-                a = 0
-                for end, wd, lrm, _ in self.segments[i]:
-                    ref_ops.adamw_step(p32[a:end], m[a:end], v[a:end], flat_g[lo + a:lo + end],
-                                       flat_p[lo + a:lo + end], lr * lrm, self.beta1, self.beta2,
-                                       self.eps, wd, t, clip)
-                    a = end
-            self._all_gather_bucket(i, b)
+                # slots 6 (clip) and 7 are device-owned: copy only the first six
+                self.hyper[:6].copy_(self.hyper_host[:6], non_blocking=True)
+            for i in reversed(range(len(self.buckets))):
+                self._update_bucket(i, lr, t)
+                if side is not None:
+                    done = torch.cuda.Event()
+                    done.record()
+                    self.ag_events[i] = done
+        if side is not None and not self.overlap_forward:
+            self.wait_all_gathers()
+
+    def _update_bucket(self, i: int, lr: float, t: int) -> None:
+        b = self.buckets[i]
+        flat_g, flat_p = self.store.flat_grads, self.store.flat_params
+        lo, hi = b.shard_range(self.rank, self.world)
+        p32, m, v = self._views(i)
+        if self.is_cuda and self.fused is not None and self.world > 1 and self.fuse_update_gather \
+                and (hi - lo) % 8 == 0:
+            se, sw, sl = self.seg_dev[i]
+            self.fused.adamw_all_gather(b, p32, m, v, flat_g[lo:hi], self.hyper, se, sw, sl)
+            return
+        if self.is_cuda:
+            from ..ops import cuda_ops
+            se, sw, sl = self.seg_dev[i]
+            cuda_ops.adamw_flat(p32, m, v, flat_g[lo:hi], flat_p[lo:hi], self.hyper, se, sw, sl)
+        else:
+            clip = float(self.hyper[6])
+            a = 0
+            for end, wd, lrm, _ in self.segments[i]:
+                ref_ops.adamw_step(p32[a:end], m[a:end], v[a:end], flat_g[lo + a:lo + end],
+                                   flat_p[lo + a:lo + end], lr * lrm, self.beta1, self.beta2,
+                                   self.eps, wd, t, clip)
+                a = end
+        self._all_gather_bucket(i, b)
 
     def _all_gather_bucket(self, i: int, b: Bucket) -> None:
+        """Gather bucket ``b`` on the current stream (apply() has already switched to the side
+        stream when there is one)."""
         if self.world == 1:
             return
         lo, hi = b.shard_range(self.rank, self.world)
@@ -199,16 +232,6 @@ class ShardedAdamW:
         shard = self.store.flat_params[lo:hi]
         if self.fused is not None:
             self.fused.all_gather_bucket(b)
-            return
-        if self.is_cuda and self.comm_stream is not None:
-            ev = torch.cuda.Event()
-            ev.record()
-            self.comm_stream.wait_event(ev)
-            with torch.cuda.stream(self.comm_stream):
-                dist.all_gather_into_tensor(full, shard, group=self.group)
-                done = torch.cuda.Event()
-                done.record()
-                self.ag_events[i] = done
         elif self.is_cuda:
             dist.all_gather_into_tensor(full, shard, group=self.group)
         else:
@@ -217,17 +240,29 @@ class ShardedAdamW:
             full.copy_(torch.cat(parts))
 
     def all_gather_params(self) -> None:
+        """Gather every bucket now (after a load or a manual change of the shards). The pushes
+        of the peer-memory gather land in the peers' parameter buffers without asking, so all
+        ranks first meet in a barrier: nobody may still be reading the values being replaced.
+        Inside a training step that guarantee comes from the gradient-norm all-reduce, which
+        every rank passes between its last read of the old parameters and :meth:`apply`."""
+        if self.fused is not None and self.world > 1:
+            self.fused.barrier()
         for i, b in enumerate(self.buckets):
             self._all_gather_bucket(i, b)
         self.wait_all_gathers()
 
+    def wait_bucket(self, i: int) -> None:
+        """Make the current stream wait until bucket ``i`` holds this step's parameters."""
+        ev = self.ag_events[i]
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+            self.ag_events[i] = None
+
     def wait_all_gathers(self) -> None:
         if self.fused is not None:
             self.fused.wait_all_gathers()
-        for i, ev in enumerate(self.ag_events):
-            if ev is not None:
-                torch.cuda.current_stream().wait_event(ev)
-                self.ag_events[i] = None
+        for i in range(len(self.ag_events)):
+            self.wait_bucket(i)
 
     # ------------------------------------------------------------------ checkpoint support
     def gather_full_state(self) -> dict[str, dict[str, torch.Tensor]]:
@@ -272,3 +307,11 @@ class ShardedAdamW:
         self.step_count = int(step_count)
         if self.step_dev is not None:
             self.step_dev.fill_(self.step_count)
+
+
+class _null_ctx:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False

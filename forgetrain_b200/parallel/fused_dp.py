@@ -30,6 +30,12 @@ NUM_FLAG_SLOTS = 8
 SCRATCH_FLOATS = 64 * 16
 
 
+def _as_i32(e: int) -> int:
+    """The bit pattern of a 32-bit epoch as the signed value an int32 tensor holds."""
+    e &= 0xFFFFFFFF
+    return e - (1 << 32) if e & 0x80000000 else e
+
+
 class SymmetricBuffers:
     """Symmetric allocations shared by the ranks of one process group."""
 
@@ -85,7 +91,9 @@ class SymmetricBuffers:
         if self._graph_mode:
             raise RuntimeError("peer-memory collectives were captured in a CUDA graph; call "
                                "resync_epochs() before launching them eagerly again")
-        self.epoch[slot] = (self.epoch[slot] + 1) & 0x7FFFFFFF
+        # full 32-bit counters: the device compares (int32)(flag - epoch) >= 0, which is only
+        # wrap-safe when host and device count modulo 2^32 alike
+        self.epoch[slot] = (self.epoch[slot] + 1) & 0xFFFFFFFF
         return self.epoch[slot]
 
     def set_epoch(self, slot: int, value: int) -> None:
@@ -103,7 +111,7 @@ class SymmetricBuffers:
         the base by what one replay consumes. Every rank must capture the same sequence."""
         if self._graph_mode:
             self.resync_epochs()
-        self.epoch_base.copy_(torch.tensor(self.epoch, dtype=torch.int32))
+        self.epoch_base.copy_(torch.tensor([_as_i32(e) for e in self.epoch], dtype=torch.int32))
         self._used = [0] * NUM_FLAG_SLOTS
         self._capturing = True
 
@@ -117,7 +125,7 @@ class SymmetricBuffers:
     def resync_epochs(self) -> None:
         """Back to eager launches after graph replays: read the base back (synchronises)."""
         base = self.epoch_base.cpu().tolist()
-        self.epoch = [int(b) & 0x7FFFFFFF for b in base]
+        self.epoch = [int(b) & 0xFFFFFFFF for b in base]
         self.epoch_base.zero_()
         self._graph_mode = False
 

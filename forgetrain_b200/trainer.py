@@ -95,7 +95,8 @@ class Trainer:
                                 param_buffer=param_buffer)
         if cfg.random_init:
             self.store.init_random(seed, cfg.init_scheme, cfg.init_std)
-        self.model = MiniCPM4(spec, self.store, self.tp_ctx, max_seq_len=max_seq_len or seq_length)
+        self.model = MiniCPM4(spec, self.store, self.tp_ctx, max_seq_len=max_seq_len or seq_length,
+                              recompute_attn=cfg.recompute_attn, recompute_mlp=cfg.recompute_mlp)
         self.mtp = None
         if cfg.mtp_num_layers > 0:
             from .models.mtp import MTPHead
@@ -140,16 +141,23 @@ class Trainer:
             weight_decay=cfg.weight_decay,
             max_grad_norm=0.0 if cfg.no_grad_clip else cfg.max_grad_norm,
             mup_lr_scaling=cfg.mup_lr_scaling, norm_reduce=norm_reduce,
-            comm_stream=self.reducer.comm_stream if cfg.opt_allgather_overlap else None,
+            comm_stream=self._optimizer_stream(cfg, dev),
             fused=self.fused_dp)
         self.opt.set_schedule(cfg.max_lr, cfg.min_lr, cfg.warmup_iters, cfg.lr_decay_iters,
                               cfg.wsd_decay_iters)
         self.num_samples = 0
         self.loss_buf = torch.zeros(1, dtype=torch.float32, device=dev)
+        # per-layer losses of the multi-token-prediction head, averaged like the main loss
+        self.mtp_loss_buf = (torch.zeros(cfg.mtp_num_layers, dtype=torch.float32, device=dev)
+                             if cfg.mtp_num_layers > 0 else None)
         self.graph = None
         self.full_graph = None
         self._fwd_graph = None
         graphable_comm = topo.world == 1 or (self.fused_dp is not None and tp == 1)
+        uses_graph = dev.type == "cuda" and (cfg.full_step_cuda_graph or cfg.step_cuda_graph)
+        if self.opt.opt_stream is not None and not uses_graph:
+            self.opt.overlap_forward = True
+            self._install_param_gate()
         if cfg.full_step_cuda_graph and dev.type == "cuda" and graphable_comm:
             from .graph.step_graph import GraphedFullStep
             self.full_graph = GraphedFullStep(self, cfg.step_cuda_graph_warmup)
@@ -160,6 +168,37 @@ class Trainer:
                                             cfg.step_cuda_graph_sanity, cfg.step_cuda_graph_tol)
 
     # ------------------------------------------------------------------ helpers
+    def _optimizer_stream(self, cfg: EngineConfig, dev):
+        """Stream of the AdamW + all-gather pipeline: the reducer's communication stream (the
+        peer-memory kernels of one process must all run in one order), else a stream of its
+        own; none with ``opt_allgather_overlap`` off, serial streams or on CPU."""
+        if dev.type != "cuda" or not cfg.opt_allgather_overlap or cfg.serial_streams:
+            return None
+        return self.reducer.comm_stream or torch.cuda.Stream(device=dev)
+
+    def _install_param_gate(self) -> None:
+        """The forward pass waits for a bucket of the previous optimizer step right before the
+        first layer that reads one of its parameters, and not earlier."""
+        by_prefix: dict[str, list[int]] = {}
+        for b in self.opt.buckets:
+            for name in b.params:
+                parts = name.split(".")
+                pre = ".".join(parts[:2]) if parts[0] == "layers" else \
+                    (".".join(parts[:3]) if parts[0] == "mtp" else parts[0])
+                if b.index not in by_prefix.setdefault(pre, []):
+                    by_prefix[pre].append(b.index)
+        opt = self.opt
+
+        def gate(prefix: str) -> None:
+            for i in by_prefix.get(prefix, ()):
+                opt.wait_bucket(i)
+        self.model.param_gate = gate
+
+    def finish_step(self) -> None:
+        """Make the current stream wait for everything the last step left running on side
+        streams (the tail of the optimizer / all-gather pipeline)."""
+        self.opt.wait_all_gathers()
+
     def _grad_ready(self, name: str) -> None:
         ps = self.store.by_name.get(name)
         if ps is not None and ps.is_norm and self.tp_ctx.sequence_parallel:
@@ -191,7 +230,7 @@ class Trainer:
         print(f"[grad-norm-diag] pre_reduce_rank{self.topo.rank}_full={total:.10f}", flush=True)
         print("[grad-norm-top] " + " | ".join(f"{g:.6f}:{n}" for g, n in rows[:12]), flush=True)
 
-    def _micro_batch(self, batch, loss_scale: float, accumulate: bool, last: bool):
+    def _micro_batch(self, batch, loss_scale: float, accumulate: bool, last: bool, prof=None):
         diag = self.cfg.grad_norm_diag and last and self.topo.dp_rank == 0
         hold = self.cfg.grad_norm_diag and last   # every rank holds its buckets back alike
         grad_ready = self._grad_ready if (last and not hold) else None
@@ -205,11 +244,24 @@ class Trainer:
                 for ps in self.store.order:
                     self._grad_ready(ps.name)
             return loss
-        if self.mtp is None:
-            loss = m.forward_backward(tokens, labels, mask, loss_scale, accumulate, grad_ready, pos)
-        else:
+        if self.mtp is not None:
             loss = self.mtp.forward_backward(tokens, labels, mask, loss_scale, accumulate,
                                              grad_ready, pos)
+        elif prof is not None and prof.deep and prof.active:
+            # PROFILE_DEEP: the phases of a micro-batch as separate segments (reference
+            # profiling.py:180-191, hooks train_loop.py:584-585,643-648). Gradient accumulation
+            # happens inside the weight-gradient GEMM epilogue here, so ``mb_accum`` closes at
+            # once after ``mb_bwd``; it is kept for the record layout.
+            logits = m.forward(tokens, pos)
+            prof.deep_mark("mb_fwd")
+            loss, dlogits = m.loss_and_dlogits(logits, labels, mask, loss_scale)
+            del logits
+            prof.deep_mark("mb_ce")
+            m.backward(tokens, dlogits, accumulate, grad_ready, pos)
+            prof.deep_mark("mb_bwd")
+            prof.deep_mark("mb_accum")
+        else:
+            loss = m.forward_backward(tokens, labels, mask, loss_scale, accumulate, grad_ready, pos)
         if hold:   # diagnostics look at the local gradients, so the buckets are released after
             if diag:
                 self._grad_norm_diag()
@@ -229,7 +281,10 @@ class Trainer:
             self.full_graph(micro_batches)
         else:
             self._device_step(micro_batches, profiler)
-        return {"loss": self.loss_buf, "grad_norm": self.opt.grad_norm, "lr": lr}
+        out = {"loss": self.loss_buf, "grad_norm": self.opt.grad_norm, "lr": lr}
+        if self.mtp_loss_buf is not None:
+            out["mtp_loss_per_layer"] = self.mtp_loss_buf
+        return out
 
     def _device_step(self, micro_batches: list[dict], prof: StepProfiler | None = None) -> None:
         """Everything of a step that runs on the device: micro-batches, bucket reductions,
@@ -238,12 +293,20 @@ class Trainer:
         n = len(micro_batches)
         if prof:
             prof.mark("step_start")
-        self.opt.wait_all_gathers()
+        if not self.opt.overlap_forward:
+            self.opt.wait_all_gathers()
         self.reducer.start_step()
         self.loss_buf.zero_()
+        if self.mtp_loss_buf is not None:
+            self.mtp_loss_buf.zero_()
         for i, batch in enumerate(micro_batches):
-            loss = self._micro_batch(batch, 1.0 / n, accumulate=i > 0, last=(i == n - 1))
+            if prof:
+                prof.deep_mark("mb_data")
+            loss = self._micro_batch(batch, 1.0 / n, accumulate=i > 0, last=(i == n - 1), prof=prof)
             self.loss_buf += loss.detach().reshape(1) / n
+            if self.mtp_loss_buf is not None:   # mean over micro-batches, per MTP layer
+                self.mtp_loss_buf += torch.stack(
+                    [l.detach().reshape(()) for l in self.mtp.last_mtp_losses]).float() / n
         if prof:
             prof.mark("microbatches")
         self.reducer.wait_all()
@@ -256,18 +319,27 @@ class Trainer:
         if prof:
             prof.mark("optimizer")
         if self.topo.dp_size > 1:
-            if self.fused_dp is not None:
-                self.fused_dp.all_reduce_small(self.loss_buf)
-            else:
-                dist.all_reduce(self.loss_buf, group=self.topo.dp_group)
-            self.loss_buf /= self.topo.dp_size
+            # mean over the data-parallel ranks, of the loss and of the per-layer MTP losses
+            # (reference train_loop.py:326-364, 767-772)
+            for buf in (self.loss_buf, self.mtp_loss_buf):
+                if buf is None:
+                    continue
+                if self.fused_dp is not None:
+                    self.fused_dp.all_reduce_small(buf)
+                else:
+                    dist.all_reduce(buf, group=self.topo.dp_group)
+                buf /= self.topo.dp_size
         if prof:
             prof.mark("loss_allreduce")
+            if prof.active:   # on profiled steps the parameter gather is closed inside the step
+                self.opt.wait_all_gathers()
+            prof.mark("allgather")
 
     # ------------------------------------------------------------------ checkpoint
     def save(self, save_dir, step: int, dataloader_state=None, async_io=True):
         """Rank-count independent checkpoint: DP shards of the optimizer state are gathered;
         with TP > 1 every TP rank of DP rank 0 writes its own ``rank_<R>.pt`` shard."""
+        self.finish_step()        # the parameters read below are complete on this stream
         opt_state = self.opt.gather_full_state()
         opt_state["step_count"] = self.opt.step_count
         opt_state["num_samples"] = self.num_samples
@@ -432,11 +504,18 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
                "lr": out["lr"], "total_step_time": dt, "mfu_e2e": flops_hw / dt / peak,
                "mfu_e2e_standard": flops_std / dt / peak,
                "tokens_per_sec_per_gpu": tokens_per_step / dt / topo.world}
+        mtp_suffix = ""
+        if "mtp_loss_per_layer" in out:
+            per_layer = [float(v) for v in out["mtp_loss_per_layer"].tolist()]
+            rec["mtp_loss_per_layer"] = per_layer
+            rec["mtp_loss"] = sum(per_layer) / len(per_layer)
+            mtp_suffix = " | mtp loss: " + ", ".join(f"{v:.6e}" for v in per_layer)
         results.append(rec)
         if (step + 1) % log_every == 0:
             _log(topo, f" iteration {step + 1:8d} | loss {loss:.6E} | local_loss {loss:.6E} | "
                        f"grad norm {gnorm:.4f} | lr {out['lr']:.4E} | time(ms) {dt * 1e3:.1f} | "
-                       f"tok/s/gpu {rec['tokens_per_sec_per_gpu']:.0f} | mfu {rec['mfu_e2e_standard'] * 100:.2f}%")
+                       f"tok/s/gpu {rec['tokens_per_sec_per_gpu']:.0f} | mfu {rec['mfu_e2e_standard'] * 100:.2f}%"
+                       f"{mtp_suffix}")
             if cfg.emit_loss_lines:
                 _log(topo, f"[LOSS] step={step + 1} global_loss={loss:.8f} grad_norm={gnorm:.6f} "
                            f"time_s={dt:.4f} mfu_e2e_standard={rec['mfu_e2e_standard']:.4f}")

@@ -343,3 +343,45 @@ def test_unsharded_optimizer_matches_zero1():
         assert torch.allclose(u[0][1][name], t, atol=1e-6), name
         assert torch.equal(u[0][1][name], u[1][1][name]), name       # replicas stay identical
     assert u[0][2] == 2 * z[0][2]
+
+
+# ------------------------------------------------------------------------------------------
+def _mtp_worker(rank, world, out_dir):
+    """MTP losses: mean over micro-batches on each rank, mean over the data-parallel ranks,
+    one value per extra layer in every step record (reference train_loop.py:326-364)."""
+    from forgetrain_b200.parallel.topology import init_topology
+    from forgetrain_b200.trainer import Trainer, run_training_loop
+    spec = _spec(tie_embeddings=False)
+    topo = init_topology(1, device="cpu")
+    cfg = _cfg(spec, mtp_num_layers=2, mtp_loss_scaling_factor=0.3,
+               profile_range="1,3", profile_output=os.path.join(out_dir, "prof.json"),
+               profile_deep=True)
+    rep = run_training_loop(spec=spec, cfg=cfg, topo=topo, num_steps=3, micro_batch_size=1,
+                            seq_length=64, num_local_microbatches=2, seed=5)
+    tr = rep["trainer"]
+    # this rank's own per-layer losses of one more step, before any cross-rank averaging
+    data = _batches(11 + rank, 2, 1, 64, spec.vocab_size)
+    local = torch.zeros(2)
+    for b in data:
+        tr.mtp.forward_backward(b["tokens"], b["labels"], b.get("loss_mask"), 0.5, False)
+        local += torch.stack([l.detach().reshape(()) for l in tr.mtp.last_mtp_losses]).float() / 2
+    out = tr.train_step(data)
+    return [s["mtp_loss_per_layer"] for s in rep["steps"]], [s["mtp_loss"] for s in rep["steps"]], \
+        local, out["mtp_loss_per_layer"].clone()
+
+
+def test_mtp_losses_are_averaged_over_microbatches_and_ranks_and_reported(tmp_path):
+    res = run_ranks(_mtp_worker, 2, str(tmp_path))
+    per_layer, total, _, _ = res[0]
+    assert len(per_layer) == 3 and all(len(p) == 2 for p in per_layer)
+    assert all(t == pytest.approx(sum(p) / 2) for p, t in zip(per_layer, total))
+    assert res[0][0] == res[1][0]                      # every rank reports the global mean
+    want = (res[0][2] + res[1][2]) / 2                 # mean of the two ranks' local means
+    assert torch.allclose(res[0][3], want, atol=1e-5) and torch.allclose(res[1][3], want, atol=1e-5)
+    # the deep profile of the same run: phases of a micro-batch and the closing gather segment
+    import json
+    doc = json.loads((tmp_path / "prof.json").read_text())
+    assert doc["deep_mode"] is True and len(doc["records"]) == 2
+    segs = doc["records"][0]["segments_ms"]
+    assert {"mb_data", "microbatches", "reduce_scatter", "grad_norm", "optimizer",
+            "loss_allreduce", "allgather"} <= set(segs)

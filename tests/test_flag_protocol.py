@@ -94,3 +94,28 @@ def test_device_side_base_makes_relative_epochs_replayable():
     stale.signal(0, 0, 1)
     assert stale.wait(0, 0, 1, limit_s=0.01) is True
     assert stale.wait(0, 0, 1, limit_s=0.01) is True       # ... and stays true: epochs must grow
+
+
+def test_host_side_epoch_counter_wraps_modulo_two_to_the_32():
+    """The host's per-slot counter, the int32 tensor that carries it to the device-side base
+    and the value read back after graph replays all count modulo 2^32, like the device's
+    signed-difference comparison: crossing 2^31 or 2^32 never yields an epoch that a stale flag
+    already satisfies."""
+    from forgetrain_b200.parallel.fused_dp import _as_i32
+    world = 2
+    boards = FlagBoards(world)
+    for start in (0x7FFFFFFE, 0xFFFFFFFE):
+        epoch = start
+        boards.flags[:] = start                      # what earlier launches left behind
+        for _ in range(4):                           # host: (epoch + 1) & 0xFFFFFFFF
+            epoch = (epoch + 1) & 0xFFFFFFFF
+            # before anyone signals, the stale flags must NOT pass for the new epoch
+            assert boards.wait(0, 0, epoch, limit_s=0.005) is False
+            boards.status = [0] * world
+            bufs = _bufs(world, 8, seed=epoch & 7)
+            want = (bufs[0] + bufs[1]) / 2
+            run_ranks(world, lambda r: reduce_scatter(boards, bufs, r, epoch=epoch))
+            assert np.allclose(bufs[0][:8], want[:8], atol=1e-6)
+            # the device base travels through an int32 tensor and back without losing bits
+            assert (_as_i32(epoch) & 0xFFFFFFFF) == epoch and -(1 << 31) <= _as_i32(epoch) < (1 << 31)
+        assert boards.status == [0, 0]

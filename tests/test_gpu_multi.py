@@ -1,4 +1,4 @@
-"""Multi-GPU tests (2 GPUs): peer-memory collectives against their NCCL counterparts, the
+"""Multi-GPU tests (2 and 4 GPUs): peer-memory collectives against their NCCL counterparts, the
 bounded-wait failure path, and fused-vs-NCCL training equivalence. Each test spawns one child
 process per GPU; every child carries a watchdog that ends it past a deadline."""
 import os
@@ -14,6 +14,7 @@ pytestmark = pytest.mark.gpu
 
 NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
 needs2 = pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
+needs4 = pytest.mark.skipif(NGPU < 4, reason="needs 4 GPUs")
 
 
 def _free_port():
@@ -31,6 +32,23 @@ def _entry(rank, world, port, fn, args, q, env):
     except BaseException as e:  # noqa: BLE001
         q.put((rank, "err", "".join(traceback.format_exception(e))))
     finally:
+        # Leave in step: no rank may exit while a peer still runs a kernel on, or holds a
+        # mapping of, the shared (symmetric / multicast) buffers. Drain this GPU, meet the
+        # others, drop the buffers, take the process group down, and only then go.
+        try:
+            import gc
+            import torch.distributed as dist
+            torch.cuda.synchronize()
+            if dist.is_initialized():
+                dist.barrier()
+                torch.cuda.synchronize()
+            gc.collect()
+            torch.cuda.synchronize()
+            if dist.is_initialized():
+                dist.barrier()
+                dist.destroy_process_group()
+        except BaseException:  # noqa: BLE001  (a failed rank: the watchdog bounds the rest)
+            pass
         q.close()
         q.join_thread()          # flush the result before leaving without interpreter teardown
         os._exit(0)
@@ -60,14 +78,14 @@ def run_gpus(fn, world, *args, env=None):
 
 
 # ------------------------------------------------------------------------------------------
-def _collectives(rank, world, use_multimem):
+def _collectives(rank, world, use_multimem, per_rank=128 * 1031):
     import torch.distributed as dist
     from forgetrain_b200.ops import _lib
     from forgetrain_b200.parallel.buckets import Bucket
     from forgetrain_b200.parallel.fused_dp import FusedDPComm, SymmetricBuffers
     from forgetrain_b200.parallel.topology import init_topology
     topo = init_topology(1)
-    n = 128 * world * 1031          # not a power of two
+    n = per_rank * world            # a bucket is any multiple of 128 * world elements
     symm = SymmetricBuffers(n + 128 * world, topo.device, topo.dp_group, rank, world,
                             use_multimem=use_multimem)
     comm = FusedDPComm(symm, timeout_ms=20000)
@@ -91,7 +109,6 @@ def _collectives(rank, world, use_multimem):
         lo, hi = b.shard_range(rank, world)
         out[f"rs_err{rep}"] = float((symm.grads[lo:hi] - ref[lo:hi]).abs().max())
         out[f"ss_err{rep}"] = abs(float(sumsq) - float(ref[lo:hi].pow(2).sum())) / float(ref[lo:hi].pow(2).sum())
-        other = [i for i in range(n) if False]
         out[f"guard{rep}"] = float((symm.grads[n:] - 7.0).abs().max())
     # all-gather of bf16 parameters
     symm.params.zero_()
@@ -142,13 +159,30 @@ def _collectives(rank, world, use_multimem):
 @pytest.mark.parametrize("use_multimem", [True, False])
 def test_fused_collectives_match_nccl(use_multimem):
     res = run_gpus(_collectives, 2, use_multimem)
+    _check_collectives(res, 2)      # two chained all-reduces: (1+2)*2 = 6 and 10*2*2 = 40
+
+
+def _check_collectives(res, world):
+    tot = float(sum(range(1, world + 1)))
     for o in res:
         assert o["rs_err0"] < 1e-6 and o["rs_err1"] < 1e-6, o
         assert o["ss_err0"] < 1e-4 and o["guard0"] == 0.0 and o["guard1"] == 0.0, o
         assert o["ag_err"] == 0.0, o
         assert o["adam_ag_err"] <= 1e-2 and o["adam_master_err"] < 1e-5, o
-        # two chained all-reduces over 2 ranks: (1+2)*2 = 6 and 10*2*2 = 40
-        assert o["small"] == [6.0, 40.0], o
+        assert o["small"] == [tot * world, 10.0 * world * world], o
+
+
+@needs4
+@pytest.mark.parametrize("use_multimem", [True, False])
+@pytest.mark.parametrize("per_rank", [128, 128 * 1031, 16 * 1024 * 1024])
+def test_fused_collectives_match_nccl_on_four_ranks(use_multimem, per_rank):
+    """Above two ranks the gathers leave through `multimem.st` (one store reaches every rank)
+    and the reductions through `multimem.ld_reduce`; sizes from one 128-element shard per rank
+    over an odd multiple to a 256 MB fp32 bucket, guard band checked every time."""
+    res = run_gpus(_collectives, 4, use_multimem, per_rank)
+    _check_collectives(res, 4)
+    if use_multimem:
+        assert all(o["multimem"] for o in res), "the NVSwitch multicast mapping was not used"
 
 
 # ------------------------------------------------------------------------------------------
@@ -219,7 +253,9 @@ def _train(rank, world, comm, full_graph=False, steps=5):
         torch.cuda.synchronize()
         _lib.check_status()
         assert float(v) == world
-    return losses, norms, len(tr.reducer.buckets)
+    # every rank must hold bit-identical parameters after the gathers
+    csum = int(tr.store.flat_params.view(torch.int16).to(torch.int64).sum())
+    return losses, norms, len(tr.reducer.buckets), csum
 
 
 @needs2
@@ -231,6 +267,26 @@ def test_dp2_fused_matches_nccl_training():
     assert fused[0][0][-1] < fused[0][0][0]
     assert fused[0][0] == pytest.approx(nccl[0][0], rel=2e-3)
     assert fused[0][1] == pytest.approx(nccl[0][1], rel=2e-2)
+    assert fused[0][3] == fused[1][3]                       # identical parameters on both ranks
+
+
+@needs4
+def test_dp4_fused_matches_nccl_training_and_whole_step_graph():
+    """Four data-parallel ranks: peer-memory collectives (multimem paths) against NCCL, then
+    the same run replayed from one whole-step CUDA graph per rank."""
+    fused = run_gpus(_train, 4, "fused")
+    nccl = run_gpus(_train, 4, "nccl")
+    assert all(f[0] == fused[0][0] for f in fused)
+    assert len({f[3] for f in fused}) == 1, "ranks disagree on the gathered parameters"
+    assert fused[0][0][-1] < fused[0][0][0]
+    assert fused[0][0] == pytest.approx(nccl[0][0], rel=2e-3)
+    assert fused[0][1] == pytest.approx(nccl[0][1], rel=2e-2)
+    eager = run_gpus(_train, 4, "fused", False, 6)
+    graph = run_gpus(_train, 4, "fused", True, 6)
+    assert all(g[0] == graph[0][0] for g in graph)
+    assert len({g[3] for g in graph}) == 1
+    assert graph[0][0] == pytest.approx(eager[0][0], rel=5e-3)
+    assert graph[0][1] == pytest.approx(eager[0][1], rel=5e-2)
 
 
 @needs2
@@ -282,6 +338,19 @@ def test_tp2_matches_tp1_on_gpu(sp):
     assert tp2[0][0] == pytest.approx(tp1[0][0], rel=5e-3)
     assert tp2[0][1] == pytest.approx(tp1[0][1], rel=3e-2)
     assert tp2[0][0][-1] < tp2[0][0][0]
+
+
+@needs4
+@pytest.mark.parametrize("comm", ["nccl", "fused"])
+def test_tp4_with_replicated_kv_heads_on_gpus(comm):
+    """TP degree 4 over 2 KV groups: query heads split four ways, k / v replicated inside a
+    group (their gradients summed over the replicas), vocabulary and FFN split four ways."""
+    tp4 = run_gpus(_tp_train, 4, 4, True, comm)
+    tp1 = run_gpus(_tp_train, 1, 1, False)
+    assert all(t[0] == pytest.approx(tp4[0][0], rel=1e-4) for t in tp4)
+    assert tp4[0][0] == pytest.approx(tp1[0][0], rel=5e-3)
+    assert tp4[0][1] == pytest.approx(tp1[0][1], rel=3e-2)
+    assert tp4[0][0][-1] < tp4[0][0][0]
 
 
 @needs2

@@ -155,3 +155,28 @@ def test_position_ids_reach_the_rotary_embedding():
         losses[name] = float(tr.train_step([batch])["loss"])
     assert losses["plain"] == losses["none"]
     assert abs(losses["reset"] - losses["none"]) > 1e-6
+
+
+@pytest.mark.parametrize("attn,mlp", [(True, False), (False, True), (True, True)])
+def test_recompute_switches_give_bitwise_the_saved_activation_gradients(attn, mlp):
+    """recompute_attn / recompute_mlp rebuild the dropped activations with the forward's own
+    ops on the same inputs, so loss and every gradient are bitwise those of the default path;
+    what the forward keeps per layer shrinks accordingly."""
+    torch.manual_seed(3)
+    spec = _small_spec(False)
+    tokens = torch.randint(0, spec.vocab_size, (2, 64))
+    labels = torch.randint(0, spec.vocab_size, (2, 64))
+    out = []
+    for kw in ({}, {"recompute_attn": attn, "recompute_mlp": mlp}):
+        store = ParamStore(spec, "cpu", torch.float32)
+        store.init_random(0)
+        model = MiniCPM4(spec, store, **kw)
+        logits = model.forward(tokens)
+        kept = [(sv.attn is not None, sv.y1 is not None, sv.act is not None) for sv in model._saved]
+        loss, dlogits = model.loss_and_dlogits(logits, labels, None, 1.0)
+        model.backward(tokens, dlogits, accumulate=False)
+        out.append((float(loss), store.flat_grads.clone(), kept))
+    (l0, g0, k0), (l1, g1, k1) = out
+    assert l0 == l1 and torch.equal(g0, g1)
+    assert all(k == (True, True, True) for k in k0)
+    assert all(k == (not attn, not mlp, not mlp) for k in k1)

@@ -38,6 +38,7 @@ def test_fifo_order_depth_and_events():
     assert len(pf.queue) == 3                      # refilled to depth after the pop
     rest = [int(b["tokens"][0, 0]) for b in pf]
     assert rest == [1, 2, 3, 4]
+    assert pf.recorded_tensors == 5 * 3            # every tensor handed out was stream-recorded
     assert FakeEvent.log.count("record") == 5 and FakeEvent.log.count("wait") == 5
 
 

@@ -18,7 +18,8 @@ def _ptr(t):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
-@pytest.mark.parametrize("T,H", [(1000, 1024), (4096, 4096), (300, 256)])
+# H = 8192 fills the scratch rows to their full width (FT_NOALLOC_MAX_HIDDEN)
+@pytest.mark.parametrize("T,H", [(1000, 1024), (4096, 4096), (300, 256), (2048, 8192)])
 def test_noalloc_entry_point_matches_regular_entry_point(T, H):
     from forgetrain_b200.ops import _lib
     lib = ctypes.CDLL(str(_lib.LIB_PATH))          # the raw exported symbols
