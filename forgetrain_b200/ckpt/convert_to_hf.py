@@ -59,15 +59,23 @@ def to_hf_state_dict(params: dict[str, torch.Tensor], spec: ModelSpec, dtype=tor
     head = params.get("output.weight", params["tok_embeddings.weight"])
     tied = head.shape == params["tok_embeddings.weight"].shape and \
         torch.equal(head, params["tok_embeddings.weight"])
-    if not tied:
-        out["lm_head.weight"] = cast(head)
+    # always written, from the trained head, so that any drift between the two tables during
+    # training is kept (the reference script does the same, scripts/convert_to_hf.py:114-117)
+    out["lm_head.weight"] = cast(head).clone() if tied else cast(head)   # own storage in the file
     return out, tied
 
 
 def hf_config(spec: ModelSpec, tied: bool, dtype: str = "bfloat16") -> dict:
     return {
         "architectures": ["MiniCPMForCausalLM"],
+        # resolved by from_pretrained(trust_remote_code=True) against the MiniCPM modeling files
+        "auto_map": {
+            "AutoConfig": "configuration_minicpm.MiniCPMConfig",
+            "AutoModel": "modeling_minicpm.MiniCPMModel",
+            "AutoModelForCausalLM": "modeling_minicpm.MiniCPMForCausalLM",
+        },
         "model_type": "minicpm",
+        "initializer_range": 0.1,
         "vocab_size": spec.vocab_size,
         "hidden_size": spec.hidden_size,
         "intermediate_size": spec.ffn_hidden_size,
@@ -86,7 +94,7 @@ def hf_config(spec: ModelSpec, tied: bool, dtype: str = "bfloat16") -> dict:
         "torch_dtype": dtype,
         "use_cache": True,
         "bos_token_id": 1,
-        "eos_token_id": 2,
+        "eos_token_id": [2, 73440] if spec.vocab_size > 73440 else 2,
     }
 
 
@@ -102,7 +110,11 @@ def convert(checkpoint: str, output: str, model: str = "0.5b", dtype: str = "bfl
             raise ValueError(f"{checkpoint}: found {len(shards)} rank files for tp_size "
                              f"{shards[0].get('tp_size')}")
         tied = "output.weight" not in shards[0]["params"]
-        spec = load_model_spec(model, tie_embeddings=tied)
+        # the full vocabulary size: stored with the shards, else the sum of the shard rows
+        # (which includes the padding of the vocabulary split, cut off again by the merge)
+        vocab = int(shards[0].get("vocab_size") or 0) or None
+        kw = {"vocab_size": vocab} if vocab else {}
+        spec = load_model_spec(model, tie_embeddings=tied, **kw)
         params = merge_tp_shards(spec, [sh["params"] for sh in shards])
     else:
         state = load_resume_checkpoint(checkpoint)

@@ -355,7 +355,8 @@ class Trainer:
                                     optimizer_state=opt_state, num_samples=self.num_samples,
                                     dataloader_state=dataloader_state, rank=writer,
                                     async_io=async_io, filename=f"rank_{self.topo.tp_rank}.pt",
-                                    extra={"tp_size": self.topo.tp_size, "tp_rank": self.topo.tp_rank})
+                                    extra={"tp_size": self.topo.tp_size, "tp_rank": self.topo.tp_rank,
+                                           "vocab_size": self.spec.vocab_size})
 
     def load(self, path) -> dict:
         p = Path(path)

@@ -9,8 +9,10 @@ iterations, bf16 inputs N(0,1) from a fixed seed).
     python microbench.py tp    (under torchrun, N = TP degree)  fused AG->GEMM / GEMM->RS [--tokens 4096]
 
 Every sub-command prints one JSON line per case with the achieved rate and its fraction of the
-measured peak (``MEASURED_PEAKS.json`` when present, else the stated fallback). ``--once`` runs
-each kernel a single time after one warm-up, for captures under a profiler.
+measured peak (``MEASURED_PEAKS.json`` when present, else the stated fallback), and a ``clocks``
+record: SM clock and throttle reasons read through NVML right after every timed iteration
+(median clock, union of the reasons seen). ``--once`` runs each kernel a single time after one
+warm-up, for captures under a profiler.
 """
 from __future__ import annotations
 
@@ -34,6 +36,58 @@ def peaks() -> dict:
 
 
 _flush_buf = None
+
+
+class _Clocks:
+    """SM clock / throttle reasons through NVML (read-only), sampled by ``time_ms``."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self):
+        self.h = None
+        self.sm, self.reasons, self.max_sm = [], set(), None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            idx = torch.cuda.current_device() if torch.cuda.is_available() else 0
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if vis:
+                idx = int(vis.split(",")[idx])
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            self.max_sm = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.h = None
+
+    def sample(self):
+        if self.h is None:
+            return
+        try:
+            self.sm.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+            bits = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+            for b, name in self.REASONS.items():
+                if bits & b:
+                    self.reasons.add(name)
+        except Exception:
+            pass
+
+    def take(self) -> dict:
+        """The record of the samples since the last call."""
+        sm = sorted(self.sm)
+        out = {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_sm,
+               "samples": len(sm), "reasons": sorted(self.reasons)}
+        self.sm, self.reasons = [], set()
+        return out
+
+
+_clocks = None
+
+
+def clocks() -> _Clocks:
+    global _clocks
+    if _clocks is None:
+        _clocks = _Clocks()
+    return _clocks
 
 
 def flush_l2():
@@ -61,12 +115,25 @@ def time_ms(fn, iters: int, once: bool = False) -> float:
         fn()
         e1.record()
         torch.cuda.synchronize()
+        clocks().sample()
         ts.append(e0.elapsed_time(e1))
     ts.sort()
-    return ts[len(ts) // 2]
+    return Timed(ts[len(ts) // 2], clocks().take())
+
+
+class Timed(float):
+    """A median time in ms that remembers the clock record of its timed iterations."""
+    def __new__(cls, ms, rec):
+        obj = super().__new__(cls, ms)
+        obj.clocks = rec
+        return obj
 
 
 def emit(**kw):
+    for k, v in list(kw.items()):
+        if isinstance(v, Timed):
+            kw["clocks" if "clocks" not in kw else f"clocks_{k}"] = v.clocks
+            kw[k] = float(v)
     print(json.dumps(kw), flush=True)
 
 

@@ -1,9 +1,21 @@
 """Candidate kernels under neighbour load on the same GPU (the reference's stress harness,
-exports/train_engine_8b/tests/_stress_runner.py, in small): while background threads keep the
-device busy with library GEMMs, device-to-device copies, allocator churn and stream/event
-traffic, the candidate op loops on its own stream. PASS = no exception, no NaN/Inf, the result
-still matches the oracle afterwards, no iteration slower than the hang limit, every worker
-alive. A watchdog ends the process past the deadline."""
+exports/train_engine_8b/tests/_stress_runner.py and _stress_workers.py, in small): while seven
+background threads keep the device busy, the candidate op loops on its own stream.
+
+Neighbours (reference W1-W7):
+    W1 compute blast   library bf16 GEMM mix (SM occupancy, tensor cores, TMEM of library kernels)
+    W2 memory blast    device-to-device copies (HBM, L2, copy engines)
+    W3 TMA storm       K-heavy library GEMM (many descriptor-driven loads per tile)
+    W4 cluster         large library GEMMs, which run as thread-block clusters on this GPU
+    W5 stream chaos    cross-stream event wiring, high-priority stream
+    W6 graph replay    a small captured graph replayed in a loop
+    W7 allocator churn caching-allocator traffic
+
+PASS = no exception, no NaN/Inf, the result still matches the oracle afterwards, no iteration
+slower than the hang limit, every worker alive. A watchdog ends the process past the deadline.
+``STRESS_KERNEL=cublas`` swaps every GEMM candidate for the library call: the negative control
+that shows the harness itself passes when the candidate is known-good. ``STRESS_DURATION_S``
+lengthens the run."""
 import os
 import threading
 import time
@@ -13,17 +25,21 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
+DURATION_S = float(os.environ.get("STRESS_DURATION_S", "3.0"))
+USE_LIBRARY = os.environ.get("STRESS_KERNEL", "") == "cublas"
+
 
 def _workers(stop):
-    def blast():
-        a = torch.randn(2048, 2048, device="cuda", dtype=torch.bfloat16)
+    def w1_compute_blast():
+        mats = [torch.randn(n, n, device="cuda", dtype=torch.bfloat16) for n in (1024, 2048, 3072)]
         s = torch.cuda.Stream()
         with torch.cuda.stream(s):
             while not stop.is_set():
-                (a @ a).sum()
+                for a in mats:
+                    (a @ a).sum()
                 s.synchronize()
 
-    def d2d():
+    def w2_mem_blast():
         a = torch.empty(64 << 20, device="cuda", dtype=torch.uint8)
         b = torch.empty_like(a)
         s = torch.cuda.Stream()
@@ -32,14 +48,26 @@ def _workers(stop):
                 b.copy_(a, non_blocking=True)
                 s.synchronize()
 
-    def churn():
-        while not stop.is_set():
-            xs = [torch.empty(1 << 20, device="cuda") for _ in range(8)]
-            del xs
-            time.sleep(0.001)
+    def w3_tma_storm():
+        a = torch.randn(256, 32768, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn(256, 32768, device="cuda", dtype=torch.bfloat16)
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            while not stop.is_set():
+                (a @ b.t()).sum()
+                s.synchronize()
 
-    def events():
-        s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    def w4_cluster():
+        a = torch.randn(8192, 4096, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn(4096, 4096, device="cuda", dtype=torch.bfloat16)
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            while not stop.is_set():
+                (a @ b).sum()
+                s.synchronize()
+
+    def w5_stream_chaos():
+        s1, s2 = torch.cuda.Stream(), torch.cuda.Stream(priority=-1)
         x = torch.ones(1 << 16, device="cuda")
         while not stop.is_set():
             with torch.cuda.stream(s1):
@@ -50,12 +78,37 @@ def _workers(stop):
             with torch.cuda.stream(s2):
                 x.mul_(1.0)
             s2.synchronize()
-    return [threading.Thread(target=f, daemon=True) for f in (blast, d2d, churn, events)]
+
+    def w6_graph_replay():
+        s = torch.cuda.Stream()
+        x = torch.ones(1 << 18, device="cuda")
+        y = torch.empty_like(x)
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                torch.add(x, 1.0, out=y)
+            s.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                torch.add(x, 1.0, out=y)
+                torch.mul(y, 0.5, out=y)
+            while not stop.is_set():
+                g.replay()
+                s.synchronize()
+
+    def w7_alloc_churn():
+        while not stop.is_set():
+            xs = [torch.empty(1 << 20, device="cuda") for _ in range(8)]
+            del xs
+            time.sleep(0.001)
+    fns = (w1_compute_blast, w2_mem_blast, w3_tma_storm, w4_cluster, w5_stream_chaos,
+           w6_graph_replay, w7_alloc_churn)
+    return [threading.Thread(target=f, daemon=True, name=f.__name__) for f in fns]
 
 
-def _stress(candidate, oracle_check, seconds=4.0, hang_s=5.0):
+def _stress(candidate, oracle_check, seconds=None, hang_s=5.0, before_each=None):
     from forgetrain_b200.ops import _lib
-    deadline = threading.Timer(90.0, lambda: os._exit(2))
+    seconds = DURATION_S if seconds is None else seconds
+    deadline = threading.Timer(90.0 + seconds, lambda: os._exit(2))
     deadline.daemon = True
     deadline.start()
     stop = threading.Event()
@@ -69,13 +122,18 @@ def _stress(candidate, oracle_check, seconds=4.0, hang_s=5.0):
         with torch.cuda.stream(stream):
             while time.time() < t_end:
                 t0 = time.time()
+                if before_each is not None:
+                    before_each()
                 out = candidate()
                 stream.synchronize()
                 worst = max(worst, time.time() - t0)
                 n += 1
                 if n % 50 == 0:
                     assert torch.isfinite(out.float()).all()
-            assert all(w.is_alive() for w in ws), "a neighbour worker died"
+            dead = [w.name for w in ws if not w.is_alive()]
+            assert not dead, f"neighbour workers died: {dead}"
+            if before_each is not None:
+                before_each()
             out = candidate()
             stream.synchronize()
     finally:
@@ -89,24 +147,70 @@ def _stress(candidate, oracle_check, seconds=4.0, hang_s=5.0):
     return n
 
 
-def test_gemm_under_neighbour_load():
+def _close(ref, rtol=0.05, atol=0.5):
+    def check(out):
+        assert torch.allclose(out.float(), ref, rtol=rtol, atol=atol)
+    return check
+
+
+@pytest.mark.parametrize("name,T,N,K", [("attn_out", 4096, 1024, 1024), ("fc1", 4096, 8192, 1024),
+                                        ("lm_head", 2048, 73448, 1024)])
+def test_forward_gemm_under_neighbour_load(name, T, N, K):
     from forgetrain_b200.ops import gemm
     torch.manual_seed(0)
-    x = torch.randn(4096, 1024, device="cuda").to(torch.bfloat16)
-    w = (torch.randn(4096, 1024, device="cuda") * 0.05).to(torch.bfloat16)
+    x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
     ref = x.float() @ w.float().t()
-
-    def check(out):
-        assert torch.allclose(out.float(), ref, rtol=0.05, atol=0.5)
-    assert _stress(lambda: gemm.linear_fwd(x, w), check) > 10
+    cand = (lambda: x @ w.t()) if USE_LIBRARY else (lambda: gemm.linear_fwd(x, w))
+    assert _stress(cand, _close(ref)) > 10
 
 
-def test_attention_under_neighbour_load():
+def test_dgrad_gemm_under_neighbour_load():
+    from forgetrain_b200.ops import gemm
+    torch.manual_seed(0)
+    dy = torch.randn(4096, 4096, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(4096, 1024, device="cuda") * 0.05).to(torch.bfloat16)
+    ref = dy.float() @ w.float()
+    cand = (lambda: dy @ w) if USE_LIBRARY else (lambda: gemm.linear_dgrad(dy, w))
+    assert _stress(cand, _close(ref)) > 10
+
+
+def test_wgrad_gemm_with_reduce_add_under_neighbour_load():
+    """The fp32 weight gradient with split-K and accumulation: partial tiles leave through TMA
+    reduce-adds into a buffer that already holds the previous micro-batch's sum."""
+    from forgetrain_b200.ops import gemm
+    torch.manual_seed(0)
+    dy = torch.randn(8192, 1024, device="cuda").to(torch.bfloat16)
+    x = torch.randn(8192, 1024, device="cuda").to(torch.bfloat16)
+    base = torch.randn(1024, 1024, device="cuda")
+    ref = base + dy.float().t() @ x.float()
+    out = torch.empty_like(base)
+
+    def reset():
+        out.copy_(base)
+
+    def cand():
+        if USE_LIBRARY:
+            out.add_(dy.float().t() @ x.float())
+        else:
+            gemm.linear_wgrad(dy, x, out, True)
+        return out
+    assert _stress(cand, _close(ref, rtol=0.02, atol=2.0), before_each=reset) > 10
+
+
+def test_attention_forward_and_backward_under_neighbour_load():
     from forgetrain_b200.ops import attention as A, reference as R
     torch.manual_seed(0)
-    qkv = torch.randn(2 * 1024, 2 * 6 * 64, device="cuda").to(torch.bfloat16)
-    ref, _ = R.attention_fwd(qkv, 2, 2, 4, 64)
+    B, S, G, g, D = 2, 1024, 2, 4, 64
+    qkv = torch.randn(B * S, G * (g + 2) * D, device="cuda").to(torch.bfloat16)
+    ref, rlse = R.attention_fwd(qkv, B, G, g, D)
+    assert _stress(lambda: A.attention_fwd(qkv, B, G, g, D)[0],
+                   _close(ref.float(), atol=0.05)) > 10
+    out, lse = A.attention_fwd(qkv, B, G, g, D)
+    do = torch.randn_like(out)
+    rd = R.attention_bwd(do, qkv, ref, rlse, B, G, g, D)
 
-    def check(out):
-        assert torch.allclose(out.float(), ref.float(), rtol=0.05, atol=0.05)
-    assert _stress(lambda: A.attention_fwd(qkv, 2, 2, 4, 64)[0], check) > 10
+    def check(d):
+        err = (d.float() - rd.float()).abs().max() / rd.float().abs().max()
+        assert float(err) < 0.03, float(err)
+    assert _stress(lambda: A.attention_bwd(do, qkv, out, lse, B, G, g, D), check) > 10

@@ -51,11 +51,13 @@ def test_export_writes_safetensors_and_config(tmp_path, tie):
     assert cfg["architectures"] == ["MiniCPMForCausalLM"] and cfg["tie_word_embeddings"] is tie
     assert cfg["scale_emb"] == 12.0 and cfg["dim_model_base"] == 256 and cfg["scale_depth"] == 1.4
     assert cfg["num_key_value_heads"] == 2 and cfg["rms_norm_eps"] == 1e-6
-    assert ("lm_head.weight" in sd) is (not tie)
+    assert "lm_head.weight" in sd                   # always written, like the reference script
+    assert cfg["auto_map"]["AutoModelForCausalLM"] == "modeling_minicpm.MiniCPMForCausalLM"
+    assert cfg["initializer_range"] == 0.1
     gate = sd["model.layers.1.mlp.gate_proj.weight"]
     assert torch.equal(gate, st.params["layers.1.feed_forward.wfc1.weight"][:256])
     assert torch.equal(sd["model.layers.0.self_attn.o_proj.weight"], st.params["layers.0.attention.wo.weight"])
-    assert len(sd) == 2 + 9 * 2 + (0 if tie else 1)
+    assert len(sd) == 2 + 9 * 2 + 1
 
 
 def test_packing_and_loader_cursor():
