@@ -381,17 +381,15 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
         for (int k = 0; k < 64; ++k)
           if (half * 64 + k > r) s[k] = 0xff800000u;  // -inf -> p = 0
       }
-      // Staged over the whole 64-column slice so that every stage is 32-64 independent
-      // instructions (the per-element chain fma -> ex2 -> mul -> cvt is long and serial).
       uint64_t* s2 = reinterpret_cast<uint64_t*>(s);    // pairs of scores / probabilities
       uint64_t* d2 = reinterpret_cast<uint64_t*>(dp);   // pairs of dP / dS
-#pragma unroll
-      for (int i = 0; i < 32; ++i) s2[i] = fma_f32x2(s2[i], sl2x2, nl2);   // t = s * scale - lse2
-#pragma unroll
-      for (int k = 0; k < 64; ++k) s[k] = __float_as_uint(fast_exp2(__uint_as_float(s[k])));
       if (ALIAS) {
         // P goes out first (dV can start); dP of this step arrives once dQ of the previous
         // step has left the columns the two share.
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s2[i] = fma_f32x2(s2[i], sl2x2, nl2);   // t = s * scale - lse2
+#pragma unroll
+        for (int k = 0; k < 64; ++k) s[k] = __float_as_uint(fast_exp2(__uint_as_float(s[k])));
         mbar_wait(&p_free[n % NPB], ((n / NPB) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
@@ -399,7 +397,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
 #pragma unroll
           for (int q2 = 0; q2 < 4; ++q2) {
             const int k = c * 8 + q2 * 2;
-            pk[q2] = pack_bf16x2_int(__uint_as_float(s[k]), __uint_as_float(s[k + 1]));
+            pk[q2] = pack_bf16x2(__uint_as_float(s[k]), __uint_as_float(s[k + 1]));
           }
           *reinterpret_cast<uint4*>(rowp + ((c ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
@@ -411,27 +409,49 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
         tmem_ld32(tm_dPt + lane_off + half * 64, dp);
         tmem_ld32(tm_dPt + lane_off + half * 64 + 32, dp + 32);
         tmem_ld_wait();
-      }
+        mbar_wait(&ds_free[n % NDS], ((n / NDS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) d2[i] = add_f32x2(d2[i], nd2);          // dd = dP - delta
+        for (int c = 0; c < 8; ++c) {
+          uint32_t dk[4];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) d2[i] = mul_f32x2(s2[i], d2[i]);        // dS = P * dd
-      // the buffers written below were last read by dV (P) and by dK / dQ (dS)
-      if (!ALIAS)
-        mbar_wait(&p_free[n % NPB], ((n / NPB) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
-      mbar_wait(&ds_free[n % NDS], ((n / NDS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint32_t pk[4], dk[4];
-#pragma unroll
-        for (int q2 = 0; q2 < 4; ++q2) {
-          const int k = c * 8 + q2 * 2;
-          if (!ALIAS) pk[q2] = pack_bf16x2_int(__uint_as_float(s[k]), __uint_as_float(s[k + 1]));
-          dk[q2] = pack_bf16x2_int(__uint_as_float(dp[k]), __uint_as_float(dp[k + 1]));
+          for (int q2 = 0; q2 < 4; ++q2) {
+            const int i = c * 4 + q2;
+            const uint64_t ds = mul_f32x2(s2[i], add_f32x2(d2[i], nd2));   // dS = P * (dP - delta)
+            float a, b2;
+            unpack_f32x2(ds, a, b2);
+            dk[q2] = pack_bf16x2(a, b2);
+          }
+          *reinterpret_cast<uint4*>(rowd + ((c ^ (r & 7)) << 4)) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
         }
-        const int chunk = (c ^ (r & 7)) << 4;
-        if (!ALIAS) *reinterpret_cast<uint4*>(rowp + chunk) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-        *reinterpret_cast<uint4*>(rowd + chunk) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
+      } else {
+        // the buffers written below were last read by dV (P) and by dK / dQ (dS) of an earlier
+        // step: long done in the steady state
+        mbar_wait(&p_free[n % NPB], ((n / NPB) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+        mbar_wait(&ds_free[n % NDS], ((n / NDS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+        // One interleaved stream over 8 chunks of 8 columns: a warp can issue an `ex2` only
+        // every ~16 cycles, so scale, exponential, dS = P * (dP - delta), the two bf16 packings
+        // and the two shared-memory stores go out in the gaps instead of in stages of their own.
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint32_t pk[4], dk[4];
+#pragma unroll
+          for (int q2 = 0; q2 < 4; ++q2) {
+            const int i = c * 4 + q2;
+            const uint64_t t = fma_f32x2(s2[i], sl2x2, nl2);               // s * scale - lse2
+            float e0, e1;
+            unpack_f32x2(t, e0, e1);
+            e0 = fast_exp2(e0);
+            e1 = fast_exp2(e1);
+            const uint64_t ds = mul_f32x2(pack_f32x2(e0, e1), add_f32x2(d2[i], nd2));
+            float a, b2;
+            unpack_f32x2(ds, a, b2);
+            pk[q2] = pack_bf16x2(e0, e1);
+            dk[q2] = pack_bf16x2(a, b2);
+          }
+          const int chunk = (c ^ (r & 7)) << 4;
+          *reinterpret_cast<uint4*>(rowp + chunk) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(rowd + chunk) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
+        }
       }
       tc_fence_before();
       fence_proxy_async_smem();

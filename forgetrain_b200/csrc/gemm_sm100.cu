@@ -235,7 +235,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = warp_idx_uniform();
   const int lane = threadIdx.x & 31;
   constexpr uint32_t TMEM_COLS = 2 * BN;  // 256 or 512: two fp32 accumulators of BN columns
 
@@ -322,11 +322,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    // The whole warp walks the tiles and waits on the barriers; one elected lane issues, so
+    // that descriptors, TMEM addresses and loop state stay warp-uniform (see elect_one_sync).
+    {
       const uint32_t idesc = make_idesc_bf16(GEMM_BM, BN, p.a_mn, p.b_mn);
       const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
       const uint32_t a_kstep = p.a_mn ? (2048u >> 4) : (32u >> 4);
       const uint32_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
+      const uint32_t smem_base = smem_u32(smem);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -341,19 +344,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int ki = 0; ki < kn; ++ki) {
           mbar_wait(&full_bar[stage], phase, abort_flag, p.status, FT_ERR_WAIT_FULL);
           tc_fence_after();
-          const uint32_t sA = smem_u32(smem + stage * L::STAGE_BYTES);
-          const uint32_t sB = sA + L::A_BYTES;
-          const uint64_t adesc = make_smem_desc(sA, a_lbo, 1024);
-          const uint64_t bdesc = make_smem_desc(sB, b_lbo, 1024);
+          if (elect_one_sync()) {
+            const uint32_t sA = smem_base + stage * L::STAGE_BYTES;
+            const uint32_t a_lo = smem_desc_lo(sA, a_lbo);
+            const uint32_t b_lo = smem_desc_lo(sA + L::A_BYTES, b_lbo);
+            umma_ss_lo_dyn(tmem_d, a_lo, b_lo, idesc, ki > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < GEMM_BK / 16; ++kk) {
-            umma_ss(tmem_d, adesc + kk * a_kstep, bdesc + kk * b_kstep, idesc,
-                    (ki > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 1; kk < GEMM_BK / 16; ++kk)
+              umma_ss_lo<1>(tmem_d, a_lo + kk * a_kstep, b_lo + kk * b_kstep, idesc);
+            umma_commit(&empty_bar[stage]);
           }
-          umma_commit(&empty_bar[stage]);
+          __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        umma_commit(&tfull_bar[buf]);
+        if (elect_one_sync()) umma_commit(&tfull_bar[buf]);
+        __syncwarp();
       }
     }
   } else {
