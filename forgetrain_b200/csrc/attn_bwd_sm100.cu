@@ -29,6 +29,12 @@ namespace ft {
 
 int get_tmap_2d(CUtensorMap* out, const void* base, int elt, uint64_t rows, uint64_t cols,
                 uint64_t ld, uint32_t box_r, uint32_t box_c);
+// main kernel for head_dim 64 (P^T / dS^T kept in TMEM), attn_bwd_kv_sm100.cu
+int launch_fa_bwd_kv64(const CUtensorMap& tq, const CUtensorMap& tdo, const CUtensorMap& tacc,
+                       int S, int Hq, int g,
+                       int n_groups, int batch, int hpc, int ld_acc, float scale_log2,
+                       const float* neg_lse2, const float* neg_delta, float* acc, int* status,
+                       cudaStream_t st);
 
 constexpr int FAB_THREADS = 512;  // WG0: TMA + MMA, WG1/WG2: softmax halves, WG3: dQ / dK / dV drain
 constexpr int FAB_BLK = 128;
@@ -37,8 +43,8 @@ struct FaBwdParams {
   int S, Hq, g, n_groups, batch, hpc;  // hpc: query heads per CTA
   int ld_acc;                          // row pitch (floats) of the fp32 accumulator
   float scale_log2;
-  const float* lse2;   // [B][Hq][S]  lse * log2(e)
-  const float* delta;  // [B][Hq][S]
+  const float* lse2;   // [B][Hq][S]  -(lse * log2(e))
+  const float* delta;  // [B][Hq][S]  -delta
   float* acc;          // [T][ld_acc] fp32, same column layout as qkv
   int* status;
 };
@@ -361,7 +367,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       uint8_t* rowp = smem + L::P_OFF + (n % NPB) * 32768 + half * 16384 + r * 128;   // P row
       uint8_t* rowd = smem + L::DS_OFF + (n % NDS) * 32768 + half * 16384 + r * 128;  // dS row
       mbar_wait(&qdo_full[n % QS], (n / QS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
-      const float nl = -stat[r], nd = -stat[128 + r];
+      const float nl = stat[r], nd = stat[128 + r];   // the statistics are stored negated
       const uint64_t nl2 = pack_f32x2(nl, nl), nd2 = pack_f32x2(nd, nd);
       mbar_wait(sdp_full, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
@@ -522,7 +528,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   }
 }
 
-// delta[b,h,s] = sum_d out*dout ; lse2 = lse*log2(e). One thread per 8 elements.
+// delta[b,h,s] = -sum_d out*dout ; lse2 = -lse*log2(e). One thread per 8 elements.
 template <int D>
 __global__ void fa_bwd_pre_kernel(const __nv_bfloat16* __restrict__ out,
                                   const __nv_bfloat16* __restrict__ dout,
@@ -549,8 +555,8 @@ __global__ void fa_bwd_pre_kernel(const __nv_bfloat16* __restrict__ out,
   if (live && sub == 0) {
     const long bidx = t / S, s = t % S;
     const long idx = (bidx * Hq + h) * S + s;
-    delta[idx] = acc;
-    lse2[idx] = lse[idx] * 1.4426950408889634f;
+    delta[idx] = -acc;     // both statistics are stored negated: the main kernels only add them
+    lse2[idx] = -lse[idx] * 1.4426950408889634f;
   }
 }
 
@@ -643,8 +649,16 @@ extern "C" int ft_attn_bwd(const void* dout, const void* qkv, const void* out, c
   p.scale_log2 = scale * 1.4426950408889634f;
   p.lse2 = d_lse2; p.delta = d_delta; p.acc = static_cast<float*>(acc);
   p.status = status;
+#ifndef FT_FAB_SMEM_P64
+  CUtensorMap tacc;   // 32 x 32 fp32 boxes over the accumulator (dQ leaves through TMA reduce-adds)
+  if (get_tmap_2d(&tacc, acc, 4, T, ncols, ncols, 32, 32)) return -8;
+  int rc = (D == 64) ? launch_fa_bwd_kv64(tq, tdo, tacc, S, Hq, g, n_groups, batch, heads_per_cta, ncols,
+                                          p.scale_log2, d_lse2, d_delta, p.acc, status, st)
+                     : launch_fa_bwd<128, 1, 1, 1, 1>(tq, tdo, p, st);
+#else   // head_dim 64 on the shared-memory hand-over kernel as well (comparison builds)
   int rc = (D == 64) ? launch_fa_bwd<64, 3, 1, 2, 2>(tq, tdo, p, st)
                      : launch_fa_bwd<128, 1, 1, 1, 1>(tq, tdo, p, st);
+#endif
   if (rc) return rc;
   {
     const long total = T * (ncols / 8);
