@@ -67,7 +67,8 @@ struct FaBwdSmem {
   static constexpr int QDO_OFF = 2 * TILE;                 // QS x (Q tile, dO tile)
   static constexpr int P_OFF = QDO_OFF + QS * 2 * TILE;    // NP x P^T (128 x 128 bf16)
   static constexpr int DS_OFF = P_OFF + NP * 32768;        // NDS x dS^T
-  static constexpr int STAT_OFF = DS_OFF + NDS * 32768;    // NST x (lse2[128], delta[128]) fp32
+  static constexpr int DQ_OFF = DS_OFF + NDS * 32768;      // dQ staging: 8 boxes of 32 x 32 fp32
+  static constexpr int STAT_OFF = DQ_OFF + 32768;          // NST x (lse2[128], delta[128]) fp32
   static constexpr int BAR_OFF = STAT_OFF + NST * 1024;
   static constexpr int TOTAL = BAR_OFF + 256;              // base must come 1024-byte aligned
 };
@@ -75,7 +76,7 @@ struct FaBwdSmem {
 template <int D, int QS, int NP, int NDS, int NST>
 __global__ void __launch_bounds__(FAB_THREADS, 1)
 fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
-              const FaBwdParams p) {
+              const __grid_constant__ CUtensorMap tm_acc, const FaBwdParams p) {
   using L = FaBwdSmem<D, QS, NP, NDS, NST>;
   // head_dim 128 fills all 512 TMEM columns with S, dP, dV and dK, so dQ has to share the
   // columns of dP. The step is then split: S of step n+1 is issued as soon as S of step n is in
@@ -145,6 +146,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
     fence_mbar_init();
     prefetch_tmap(&tm_qkv);
     prefetch_tmap(&tm_do);
+    prefetch_tmap(&tm_acc);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -467,36 +469,55 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
     reg_dealloc<72>();
     // ---------------- drain warpgroup: dQ every step (thread r owns query row r), dK / dV at
     // the end (thread r owns kv row r) ----------------
+    // The dQ tile leaves through TMA reduce-adds: each warp stages 32 rows x 64 columns as two
+    // swizzled 32 x 32 fp32 boxes and one lane sends them off, so the fp32 accumulation in L2 is
+    // done by the copy engine in whole 128-byte lines (per-thread `red.global` instructions for
+    // the same bytes keep the SM's load / store pipe so busy that the softmax warps' own
+    // shared-memory traffic stalls behind them).
     const int r = threadIdx.x - 384;
-    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int q4 = warp & 3;
+    const uint32_t lane_off = static_cast<uint32_t>(q4 * 32) << 16;
+    uint8_t* stage = smem + L::DQ_OFF + q4 * 8192;           // this warp's two 4 KB boxes
+    int nsent = 0;
     for (int n = 0; n < N; ++n) {
       const int head = step_head(n), qt = step_qtile(n);
       const int q_col = (grp * (p.g + 2) + head % p.g) * D;
-      float* acc_row = p.acc + static_cast<long>(row_base + qt * FAB_BLK + r) * p.ld_acc + q_col;
       mbar_wait_relaxed(dq_full, n & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
-      // 16 x 256-bit loads: four lanes hold one aligned 32-byte piece of a row, so every
-      // reduction instruction of the warp updates whole sectors.
-      float* acc_tile = p.acc + static_cast<long>(row_base + qt * FAB_BLK + (warp & 3) * 32) * p.ld_acc + q_col;
+      const int y = row_base + qt * FAB_BLK + q4 * 32;
 #pragma unroll 1
       for (int c = 0; c < D / 64; ++c) {
-#pragma unroll 1
-        for (int hrow = 0; hrow < 2; ++hrow) {
-          uint32_t o[32];
-          tmem_ld_16x256b_x8(tm_dQ + lane_off + (static_cast<uint32_t>(hrow * 16) << 16) + c * 64, o);
-          tmem_ld_wait();
-          float* a0 = acc_tile + static_cast<long>(hrow * 16 + (lane >> 2)) * p.ld_acc + c * 64 + 2 * (lane & 3);
-          float* a1 = a0 + 8L * p.ld_acc;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            red_add_v2(a0 + 8 * i, __uint_as_float(o[4 * i]), __uint_as_float(o[4 * i + 1]));
-            red_add_v2(a1 + 8 * i, __uint_as_float(o[4 * i + 2]), __uint_as_float(o[4 * i + 3]));
-          }
+        uint32_t o[64];
+        tmem_ld32(tm_dQ + lane_off + c * 64, o);
+        tmem_ld32(tm_dQ + lane_off + c * 64 + 32, o + 32);
+        tmem_ld_wait();
+        if (c == D / 64 - 1) {     // the accumulator is in registers: the columns are free again
+          tc_fence_before();
+          mbar_arrive(dq_drained);
         }
+        if (nsent > 0) {           // the boxes sent last have been read
+          if (lane == 0) tma_wait_group_read<0>();
+          __syncwarp();
+        }
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb)
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            *reinterpret_cast<uint4*>(stage + hb * 4096 + lane * 128 + ((k ^ (lane & 7)) << 4)) =
+                make_uint4(o[hb * 32 + 4 * k], o[hb * 32 + 4 * k + 1], o[hb * 32 + 4 * k + 2],
+                           o[hb * 32 + 4 * k + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_reduce_add_2d(&tm_acc, stage, q_col + c * 64, y);
+          tma_reduce_add_2d(&tm_acc, stage + 4096, q_col + c * 64 + 32, y);
+          tma_commit_group();
+        }
+        ++nsent;
       }
-      tc_fence_before();
-      mbar_arrive(dq_drained);
     }
+    if (lane == 0) tma_wait_group<0>();
+    __syncwarp();
     mbar_wait_relaxed(dkv_full, 0, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL, 256);
     tc_fence_after();
     float* acc_row = p.acc + static_cast<long>(row_base + j * FAB_BLK + r) * p.ld_acc;
@@ -584,8 +605,8 @@ __global__ void fa_bwd_post_kernel(const float* __restrict__ acc, __nv_bfloat16*
 }
 
 template <int D, int QS, int NP, int NDS, int NST>
-static int launch_fa_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const FaBwdParams& p,
-                         cudaStream_t st) {
+static int launch_fa_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUtensorMap& tacc,
+                         const FaBwdParams& p, cudaStream_t st) {
   using L = FaBwdSmem<D, QS, NP, NDS, NST>;
   static bool attr = false;
   if (!attr) {
@@ -595,7 +616,7 @@ static int launch_fa_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const Fa
     attr = true;
   }
   const int grid = (p.S / FAB_BLK) * p.batch * p.n_groups * (p.g / p.hpc);
-  fa_bwd_kernel<D, QS, NP, NDS, NST><<<grid, FAB_THREADS, L::TOTAL, st>>>(tq, tdo, p);
+  fa_bwd_kernel<D, QS, NP, NDS, NST><<<grid, FAB_THREADS, L::TOTAL, st>>>(tq, tdo, tacc, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -649,15 +670,15 @@ extern "C" int ft_attn_bwd(const void* dout, const void* qkv, const void* out, c
   p.scale_log2 = scale * 1.4426950408889634f;
   p.lse2 = d_lse2; p.delta = d_delta; p.acc = static_cast<float*>(acc);
   p.status = status;
-#ifndef FT_FAB_SMEM_P64
   CUtensorMap tacc;   // 32 x 32 fp32 boxes over the accumulator (dQ leaves through TMA reduce-adds)
   if (get_tmap_2d(&tacc, acc, 4, T, ncols, ncols, 32, 32)) return -8;
+#ifndef FT_FAB_SMEM_P64
   int rc = (D == 64) ? launch_fa_bwd_kv64(tq, tdo, tacc, S, Hq, g, n_groups, batch, heads_per_cta, ncols,
                                           p.scale_log2, d_lse2, d_delta, p.acc, status, st)
-                     : launch_fa_bwd<128, 1, 1, 1, 1>(tq, tdo, p, st);
+                     : launch_fa_bwd<128, 1, 1, 1, 1>(tq, tdo, tacc, p, st);
 #else   // head_dim 64 on the shared-memory hand-over kernel as well (comparison builds)
-  int rc = (D == 64) ? launch_fa_bwd<64, 3, 1, 2, 2>(tq, tdo, p, st)
-                     : launch_fa_bwd<128, 1, 1, 1, 1>(tq, tdo, p, st);
+  int rc = (D == 64) ? launch_fa_bwd<64, 3, 1, 1, 2>(tq, tdo, tacc, p, st)
+                     : launch_fa_bwd<128, 1, 1, 1, 1>(tq, tdo, tacc, p, st);
 #endif
   if (rc) return rc;
   {
