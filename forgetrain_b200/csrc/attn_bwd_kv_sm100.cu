@@ -48,8 +48,8 @@ __device__ __forceinline__ void kv_red_add_v4(float* addr, float a, float b, flo
                : "memory");
 }
 
-// QS: Q/dO stages, NDS: dS^T buffers in shared memory, NST: (-lse2, -delta) buffers
-template <int QS, int NDS, int NST>
+// QS: Q/dO stages (each with its (-lse2, -delta) rows), NDS: dS^T buffers in shared memory
+template <int QS, int NDS>
 struct FaBwdKvSmem {
   static constexpr int TILE = FABK_BLK * FABK_D * 2;        // 16 KB
   static constexpr int K_OFF = 0;
@@ -57,16 +57,16 @@ struct FaBwdKvSmem {
   static constexpr int QDO_OFF = 2 * TILE;                  // QS x (Q tile, dO tile)
   static constexpr int DS_OFF = QDO_OFF + QS * 2 * TILE;    // NDS x dS^T (128 kv x 128 q bf16)
   static constexpr int DQ_OFF = DS_OFF + NDS * 32768;       // dQ staging: 8 boxes of 32 x 32 fp32
-  static constexpr int STAT_OFF = DQ_OFF + 32768;           // NST x (-lse2[128], -delta[128])
-  static constexpr int BAR_OFF = STAT_OFF + NST * 1024;
+  static constexpr int STAT_OFF = DQ_OFF + 32768;           // QS x (-lse2[128], -delta[128])
+  static constexpr int BAR_OFF = STAT_OFF + QS * 1024;
   static constexpr int TOTAL = BAR_OFF + 512;               // base must come 1024-byte aligned
 };
 
-template <int QS, int NDS, int NST>
+template <int QS, int NDS>
 __global__ void __launch_bounds__(FABK_THREADS, 1)
 fa_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
                  const __grid_constant__ CUtensorMap tm_acc, const FaBwdParams p) {
-  using L = FaBwdKvSmem<QS, NDS, NST>;
+  using L = FaBwdKvSmem<QS, NDS>;
   constexpr int D = FABK_D;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
@@ -178,11 +178,10 @@ fa_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
         } else if (lane == 1) {
           tma_load_2d(dst + L::TILE, &tm_do, &qdo_full[s], head * D, row_base + qt * FABK_BLK);
         } else {
+          // the statistics rows live and die with the Q / dO stage: the stage is handed back
+          // after dK of its step, i.e. after the softmax threads have finished with them
           const long soff = (static_cast<long>(b) * p.Hq + head) * p.S + qt * FABK_BLK;
-          if (n >= NST)   // the statistics slot is free once the softmax of step n-NST is done
-            mbar_wait_relaxed(&pds_ready[(n - NST) % NDS], ((n - NST) / NDS) & 1, abort_flag,
-                              p.status, FT_ERR_WAIT_MISC);
-          float* st = reinterpret_cast<float*>(smem + L::STAT_OFF + (n % NST) * 1024);
+          float* st = reinterpret_cast<float*>(smem + L::STAT_OFF + s * 1024);
           if (lane == 2)
             bulk_load_1d(st, p.lse2 + soff, 512, &qdo_full[s]);
           else
@@ -306,7 +305,7 @@ fa_bwd_kv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
     const uint64_t sl2x2 = pack_f32x2(p.scale_log2, p.scale_log2);
     for (int n = 0; n < N; ++n) {
       const int qt = step_qtile(n);
-      const float4* nl4 = reinterpret_cast<const float4*>(smem + L::STAT_OFF + (n % NST) * 1024) + half * 16;
+      const float4* nl4 = reinterpret_cast<const float4*>(smem + L::STAT_OFF + (n % QS) * 1024) + half * 16;
       const float4* nd4 = nl4 + 32;
       uint8_t* rowd = smem + L::DS_OFF + (n % NDS) * 32768 + half * 16384 + r * 128;  // dS^T row
       mbar_wait(&qdo_full[n % QS], (n / QS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
@@ -471,10 +470,10 @@ int launch_fa_bwd_kv64(const CUtensorMap& tq, const CUtensorMap& tdo, const CUte
                        int n_groups, int batch, int hpc, int ld_acc, float scale_log2,
                        const float* neg_lse2, const float* neg_delta, float* acc, int* status,
                        cudaStream_t st) {
-  using L = FaBwdKvSmem<3, 1, 2>;
+  using L = FaBwdKvSmem<3, 1>;
   static bool attr = false;
   if (!attr) {
-    if (cudaFuncSetAttribute(fa_bwd_kv_kernel<3, 1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(fa_bwd_kv_kernel<3, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              L::TOTAL) != cudaSuccess)
       return -10;
     attr = true;
@@ -486,7 +485,7 @@ int launch_fa_bwd_kv64(const CUtensorMap& tq, const CUtensorMap& tdo, const CUte
   p.lse2 = neg_lse2; p.delta = neg_delta; p.acc = acc;
   p.status = status;
   const int grid = (S / FABK_BLK) * batch * n_groups * (g / hpc);
-  fa_bwd_kv_kernel<3, 1, 2><<<grid, FABK_THREADS, L::TOTAL, st>>>(tq, tdo, tacc, p);
+  fa_bwd_kv_kernel<3, 1><<<grid, FABK_THREADS, L::TOTAL, st>>>(tq, tdo, tacc, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

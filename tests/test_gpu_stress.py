@@ -79,21 +79,27 @@ def _workers(stop):
                 x.mul_(1.0)
             s2.synchronize()
 
+    # W6's graph is captured here, before any neighbour thread runs: allocator or launch traffic
+    # of another thread during a capture invalidates it (the reference keeps this worker eager by
+    # default for that reason, _stress_workers.py:24-28); the worker thread only replays.
+    g_stream = torch.cuda.Stream()
+    gx = torch.ones(1 << 18, device="cuda")
+    gy = torch.empty_like(gx)
+    with torch.cuda.stream(g_stream):
+        for _ in range(2):
+            torch.add(gx, 1.0, out=gy)
+        g_stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=g_stream, capture_error_mode="thread_local"):
+            torch.add(gx, 1.0, out=gy)
+            torch.mul(gy, 0.5, out=gy)
+    torch.cuda.synchronize()
+
     def w6_graph_replay():
-        s = torch.cuda.Stream()
-        x = torch.ones(1 << 18, device="cuda")
-        y = torch.empty_like(x)
-        with torch.cuda.stream(s):
-            for _ in range(2):
-                torch.add(x, 1.0, out=y)
-            s.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=s):
-                torch.add(x, 1.0, out=y)
-                torch.mul(y, 0.5, out=y)
+        with torch.cuda.stream(g_stream):
             while not stop.is_set():
-                g.replay()
-                s.synchronize()
+                graph.replay()
+                g_stream.synchronize()
 
     def w7_alloc_churn():
         while not stop.is_set():
