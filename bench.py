@@ -138,7 +138,8 @@ def run_reference(args) -> int:
     # TransformerEngine is present: run the engine's own CLI. Its ``pretrain`` sub-command has no
     # synthetic source, so it gets a generated corpus and a word-level tokenizer written locally.
     rank = int(os.environ.get("RANK", "0"))
-    work = os.path.join(ROOT, "gpurun_out", "reference_arm")
+    import tempfile
+    work = os.path.join(tempfile.gettempdir(), "ft_reference_arm")
     try:
         if rank == 0:
             _write_reference_corpus(work, args.seq, args.mbs * max(args.gpus, 1) * (args.steps + args.warmup + 2))
@@ -254,6 +255,7 @@ def time_config(*, model: str, tp: int, mbs: int, gas: int, seq: int, K: int, W:
     t0 = time.perf_counter()
     h2d = 0
     last_loss = 0.0
+    pending = None
     for i in range(K):
         h2d = 0
         batches = []
@@ -261,7 +263,13 @@ def time_config(*, model: str, tp: int, mbs: int, gas: int, seq: int, K: int, W:
             batches.append(next(prefetch))
             h2d += prefetch.bytes_last
         out = trainer.train_step(batches)
-        last_loss = float(out["loss"])            # device -> host, 4 bytes
+        # device -> host: the loss (and gradient norm) of EVERY step is copied into pinned memory
+        # inside the region; the host consumes it one step late, so it stays ahead of the device
+        handle = trainer.loss_to_host_async()
+        if pending is not None:
+            last_loss, _ = pending.value()
+        pending = handle
+    last_loss, _ = pending.value()
     trainer.finish_step()
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
@@ -362,7 +370,7 @@ def main() -> int:
                     "mfu_standard": s["mfu_standard"], "mfu_standard_nominal_peak": s["mfu_standard_nominal"],
                     "mfu_vs_published_mfu": s["mfu_standard_nominal"] / PUBLISHED_MFU["8b"],
                     "e2e": {"value": s["e2e_value"], "unit": "tokens/s", "ms_per_step": s["e2e_ms_per_step"],
-                            "h2d_bytes_per_step": s["h2d_bytes_per_step"], "d2h_bytes_per_step": 4},
+                            "h2d_bytes_per_step": s["h2d_bytes_per_step"], "d2h_bytes_per_step": 8},
                     "gpu_launches": s["launches"], "clocks": s["clocks"], "loss": s["loss"],
                     "params_identical_across_dp_ranks": s["params_equal"],
                 }
@@ -393,7 +401,8 @@ def main() -> int:
             "mfu_vs_published_mfu": r["mfu_standard_nominal"] / PUBLISHED_MFU["0.5b"]
             if args.model == "0.5b" else None,
             "e2e": {"value": r["e2e_value"], "unit": "tokens/s", "ms_per_step": r["e2e_ms_per_step"],
-                    "h2d_bytes_per_step": r["h2d_bytes_per_step"], "d2h_bytes_per_step": 4},
+                    "h2d_bytes_per_step": r["h2d_bytes_per_step"], "d2h_bytes_per_step": 8,
+                    "d2h": "loss and gradient norm of every step, consumed one step late"},
             "gpu_launches": r["launches"],
             "clocks": r["clocks"],
             "loss": r["loss"],

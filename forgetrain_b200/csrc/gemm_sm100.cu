@@ -49,6 +49,10 @@ struct GemmParams {
   int m_tiles, n_tiles, k_iters;
   int* status;
   int swiglu_F;       // > 0 (SWIGLU kernel only): B is [2F][K] = [gate rows ; up rows]
+  // Work units [0, split_from) are whole 128 x BN tiles; from split_from on, each tile of the
+  // last, partly filled wave is cut into two 128 x BN/2 halves (units 2i, 2i+1), so that the
+  // tail of the schedule costs about 0.6 instead of 1.0 tile times. total_units counts both.
+  int split_from, total_units;
 };
 
 template <int BN, int STAGES>
@@ -62,8 +66,15 @@ struct GemmSmem {
   static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;      // + barriers + alignment slack
 };
 
+// `half`: -1 for a whole tile, else which half of the tile's columns this unit covers.
 __device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int& mt, int& nt,
-                                            int& kb, int& kn) {
+                                            int& kb, int& kn, int& half) {
+  half = -1;
+  if (tile >= p.split_from) {
+    const int t = tile - p.split_from;
+    half = t & 1;
+    tile = p.split_from + (t >> 1);
+  }
   const int per_split = p.m_tiles * p.n_tiles;
   const int ks = tile / per_split;
   const int r = tile - ks * per_split;
@@ -79,18 +90,17 @@ __device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int& 
   kn = base + (ks < rem ? 1 : 0);
 }
 
-// Epilogue of one 128 x BN accumulator for one warp: its 32 TMEM lanes (rows row0..row0+31),
+// Epilogue of one 128 x ncols accumulator for one warp: its 32 TMEM lanes (rows row0..row0+31),
 // column half `chalf`. TMEM -> registers -> (alpha, convert) -> swizzled staging buffer ->
 // TMA store / reduce-add. `nstores` counts this warp's bulk groups so the staging buffer is
 // only rewritten after the previous store has read it.
-template <int BN>
 __device__ __forceinline__ void drain_tile(const GemmParams& p, const CUtensorMap* tmD,
-                                           uint32_t taddr, int row0, int colbase, int chalf,
-                                           uint8_t* sbuf, int lane, int& nstores) {
+                                           uint32_t taddr, int row0, int colbase, int ncols,
+                                           int chalf, uint8_t* sbuf, int lane, int& nstores) {
   const bool rows_live = row0 < p.M;
   if (p.out_mode == OUT_BF16) {
 #pragma unroll 1
-    for (int c = chalf * (BN / 128); c < (chalf + 1) * (BN / 128); ++c) {
+    for (int c = chalf * (ncols / 128); c < (chalf + 1) * (ncols / 128); ++c) {
       const int col0 = colbase + c * 64;
       if (col0 >= p.N || !rows_live) break;
       uint32_t r[64];
@@ -124,7 +134,7 @@ __device__ __forceinline__ void drain_tile(const GemmParams& p, const CUtensorMa
     }
   } else {
 #pragma unroll 1
-    for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
+    for (int c = chalf * (ncols / 64); c < (chalf + 1) * (ncols / 64); ++c) {
       const int col0 = colbase + c * 32;
       if (col0 >= p.N || !rows_live) break;
       uint32_t r[32];
@@ -264,7 +274,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_tiles = p.m_tiles * p.n_tiles * p.splitk;
+  const int total_tiles = p.total_units;
 
   if (warp == 0 || warp == GEMM_PRODUCER_WARP2) {
     // ------------------------------ TMA producers ------------------------------
@@ -277,30 +287,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-        int mt, nt, kb, kn;
-        decode_tile(p, tile, mt, nt, kb, kn);
+        int mt, nt, kb, kn, half;
+        decode_tile(p, tile, mt, nt, kb, kn, half);
+        // a half tile loads only its half of the B boxes, into the start of the B buffer
+        const int nBt = half < 0 ? nB : nB / 2;
+        const int jb0 = half <= 0 ? 0 : nB / 2;
+        const uint32_t tx = L::A_BYTES + (half < 0 ? L::B_BYTES : L::B_BYTES / 2);
         for (int ki = kb; ki < kb + kn; ++ki) {
           if ((stage & 1) == pid) {
             mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
             uint8_t* sA = smem + stage * L::STAGE_BYTES;
             uint8_t* sB = sA + L::A_BYTES;
-            if (lane == 0) mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+            if (lane == 0) mbar_expect_tx(&full_bar[stage], tx);
             if (lane < nA) {
               if (!p.a_mn)
                 tma_load_2d(sA, &tmA, &full_bar[stage], ki * GEMM_BK, mt * GEMM_BM);
               else
                 tma_load_2d(sA + lane * 8192, &tmA, &full_bar[stage], mt * GEMM_BM + lane * 64,
                             ki * GEMM_BK);
-            } else {
-              const int j = lane - nA;
+            } else if (lane - nA < nBt) {
+              const int j = lane - nA;           // slot in the B buffer; jb0 + j: box of the tile
               if (SWIGLU)   // box 0: 128 gate rows, box 1: the 128 up rows of the same columns
                 tma_load_2d(sB + j * 16384, &tmB, &full_bar[stage], ki * GEMM_BK,
                             nt * 128 + j * p.swiglu_F);
               else if (!p.b_mn)
                 tma_load_2d(sB + j * 16384, &tmB, &full_bar[stage], ki * GEMM_BK,
-                            nt * BN + j * 128);
+                            nt * BN + (jb0 + j) * 128);
               else
-                tma_load_2d(sB + j * 8192, &tmB, &full_bar[stage], nt * BN + j * 64,
+                tma_load_2d(sB + j * 8192, &tmB, &full_bar[stage], nt * BN + (jb0 + j) * 64,
                             ki * GEMM_BK);
             }
           }
@@ -325,7 +339,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // The whole warp walks the tiles and waits on the barriers; one elected lane issues, so
     // that descriptors, TMEM addresses and loop state stay warp-uniform (see elect_one_sync).
     {
-      const uint32_t idesc = make_idesc_bf16(GEMM_BM, BN, p.a_mn, p.b_mn);
+      const uint32_t idesc_full = make_idesc_bf16(GEMM_BM, BN, p.a_mn, p.b_mn);
+      const uint32_t idesc_half = make_idesc_bf16(GEMM_BM, BN / 2, p.a_mn, p.b_mn);
       const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
       const uint32_t a_kstep = p.a_mn ? (2048u >> 4) : (32u >> 4);
       const uint32_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
@@ -334,8 +349,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int it = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-        int mt, nt, kb, kn;
-        decode_tile(p, tile, mt, nt, kb, kn);
+        int mt, nt, kb, kn, half;
+        decode_tile(p, tile, mt, nt, kb, kn, half);
+        const uint32_t idesc = half < 0 ? idesc_full : idesc_half;
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         mbar_wait(&tempty_bar[buf], acc_phase ^ 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
@@ -369,8 +385,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int it = 0;
     int nstores = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-      int mt, nt, kb, kn;
-      decode_tile(p, tile, mt, nt, kb, kn);
+      int mt, nt, kb, kn, half;
+      decode_tile(p, tile, mt, nt, kb, kn, half);
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       mbar_wait(&tfull_bar[buf], acc_phase, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
@@ -380,7 +396,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (SWIGLU)
         drain_tile_swiglu(p, &tmD, &tmD2, taddr, row0, nt * 128, chalf, my_epi, lane, nstores);
       else
-        drain_tile<BN>(p, &tmD, taddr, row0, nt * BN, chalf, my_epi, lane, nstores);
+        drain_tile(p, &tmD, taddr, row0, nt * BN + (half > 0 ? BN / 2 : 0),
+                   half < 0 ? BN : BN / 2, chalf, my_epi, lane, nstores);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
@@ -490,7 +507,7 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t phase = 0;
       for (int tile = pair; tile < total_tiles; tile += npairs) {
         int mt, nt, kb, kn;
-        decode_tile(p, tile, mt, nt, kb, kn);
+        int half_unused; decode_tile(p, tile, mt, nt, kb, kn, half_unused);
         const int arow = mt * 256 + static_cast<int>(rank) * 128;
         const int brow = nt * BN + static_cast<int>(rank) * 128;
         for (int ki = kb; ki < kb + kn; ++ki) {
@@ -542,7 +559,7 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
       int it = 0;
       for (int tile = pair; tile < total_tiles; tile += npairs, ++it) {
         int mt, nt, kb, kn;
-        decode_tile(p, tile, mt, nt, kb, kn);
+        int half_unused; decode_tile(p, tile, mt, nt, kb, kn, half_unused);
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         mbar_wait(&tempty_bar[buf], acc_phase ^ 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
@@ -582,14 +599,14 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
     int nstores = 0;
     for (int tile = pair; tile < total_tiles; tile += npairs, ++it) {
       int mt, nt, kb, kn;
-      decode_tile(p, tile, mt, nt, kb, kn);
+      int half_unused; decode_tile(p, tile, mt, nt, kb, kn, half_unused);
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       mbar_wait(&tfull_bar[buf], acc_phase, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
       const int row0 = mt * 256 + static_cast<int>(rank) * 128 + q * 32;
-      drain_tile<BN>(p, &tmD, taddr, row0, nt * BN, chalf, my_epi, lane, nstores);
+      drain_tile(p, &tmD, taddr, row0, nt * BN, BN, chalf, my_epi, lane, nstores);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty0 + buf * 8);
@@ -683,7 +700,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
     if (e != cudaSuccess) return -10;
     attr_set = true;
   }
-  const int total = p.m_tiles * p.n_tiles * p.splitk;
+  const int total = p.total_units;
   int grid = total < max_ctas ? total : max_ctas;
   if (grid < 1) grid = 1;
   gemm_bf16_kernel<BN, STAGES, SWIGLU>
@@ -759,6 +776,22 @@ extern "C" int ft_gemm_bf16(const void* A, const void* B, void* D, int M, int N,
   p.m_tiles = m_tiles; p.n_tiles = n_tiles; p.k_iters = k_iters;
   p.status = status;
   p.swiglu_F = 0;
+  {
+    // Tail of the schedule: when the last wave is at most half full, its tiles are cut in two
+    // (128 x 128 halves on twice as many CTAs). Shapes of the 0.5B model at 16384 tokens: the
+    // attention-output, FC2-forward and FC1-dgrad GEMMs have 512 tiles = 3.46 waves of 148, the
+    // QKV forward 640 = 4.32; a half tile costs about 0.6 of a whole one.
+    const int total = m_tiles * n_tiles * splitk;
+    p.split_from = total;
+    p.total_units = total;
+    if (bn == 256 && splitk == 1 && max_ctas >= 2) {
+      const int rem = total % max_ctas;
+      if (rem > 0 && 2 * rem <= max_ctas) {
+        p.split_from = total - rem;
+        p.total_units = total + rem;
+      }
+    }
+  }
   if (out_dtype == 0) p.out_mode = OUT_BF16;
   else p.out_mode = (accumulate || splitk > 1) ? OUT_F32_ADD : OUT_F32;
   if (out_dtype == 1 && !accumulate && splitk > 1) {
@@ -806,6 +839,7 @@ extern "C" int ft_gemm_swiglu_bf16(const void* A, const void* W, void* Y, void* 
   p.k_iters = (K + GEMM_BK - 1) / GEMM_BK;
   p.status = status;
   p.swiglu_F = F;
+  p.split_from = p.total_units = p.m_tiles * p.n_tiles;
   CUtensorMap tmA, tmB, tmY, tmAct;
   if (get_tmap_2d(&tmA, A, 2, M, K, lda, GEMM_BM, GEMM_BK)) return -4;
   if (get_tmap_2d(&tmB, W, 2, 2 * static_cast<uint64_t>(F), K, ldw, 128, GEMM_BK)) return -5;

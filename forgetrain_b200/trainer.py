@@ -194,6 +194,13 @@ class Trainer:
                 opt.wait_bucket(i)
         self.model.param_gate = gate
 
+    def loss_to_host_async(self) -> "LossReadback":
+        """Start a device-to-host copy of the last step's loss (and gradient norm) into pinned
+        memory on the current stream and return a handle; ``handle.value()`` waits for that
+        copy only. Reading step i's loss after step i+1 has been enqueued keeps the host one
+        step ahead of the device instead of draining the GPU at every step."""
+        return LossReadback(self.loss_buf, self.opt.grad_norm)
+
     def finish_step(self) -> None:
         """Make the current stream wait for everything the last step left running on side
         streams (the tail of the optimizer / all-gather pipeline)."""
@@ -430,6 +437,27 @@ class Trainer:
         else:
             self.opt.sync_master_from_params()
         return state
+
+
+class LossReadback:
+    """Asynchronous read-back of (loss, grad_norm): 8 bytes, device -> pinned host."""
+    nbytes = 8
+
+    def __init__(self, loss: torch.Tensor, grad_norm: torch.Tensor):
+        self._cuda = loss.is_cuda
+        if self._cuda:
+            self._host = torch.empty(2, dtype=torch.float32, pin_memory=True)
+            self._host[0:1].copy_(loss.reshape(1), non_blocking=True)
+            self._host[1:2].copy_(grad_norm.reshape(1), non_blocking=True)
+            self._event = torch.cuda.Event()
+            self._event.record()
+        else:
+            self._host = torch.stack([loss.reshape(()), grad_norm.reshape(())]).float().clone()
+
+    def value(self) -> tuple[float, float]:
+        if self._cuda:
+            self._event.synchronize()
+        return float(self._host[0]), float(self._host[1])
 
 
 # ---------------------------------------------------------------------------------------------

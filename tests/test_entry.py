@@ -76,3 +76,10 @@ def test_entry_points_also_take_a_checkpoint_of_this_engine(tmp_path):
     assert per_tok.shape == (2, 32) and loss > 0
     from training_engine_tensor.entry import run_forward, run_training
     assert run_forward is entry.run_forward and callable(run_training)
+
+
+def test_loss_readback_handle_returns_the_step_result_on_cpu():
+    import torch
+    from forgetrain_b200.trainer import LossReadback
+    h = LossReadback(torch.tensor([2.5]), torch.tensor([0.75]))
+    assert h.value() == (2.5, 0.75) and h.nbytes == 8

@@ -23,8 +23,12 @@ def _seed_and_status():
     _lib.check_status()
 
 
+# (1280, 4096, 512): 160 tiles of 128 x 256 = one full wave of 148 CTAs + 12 tiles that the
+# scheduler cuts into halves; (16384, 1024, 256): 512 tiles = 3 waves + 68 split tiles;
+# (640, 1160, 320): every tile is split and the split meets a partial last column tile
 @pytest.mark.parametrize("T,N,K", [(128, 128, 64), (384, 200, 72), (1000, 1280, 1024), (512, 73448, 256),
-                                   (4096, 1024, 4096)])
+                                   (4096, 1024, 4096), (1280, 4096, 512), (16384, 1024, 256),
+                                   (640, 1160, 320)])
 def test_gemm_fwd_dgrad_wgrad(T, N, K):
     x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
     w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
