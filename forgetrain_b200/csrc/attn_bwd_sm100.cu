@@ -581,26 +581,59 @@ __global__ void fa_bwd_pre_kernel(const __nv_bfloat16* __restrict__ out,
   }
 }
 
-// dqkv[t][c] = bf16(acc[t][c] * (v column ? 1 : scale))
+// dqkv[t][c] = bf16(acc[t][c] * (v column ? 1 : scale)), and, when a rotary table is given, the
+// transposed rotation of the q and k heads (the backward of RoPE) in the same pass: one thread
+// owns 8 columns of a head's first half and the matching 8 of its second half.
 __global__ void fa_bwd_post_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dqkv,
                                    long T, int ncols, int ld_acc, int ld_dqkv, int g, int D,
-                                   float scale) {
-  const int vpr = ncols / 8;
-  const long total = T * vpr;
+                                   float scale, const float* __restrict__ cos_t,
+                                   const float* __restrict__ sin_t,
+                                   const int* __restrict__ position_ids, int S) {
+  const int half = D / 2;
+  const int vph = half / 8;                 // threads per head
+  const int heads = ncols / D;
+  const long total = T * heads * vph;
   for (long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
        idx += static_cast<long>(gridDim.x) * blockDim.x) {
-    const long t = idx / vpr;
-    const int c = (idx % vpr) * 8;
-    const int in_grp = (c / D) % (g + 2);
-    const float sc = (in_grp == g + 1) ? 1.f : scale;
-    const float4 a = *reinterpret_cast<const float4*>(acc + t * ld_acc + c);
-    const float4 b2 = *reinterpret_cast<const float4*>(acc + t * ld_acc + c + 4);
+    const int v = idx % vph;
+    const long r1 = idx / vph;
+    const int hs = r1 % heads;
+    const long t = r1 / heads;
+    const bool is_v = (hs % (g + 2)) == g + 1;
+    const float sc = is_v ? 1.f : scale;
+    const int c0 = hs * D + v * 8;
+    const float* a = acc + t * ld_acc + c0;
+    float x1[8], x2[8];
+    *reinterpret_cast<float4*>(x1) = *reinterpret_cast<const float4*>(a);
+    *reinterpret_cast<float4*>(x1 + 4) = *reinterpret_cast<const float4*>(a + 4);
+    *reinterpret_cast<float4*>(x2) = *reinterpret_cast<const float4*>(a + half);
+    *reinterpret_cast<float4*>(x2 + 4) = *reinterpret_cast<const float4*>(a + half + 4);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { x1[k] *= sc; x2[k] *= sc; }
+    if (cos_t != nullptr && !is_v) {
+      const int pos = position_ids ? position_ids[t] : static_cast<int>(t % S);
+      float c[8], sn[8];
+      const float4* c4 = reinterpret_cast<const float4*>(cos_t + static_cast<long>(pos) * half + v * 8);
+      const float4* s4 = reinterpret_cast<const float4*>(sin_t + static_cast<long>(pos) * half + v * 8);
+      *reinterpret_cast<float4*>(c) = c4[0];
+      *reinterpret_cast<float4*>(c + 4) = c4[1];
+      *reinterpret_cast<float4*>(sn) = s4[0];
+      *reinterpret_cast<float4*>(sn + 4) = s4[1];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float o1 = x1[k] * c[k] + x2[k] * sn[k];
+        const float o2 = x2[k] * c[k] - x1[k] * sn[k];
+        x1[k] = o1;
+        x2[k] = o2;
+      }
+    }
     uint4 o;
-    o.x = pack_bf16x2(a.x * sc, a.y * sc);
-    o.y = pack_bf16x2(a.z * sc, a.w * sc);
-    o.z = pack_bf16x2(b2.x * sc, b2.y * sc);
-    o.w = pack_bf16x2(b2.z * sc, b2.w * sc);
-    *reinterpret_cast<uint4*>(dqkv + t * ld_dqkv + c) = o;
+    o.x = pack_bf16x2(x1[0], x1[1]); o.y = pack_bf16x2(x1[2], x1[3]);
+    o.z = pack_bf16x2(x1[4], x1[5]); o.w = pack_bf16x2(x1[6], x1[7]);
+    *reinterpret_cast<uint4*>(dqkv + t * ld_dqkv + c0) = o;
+    o.x = pack_bf16x2(x2[0], x2[1]); o.y = pack_bf16x2(x2[2], x2[3]);
+    o.z = pack_bf16x2(x2[4], x2[5]); o.w = pack_bf16x2(x2[6], x2[7]);
+    *reinterpret_cast<uint4*>(dqkv + t * ld_dqkv + c0 + half) = o;
   }
 }
 
@@ -629,10 +662,14 @@ static int launch_fa_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CU
 // heads_per_cta <= 0 picks the largest value that keeps the grid at three CTAs per SM or more
 // (measured optimum: longer CTAs amortise the K/V load and the dK/dV drain, but the causal
 // triangle needs a few waves to balance).
+// cos_t / sin_t ([positions][D/2] fp32, may be NULL) and position_ids ([batch*S] int32 or NULL =
+// position inside the sequence): when given, the gradient of the q and k heads leaves with the
+// backward of the rotary embedding already applied (no separate pass over the buffer).
 extern "C" int ft_attn_bwd(const void* dout, const void* qkv, const void* out, const void* lse,
                            void* dqkv, void* acc, void* delta, int batch, int S, int n_groups,
                            int g, int D, int ld_qkv, int ld_out, int ld_dout, float scale,
-                           int heads_per_cta, int* status, cudaStream_t st) {
+                           int heads_per_cta, const void* cos_t, const void* sin_t,
+                           const void* position_ids, int* status, cudaStream_t st) {
   using namespace ft;
   if (S % FAB_BLK || (D != 64 && D != 128)) return -1;
   const long T = static_cast<long>(batch) * S;
@@ -682,11 +719,12 @@ extern "C" int ft_attn_bwd(const void* dout, const void* qkv, const void* out, c
 #endif
   if (rc) return rc;
   {
-    const long total = T * (ncols / 8);
+    const long total = T * (ncols / 16);
     long blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     fa_bwd_post_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(
-        (const float*)acc, (__nv_bfloat16*)dqkv, T, ncols, ncols, ld_qkv, g, D, scale);
+        (const float*)acc, (__nv_bfloat16*)dqkv, T, ncols, ncols, ld_qkv, g, D, scale,
+        (const float*)cos_t, (const float*)sin_t, (const int*)position_ids, S);
     if (cudaGetLastError() != cudaSuccess) return -7;
   }
   return 0;

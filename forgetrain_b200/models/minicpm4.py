@@ -247,12 +247,12 @@ class MiniCPM4:
                                                 sp.head_dim)
         dattn, dh_full = tp.dgrad_gather(dh, p[n_wo], alpha=r, key="bwd.attn")
         ops.linear_wgrad(dh_full, sv.attn, g[n_wo], accumulate, alpha=r)
+        # the rotary embedding's backward rides in the attention backward's last kernel
         dqkv = ops.attention_bwd(dattn, sv.qkv, sv.attn, sv.lse, batch, self.local_groups,
-                                 self.local_g, sp.head_dim)
+                                 self.local_g, sp.head_dim,
+                                 rope=(self.cos, self.sin, position_ids))
         del dattn
         sv.attn = sv.lse = None
-        ops.rope_(dqkv, self.cos, self.sin, batch, self.local_groups, self.local_g, sp.head_dim,
-                  inverse=True, position_ids=position_ids)
         ops.linear_wgrad(dqkv, sv.n1_full, g[n_qkv], accumulate)
         if tp.replica_size > 1:
             self._reduce_kv_replicas(g[n_qkv])

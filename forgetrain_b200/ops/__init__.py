@@ -56,9 +56,20 @@ def attention_fwd(qkv, batch, n_groups, heads_per_group, head_dim, scale=None):
     return _pick(qkv).attention_fwd(qkv, batch, n_groups, heads_per_group, head_dim, scale)
 
 
-def attention_bwd(dout, qkv, out, lse, batch, n_groups, heads_per_group, head_dim, scale=None):
-    return _pick(qkv).attention_bwd(dout, qkv, out, lse, batch, n_groups, heads_per_group,
-                                    head_dim, scale)
+def attention_bwd(dout, qkv, out, lse, batch, n_groups, heads_per_group, head_dim, scale=None,
+                  rope=None):
+    """``rope = (cos, sin, position_ids)``: also apply the backward of the rotary embedding to
+    the q / k gradients (fused into the CUDA kernel; a second step on the reference path)."""
+    mod = _pick(qkv)
+    if rope is None:
+        return mod.attention_bwd(dout, qkv, out, lse, batch, n_groups, heads_per_group, head_dim,
+                                 scale)
+    if mod is _ref:
+        d = mod.attention_bwd(dout, qkv, out, lse, batch, n_groups, heads_per_group, head_dim, scale)
+        return mod.rope_(d, rope[0], rope[1], batch, n_groups, heads_per_group, head_dim,
+                         inverse=True, position_ids=rope[2])
+    return mod.attention_bwd(dout, qkv, out, lse, batch, n_groups, heads_per_group, head_dim, scale,
+                             rope=rope)
 
 
 def swiglu_fwd(y1):

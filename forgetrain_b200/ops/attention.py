@@ -40,12 +40,23 @@ def attention_fwd(qkv: torch.Tensor, batch: int, n_groups: int, heads_per_group:
 
 def attention_bwd(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse: torch.Tensor,
                   batch: int, n_groups: int, heads_per_group: int, head_dim: int,
-                  scale: float | None = None, heads_per_cta: int = 0) -> torch.Tensor:
-    """Gradient wrt the interleaved qkv buffer (bf16, same layout as ``qkv``)."""
+                  scale: float | None = None, heads_per_cta: int = 0,
+                  rope: tuple | None = None) -> torch.Tensor:
+    """Gradient wrt the interleaved qkv buffer (bf16, same layout as ``qkv``). ``rope`` =
+    ``(cos, sin, position_ids or None)``: the gradient of the q and k heads comes back with the
+    backward of the rotary embedding applied (fused into the kernel that converts the fp32
+    accumulator), i.e. it is the gradient wrt the UNROTATED projection output."""
     T = qkv.shape[0]
     S = T // batch
     scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
     L = _lib.lib()
+    cos = sin = pos = None
+    if rope is not None:
+        cos, sin, pos = rope
+        if cos.dtype != torch.float32 or cos.shape[1] != head_dim // 2 or cos.shape[0] < S:
+            raise ValueError("attention_bwd: rope tables must be fp32 [>= seq][head_dim / 2]")
+        if pos is not None:
+            pos = pos.reshape(-1).to(torch.int32)
     dqkv = torch.empty_like(qkv)
     Hq = n_groups * heads_per_group
     # fp32 scratch: accumulator laid out like qkv, and [delta | lse*log2(e)] per (b, head, s)
@@ -55,6 +66,7 @@ def attention_bwd(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse:
                        c_int(batch), c_int(S), c_int(n_groups), c_int(heads_per_group),
                        c_int(head_dim), c_int(qkv.stride(0)), c_int(out.stride(0)),
                        c_int(dout.stride(0)), c_float(scale), c_int(heads_per_cta),
+                       P(cos), P(sin), P(pos),
                        P(_lib.status_word(qkv.device)), _lib.stream())
     _lib.check_rc(rc, "ft_attn_bwd")
     return dqkv

@@ -239,7 +239,8 @@ def attention_fwd(qkv, batch, n_groups, heads_per_group, head_dim, scale=None):
     return attention.attention_fwd(qkv, batch, n_groups, heads_per_group, head_dim, scale)
 
 
-def attention_bwd(dout, qkv, out, lse, batch, n_groups, heads_per_group, head_dim, scale=None):
+def attention_bwd(dout, qkv, out, lse, batch, n_groups, heads_per_group, head_dim, scale=None,
+                  rope=None):
     from . import attention
     return attention.attention_bwd(dout, qkv, out, lse, batch, n_groups, heads_per_group,
-                                   head_dim, scale)
+                                   head_dim, scale, rope=rope)

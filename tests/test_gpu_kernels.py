@@ -287,3 +287,23 @@ def test_device_side_schedule_matches_host_schedule():
     for it in range(8):
         C.adam_hyper_step(step, sched, hyper)
         assert float(hyper[0]) == pytest.approx(compute_lr(it, max_lr, min_lr, warm, decay, 0), rel=1e-6)
+
+
+@pytest.mark.parametrize("B,S,G,g,D", [(2, 512, 2, 2, 64), (1, 512, 1, 2, 128)])
+def test_attention_backward_with_the_rope_backward_fused(B, S, G, g, D):
+    """The last kernel of the attention backward can apply the transposed rotation to the q / k
+    gradients; same result as the stand-alone RoPE kernel run on the unfused output (up to the
+    one bf16 rounding the fusion saves), with and without explicit position ids."""
+    from forgetrain_b200 import ops
+    qkv = torch.randn(B * S, G * (g + 2) * D, device="cuda").to(torch.bfloat16)
+    o, lse = A.attention_fwd(qkv, B, G, g, D)
+    do = torch.randn_like(o)
+    cos, sin = ops.rope_tables(S, D, 10000.0, device="cuda")
+    pos = torch.randint(0, S, (B, S), device="cuda")
+    for p in (None, pos):
+        plain = A.attention_bwd(do, qkv, o, lse, B, G, g, D)
+        want = ops.rope_(plain.clone(), cos, sin, B, G, g, D, inverse=True, position_ids=p)
+        got = A.attention_bwd(do, qkv, o, lse, B, G, g, D, rope=(cos, sin, p))
+        assert rel(got, want) < 0.01
+        v = got.view(B * S, G, g + 2, D)[:, :, g + 1]
+        assert torch.equal(v, plain.view(B * S, G, g + 2, D)[:, :, g + 1])   # v is not rotated
