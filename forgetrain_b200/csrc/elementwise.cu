@@ -154,8 +154,11 @@ add_rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ res, const __nv_bfloat1
 // (may alias dres); per-CTA weight-gradient partials sum_rows dy * xhat go to
 // dw_partial[gridDim.x][H] and are folded by colsum_partials_kernel.
 // ---------------------------------------------------------------------------------------
+#ifndef FT_NORM_BWD_CPS
+#define FT_NORM_BWD_CPS 3   // resident CTAs per SM the backward kernel is sized for
+#endif
 template <int NV, int TPR>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, FT_NORM_BWD_CPS)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
                    const __nv_bfloat16* dres, __nv_bfloat16* dx_out,
@@ -694,7 +697,7 @@ extern "C" int ft_rmsnorm_bwd_partials(int T, int H) {
   int nv, tpr;
   if (!norm_cfg(H, &nv, &tpr)) return -1;
   const int rows_per_cta = 128 / tpr;
-  return grid_for((long)(T + rows_per_cta - 1) / rows_per_cta, 1, 3);
+  return grid_for((long)(T + rows_per_cta - 1) / rows_per_cta, 1, FT_NORM_BWD_CPS);
 }
 
 extern "C" int ft_rmsnorm_bwd(const void* dy, const void* h, const void* w, const void* rstd,

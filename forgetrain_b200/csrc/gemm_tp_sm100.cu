@@ -145,7 +145,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_last = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = warp_idx_uniform();
   const int lane = threadIdx.x & 31;
   constexpr uint32_t TMEM_COLS = 2 * BN;
   const int rot = p.mode == 1 ? p.rank * p.tiles_per_slot
@@ -228,10 +228,12 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    // The whole warp walks the tiles and waits; one elected lane issues (see elect_one_sync).
+    {
       const uint32_t idesc = make_idesc_bf16(TP_BM, BN, 0, p.b_mn);
       const uint32_t b_lbo = p.b_mn ? 8192u : 16u;
       const uint32_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
+      const uint32_t smem_base = smem_u32(smem);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -244,18 +246,21 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int ki = 0; ki < p.k_iters; ++ki) {
           mbar_wait(&full_bar[stage], phase, abort_flag, p.status, FT_ERR_WAIT_FULL);
           tc_fence_after();
-          const uint32_t sA = smem_u32(smem + stage * L::STAGE_BYTES);
-          const uint32_t sB = sA + L::A_BYTES;
-          const uint64_t adesc = make_smem_desc(sA, 16, 1024);
-          const uint64_t bdesc = make_smem_desc(sB, b_lbo, 1024);
+          if (elect_one_sync()) {
+            const uint32_t sA = smem_base + stage * L::STAGE_BYTES;
+            const uint32_t a_lo = smem_desc_lo(sA, 16);
+            const uint32_t b_lo = smem_desc_lo(sA + L::A_BYTES, b_lbo);
+            umma_ss_lo_dyn(tmem_d, a_lo, b_lo, idesc, ki > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < TP_BK / 16; ++kk)
-            umma_ss(tmem_d, adesc + kk * 2, bdesc + kk * b_kstep, idesc,
-                    (ki > 0 || kk > 0) ? 1u : 0u);
-          umma_commit(&empty_bar[stage]);
+            for (int kk = 1; kk < TP_BK / 16; ++kk)
+              umma_ss_lo<1>(tmem_d, a_lo + kk * 2, b_lo + kk * b_kstep, idesc);
+            umma_commit(&empty_bar[stage]);
+          }
+          __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        umma_commit(&tfull_bar[buf]);
+        if (elect_one_sync()) umma_commit(&tfull_bar[buf]);
+        __syncwarp();
       }
     }
   } else if (warp < 6) {

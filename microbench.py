@@ -231,6 +231,8 @@ def bench_elem(args):
     lab = torch.randint(0, V, (T,), device="cuda")
     qkv = torch.randn(T, 1280, device="cuda").to(torch.bfloat16)
     cos, sin = R.rope_tables(4096, 64, 10000.0, device="cuda")
+    ids = torch.randint(0, V, (T,), device="cuda")
+    gw = torch.zeros(V, H, device="cuda")
     n = 64 * 1024 * 1024
     p32 = torch.randn(n, device="cuda"); m = torch.zeros(n, device="cuda"); v = torch.zeros(n, device="cuda")
     g = torch.randn(n, device="cuda"); pb = torch.empty(n, device="cuda", dtype=torch.bfloat16)
@@ -245,6 +247,7 @@ def bench_elem(args):
         ("cross_entropy_fwd_bwd", lambda: C.cross_entropy_fwd_bwd(lg, lab, None, 1.0), 2 * T * V * 2),
         ("rope", lambda: C.rope_(qkv, cos, sin, T // 4096, 2, 8, 64), 2 * T * 1152 * 2),
         ("adamw", lambda: C.adamw_flat(p32, m, v, g, pb, hyper, se, sw, sl), n * (4 * 7 + 2)),
+        ("embedding_bwd", lambda: C.embedding_bwd(ids, x, 12.0, gw), T * H * (2 + 4 + 4)),
     ]
     for name, fn, nbytes in cases:
         if args.only and name != args.only:
