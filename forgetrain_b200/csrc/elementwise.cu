@@ -9,6 +9,7 @@
 // (exports/train_engine_0.5B/src/training_engine_tensor/triton_kernels.py:39-1397 and
 // exports/train_engine_8b/src/training_engine_tensor/kernels.py:144-2054).
 #include "ptx.cuh"
+#include "swiglu_math.cuh"
 
 namespace ft {
 
@@ -362,11 +363,7 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dact,
     unpack8(*reinterpret_cast<const bf16x8*>(y1 + t * ld_y1 + F + v * 8), up);
     unpack8(*reinterpret_cast<const bf16x8*>(dact + t * ld_dact + v * 8), d);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float sig = 1.f / (1.f + __expf(-gt[k]));
-      dg[k] = d[k] * sig * (1.f + gt[k] * (1.f - sig)) * up[k];
-      du[k] = d[k] * gt[k] * sig;
-    }
+    for (int k = 0; k < 8; ++k) swiglu_bwd_elem(d[k], gt[k], up[k], dg[k], du[k]);
     *reinterpret_cast<bf16x8*>(dy1 + t * ld_y1 + v * 8) = pack8(dg);
     *reinterpret_cast<bf16x8*>(dy1 + t * ld_y1 + F + v * 8) = pack8(du);
   }

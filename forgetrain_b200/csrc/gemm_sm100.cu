@@ -22,6 +22,7 @@
 #include <stdlib.h>
 
 #include "ptx.cuh"
+#include "swiglu_math.cuh"
 #include "tma_host.h"
 
 namespace ft {
@@ -39,6 +40,8 @@ constexpr int GEMM_EPI_WARPS = 8;    // two warps per TMEM lane quarter, each ta
 constexpr int GEMM_GROUP_M = 16;
 
 enum : int { OUT_BF16 = 0, OUT_F32 = 1, OUT_F32_ADD = 2 };
+// what the epilogue does besides scaling and storing the accumulator
+enum : int { EPI_PLAIN = 0, EPI_SWIGLU_FWD = 1, EPI_SWIGLU_BWD = 2 };
 
 struct GemmParams {
   int M, N, K;
@@ -48,22 +51,23 @@ struct GemmParams {
   int splitk;
   int m_tiles, n_tiles, k_iters;
   int* status;
-  int swiglu_F;       // > 0 (SWIGLU kernel only): B is [2F][K] = [gate rows ; up rows]
+  int swiglu_F;       // > 0 (EPI_SWIGLU_FWD): B is [2F][K] = [gate rows ; up rows];
+                      //     (EPI_SWIGLU_BWD): N == F, D is [M][2F] = [d gate ; d up]
   // Work units [0, split_from) are whole 128 x BN tiles; from split_from on, each tile of the
   // last, partly filled wave is cut into two 128 x BN/2 halves (units 2i, 2i+1), so that the
   // tail of the schedule costs about 0.6 instead of 1.0 tile times. total_units counts both.
   int split_from, total_units;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int EPI_BUFS = 1>
 struct GemmSmem {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
   static constexpr int B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int EPI_BUF_BYTES = 4096;                 // 32 rows x 128 B
+  static constexpr int EPI_BUF_BYTES = 4096 * EPI_BUFS;      // boxes of 32 rows x 128 B
   static constexpr int EPI_BYTES = GEMM_EPI_WARPS * EPI_BUF_BYTES;  // one buffer per warp
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES + EPI_BYTES;
-  static constexpr int TOTAL = BAR_OFFSET + 256 + 1024;      // + barriers + alignment slack
+  static constexpr int TOTAL = BAR_OFFSET + 512 + 1024;      // + barriers + alignment slack
 };
 
 // `half`: -1 for a whole tile, else which half of the tile's columns this unit covers.
@@ -227,13 +231,43 @@ __device__ __forceinline__ void drain_tile_swiglu(const GemmParams& p, const CUt
   put(g, tmAct, gcol);
 }
 
-template <int BN, int STAGES, bool SWIGLU = false>
+// Epilogue of the fused FC2 dgrad + SwiGLU backward kernel (EPI_SWIGLU_BWD), one warp's share.
+// The accumulator holds d act = alpha * dY W2 for 256 (or 128) columns of F; the warp owns 32 rows
+// and half of the columns and walks them in pieces of 32 columns. For every piece the gate box and
+// the up box (32 rows x 32 columns, bf16) of the FC1 output of the forward pass come into one of
+// two staging sets by TMA, every thread reads its own row of both, and d gate / d up go back out
+// through the same set into D[M][2F]; the [M][F] gradient of the activation never goes to memory.
+// The loads of piece i+1 (which may belong to the next tile) are issued while piece i is being
+// computed, so their latency is hidden. (Row-owner threads reading their rows straight from
+// global memory touch 32 different lines per instruction; that ran at a tenth of the memory
+// bandwidth.) d act is rounded to bf16 first and the arithmetic is swiglu_bwd_elem, so the result
+// is bitwise what the dgrad GEMM followed by swiglu_bwd_kernel produces.
+struct SwigluBwdCursor {   // position of the load look-ahead in this warp's list of pieces
+  int tile, sub, nvalid, row0, col0;
+};
+
+template <int BN>
+__device__ __forceinline__ void swiglu_bwd_tile_info(const GemmParams& p, int tile, int q,
+                                                     int chalf, int& row0, int& col0, int& ncols,
+                                                     int& nvalid) {
+  int mt, nt, kb, kn, half;
+  decode_tile(p, tile, mt, nt, kb, kn, half);
+  ncols = half < 0 ? BN : BN / 2;
+  row0 = mt * GEMM_BM + q * 32;
+  col0 = nt * BN + (half > 0 ? BN / 2 : 0) + chalf * (ncols / 2);
+  // F is a multiple of 64, so a 32-column piece is inside or outside as a whole
+  const int left = (p.swiglu_F - col0) / 32;
+  nvalid = row0 < p.M ? max(0, min(ncols / 64, left)) : 0;
+}
+
+template <int BN, int STAGES, int EPI = EPI_PLAIN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmD2,
                  const GemmParams p) {
-  static_assert(!SWIGLU || BN == 256, "the fused SwiGLU epilogue needs a 128 + 128 column tile");
-  using L = GemmSmem<BN, STAGES>;
+  constexpr bool SWIGLU = EPI == EPI_SWIGLU_FWD;
+  static_assert(EPI == EPI_PLAIN || BN == 256, "the fused SwiGLU epilogues are built for 256-column tiles");
+  using L = GemmSmem<BN, STAGES, EPI == EPI_SWIGLU_BWD ? 2 : 1>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -242,7 +276,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* ybar = tempty_bar + 2;   // EPI_SWIGLU_BWD: two per epilogue warp (gate / up boxes landed)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ybar + 2 * GEMM_EPI_WARPS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = warp_idx_uniform();
@@ -258,12 +293,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&tfull_bar[b], 1);
       mbar_init(&tempty_bar[b], GEMM_EPI_WARPS);
     }
+    for (int w = 0; w < 2 * GEMM_EPI_WARPS; ++w) mbar_init(&ybar[w], 1);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
     prefetch_tmap(&tmD);
-    if (SWIGLU) prefetch_tmap(&tmD2);
+    if (EPI != EPI_PLAIN) prefetch_tmap(&tmD2);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -384,6 +420,127 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint8_t* my_epi = epi_base + (warp - 2) * L::EPI_BUF_BYTES;
     int it = 0;
     int nstores = 0;
+    if constexpr (EPI == EPI_SWIGLU_BWD) {
+      uint64_t* yb = &ybar[(warp - 2) * 2];   // loads of staging set 0 / 1 have landed
+      const int total = total_tiles;
+      auto advance = [&](SwigluBwdCursor& c) {   // to the next piece that exists
+        ++c.sub;
+        while (c.tile < total && c.sub >= c.nvalid) {
+          c.tile += gridDim.x;
+          c.sub = 0;
+          if (c.tile < total) {
+            int nc;
+            swiglu_bwd_tile_info<BN>(p, c.tile, q, chalf, c.row0, c.col0, nc, c.nvalid);
+          }
+        }
+      };
+      auto issue = [&](const SwigluBwdCursor& c, int set) {   // lane 0 only
+        uint8_t* dst = my_epi + set * 4096;
+        mbar_expect_tx(&yb[set], 4096);
+        tma_load_2d(dst, &tmD2, &yb[set], c.col0 + c.sub * 32, c.row0);
+        tma_load_2d(dst + 2048, &tmD2, &yb[set], p.swiglu_F + c.col0 + c.sub * 32, c.row0);
+      };
+      SwigluBwdCursor la;
+      la.tile = blockIdx.x;
+      la.sub = -1;
+      la.nvalid = 0;
+      if (la.tile < total) {
+        int nc;
+        swiglu_bwd_tile_info<BN>(p, la.tile, q, chalf, la.row0, la.col0, nc, la.nvalid);
+      }
+      advance(la);
+      if (la.tile < total) {   // the first piece's boxes: on their way before the first accumulator
+        if (lane == 0) issue(la, 0);
+        advance(la);
+      }
+      uint32_t nitem = 0;
+      for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
+        int row0, col0, ncols, nvalid;
+        swiglu_bwd_tile_info<BN>(p, tile, q, chalf, row0, col0, ncols, nvalid);
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        mbar_wait(&tfull_bar[buf], acc_phase, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN +
+                               chalf * (ncols / 2);
+        if (tile + static_cast<int>(gridDim.x) < total) {
+          // the boxes of this warp's pieces of the NEXT tile go to L2 a tile time ahead
+          int r2, c2, nc2, nv2;
+          swiglu_bwd_tile_info<BN>(p, tile + gridDim.x, q, chalf, r2, c2, nc2, nv2);
+          if (lane < 2 * nv2)
+            tma_prefetch_l2_2d(&tmD2, c2 + (lane >> 1) * 32 + (lane & 1) * p.swiglu_F, r2);
+        }
+#pragma unroll 1
+        for (int sub = 0; sub < nvalid; ++sub, ++nitem) {
+          const int set = nitem & 1;
+          uint8_t* const bufG = my_epi + set * 4096;
+          uint8_t* const bufU = bufG + 2048;
+          // this row's 32 accumulator values, scaled and rounded to bf16
+          uint32_t d[16];
+          {
+            uint32_t r[32];
+            tmem_ld32(taddr + sub * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              d[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * p.alpha,
+                                 __uint_as_float(r[2 * i + 1]) * p.alpha);
+          }
+          mbar_wait(&yb[set], (nitem >> 1) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
+          // 64-byte rows under the 64-byte swizzle: 16-byte piece j of row r sits at piece
+          // j ^ ((r / 2) % 4) of the row (address bits 4-5 xor bits 7-8)
+          uint32_t g[16], u[16];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int off = lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+            const uint4 gv = *reinterpret_cast<const uint4*>(bufG + off);
+            const uint4 uv = *reinterpret_cast<const uint4*>(bufU + off);
+            g[4 * j] = gv.x; g[4 * j + 1] = gv.y; g[4 * j + 2] = gv.z; g[4 * j + 3] = gv.w;
+            u[4 * j] = uv.x; u[4 * j + 1] = uv.y; u[4 * j + 2] = uv.z; u[4 * j + 3] = uv.w;
+          }
+          // the other set: free once the previous piece's stores have read it; the next piece's
+          // boxes start now and land while this piece is computed
+          if (la.tile < total) {
+            if (lane == 0) {
+              if (nstores >= 1) tma_wait_group_read<0>();
+              issue(la, set ^ 1);
+            }
+            advance(la);
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float d0 = __uint_as_float(d[i] << 16), d1 = __uint_as_float(d[i] & 0xffff0000u);
+            const float g0 = __uint_as_float(g[i] << 16), g1 = __uint_as_float(g[i] & 0xffff0000u);
+            const float u0 = __uint_as_float(u[i] << 16), u1 = __uint_as_float(u[i] & 0xffff0000u);
+            float dg0, du0, dg1, du1;
+            swiglu_bwd_elem(d0, g0, u0, dg0, du0);
+            swiglu_bwd_elem(d1, g1, u1, dg1, du1);
+            g[i] = pack_bf16x2(dg0, dg1);
+            u[i] = pack_bf16x2(du0, du1);
+          }
+          __syncwarp();   // every lane has read its rows: the set may be overwritten
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int off = lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+            *reinterpret_cast<uint4*>(bufG + off) =
+                make_uint4(g[4 * j], g[4 * j + 1], g[4 * j + 2], g[4 * j + 3]);
+            *reinterpret_cast<uint4*>(bufU + off) =
+                make_uint4(u[4 * j], u[4 * j + 1], u[4 * j + 2], u[4 * j + 3]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmD, bufG, col0 + sub * 32, row0);
+            tma_store_2d(&tmD, bufU, p.swiglu_F + col0 + sub * 32, row0);
+            tma_commit_group();
+          }
+          ++nstores;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+      }
+    } else {
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
       int mt, nt, kb, kn, half;
       decode_tile(p, tile, mt, nt, kb, kn, half);
@@ -401,6 +558,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+    }
     }
     if (lane == 0) tma_wait_group<0>();
     __syncwarp();
@@ -639,17 +797,17 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
 struct TmapKey {
   const void* base;
   uint64_t rows, cols, ld;
-  uint32_t box_r, box_c, elt;
+  uint32_t box_r, box_c, elt, swz;
   bool operator==(const TmapKey& o) const {
     return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_r == o.box_r &&
-           box_c == o.box_c && elt == o.elt;
+           box_c == o.box_c && elt == o.elt && swz == o.swz;
   }
 };
 struct TmapKeyHash {
   size_t operator()(const TmapKey& k) const {
     size_t h = reinterpret_cast<size_t>(k.base);
     auto mix = [&](uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); };
-    mix(k.rows); mix(k.cols); mix(k.ld); mix(k.box_r); mix(k.box_c); mix(k.elt);
+    mix(k.rows); mix(k.cols); mix(k.ld); mix(k.box_r); mix(k.box_c); mix(k.elt); mix(k.swz);
     return h;
   }
 };
@@ -657,11 +815,15 @@ struct TmapKeyHash {
 static std::mutex g_tmap_mu;
 static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmap_cache;
 
-// Cached 128-byte-swizzled 2-D tensor map. A map only encodes address + geometry, so a cached
-// entry stays valid for as long as the same geometry is asked for at the same address.
-int get_tmap_2d(CUtensorMap* out, const void* base, int elt, uint64_t rows, uint64_t cols,
-                uint64_t ld, uint32_t box_r, uint32_t box_c) {
-  TmapKey k{base, rows, cols, ld, box_r, box_c, static_cast<uint32_t>(elt)};
+// Cached 2-D tensor map. A map only encodes address + geometry, so a cached entry stays valid
+// for as long as the same geometry is asked for at the same address. The inner extent of the
+// box in bytes has to EQUAL the swizzle span: with a shorter inner extent the rows of the box
+// do not lie at the pitch of the inner extent in shared memory.
+static int get_tmap_2d_swz(CUtensorMap* out, const void* base, int elt, uint64_t rows,
+                           uint64_t cols, uint64_t ld, uint32_t box_r, uint32_t box_c,
+                           CUtensorMapSwizzle swz) {
+  TmapKey k{base, rows, cols, ld, box_r, box_c, static_cast<uint32_t>(elt),
+            static_cast<uint32_t>(swz)};
   std::lock_guard<std::mutex> g(g_tmap_mu);
   auto it = g_tmap_cache.find(k);
   if (it != g_tmap_cache.end()) {
@@ -669,12 +831,19 @@ int get_tmap_2d(CUtensorMap* out, const void* base, int elt, uint64_t rows, uint
     return 0;
   }
   CUtensorMap tm;
-  int rc = make_tmap_2d(&tm, base, elt, rows, cols, ld, box_r, box_c, CU_TENSOR_MAP_SWIZZLE_128B);
+  int rc = make_tmap_2d(&tm, base, elt, rows, cols, ld, box_r, box_c, swz);
   if (rc) return rc;
   if (g_tmap_cache.size() > 65536) g_tmap_cache.clear();
   g_tmap_cache.emplace(k, tm);
   *out = tm;
   return 0;
+}
+
+// The 128-byte-swizzled map that every other kernel of the library uses.
+int get_tmap_2d(CUtensorMap* out, const void* base, int elt, uint64_t rows, uint64_t cols,
+                uint64_t ld, uint32_t box_r, uint32_t box_c) {
+  return get_tmap_2d_swz(out, base, elt, rows, cols, ld, box_r, box_c,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 static int g_num_sms = 0;
@@ -688,14 +857,14 @@ static int num_sms() {
   return g_num_sms;
 }
 
-template <int BN, int STAGES, bool SWIGLU = false>
+template <int BN, int STAGES, int EPI = EPI_PLAIN>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD,
                        const CUtensorMap& tmD2, const GemmParams& p, int max_ctas,
                        cudaStream_t stream) {
-  using L = GemmSmem<BN, STAGES>;
+  using L = GemmSmem<BN, STAGES, EPI == EPI_SWIGLU_BWD ? 2 : 1>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES, SWIGLU>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES, EPI>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
     if (e != cudaSuccess) return -10;
     attr_set = true;
@@ -703,7 +872,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   const int total = p.total_units;
   int grid = total < max_ctas ? total : max_ctas;
   if (grid < 1) grid = 1;
-  gemm_bf16_kernel<BN, STAGES, SWIGLU>
+  gemm_bf16_kernel<BN, STAGES, EPI>
       <<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmD, tmD2, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
@@ -845,7 +1014,52 @@ extern "C" int ft_gemm_swiglu_bf16(const void* A, const void* W, void* Y, void* 
   if (get_tmap_2d(&tmB, W, 2, 2 * static_cast<uint64_t>(F), K, ldw, 128, GEMM_BK)) return -5;
   if (get_tmap_2d(&tmY, Y, 2, M, 2 * static_cast<uint64_t>(F), ldy, 32, 64)) return -6;
   if (get_tmap_2d(&tmAct, ACT, 2, M, F, ldact, 32, 64)) return -6;
-  return launch_gemm<256, 4, true>(tmA, tmB, tmY, tmAct, p, max_ctas, stream);
+  return launch_gemm<256, 4, EPI_SWIGLU_FWD>(tmA, tmB, tmY, tmAct, p, max_ctas, stream);
+}
+
+// FC2 dgrad with the SwiGLU backward in the epilogue: DY1[M][2F] = swiglu_bwd(alpha * DY W2, Y1),
+// where DY is [M][ldy] (K = hidden size, reduction index contiguous), W2 is [K][ldw] with F
+// contiguous columns, Y1 = [gate ; up] is the FC1 output of the forward pass. Bitwise equal to
+// ft_gemm_bf16 (dgrad, bf16 out) followed by ft_swiglu_bwd. F must be a multiple of 64.
+extern "C" int ft_gemm_swiglu_bwd_bf16(const void* DY, const void* W2, const void* Y1, void* DY1,
+                                       int M, int F, int K, int lddy, int ldw, int ldy1,
+                                       int lddy1, float alpha, int max_ctas, int* status,
+                                       cudaStream_t stream) {
+  using namespace ft;
+  if (M <= 0 || F <= 0 || K <= 0) return -1;
+  if (F % 64 || ldy1 % 8 || (reinterpret_cast<uintptr_t>(Y1) & 15)) return -2;
+  const int sms = num_sms();
+  if (max_ctas <= 0 || max_ctas > sms) max_ctas = sms;
+  GemmParams p;
+  p.M = M; p.N = F; p.K = K;
+  p.a_mn = 0; p.b_mn = 1;
+  p.out_mode = OUT_BF16;
+  p.alpha = alpha;
+  p.splitk = 1;
+  p.m_tiles = (M + GEMM_BM - 1) / GEMM_BM;
+  p.n_tiles = (F + 255) / 256;
+  p.k_iters = (K + GEMM_BK - 1) / GEMM_BK;
+  p.status = status;
+  p.swiglu_F = F;
+  const int total = p.m_tiles * p.n_tiles;
+  p.split_from = p.total_units = total;
+  const int rem = total % max_ctas;
+  if (max_ctas >= 2 && rem > 0 && 2 * rem <= max_ctas) {
+    p.split_from = total - rem;
+    p.total_units = total + rem;
+  }
+  CUtensorMap tmA, tmB, tmD, tmY;
+  if (get_tmap_2d(&tmA, DY, 2, M, K, lddy, GEMM_BM, GEMM_BK)) return -4;
+  if (get_tmap_2d(&tmB, W2, 2, K, F, ldw, GEMM_BK, 64)) return -5;
+  // boxes of 32 rows x 32 bf16 columns = 64-byte rows, 64-byte swizzle
+  if (get_tmap_2d_swz(&tmD, DY1, 2, M, 2 * static_cast<uint64_t>(F), lddy1, 32, 32,
+                      CU_TENSOR_MAP_SWIZZLE_64B))
+    return -6;
+  if (get_tmap_2d_swz(&tmY, Y1, 2, M, 2 * static_cast<uint64_t>(F), ldy1, 32, 32,
+                      CU_TENSOR_MAP_SWIZZLE_64B))
+    return -6;
+  // three operand stages instead of four: the second staging buffer per epilogue warp needs 32 KB
+  return launch_gemm<256, 3, EPI_SWIGLU_BWD>(tmA, tmB, tmD, tmY, p, max_ctas, stream);
 }
 
 extern "C" void ft_tmap_cache_clear() {

@@ -225,16 +225,18 @@ class MiniCPM4:
         # ---- feed-forward branch
         y1, act = (sv.y1, sv.act) if sv.y1 is not None else self._recompute_mlp(prefix, sv)
         sv.y1 = sv.act = None
-        dact, dh_full = tp.dgrad_gather(dh, p[n_w2], alpha=r, key="bwd.ffn")
+        if diag is None:   # FC2 dgrad with the activation backward in its epilogue
+            dy1, dh_full = tp.dgrad_gather_swiglu_bwd(dh, p[n_w2], y1, alpha=r, key="bwd.ffn")
+        else:              # the last block keeps the intermediate gradient for the diagnostics
+            dact, dh_full = tp.dgrad_gather(dh, p[n_w2], alpha=r, key="bwd.ffn")
+            dy1 = ops.swiglu_bwd(dact, y1)
+            diag["d_intermediate_last"] = dact.detach().clone()
+            diag["d_fc1_last"] = dy1.detach().clone()
+            del dact
+        del y1
         ops.linear_wgrad(dh_full, act, g[n_w2], accumulate, alpha=r)
         del act
         emit(n_w2)
-        dy1 = ops.swiglu_bwd(dact, y1)
-        del y1
-        if diag is not None:
-            diag["d_intermediate_last"] = dact.detach().clone()
-            diag["d_fc1_last"] = dy1.detach().clone()
-        del dact
         ops.linear_wgrad(dy1, sv.n2_full, g[n_fc1], accumulate)
         emit(n_fc1)
         dn2 = tp.dgrad_scatter(dy1, p[n_fc1])

@@ -93,6 +93,11 @@ def linear_dgrad(dy, w, alpha: float = 1.0):
     return _pick(dy).linear_dgrad(dy, w, alpha)
 
 
+def linear_dgrad_swiglu_bwd(dy, w2, y1, alpha: float = 1.0):
+    """``swiglu_bwd(alpha * dy @ w2, y1)``: FC2 dgrad and the activation backward, one kernel on CUDA."""
+    return _pick(dy).linear_dgrad_swiglu_bwd(dy, w2, y1, alpha)
+
+
 def linear_wgrad(dy, x, out, accumulate: bool, alpha: float = 1.0):
     return _pick(dy).linear_wgrad(dy, x, out, accumulate, alpha)
 

@@ -131,6 +131,12 @@ def linear_dgrad(dy, w, alpha=1.0):
     return gemm.linear_dgrad(dy, w, alpha=alpha)
 
 
+def linear_dgrad_swiglu_bwd(dy, w2, y1, alpha=1.0):
+    if w2.shape[1] % 64:
+        return swiglu_bwd(gemm.linear_dgrad(dy, w2, alpha=alpha), y1)
+    return gemm.linear_dgrad_swiglu_bwd(dy, w2, y1, alpha=alpha)
+
+
 def linear_wgrad(dy, x, out, accumulate, alpha=1.0):
     return gemm.linear_wgrad(dy, x, out=out, accumulate=accumulate, alpha=alpha)
 

@@ -7,6 +7,7 @@ operand majors, so no transposed copies are made:
 * :func:`linear_dgrad` ``dx = alpha * dy @ w``            (bf16 out)
 * :func:`linear_wgrad` ``dw (+)= dy.T @ x``               (fp32 out, optional accumulate)
 * :func:`linear_swiglu_fwd` FC1 forward with ``silu(gate) * up`` computed in the epilogue
+* :func:`linear_dgrad_swiglu_bwd` FC2 dgrad with the SwiGLU backward computed in the epilogue
 
 Plays the role of the reference's ``custom_gemm_<op>_{fwd,dgrad,wgrad}`` shims
 (exports/train_engine_8b/src/training_engine_tensor/custom_gemm.py:81-225) for all five
@@ -92,6 +93,26 @@ def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = N
     _check2d(out, "out", torch.bfloat16)
     gemm_raw(dy, w, out, T, K, N, 0, 1, alpha=alpha, **kw)
     return out
+
+
+def linear_dgrad_swiglu_bwd(dy: torch.Tensor, w2: torch.Tensor, y1: torch.Tensor,
+                            alpha: float = 1.0, max_ctas: int = 0) -> torch.Tensor:
+    """``dy1[T,2F] = swiglu_bwd(alpha * dy[T,H] @ w2[H,F], y1[T,2F])`` in one kernel: the gradient of
+    the activation stays in the accumulator. Bitwise what ``linear_dgrad`` followed by
+    ``swiglu_bwd`` returns. ``F`` must be a multiple of 64."""
+    _check2d(dy, "dy", torch.bfloat16)
+    _check2d(w2, "w2", torch.bfloat16)
+    _check2d(y1, "y1", torch.bfloat16)
+    T, H = dy.shape
+    F = w2.shape[1]
+    assert w2.shape[0] == H and y1.shape == (T, 2 * F) and F % 64 == 0
+    dy1 = torch.empty(T, 2 * F, dtype=torch.bfloat16, device=dy.device)
+    rc = _lib.lib().ft_gemm_swiglu_bwd_bf16(
+        _lib.ptr(dy), _lib.ptr(w2), _lib.ptr(y1), _lib.ptr(dy1), c_int(T), c_int(F), c_int(H),
+        c_int(dy.stride(0)), c_int(w2.stride(0)), c_int(y1.stride(0)), c_int(dy1.stride(0)),
+        c_float(alpha), c_int(max_ctas), _lib.ptr(_lib.status_word(dy.device)), _lib.stream())
+    _lib.check_rc(rc, "ft_gemm_swiglu_bwd_bf16")
+    return dy1
 
 
 def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None,

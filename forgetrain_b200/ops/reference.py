@@ -199,6 +199,11 @@ def linear_swiglu_fwd(x: torch.Tensor, w: torch.Tensor, alpha: float = 1.0):
     return y, swiglu_fwd(y)
 
 
+def linear_dgrad_swiglu_bwd(dy: torch.Tensor, w2: torch.Tensor, y1: torch.Tensor,
+                            alpha: float = 1.0) -> torch.Tensor:
+    return swiglu_bwd(linear_dgrad(dy, w2, alpha), y1)
+
+
 def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, alpha: float = 1.0) -> torch.Tensor:
     dx = dy.float() @ w.float()
     return (dx * alpha).to(dy.dtype) if alpha != 1.0 else dx.to(dy.dtype)

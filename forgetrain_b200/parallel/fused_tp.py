@@ -131,6 +131,12 @@ class FusedTPContext(TPContext):
         return r if r is not None else super().dgrad_gather(dy, w, alpha, key)
 
     # ------------------------------------------------------------------ GEMM -> reduce-scatter
+    def dgrad_gather_swiglu_bwd(self, dy, w2, y1, alpha: float = 1.0, key: str | None = None):
+        # the all-gather -> GEMM kernel has the plain epilogue: activation backward as a second kernel
+        from .. import ops
+        dact, df = self.dgrad_gather(dy, w2, alpha, key)
+        return ops.swiglu_bwd(dact, y1), df
+
     def _gemm_rs(self, x, w, alpha, b_mn: bool):
         M, K = x.shape
         N = w.shape[1] if b_mn else w.shape[0]

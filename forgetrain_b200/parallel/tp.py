@@ -89,6 +89,13 @@ class TPContext:
         df = self.gather(dy)
         return ops.linear_dgrad(df, w, alpha), df
 
+    def dgrad_gather_swiglu_bwd(self, dy, w2, y1, alpha: float = 1.0, key: str | None = None):
+        """``(swiglu_bwd(alpha * gather(dy) @ w2, y1), gather(dy))``: FC2 dgrad with the
+        activation backward in the GEMM epilogue (one kernel on CUDA)."""
+        from .. import ops
+        df = self.gather(dy)
+        return ops.linear_dgrad_swiglu_bwd(df, w2, y1, alpha), df
+
     def dgrad_scatter(self, dy, w, alpha: float = 1.0):
         """``scatter_reduce(alpha * dy @ w)``: backward of ``linear_gather``."""
         from .. import ops

@@ -210,6 +210,15 @@ def bench_gemm(args):
             _lib.check_status()
             emit(kernel="fc1_fwd_plus_swiglu_two_kernels", M=T, N=N, K=K, ms=t_two)
             emit(kernel="fc1_fwd_swiglu_epilogue", M=T, N=N, K=K, ms=t_one, tflops=fl / t_one / 1e9)
+        if name == "fc2" and K % 64 == 0:
+            from forgetrain_b200.ops import cuda_ops as C
+            y1 = torch.randn(T, 2 * K, device="cuda").to(torch.bfloat16)
+            t_two = time_ms(lambda: C.swiglu_bwd(gemm.linear_dgrad(dy, w, out=dx), y1), args.iters, args.once)
+            t_one = time_ms(lambda: gemm.linear_dgrad_swiglu_bwd(dy, w, y1), args.iters, args.once)
+            _lib.check_status()
+            emit(kernel="fc2_dgrad_plus_swiglu_bwd_two_kernels", M=T, N=K, K=N, ms=t_two)
+            emit(kernel="fc2_dgrad_swiglu_bwd_epilogue", M=T, N=K, K=N, ms=t_one, tflops=fl / t_one / 1e9)
+            del y1
         for k, t in res.items():
             emit(kernel=f"gemm_{name}_{k}", M=T, N=N, K=K, ms=t, tflops=fl / t / 1e9,
                  frac_of_peak=fl / t / 1e9 / pk["bf16_tflops"], peak_kind=pk["kind"],

@@ -88,6 +88,28 @@ def test_fc1_with_swiglu_in_the_epilogue(T, F, K):
     assert torch.equal(act3, C.swiglu_fwd(gemm.linear_fwd(x, w3)))
 
 
+@pytest.mark.parametrize("T,F,H", [(128, 64, 64), (300, 192, 200), (1000, 1024, 256), (4096, 4096, 1024)])
+def test_fc2_dgrad_with_swiglu_backward_in_the_epilogue(T, F, H):
+    """One kernel computes d act = dy w2 in its accumulator and writes (d gate, d up); BITWISE what
+    the plain dgrad GEMM followed by the SwiGLU backward kernel give, and close to fp32. The last
+    shape has a half-full last wave, so the 128 x 128 half tiles run too."""
+    dy = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    w2 = (torch.randn(H, F, device="cuda") * 0.08).to(torch.bfloat16)
+    y1 = torch.randn(T, 2 * F, device="cuda").to(torch.bfloat16)
+    for alpha in (1.0, 0.5):
+        got = gemm.linear_dgrad_swiglu_bwd(dy, w2, y1, alpha=alpha)
+        ref = C.swiglu_bwd(gemm.linear_dgrad(dy, w2, alpha=alpha), y1)
+        assert torch.equal(got, ref)
+    yf = y1.float()
+    da = dy.float() @ w2.float()
+    sig = torch.sigmoid(yf[:, :F])
+    ref32 = torch.cat([da * sig * (1 + yf[:, :F] * (1 - sig)) * yf[:, F:], da * yf[:, :F] * sig], dim=1)
+    assert rel(gemm.linear_dgrad_swiglu_bwd(dy, w2, y1), ref32) < 0.02
+    # a width that is not a multiple of 64 takes the two-kernel route through the same front end
+    w3, y3 = w2[:, :40].contiguous(), y1[:, :80].contiguous()
+    assert torch.equal(C.linear_dgrad_swiglu_bwd(dy, w3, y3), C.swiglu_bwd(gemm.linear_dgrad(dy, w3), y3))
+
+
 def test_gemm_strided_views():
     """Operands that are column slices of a wider buffer (row pitch != width)."""
     big = torch.randn(512, 3 * 256, device="cuda").to(torch.bfloat16)

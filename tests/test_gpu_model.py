@@ -154,3 +154,40 @@ def test_fused_fc1_swiglu_step_is_bitwise_the_two_kernel_step(monkeypatch):
     assert out[0][0] == out[1][0]                      # forward is bitwise identical
     assert torch.equal(out[0][1], out[1][1])           # head gradient depends on the forward only
     assert torch.equal(out[0][2], out[1][2])           # last layer's W2 gradient: act and dy only
+
+
+def test_mtp_head_on_gpu_matches_fp32_cpu_model():
+    """The multi-token-prediction head (two extra layers sharing the embedding and output tables)
+    on the native bf16 kernels against the same head on the fp32 CPU model: main loss, per-layer
+    MTP losses and every gradient, the MTP-only parameters included."""
+    from forgetrain_b200.config import load_model_spec
+    from forgetrain_b200.models.minicpm4 import MiniCPM4
+    from forgetrain_b200.models.mtp import MTPHead
+    from forgetrain_b200.models.params import ParamStore
+    from forgetrain_b200.ops import _lib
+    spec = load_model_spec("0.5b", num_layers=2, vocab_size=4096, seq_length=256,
+                           max_position_embeddings=256, tie_embeddings=False)
+    K, factor = 2, 0.3
+    cpu = ParamStore(spec, "cpu", torch.float32, mtp_num_layers=K)
+    gpu = ParamStore(spec, "cuda", torch.bfloat16, mtp_num_layers=K)
+    gpu.init_random(0, "normal", 0.02)
+    for ps in cpu.specs:
+        cpu.params[ps.name].copy_(gpu.params[ps.name].float().cpu())
+    tok, lab = _batch(spec)
+    msk = (torch.rand(2, 256, generator=torch.Generator().manual_seed(3)) > 0.2).float()
+    h_cpu = MTPHead(MiniCPM4(spec, cpu), K, factor)
+    h_gpu = MTPHead(MiniCPM4(spec, gpu), K, factor)
+    l_cpu = h_cpu.forward_backward(tok, lab, msk, 1.0)
+    l_gpu = h_gpu.forward_backward(tok.cuda(), lab.cuda(), msk.cuda(), 1.0)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert abs(float(l_gpu) - float(l_cpu)) / float(l_cpu) < 5e-3
+    assert len(h_gpu.last_mtp_losses) == K
+    for a, b in zip(h_gpu.last_mtp_losses, h_cpu.last_mtp_losses):
+        assert abs(float(a) - float(b)) / abs(float(b)) < 5e-3
+    assert any(ps.name.startswith("mtp.layers.1.") for ps in cpu.specs)
+    for ps in cpu.specs:
+        a, b = gpu.grads[ps.name].float().cpu(), cpu.grads[ps.name]
+        cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0)
+        assert cos > 0.99, (ps.name, float(cos))
+        assert abs(float(a.norm()) / float(b.norm()) - 1) < 0.05, ps.name
