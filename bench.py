@@ -226,7 +226,10 @@ def time_config(*, model: str, tp: int, mbs: int, gas: int, seq: int, K: int, W:
         return [next(prefetch) for _ in range(gas)]
 
     # ---- warm-up (also builds tensor maps, allocator pools, NCCL / peer-memory state)
-    for _ in range(W):
+    # a graph mode runs its own eager calls first and captures on the call after them: all of
+    # that belongs to the warm-up, not to the timed region
+    extra = cfg.step_cuda_graph_warmup + 1 if graph else 0
+    for _ in range(W + extra):
         out = trainer.train_step(next_step_batches())
     trainer.finish_step()
     barrier()
