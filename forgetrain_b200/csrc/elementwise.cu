@@ -259,22 +259,31 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   }
 }
 
-// out[c] (=|+=) sum_p partial[p][c]. One CTA per 32 columns; 8 row-groups of 32 lanes each
-// walk the partial rows with stride 8 and are folded through shared memory.
-__global__ void __launch_bounds__(256)
+// out[c] (=|+=) sum_p partial[p][c]. One CTA per 32 columns; COLSUM_GROUPS row-groups of 32 lanes
+// each walk the partial rows with stride COLSUM_GROUPS (a handful of independent loads per
+// thread: the kernel is pure latency) and are folded through shared memory in a fixed order.
+constexpr int COLSUM_GROUPS = 32;
+__global__ void __launch_bounds__(32 * COLSUM_GROUPS)
 colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ out, int P, int H,
                        int accumulate) {
-  __shared__ float red[8][32];
+  __shared__ float red[COLSUM_GROUPS][33];
   const int cx = threadIdx.x & 31, px = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cx;
-  float s = 0.f;
-  if (c < H)
-    for (int p = px; p < P; p += 8) s += partial[(long)p * H + c];
-  red[px][cx] = s;
+  float s0 = 0.f, s1 = 0.f;
+  if (c < H) {
+    int p = px;
+    for (; p + COLSUM_GROUPS < P; p += 2 * COLSUM_GROUPS) {
+      s0 += partial[(long)p * H + c];
+      s1 += partial[(long)(p + COLSUM_GROUPS) * H + c];
+    }
+    if (p < P) s0 += partial[(long)p * H + c];
+  }
+  red[px][cx] = s0 + s1;
   __syncthreads();
   if (px == 0 && c < H) {
+    float s = red[0][cx];
 #pragma unroll
-    for (int k = 1; k < 8; ++k) s += red[k][cx];
+    for (int k = 1; k < COLSUM_GROUPS; ++k) s += red[k][cx];
     out[c] = accumulate ? out[c] + s : s;
   }
 }
@@ -717,7 +726,7 @@ extern "C" int ft_rmsnorm_bwd(const void* dy, const void* h, const void* w, cons
   FT_NORM_DISPATCH(8, 128, CALL_BWD)
 #undef CALL_BWD
   if (cudaGetLastError() != cudaSuccess) return -100;
-  colsum_partials_kernel<<<(H + 31) / 32, 256, 0, st>>>((const float*)dw_partial, (float*)dw,
+  colsum_partials_kernel<<<(H + 31) / 32, 32 * COLSUM_GROUPS, 0, st>>>((const float*)dw_partial, (float*)dw,
                                                         grid, H, accumulate);
   return FT_LAUNCH_OK();
 }
@@ -854,6 +863,6 @@ extern "C" int ft_rmsnorm_bwd_noalloc(const void* dy, const void* h, const void*
   FT_NORM_DISPATCH(8, 128, CALL_BWD_NA)
 #undef CALL_BWD_NA
   if (cudaGetLastError() != cudaSuccess) return -100;
-  colsum_partials_kernel<<<(H + 31) / 32, 256, 0, st>>>(scratch, (float*)dw, grid, H, accumulate);
+  colsum_partials_kernel<<<(H + 31) / 32, 32 * COLSUM_GROUPS, 0, st>>>(scratch, (float*)dw, grid, H, accumulate);
   return FT_LAUNCH_OK();
 }
