@@ -49,6 +49,9 @@ struct TpGemmParams {
   int m_tiles, n_tiles, k_iters;
   int tp, rank, tiles_per_slot, slot_rows;
   int mode;               // 1: all-gather -> GEMM, 2: GEMM -> reduce-scatter
+  // Work units [0, split_from) are whole 128 x 256 tiles; from split_from on, each tile of the
+  // last, at most half-full wave is cut into two 128 x 128 halves (units 2i, 2i+1).
+  int split_from, total_units;
   // all-gather side
   const uint8_t* a_peers[TP_MAX];  // peer base pointers of the gathered A buffer (own = local)
   long a_row_bytes;                // bytes per row (rows are contiguous)
@@ -110,10 +113,17 @@ __device__ __forceinline__ bool tp_wait_flag(const uint32_t* f, uint32_t epoch, 
   return true;
 }
 
-// logical tile -> (physical m tile, n tile). `rot` rotates the m order so that a rank starts
-// with the row slot that needs no communication (mode 1) or ends with it (mode 2).
+// work unit -> (physical m tile, n tile, half). `rot` rotates the m order so that a rank starts
+// with the row slot that needs no communication (mode 1) or ends with it (mode 2). `half`: -1
+// for a whole tile, else which 128-column half of the tile this unit covers.
 __device__ __forceinline__ void tp_decode_tile(const TpGemmParams& p, int tile, int rot, int& mt,
-                                               int& nt) {
+                                               int& nt, int& half) {
+  half = -1;
+  if (tile >= p.split_from) {
+    const int t = tile - p.split_from;
+    half = t & 1;
+    tile = p.split_from + (t >> 1);
+  }
   const int group_sz = TP_GROUP_M * p.n_tiles;
   const int g = tile / group_sz;
   const int first_m = g * TP_GROUP_M;
@@ -172,19 +182,23 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int total_tiles = p.total_units;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     // One box per lane (lane 0: A, lanes 1..: B): a thread that issues a tiled TMA load is held
     // for several hundred cycles per instruction, so the boxes of a stage leave together.
-    const int nB = p.b_mn ? BN / 64 : 1;
+    const int nB = p.b_mn ? BN / 64 : BN / 128;
     if (lane < 1 + nB) {
       int stage = 0;
       uint32_t phase = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-        int mt, nt;
-        tp_decode_tile(p, tile, rot, mt, nt);
+        int mt, nt, half;
+        tp_decode_tile(p, tile, rot, mt, nt, half);
+        // a half tile loads only its half of the B boxes, into the start of the B buffer
+        const int nBt = half < 0 ? nB : nB / 2;
+        const int jb0 = half <= 0 ? 0 : nB / 2;
+        const uint32_t tx = L::A_BYTES + (half < 0 ? L::B_BYTES : L::B_BYTES / 2);
         if (p.mode == 1 && lane == 0) {
           const int owner = mt / p.tiles_per_slot;
           if (owner != p.rank) {
@@ -210,13 +224,16 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           uint8_t* sB = sA + L::A_BYTES;
           if (lane == 0) {
             // only this lane reads the gathered A operand, after its wait above
-            mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+            mbar_expect_tx(&full_bar[stage], tx);
             tma_load_2d(sA, &tmA, &full_bar[stage], ki * TP_BK, mt * TP_BM);
-          } else if (!p.b_mn) {
-            tma_load_2d(sB, &tmB, &full_bar[stage], ki * TP_BK, nt * BN);
-          } else {
-            const int c = lane - 1;
-            tma_load_2d(sB + c * 8192, &tmB, &full_bar[stage], nt * BN + c * 64, ki * TP_BK);
+          } else if (lane - 1 < nBt) {
+            const int j = lane - 1;   // slot in the B buffer; jb0 + j: box of the tile
+            if (!p.b_mn)
+              tma_load_2d(sB + j * 16384, &tmB, &full_bar[stage], ki * TP_BK,
+                          nt * BN + (jb0 + j) * 128);
+            else
+              tma_load_2d(sB + j * 8192, &tmB, &full_bar[stage], nt * BN + (jb0 + j) * 64,
+                          ki * TP_BK);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -230,7 +247,8 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------ MMA issuer ------------------------------
     // The whole warp walks the tiles and waits; one elected lane issues (see elect_one_sync).
     {
-      const uint32_t idesc = make_idesc_bf16(TP_BM, BN, 0, p.b_mn);
+      const uint32_t idesc_full = make_idesc_bf16(TP_BM, BN, 0, p.b_mn);
+      const uint32_t idesc_half = make_idesc_bf16(TP_BM, BN / 2, 0, p.b_mn);
       const uint32_t b_lbo = p.b_mn ? 8192u : 16u;
       const uint32_t b_kstep = p.b_mn ? (2048u >> 4) : (32u >> 4);
       const uint32_t smem_base = smem_u32(smem);
@@ -238,6 +256,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t phase = 0;
       int it = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+        const uint32_t idesc = tile < p.split_from ? idesc_full : idesc_half;
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         mbar_wait(&tempty_bar[buf], acc_phase ^ 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
@@ -269,8 +288,10 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint8_t* my_epi = epi_base + q * 2 * L::EPI_BUF_BYTES;
     int it = 0, nstores = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-      int mt, nt;
-      tp_decode_tile(p, tile, rot, mt, nt);
+      int mt, nt, half;
+      tp_decode_tile(p, tile, rot, mt, nt, half);
+      const int ncols = half < 0 ? BN : BN / 2;
+      const int colbase = nt * BN + (half > 0 ? BN / 2 : 0);
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       mbar_wait(&tfull_bar[buf], acc_phase, abort_flag, p.status, FT_ERR_WAIT_TMEM_FULL);
@@ -288,8 +309,8 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       const bool rows_live = row0 < row_limit;
 #pragma unroll 1
-      for (int c = 0; c < BN / 64; ++c) {
-        const int col0 = nt * BN + c * 64;
+      for (int c = 0; c < ncols / 64; ++c) {
+        const int col0 = colbase + c * 64;
         if (col0 >= p.N || !rows_live) break;
         uint32_t r[64];
         tmem_ld32(taddr + c * 64, r);
@@ -477,6 +498,19 @@ static int tp_grid() {
   return sms > 0 ? sms : 148;
 }
 
+// Tail of the schedule, as in ft_gemm_bf16: when the last wave is at most half full, its tiles
+// are cut into 128 x 128 halves on twice as many CTAs (a tensor-parallel rank of the 8B model at
+// 4096 tokens has 512 tiles = 3.46 waves in the O-proj / FC2 forward and the QKV / FC1 dgrad).
+static void tp_set_tail_split(TpGemmParams& p, int grid) {
+  const int total = p.m_tiles * p.n_tiles;
+  p.split_from = p.total_units = total;
+  const int rem = total % grid;
+  if (grid >= 2 && rem > 0 && 2 * rem <= grid) {
+    p.split_from = total - rem;
+    p.total_units = total + rem;
+  }
+}
+
 // D[M,N] = alpha * gather(A)[M,K] * B^T. `a_peers[r]` is rank r's mapping of the symmetric
 // gathered buffer ([M][K] bf16, contiguous rows); this rank's slot (rows rank*M/tp ..) holds
 // its data, the other slots are filled by this call. B: [N][K] (b_mn = 0) or [K][N] (b_mn = 1)
@@ -498,6 +532,7 @@ extern "C" int ft_gemm_ag(const void* const* a_peers, const void* B, void* D, in
   if (slot_rows % TP_BM) return -2;  // row slots must be whole tiles
   p.tp = tp; p.rank = rank; p.tiles_per_slot = slot_rows / TP_BM; p.slot_rows = slot_rows;
   p.mode = 1;
+  tp_set_tail_split(p, tp_grid());
   for (int i = 0; i < tp; ++i) {
     p.a_peers[i] = static_cast<const uint8_t*>(a_peers[i]);
     p.flags[i] = static_cast<uint32_t*>(const_cast<void*>(flags[i]));
@@ -513,7 +548,7 @@ extern "C" int ft_gemm_ag(const void* const* a_peers, const void* B, void* D, in
   if (cudaMemsetAsync(chunk_ready, 0, sizeof(int) * n_chunks, st) != cudaSuccess) return -3;
   CUtensorMap tA, tB, tD[8];
   if (get_tmap_2d(&tA, a_peers[rank], 2, M, K, K, TP_BM, TP_BK)) return -4;
-  int rc = b_mn ? get_tmap_2d(&tB, B, 2, K, N, ldb, TP_BK, 64) : get_tmap_2d(&tB, B, 2, N, K, ldb, TP_BN, TP_BK);
+  int rc = b_mn ? get_tmap_2d(&tB, B, 2, K, N, ldb, TP_BK, 64) : get_tmap_2d(&tB, B, 2, N, K, ldb, 128, TP_BK);
   if (rc) return -5;
   if (get_tmap_2d(&tD[0], D, 2, M, N, ldd, 32, 64)) return -6;
   for (int i = 1; i < 8; ++i) tD[i] = tD[0];
@@ -540,13 +575,14 @@ extern "C" int ft_gemm_rs(const void* A, const void* B, const void* const* d_pee
   p.k_iters = (K + TP_BK - 1) / TP_BK;
   p.tp = tp; p.rank = rank; p.tiles_per_slot = slot_rows / TP_BM; p.slot_rows = slot_rows;
   p.mode = 2;
+  tp_set_tail_split(p, tp_grid());
   for (int i = 0; i < tp; ++i) p.flags[i] = static_cast<uint32_t*>(const_cast<void*>(flags[i]));
   p.epoch = epoch; p.limit_ns = limit_ns;
   p.done_ctr = static_cast<unsigned int*>(done_ctr);
   p.status = status;
   CUtensorMap tA, tB, tD[8];
   if (get_tmap_2d(&tA, A, 2, M, K, lda, TP_BM, TP_BK)) return -4;
-  int rc = b_mn ? get_tmap_2d(&tB, B, 2, K, N, ldb, TP_BK, 64) : get_tmap_2d(&tB, B, 2, N, K, ldb, TP_BN, TP_BK);
+  int rc = b_mn ? get_tmap_2d(&tB, B, 2, K, N, ldb, TP_BK, 64) : get_tmap_2d(&tB, B, 2, N, K, ldb, 128, TP_BK);
   if (rc) return -5;
   for (int o = 0; o < 8; ++o) {
     const int oo = o < tp ? o : 0;
