@@ -35,6 +35,10 @@ int launch_fa_bwd_kv64(const CUtensorMap& tq, const CUtensorMap& tdo, const CUte
                        int n_groups, int batch, int hpc, int ld_acc, float scale_log2,
                        const float* neg_lse2, const float* neg_delta, float* acc, int* status,
                        cudaStream_t st);
+int launch_fa_bwd_kv128(const CUtensorMap& tkv, const CUtensorMap& tq, const CUtensorMap& tdo,
+                        const CUtensorMap& tacc, int S, int Hq, int g, int n_groups, int batch,
+                        int hpc, int ld_acc, float scale_log2, const float* neg_lse2,
+                        const float* neg_delta, float* acc, int* status, cudaStream_t st);
 
 constexpr int FAB_THREADS = 512;  // WG0: TMA + MMA, WG1/WG2: softmax halves, WG3: dQ / dK / dV drain
 constexpr int FAB_BLK = 128;
@@ -710,9 +714,22 @@ extern "C" int ft_attn_bwd(const void* dout, const void* qkv, const void* out, c
   CUtensorMap tacc;   // 32 x 32 fp32 boxes over the accumulator (dQ leaves through TMA reduce-adds)
   if (get_tmap_2d(&tacc, acc, 4, T, ncols, ncols, 32, 32)) return -8;
 #ifndef FT_FAB_SMEM_P64
-  int rc = (D == 64) ? launch_fa_bwd_kv64(tq, tdo, tacc, S, Hq, g, n_groups, batch, heads_per_cta, ncols,
-                                          p.scale_log2, d_lse2, d_delta, p.acc, status, st)
-                     : launch_fa_bwd<128, 1, 1, 1, 1>(tq, tdo, tacc, p, st);
+  int rc;
+  if (D == 64) {
+    rc = launch_fa_bwd_kv64(tq, tdo, tacc, S, Hq, g, n_groups, batch, heads_per_cta, ncols,
+                            p.scale_log2, d_lse2, d_delta, p.acc, status, st);
+  } else {
+#ifndef FT_FAB_SMEM_P128
+    // head_dim 128: the TMEM-operand kernel walks the query rows in tiles of 64
+    CUtensorMap tq64, tdo64;
+    if (get_tmap_2d(&tq64, qkv, 2, T, ncols, ld_qkv, 64, 64)) return -2;
+    if (get_tmap_2d(&tdo64, dout, 2, T, static_cast<uint64_t>(Hq) * D, ld_dout, 64, 64)) return -3;
+    rc = launch_fa_bwd_kv128(tq, tq64, tdo64, tacc, S, Hq, g, n_groups, batch, heads_per_cta,
+                             ncols, p.scale_log2, d_lse2, d_delta, p.acc, status, st);
+#else   // the shared-memory hand-over kernel (comparison builds)
+    rc = launch_fa_bwd<128, 1, 1, 1, 1>(tq, tdo, tacc, p, st);
+#endif
+  }
 #else   // head_dim 64 on the shared-memory hand-over kernel as well (comparison builds)
   int rc = (D == 64) ? launch_fa_bwd<64, 3, 1, 1, 2>(tq, tdo, tacc, p, st)
                      : launch_fa_bwd<128, 1, 1, 1, 1>(tq, tdo, tacc, p, st);
