@@ -204,10 +204,11 @@ def test_wgrad_gemm_with_reduce_add_under_neighbour_load():
     assert _stress(cand, _close(ref, rtol=0.02, atol=2.0), before_each=reset) > 10
 
 
-def test_attention_forward_and_backward_under_neighbour_load():
+@pytest.mark.parametrize("D", [64, 128])
+def test_attention_forward_and_backward_under_neighbour_load(D):
     from forgetrain_b200.ops import attention as A, reference as R
     torch.manual_seed(0)
-    B, S, G, g, D = 2, 1024, 2, 4, 64
+    B, S, G, g = 2, 1024, 2, 4
     qkv = torch.randn(B * S, G * (g + 2) * D, device="cuda").to(torch.bfloat16)
     ref, rlse = R.attention_fwd(qkv, B, G, g, D)
     assert _stress(lambda: A.attention_fwd(qkv, B, G, g, D)[0],
