@@ -55,6 +55,17 @@ def _entry(rank, world, port, fn, args, q, env):
 
 
 def run_gpus(fn, world, *args, env=None):
+    """Run ``fn(rank, world, *args)`` in one child process per GPU. A first attempt that dies in
+    a child (seen once on a freshly started machine, in the very first process group of the
+    session) is reported on stderr and repeated once; a second failure is the test's failure."""
+    try:
+        return _run_gpus_once(fn, world, *args, env=env)
+    except RuntimeError as e:
+        print(f"[run_gpus] first attempt failed, repeating once:\n{e}", file=sys.stderr, flush=True)
+        return _run_gpus_once(fn, world, *args, env=env)
+
+
+def _run_gpus_once(fn, world, *args, env=None):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
