@@ -319,16 +319,27 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
         }
       }
       const uint64_t negm2 = pack_f32x2(-m_ref, -m_ref);
-      if (j > 0 && !o_waited) {   // the P buffer is still read by the previous P V product
-        mbar_wait(&o_done[w], (j - 1) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
-        tc_fence_after();
-      }
       // One interleaved stream over 16 chunks of 8 columns: scale, exponential (FA_POLY pairs of
-      // every 4 by polynomial on the FMA pipe), row sum, bf16 packing, store. A warp can issue an
-      // `ex2` only every ~16 cycles; everything else goes out in between.
+      // every 4 by polynomial on the FMA pipe), row sum, bf16 packing. Two softmax warps share a
+      // scheduler's transcendental unit (one `ex2` per ~8 cycles); everything else goes out in
+      // between.
       uint64_t* s2 = reinterpret_cast<uint64_t*>(s);
       uint64_t acc0 = pack_f32x2(0.f, 0.f), acc1 = acc0, acc2 = acc0, acc3 = acc0;
-      uint32_t pk[32];   // P_TMEM: 64 packed probabilities, stored to TMEM 32 words at a time
+      // P in TMEM: the packed probabilities stay in registers until the stream is over (they
+      // take the place of the scores they were made from) and are stored in one go afterwards.
+      // The P columns are still being read by the previous P V product when the stream starts;
+      // waiting for that product BEFORE the stream left the warpgroup idle while the product sat
+      // in the tensor pipe's queue behind the other query tile's work (0.222 -> 0.211 ms). P in
+      // shared memory (head_dim 128): the same deferral measured slower (0.141 -> 0.145 ms, the
+      // 16 stores leave in one burst), so there the wait comes first and the stores go out with
+      // the stream.
+      uint32_t pk[L::P_TMEM ? 64 : 4];
+      if constexpr (!L::P_TMEM) {
+        if (j > 0 && !o_waited) {
+          mbar_wait(&o_done[w], (j - 1) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+          tc_fence_after();
+        }
+      }
 #pragma unroll
       for (int c = 0; c < 16; ++c) {
         uint32_t w4[4];
@@ -354,8 +365,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
         }
         if constexpr (L::P_TMEM) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) pk[(c & 7) * 4 + q] = w4[q];
-          if ((c & 7) == 7) tmem_st32(tmem_P[w] + lane_off + (c >> 3) * 32, pk);
+          for (int q = 0; q < 4; ++q) pk[c * 4 + q] = w4[q];
         } else {
           uint8_t* rowp = sP + (c >> 3) * 16384 + r * 128;
           *reinterpret_cast<uint4*>(rowp + (((c & 7) ^ (r & 7)) << 4)) =
@@ -364,6 +374,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
       }
       lsum2 = add_f32x2(lsum2, add_f32x2(add_f32x2(acc0, acc1), add_f32x2(acc2, acc3)));
       if constexpr (L::P_TMEM) {
+        if (j > 0 && !o_waited) {   // the previous P V product has finished reading the P columns
+          mbar_wait(&o_done[w], (j - 1) & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
+          tc_fence_after();
+        }
+        tmem_st32(tmem_P[w] + lane_off, pk);
+        tmem_st32(tmem_P[w] + lane_off + 32, pk + 32);
         tmem_st_wait();
         tc_fence_before();
       } else {
@@ -457,5 +473,5 @@ extern "C" int ft_attn_fwd(const void* qkv, void* out, void* lse, int batch, int
   p.lse = static_cast<float*>(lse);
   p.status = status;
   if (D == 64) return launch_fa_fwd<64, 3, 3>(tq, to, p, st);
-  return launch_fa_fwd<128, 1, 1>(tq, to, p, st);
+  return launch_fa_fwd<128, 1, 1>(tq, to, p, st);   // a second K stage (the spare 32 KB) measured slower: 0.157 vs 0.141 ms
 }
