@@ -498,6 +498,23 @@ static int tp_grid() {
   return sms > 0 ? sms : 148;
 }
 
+// The all-gather -> GEMM grid waits on chunks that OTHER CTAs of the same grid bring in, so all
+// of it has to be able to be resident at once: the launch is refused unless the device can hold
+// `grid` CTAs of this kernel by itself. (Kernels of other streams can still delay single CTAs;
+// they leave on their own, and every wait in the kernel is bounded.)
+static bool tp_grid_fits(int grid) {
+  static int per_sm = -1;
+  if (per_sm < 0) {
+    cudaFuncSetAttribute(gemm_tp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TpSmem::TOTAL);
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemm_tp_kernel, TP_THREADS,
+                                                      TpSmem::TOTAL) != cudaSuccess)
+      n = 0;
+    per_sm = n;
+  }
+  return per_sm >= 1 && grid <= per_sm * tp_grid();
+}
+
 // Tail of the schedule, as in ft_gemm_bf16: when the last wave is at most half full, its tiles
 // are cut into 128 x 128 halves on twice as many CTAs (a tensor-parallel rank of the 8B model at
 // 4096 tokens has 512 tiles = 3.46 waves in the O-proj / FC2 forward and the QKV / FC1 dgrad).
@@ -543,6 +560,7 @@ extern "C" int ft_gemm_ag(const void* const* a_peers, const void* B, void* D, in
   p.done_ctr = static_cast<unsigned int*>(done_ctr);
   p.status = status;
   const int grid = tp_grid();
+  if (!tp_grid_fits(grid)) return -7;
   const int n_chunks = (tp - 1) * p.tiles_per_slot;
   p.copy_group = n_chunks <= grid ? grid / n_chunks : 1;
   if (cudaMemsetAsync(chunk_ready, 0, sizeof(int) * n_chunks, st) != cudaSuccess) return -3;

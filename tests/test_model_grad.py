@@ -180,3 +180,24 @@ def test_recompute_switches_give_bitwise_the_saved_activation_gradients(attn, ml
     assert l0 == l1 and torch.equal(g0, g1)
     assert all(k == (True, True, True) for k in k0)
     assert all(k == (not attn, not mlp, not mlp) for k in k1)
+
+
+def test_fused_fc2_dgrad_swiglu_backward_front_ends_agree():
+    """``ops.linear_dgrad_swiglu_bwd`` and the tensor-parallel context's ``dgrad_gather_swiglu_bwd``
+    are the composition of the dgrad GEMM and the SwiGLU backward (on CUDA one kernel computes it;
+    the model calls the fused front end for every block but the last, whose intermediate gradient
+    the diagnostics keep)."""
+    from forgetrain_b200.parallel.tp import NO_TP
+    torch.manual_seed(0)
+    T, H, F = 24, 16, 32
+    dy, w2, y1 = torch.randn(T, H), torch.randn(H, F) * 0.1, torch.randn(T, 2 * F)
+    ref = ops.swiglu_bwd(ops.linear_dgrad(dy, w2, 0.7), y1)
+    assert torch.equal(ops.linear_dgrad_swiglu_bwd(dy, w2, y1, 0.7), ref)
+    got, gathered = NO_TP.dgrad_gather_swiglu_bwd(dy, w2, y1, alpha=0.7, key="bwd.ffn")
+    assert torch.equal(got, ref) and gathered is dy
+    # the closed form, for the record: d gate = d act * sig * (1 + g (1 - sig)) * u, d up = d act * g * sig
+    da = 0.7 * dy @ w2
+    g, u = y1[:, :F], y1[:, F:]
+    sig = torch.sigmoid(g)
+    closed = torch.cat([da * sig * (1 + g * (1 - sig)) * u, da * g * sig], dim=1)
+    assert torch.allclose(ref, closed, rtol=1e-5, atol=1e-6)
