@@ -19,7 +19,7 @@ namespace ft {
 constexpr int FA1_THREADS = 256;   // warpgroup 0: producer, issuer, two idle warps; warpgroup 1: softmax
 constexpr int FA1_BLK = 128;
 constexpr int FA1_D = 64;
-constexpr int FA1_STAGES = 2;   // K and V stages
+constexpr int FA1_STAGES = 3;   // K and V stages
 
 struct FaFwd1Params {
   int S, Hq, g, n_groups, batch;
@@ -34,7 +34,7 @@ struct FaFwd1Smem {
   static constexpr int K_OFF = TILE;
   static constexpr int V_OFF = K_OFF + FA1_STAGES * TILE;
   static constexpr int BAR_OFF = V_OFF + FA1_STAGES * TILE;
-  static constexpr int TOTAL = BAR_OFF + 256 + 1024;   // + barriers + alignment slack
+  static constexpr int TOTAL = BAR_OFF + 256;   // base must come 1024-byte aligned (checked)
 };
 
 __global__ void __launch_bounds__(FA1_THREADS, 2)
@@ -43,19 +43,22 @@ fa_fwd1_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
   using L = FaFwd1Smem;
   constexpr int D = FA1_D, KS = FA1_STAGES, VS = FA1_STAGES;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {  // swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, FT_ERR_WAIT_MISC);
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* q_full = bars;            // 1
-  uint64_t* k_full = bars + 1;        // KS
-  uint64_t* k_empty = bars + 3;
-  uint64_t* v_full = bars + 5;        // VS
-  uint64_t* v_empty = bars + 7;
-  uint64_t* s_full = bars + 9;
-  uint64_t* p_ready = bars + 10;      // (count 128)
-  uint64_t* o_done = bars + 11;
-  uint64_t* s_free = bars + 12;       // (count 128): the score row of a step is in registers
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* k_full = bars + 1;        // KS (<= 4)
+  uint64_t* k_empty = bars + 5;
+  uint64_t* v_full = bars + 9;        // VS (<= 4)
+  uint64_t* v_empty = bars + 13;
+  uint64_t* s_full = bars + 17;
+  uint64_t* p_ready = bars + 18;      // (count 128)
+  uint64_t* o_done = bars + 19;
+  uint64_t* s_free = bars + 20;       // (count 128): the score row of a step is in registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 22);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = warp_idx_uniform();
