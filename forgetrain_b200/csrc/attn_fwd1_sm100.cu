@@ -1,5 +1,5 @@
-// Causal GQA FlashAttention forward, head_dim 64, ONE 128-row query tile per CTA and TWO CTAs per
-// SM. Same arithmetic, layouts and softmax stream as attn_fwd_sm100.cu (P in TMEM, lazy rescale,
+// Causal GQA FlashAttention forward, ONE 128-row query tile per CTA and TWO CTAs per SM (head_dim
+// 64, and head_dim 128 in the variant described at the end of this comment). Same arithmetic, layouts and softmax stream as attn_fwd_sm100.cu (P in TMEM, lazy rescale,
 // one pair of exponentials in four by polynomial); what changes is who shares an SM. A CTA of that
 // kernel ping-pongs two query tiles and owns all of TMEM, so an SM runs one CTA at a time and the
 // launch of a CTA, its barrier / TMEM set-up, the first Q / K / V loads, the output pass and the
@@ -11,6 +11,12 @@
 //   warp 1      MMA issuer (S = Q K_j^T, O += P V_j)
 //   warps 2, 3  idle (register reallocation works on whole warpgroups)
 //   warps 4-7   softmax, one thread per query row
+// head_dim 128: S (128 columns) and O (128) already fill the 256 columns, so the packed
+// probabilities are written over the first 64 columns of S itself (every thread touches only its
+// own TMEM lane, and its score row is in registers by then). The next score block can then only be
+// issued behind the P V product that reads them (the tensor pipe runs one thread's products in
+// order), so a CTA alternates softmax and tensor work, and the OTHER resident CTA fills the gaps.
+// Shared memory: Q, one K and one V stage of 32 KB each.
 #include "ptx.cuh"
 #include "tma_host.h"
 
@@ -18,8 +24,16 @@ namespace ft {
 
 constexpr int FA1_THREADS = 256;   // warpgroup 0: producer, issuer, two idle warps; warpgroup 1: softmax
 constexpr int FA1_BLK = 128;
-constexpr int FA1_D = 64;
-constexpr int FA1_STAGES = 3;   // K and V stages
+#ifndef FA1_POLY64
+#define FA1_POLY64 1
+#define FA1_POLY128 0
+#endif
+template <int D>
+struct FaFwd1Cfg {
+  static constexpr int STAGES = D == 64 ? 3 : 1;   // K and V stages
+  static constexpr bool P_OVER_S = D == 128;       // P stored over the first 64 columns of S
+  static constexpr int POLY = D == 64 ? FA1_POLY64 : FA1_POLY128;   // pairs in four whose 2^x goes to the FMA pipe
+};
 
 struct FaFwd1Params {
   int S, Hq, g, n_groups, batch;
@@ -28,20 +42,23 @@ struct FaFwd1Params {
   int* status;
 };
 
+template <int D>
 struct FaFwd1Smem {
-  static constexpr int TILE = FA1_BLK * FA1_D * 2;   // 16 KB
+  static constexpr int TILE = FA1_BLK * D * 2;   // 16 / 32 KB, blocks of 128 rows x 64 columns
   static constexpr int Q_OFF = 0;
   static constexpr int K_OFF = TILE;
-  static constexpr int V_OFF = K_OFF + FA1_STAGES * TILE;
-  static constexpr int BAR_OFF = V_OFF + FA1_STAGES * TILE;
+  static constexpr int V_OFF = K_OFF + FaFwd1Cfg<D>::STAGES * TILE;
+  static constexpr int BAR_OFF = V_OFF + FaFwd1Cfg<D>::STAGES * TILE;
   static constexpr int TOTAL = BAR_OFF + 256;   // base must come 1024-byte aligned (checked)
 };
 
+template <int D>
 __global__ void __launch_bounds__(FA1_THREADS, 2)
 fa_fwd1_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_out,
                const FaFwd1Params p) {
-  using L = FaFwd1Smem;
-  constexpr int D = FA1_D, KS = FA1_STAGES, VS = FA1_STAGES;
+  using L = FaFwd1Smem<D>;
+  using C = FaFwd1Cfg<D>;
+  constexpr int KS = C::STAGES, VS = C::STAGES, NBOX = D / 64;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (smem_u32(smem) & 1023u) {  // swizzled tiles need a 1024-byte aligned base
@@ -103,31 +120,33 @@ fa_fwd1_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base;          // 128 columns
-  const uint32_t tmem_O = tmem_base + 128;    // 64
-  const uint32_t tmem_P = tmem_base + 192;    // 64 (packed bf16 pairs)
+  const uint32_t tmem_O = tmem_base + 128;    // D
+  const uint32_t tmem_P = C::P_OVER_S ? tmem_base : tmem_base + 192;   // 64 (packed bf16 pairs)
 
   if (warp < 4) {
   reg_dealloc<56>();   // the softmax warpgroup takes these registers (whole warpgroups only)
   if (warp == 0) {
-    // ---------------- producer: lane 0 loads Q and the K blocks, lane 1 the V blocks ----------------
-    if (lane < 2) {
-      const bool is_v = lane == 1;
-      if (lane == 0) {
-        mbar_expect_tx(q_full, L::TILE);
-        tma_load_2d(smem + L::Q_OFF, &tm_qkv, q_full, q_col, row_base + qt * FA1_BLK);
-      }
+    // ---------------- producer: lanes [0, NBOX) load Q and the K blocks, lanes [NBOX, 2 NBOX)
+    // the V blocks, one 64-column box each ----------------
+    if (lane < 2 * NBOX) {
+      const int c = lane % NBOX;
+      const bool is_v = lane >= NBOX;
+      if (lane == 0) mbar_expect_tx(q_full, L::TILE);
+      if (!is_v)
+        tma_load_2d(smem + L::Q_OFF + c * 16384, &tm_qkv, q_full, q_col + c * 64,
+                    row_base + qt * FA1_BLK);
       for (int j = 0; j < nk; ++j) {
         const int st = j % KS;
         if (!is_v) {
           mbar_wait(&k_empty[st], ((j / KS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
-          mbar_expect_tx(&k_full[st], L::TILE);
-          tma_load_2d(smem + L::K_OFF + st * L::TILE, &tm_qkv, &k_full[st], k_col,
-                      row_base + j * FA1_BLK);
+          if (c == 0) mbar_expect_tx(&k_full[st], L::TILE);
+          tma_load_2d(smem + L::K_OFF + st * L::TILE + c * 16384, &tm_qkv, &k_full[st],
+                      k_col + c * 64, row_base + j * FA1_BLK);
         } else {
           mbar_wait(&v_empty[st], ((j / VS) & 1) ^ 1, abort_flag, p.status, FT_ERR_WAIT_EMPTY);
-          mbar_expect_tx(&v_full[st], L::TILE);
-          tma_load_2d(smem + L::V_OFF + st * L::TILE, &tm_qkv, &v_full[st], v_col,
-                      row_base + j * FA1_BLK);
+          if (c == 0) mbar_expect_tx(&v_full[st], L::TILE);
+          tma_load_2d(smem + L::V_OFF + st * L::TILE + c * 16384, &tm_qkv, &v_full[st],
+                      v_col + c * 64, row_base + j * FA1_BLK);
         }
       }
       if (lane == 0 && *abort_flag) {
@@ -145,17 +164,19 @@ fa_fwd1_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
     constexpr uint32_t TL = L::TILE >> 4;
     const uint32_t qa = smem_desc_lo(sQ, 16), kK0 = smem_desc_lo(sK, 16);
     const uint32_t vMN0 = smem_desc_lo(sV, 16384);
-    // K-major operand, reduction step kk (16 elements): + kk*32 bytes (head_dim 64 = one
-    // 128-byte swizzle row); MN-major operand, step kk (16 rows of 128 B): + kk*2048 bytes
+    // K-major operand, reduction step kk (16 elements): + (kk/4)*16384 + (kk%4)*32 bytes (blocks
+    // of 64 columns); MN-major operand, step kk (16 rows of 128 B): + kk*2048 bytes
+#define FT_KOFF(kk) ((((kk) / 4) * 16384 + ((kk) % 4) * 32) >> 4)
     auto issue_S = [&](int j) {
       const uint32_t ka = kK0 + (j % KS) * TL;
       umma_ss_lo<0>(tmem_S, qa, ka, idesc_s);
 #pragma unroll
       for (int kk = 1; kk < D / 16; ++kk)
-        umma_ss_lo<1>(tmem_S, qa + ((kk * 32) >> 4), ka + ((kk * 32) >> 4), idesc_s);
+        umma_ss_lo<1>(tmem_S, qa + FT_KOFF(kk), ka + FT_KOFF(kk), idesc_s);
       umma_commit(s_full);
       umma_commit(&k_empty[j % KS]);
     };
+#undef FT_KOFF
     auto issue_PV = [&](int j) {
       const uint32_t va = vMN0 + (j % VS) * TL;
       umma_ts_lo_dyn(tmem_O, tmem_P, va, idesc_o, j > 0 ? 1u : 0u);
@@ -171,20 +192,32 @@ fa_fwd1_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
     if (elect_one_sync()) issue_S(0);
     __syncwarp();
     for (int j = 0; j < nk; ++j) {
-      // S of step j+1 goes to the tensor pipe as soon as the softmax warpgroup holds the score
-      // row of step j in registers, i.e. while it is still exponentiating it
-      if (j + 1 < nk) {
-        mbar_wait(s_free, j & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
-        mbar_wait(&k_full[(j + 1) % KS], ((j + 1) / KS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
-        tc_fence_after();
-        if (elect_one_sync()) issue_S(j + 1);
-        __syncwarp();
+      if constexpr (!C::P_OVER_S) {
+        // S of step j+1 goes to the tensor pipe as soon as the softmax warpgroup holds the score
+        // row of step j in registers, i.e. while it is still exponentiating it
+        if (j + 1 < nk) {
+          mbar_wait(s_free, j & 1, abort_flag, p.status, FT_ERR_WAIT_TMEM_EMPTY);
+          mbar_wait(&k_full[(j + 1) % KS], ((j + 1) / KS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
+          tc_fence_after();
+          if (elect_one_sync()) issue_S(j + 1);
+          __syncwarp();
+        }
       }
       mbar_wait(&v_full[j % VS], (j / VS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
       mbar_wait(p_ready, j & 1, abort_flag, p.status, FT_ERR_WAIT_MISC);
       tc_fence_after();
       if (elect_one_sync()) issue_PV(j);
       __syncwarp();
+      if constexpr (C::P_OVER_S) {
+        // P sits in the columns of S: the next score block goes out BEHIND the P V product
+        // that reads it (one thread's products run in order)
+        if (j + 1 < nk) {
+          mbar_wait(&k_full[(j + 1) % KS], ((j + 1) / KS) & 1, abort_flag, p.status, FT_ERR_WAIT_FULL);
+          tc_fence_after();
+          if (elect_one_sync()) issue_S(j + 1);
+          __syncwarp();
+        }
+      }
     }
   }
   } else {
@@ -209,7 +242,7 @@ fa_fwd1_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
       tmem_ld32(tmem_S + lane_off + 96, s + 96);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(s_free);
+      if constexpr (!C::P_OVER_S) mbar_arrive(s_free);
       if (j == qt) {  // diagonal tile: columns beyond the row are masked
 #pragma unroll
         for (int k = 0; k < 128; ++k)
@@ -262,7 +295,7 @@ fa_fwd1_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
           const int i = c * 4 + q;
           uint64_t t = fma_f32x2(s2[i], sl2x2, negm2);
           float e0, e1;
-          if (q < 1) {
+          if (q < C::POLY) {
             t = exp2_poly_f32x2(t);
             unpack_f32x2(t, e0, e1);
           } else {
@@ -303,7 +336,7 @@ fa_fwd1_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
       uint32_t o[32];
       tmem_ld32(tmem_O + lane_off + c * 32, o);
       tmem_ld_wait();
-      uint8_t* rowp = sO + r * 128;
+      uint8_t* rowp = sO + (c >> 1) * 16384 + r * 128;
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) {
         uint4 u;
@@ -311,7 +344,7 @@ fa_fwd1_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
         u.y = pack_bf16x2(__uint_as_float(o[8 * jj + 2]) * inv_l, __uint_as_float(o[8 * jj + 3]) * inv_l);
         u.z = pack_bf16x2(__uint_as_float(o[8 * jj + 4]) * inv_l, __uint_as_float(o[8 * jj + 5]) * inv_l);
         u.w = pack_bf16x2(__uint_as_float(o[8 * jj + 6]) * inv_l, __uint_as_float(o[8 * jj + 7]) * inv_l);
-        const int chunk = c * 4 + jj;
+        const int chunk = (c & 1) * 4 + jj;
         *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) = u;
       }
     }
@@ -320,7 +353,9 @@ fa_fwd1_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
     fence_proxy_async_smem();
     named_bar_sync(1, 128);
     if (warp == 4 && lane == 0) {
-      tma_store_2d(&tm_out, sO, head * D, row_base + qt * FA1_BLK);
+#pragma unroll
+      for (int c = 0; c < NBOX; ++c)
+        tma_store_2d(&tm_out, sO + c * 16384, head * D + c * 64, row_base + qt * FA1_BLK);
       tma_commit_group();
       tma_wait_group<0>();
     }
@@ -334,15 +369,16 @@ fa_fwd1_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant
   }
 }
 
-// Launch of the one-tile forward kernel (head_dim 64). `tq`: qkv map with 128 x 64 boxes, `to`:
-// output map with 128 x 64 boxes.
-int launch_fa_fwd1_d64(const CUtensorMap& tq, const CUtensorMap& to, int S, int Hq, int g,
-                       int n_groups, int batch, float scale_log2, float* lse, int* status,
-                       cudaStream_t st) {
-  using L = FaFwd1Smem;
+// Launch of the one-tile forward kernel. `tq`: qkv map with 128 x 64 boxes, `to`: output map
+// with 128 x 64 boxes.
+template <int D>
+static int launch_fa_fwd1_t(const CUtensorMap& tq, const CUtensorMap& to, int S, int Hq, int g,
+                            int n_groups, int batch, float scale_log2, float* lse, int* status,
+                            cudaStream_t st) {
+  using L = FaFwd1Smem<D>;
   static bool attr = false;
   if (!attr) {
-    if (cudaFuncSetAttribute(fa_fwd1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(fa_fwd1_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              L::TOTAL) != cudaSuccess)
       return -10;
     attr = true;
@@ -353,8 +389,16 @@ int launch_fa_fwd1_d64(const CUtensorMap& tq, const CUtensorMap& to, int S, int 
   p.lse = lse;
   p.status = status;
   const int grid = (S / FA1_BLK) * batch * Hq;
-  fa_fwd1_kernel<<<grid, FA1_THREADS, L::TOTAL, st>>>(tq, to, p);
+  fa_fwd1_kernel<D><<<grid, FA1_THREADS, L::TOTAL, st>>>(tq, to, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+int launch_fa_fwd1(const CUtensorMap& tq, const CUtensorMap& to, int D, int S, int Hq, int g,
+                   int n_groups, int batch, float scale_log2, float* lse, int* status,
+                   cudaStream_t st) {
+  if (D == 64)
+    return launch_fa_fwd1_t<64>(tq, to, S, Hq, g, n_groups, batch, scale_log2, lse, status, st);
+  return launch_fa_fwd1_t<128>(tq, to, S, Hq, g, n_groups, batch, scale_log2, lse, status, st);
 }
 
 }  // namespace ft

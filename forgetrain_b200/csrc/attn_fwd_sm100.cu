@@ -30,9 +30,9 @@ namespace ft {
 
 int get_tmap_2d(CUtensorMap* out, const void* base, int elt, uint64_t rows, uint64_t cols,
                 uint64_t ld, uint32_t box_r, uint32_t box_c);
-int launch_fa_fwd1_d64(const CUtensorMap& tq, const CUtensorMap& to, int S, int Hq, int g,
-                       int n_groups, int batch, float scale_log2, float* lse, int* status,
-                       cudaStream_t st);
+int launch_fa_fwd1(const CUtensorMap& tq, const CUtensorMap& to, int D, int S, int Hq, int g,
+                   int n_groups, int batch, float scale_log2, float* lse, int* status,
+                   cudaStream_t st);
 
 constexpr int FA_THREADS = 384;
 constexpr int FA_BLK = 128;
@@ -45,6 +45,9 @@ constexpr int FA_BLK = 128;
 #ifndef FA_REG_SOFTMAX
 #define FA_REG_SOFTMAX 200
 #define FA_REG_CONTROL 96
+#endif
+#ifndef FT_FA_FWD1_D128
+#define FT_FA_FWD1_D128 1   // head_dim 128 on the one-tile kernel as well
 #endif
 #ifndef FA_PACK
 #define FA_PACK pack_bf16x2   // fp32 pair -> packed bf16 (cvt), or pack_bf16x2_int (integer pipe)
@@ -476,9 +479,11 @@ extern "C" int ft_attn_fwd(const void* qkv, void* out, void* lse, int batch, int
   p.lse = static_cast<float*>(lse);
   p.status = status;
 #ifndef FT_FA_FWD_TWO_TILES
-  // head_dim 64: one query tile per CTA, two CTAs per SM (attn_fwd1_sm100.cu)
-  if (D == 64)
-    return launch_fa_fwd1_d64(tq, to, S, p.Hq, g, n_groups, batch, p.scale_log2, p.lse, status, st);
+  // one query tile per CTA, two CTAs per SM (attn_fwd1_sm100.cu)
+  // (head_dim 128 at long sequences stays on the two-tile kernel: 0.450 vs 0.464 ms at S = 8192,
+  // where the one-tile kernel's second copy of the K / V traffic shows; 0.137 vs 0.141 ms at 4096)
+  if (D == 64 || (FT_FA_FWD1_D128 && S <= 4096))
+    return launch_fa_fwd1(tq, to, D, S, p.Hq, g, n_groups, batch, p.scale_log2, p.lse, status, st);
 #endif
   if (D == 64) return launch_fa_fwd<64, 3, 3>(tq, to, p, st);
   return launch_fa_fwd<128, 1, 1>(tq, to, p, st);   // the spare 32 KB as a second K stage measured slower (0.157 vs 0.141 ms), as a second V stage the same (0.143)
