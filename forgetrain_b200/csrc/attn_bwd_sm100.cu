@@ -553,15 +553,21 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant_
   }
 }
 
-// delta[b,h,s] = -sum_d out*dout ; lse2 = -lse*log2(e). One thread per 8 elements.
+// delta[b,h,s] = -sum_d out*dout ; lse2 = -lse*log2(e). One thread per 8 elements. The same
+// pass zeroes the fp32 accumulator (`acc4`: n_acc4 float4) that the main kernel reduces into, so
+// no separate fill runs and the stores ride along with this kernel's loads.
 template <int D>
 __global__ void fa_bwd_pre_kernel(const __nv_bfloat16* __restrict__ out,
                                   const __nv_bfloat16* __restrict__ dout,
                                   const float* __restrict__ lse, float* __restrict__ delta,
                                   float* __restrict__ lse2, long T, int S, int Hq, int ld_out,
-                                  int ld_dout) {
+                                  int ld_dout, float4* __restrict__ acc4, long n_acc4) {
   constexpr int TPH = D / 8;  // threads per (token, head)
   const long gid = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  {
+    const long nthreads = static_cast<long>(gridDim.x) * blockDim.x;
+    for (long k = gid; k < n_acc4; k += nthreads) acc4[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   const long pair = gid / TPH;
   const int sub = gid % TPH;
   const bool live = pair < T * Hq;
@@ -688,18 +694,21 @@ extern "C" int ft_attn_bwd(const void* dout, const void* qkv, const void* out, c
   if (g % heads_per_cta) return -4;
   float* d_delta = static_cast<float*>(delta);
   float* d_lse2 = d_delta + static_cast<long>(batch) * Hq * S;
-  if (cudaMemsetAsync(acc, 0, static_cast<size_t>(T) * ncols * 4, st) != cudaSuccess) return -5;
+  if (ncols % 4 || (reinterpret_cast<uintptr_t>(acc) & 15)) return -5;
+  const long n_acc4 = T * ncols / 4;   // the accumulator is zeroed by the preprocess kernel
   {
     const long threads = T * Hq * (D / 8);
     const int blocks = static_cast<int>((threads + 255) / 256);
     if (D == 64)
       fa_bwd_pre_kernel<64><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)out,
                                                     (const __nv_bfloat16*)dout, (const float*)lse,
-                                                    d_delta, d_lse2, T, S, Hq, ld_out, ld_dout);
+                                                    d_delta, d_lse2, T, S, Hq, ld_out, ld_dout,
+                                                    static_cast<float4*>(acc), n_acc4);
     else
       fa_bwd_pre_kernel<128><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)out,
                                                      (const __nv_bfloat16*)dout, (const float*)lse,
-                                                     d_delta, d_lse2, T, S, Hq, ld_out, ld_dout);
+                                                     d_delta, d_lse2, T, S, Hq, ld_out, ld_dout,
+                                                     static_cast<float4*>(acc), n_acc4);
     if (cudaGetLastError() != cudaSuccess) return -6;
   }
   CUtensorMap tq, tdo;
