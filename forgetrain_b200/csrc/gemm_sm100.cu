@@ -900,6 +900,23 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB,
 
 }  // namespace ft
 
+// Tile selection, per shape class (what the rules below resolve to for the two model families at
+// their benchmark token counts; TFLOP/s measured on a B200 at boost clock, cuBLAS in brackets):
+//
+//   shape (M x N x K)                 tile      split / tail              fwd    dgrad  wgrad
+//   0.5B qkv      16384 x 1280 x 1024 128x256   tail: 48 tiles halved      975    999    819  (1135/1076/893)
+//   0.5B attn_out 16384 x 1024 x 1024 128x256   tail: 68 tiles halved      932    932    780  ( 959/1015/818)
+//   0.5B fc1      16384 x 8192 x 1024 128x256   -  (27.7 waves)           1370   1383   1316  (1498/1588/1627)
+//   0.5B fc2      16384 x 1024 x 4096 128x256   tail: 68 tiles halved     1291   1329   1231  (1384/1329/1443)
+//   0.5B lm_head  16384 x 73448 x 1024 128x256  -  (248 waves)            1224   1226   1164  (1117/1317/1556)
+//   8B/TP2 qkv     8192 x 2304 x 4096 128x256   -                         1451   1452   1325  (1623/1438/1696)
+//   8B/TP2 fc1     8192 x 16384 x 4096 128x256  -                         1473   1465   1219  (1404/1305/1545)
+//   N <= 128 (test shapes only)       128x128   six stages
+//   weight gradients whose M x N gives fewer tiles than SMs: split-K over the token dimension
+//   (up to 16 ways, at least 8 k-steps per split), partial tiles summed by TMA reduce-add.
+// The forward of fc1 and the dgrad of fc2 run the variants with the SwiGLU passes in their
+// epilogues (ft_gemm_swiglu_bf16, ft_gemm_swiglu_bwd_bf16 below).
+//
 // D[M,N] (=|+=) alpha * A * B^T with bf16 operands.
 //   a_mn == 0: A is stored [M][lda] (reduction index contiguous); a_mn == 1: A is stored
 //   [K][lda] (row index contiguous). Same for B with N. out_dtype: 0 bf16, 1 fp32.
