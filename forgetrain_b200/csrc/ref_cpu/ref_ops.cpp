@@ -201,6 +201,28 @@ void ftref_swiglu_bwd(const float* dact, const float* y1, float* dy1, int T, int
     }
 }
 
+// FC2 dgrad with the SwiGLU backward folded in, the statement of the device kernel's fused
+// epilogue: per row, d act_j = alpha * <dy, w2[:, j]> is ROUNDED as the separate dgrad GEMM would
+// store it and (d gate_j, d up_j) follow from it and the forward FC1 output; the [M][F] gradient of
+// the activation is never materialised. W2 is stored [K][ldw] (K = hidden size, F columns).
+void ftref_linear_dgrad_swiglu_bwd(const float* DY, const float* W2, const float* Y1, float* DY1,
+                                   int M, int F, int K, int lddy, int ldw, float alpha,
+                                   int round_bf16) {
+#pragma omp parallel for schedule(static)
+  for (int m = 0; m < M; ++m) {
+    const float* dy = DY + (size_t)m * lddy;
+    for (int j = 0; j < F; ++j) {
+      double a = 0.0;
+      for (int k = 0; k < K; ++k) a += (double)dy[k] * W2[(size_t)k * ldw + j];
+      const float g = store(static_cast<float>(a) * alpha, round_bf16);
+      const float gate = Y1[(size_t)m * 2 * F + j], up = Y1[(size_t)m * 2 * F + F + j];
+      const float sig = 1.f / (1.f + std::exp(-gate));
+      DY1[(size_t)m * 2 * F + j] = store(g * sig * (1.f + gate * (1.f - sig)) * up, round_bf16);
+      DY1[(size_t)m * 2 * F + F + j] = store(g * gate * sig, round_bf16);
+    }
+  }
+}
+
 // loss = sum(mask*ce)/valid (returned); dlogits = (softmax - onehot) * mask/valid * loss_scale.
 // Labels outside [vocab_start, vocab_start+V) contribute no target logit (vocabulary shard).
 float ftref_cross_entropy(const float* logits, const int64_t* labels, const float* mask,

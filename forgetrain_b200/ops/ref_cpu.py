@@ -133,6 +133,18 @@ def linear_swiglu_fwd(x, w, alpha=1.0):
     return _back(y, x), _back(act, x)
 
 
+def linear_dgrad_swiglu_bwd(dy, w2, y1, alpha=1.0):
+    """``swiglu_bwd(alpha * dy @ w2, y1)`` in one pass per row (no ``[T, F]`` intermediate)."""
+    DY, W, Y = _f(dy), _f(w2), _f(y1)
+    T, K = DY.shape
+    F = W.shape[1]
+    dy1 = torch.empty(T, 2 * F)
+    lib().ftref_linear_dgrad_swiglu_bwd(_p(DY), _p(W), _p(Y), _p(dy1), c_int(T), c_int(F), c_int(K),
+                                        c_int(DY.stride(0)), c_int(W.stride(0)), c_float(alpha),
+                                        c_int(_rnd(dy)))
+    return _back(dy1, dy)
+
+
 def swiglu_bwd(dact, y1):
     D, Y = _f(dact), _f(y1)
     T, F2 = Y.shape

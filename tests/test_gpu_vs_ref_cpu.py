@@ -42,6 +42,12 @@ def test_fc1_swiglu_epilogue_against_cpp():
     assert rel(act, C.swiglu_fwd(cy)) < 0.02
 
 
+def test_fc2_dgrad_swiglu_backward_epilogue_against_cpp():
+    dy, w2, y1 = bf(384, 192), bf(192, 256, scale=0.08), bf(384, 2 * 256)
+    got = gemm.linear_dgrad_swiglu_bwd(dy, w2, y1, alpha=0.5)
+    assert rel(got, C.linear_dgrad_swiglu_bwd(dy, w2, y1, 0.5)) < 0.02
+
+
 def test_embedding_norm_rope_swiglu_against_cpp():
     w = bf(512, 256)
     ids = torch.randint(0, 512, (300,), device="cuda")

@@ -129,3 +129,20 @@ def test_fused_fc1_swiglu_reference_equals_the_two_op_composition():
     assert rel(y, ry) < 1e-2 and rel(act, ract) < 2e-2
     yf, actf = C.linear_swiglu_fwd(x.float(), w.float())          # fp32 storage: no rounding
     assert rel(actf, torch.nn.functional.silu(yf[:, :24]) * yf[:, 24:]) < 1e-6
+
+
+def test_fused_fc2_dgrad_swiglu_backward_reference_equals_the_two_op_composition():
+    """The one-pass C++ statement of the fused FC2-dgrad epilogue gives bitwise what the dgrad GEMM
+    followed by the SwiGLU backward gives (d act is rounded to the storage type in both)."""
+    torch.manual_seed(0)
+    dy = torch.randn(37, 48).to(torch.bfloat16)
+    w2 = (torch.randn(48, 24) * 0.2).to(torch.bfloat16)
+    y1 = torch.randn(37, 2 * 24).to(torch.bfloat16)
+    got = C.linear_dgrad_swiglu_bwd(dy, w2, y1, 0.5)
+    assert torch.equal(got, C.swiglu_bwd(C.linear_dgrad(dy, w2, 0.5), y1))
+    assert rel(got, R.linear_dgrad_swiglu_bwd(dy, w2, y1, 0.5)) < 2e-2
+    gf = C.linear_dgrad_swiglu_bwd(dy.float(), w2.float(), y1.float())      # fp32 storage
+    da = dy.float() @ w2.float()
+    g, u = y1.float()[:, :24], y1.float()[:, 24:]
+    sig = torch.sigmoid(g)
+    assert rel(gf, torch.cat([da * sig * (1 + g * (1 - sig)) * u, da * g * sig], dim=1)) < 1e-5
