@@ -38,6 +38,7 @@ class EngineConfig:
     # ---- communication ----
     comm: str = "fused"                  # "fused": peer-memory kernels; "nccl": library baseline
     wgrad_overlap: bool = True           # reduce buckets while backward is still running
+    wgrad_side_stream: bool = False      # decoder weight-gradient GEMMs on a stream of their own
     wgrad_bucket_target_elems: int = 100 * 1024 * 1024
     opt_allgather_overlap: bool = True
     async_loss_ar: bool = True           # accepted; the loss all-reduce never blocks the host here
@@ -109,6 +110,7 @@ _ENV_MAP: dict[str, tuple[str, Callable[[str], Any]]] = {
     "SERIAL_STREAMS": ("serial_streams", lambda v: v.lower() in _BOOL_TRUE),
     "FT_COMM": ("comm", str),
     "WGRAD_OVERLAP": ("wgrad_overlap", lambda v: v.lower() in _BOOL_TRUE),
+    "WGRAD_SIDE_STREAM": ("wgrad_side_stream", lambda v: v.lower() in _BOOL_TRUE),
     "WGRAD_BUCKET_TARGET_ELEMS": ("wgrad_bucket_target_elems", int),
     "OPT_ALLGATHER_OVERLAP": ("opt_allgather_overlap", lambda v: v.lower() in _BOOL_TRUE),
     "ASYNC_LOSS_AR": ("async_loss_ar", lambda v: v.lower() in _BOOL_TRUE),

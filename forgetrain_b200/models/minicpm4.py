@@ -79,6 +79,12 @@ class MiniCPM4:
         # right before the forward first reads parameters under it: the trainer hangs the
         # per-bucket "updated and gathered" events of the previous optimizer step on it
         self.param_gate: Callable[[str], None] | None = None
+        # a CUDA stream for the weight-gradient GEMMs of the decoder blocks (None: they run in
+        # line). On it they overlap the tensor-parallel collective that follows the data gradient
+        # of the same layer (reference backward.py:452-463,555-564); the parameter's "gradient
+        # ready" call is made after the main stream has joined that GEMM.
+        self.wgrad_stream = None
+        self._wgrad_done: dict[str, object] = {}
         # FC1 + SwiGLU in one kernel where FC1 is a plain local GEMM (no tensor parallelism)
         self.fuse_fc1_swiglu = tpn == 1 and os.environ.get("FT_FUSE_FC1_SWIGLU", "1") != "0"
         self._ensure_rope(S)
@@ -208,6 +214,31 @@ class MiniCPM4:
         self._head_saved = None
         return dh
 
+    def _wgrad(self, dy, x, name: str, accumulate: bool, alpha: float = 1.0) -> None:
+        """Weight gradient of parameter ``name``: in line, or on ``wgrad_stream`` behind an event
+        of the current stream (the operands are complete there)."""
+        ws = self.wgrad_stream
+        if ws is None or not dy.is_cuda:
+            ops.linear_wgrad(dy, x, self.g[name], accumulate, alpha=alpha)
+            return
+        ready = torch.cuda.Event()
+        ready.record()
+        with torch.cuda.stream(ws):
+            ws.wait_event(ready)
+            ops.linear_wgrad(dy, x, self.g[name], accumulate, alpha=alpha)
+            dy.record_stream(ws)     # the caching allocator must not hand these blocks out
+            x.record_stream(ws)      # again before the side stream has read them
+            done = torch.cuda.Event()
+            done.record()
+        self._wgrad_done[name] = done
+
+    def _emit_after_wgrad(self, emit, name: str) -> None:
+        """``emit(name)`` once the current stream is behind the weight-gradient GEMM of ``name``."""
+        done = self._wgrad_done.pop(name, None)
+        if done is not None:
+            torch.cuda.current_stream().wait_event(done)
+        emit(name)
+
     def layer_backward(self, prefix: str, dh, sv: LayerSaved, batch: int, accumulate: bool, emit,
                        position_ids=None):
         """``dh``: gradient wrt the block output (token shard). Returns the gradient wrt the
@@ -234,13 +265,13 @@ class MiniCPM4:
             diag["d_fc1_last"] = dy1.detach().clone()
             del dact
         del y1
-        ops.linear_wgrad(dh_full, act, g[n_w2], accumulate, alpha=r)
+        self._wgrad(dh_full, act, n_w2, accumulate, alpha=r)
         del act
-        emit(n_w2)
-        ops.linear_wgrad(dy1, sv.n2_full, g[n_fc1], accumulate)
-        emit(n_fc1)
-        dn2 = tp.dgrad_scatter(dy1, p[n_fc1])
+        self._wgrad(dy1, sv.n2_full, n_fc1, accumulate)
+        dn2 = tp.dgrad_scatter(dy1, p[n_fc1])     # its collective overlaps the two GEMMs above
         del dy1
+        self._emit_after_wgrad(emit, n_w2)
+        self._emit_after_wgrad(emit, n_fc1)
         dh = ops.rmsnorm_bwd(dn2, sv.h_mid, p[n_fn], sv.rs2, dh, g[n_fn], accumulate)
         emit(n_fn)
         # ---- attention branch
@@ -248,22 +279,25 @@ class MiniCPM4:
             sv.attn, sv.lse = ops.attention_fwd(sv.qkv, batch, self.local_groups, self.local_g,
                                                 sp.head_dim)
         dattn, dh_full = tp.dgrad_gather(dh, p[n_wo], alpha=r, key="bwd.attn")
-        ops.linear_wgrad(dh_full, sv.attn, g[n_wo], accumulate, alpha=r)
+        self._wgrad(dh_full, sv.attn, n_wo, accumulate, alpha=r)
         # the rotary embedding's backward rides in the attention backward's last kernel
         dqkv = ops.attention_bwd(dattn, sv.qkv, sv.attn, sv.lse, batch, self.local_groups,
                                  self.local_g, sp.head_dim,
                                  rope=(self.cos, self.sin, position_ids))
         del dattn
         sv.attn = sv.lse = None
-        ops.linear_wgrad(dqkv, sv.n1_full, g[n_qkv], accumulate)
+        self._wgrad(dqkv, sv.n1_full, n_qkv, accumulate)
+        dn1 = tp.dgrad_scatter(dqkv, p[n_qkv])    # its collective overlaps the GEMM above
+        done = self._wgrad_done.pop(n_qkv, None)
+        if done is not None:
+            torch.cuda.current_stream().wait_event(done)
         if tp.replica_size > 1:
             self._reduce_kv_replicas(g[n_qkv])
         emit(n_qkv)
-        dn1 = tp.dgrad_scatter(dqkv, p[n_qkv])
         del dqkv
         dh = ops.rmsnorm_bwd(dn1, sv.h_in, p[n_an], sv.rs1, dh, g[n_an], accumulate)
         emit(n_an)
-        emit(n_wo)
+        self._emit_after_wgrad(emit, n_wo)
         return dh
 
     def _reduce_kv_replicas(self, gqkv: torch.Tensor) -> None:

@@ -196,3 +196,30 @@ def test_mtp_head_on_gpu_matches_fp32_cpu_model():
         cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0)
         assert cos > 0.99, (ps.name, float(cos))
         assert abs(float(a.norm()) / float(b.norm()) - 1) < 0.05, ps.name
+
+
+def test_weight_gradients_on_a_side_stream_give_the_same_step():
+    """``wgrad_side_stream``: the decoder weight-gradient GEMMs run on their own stream between an
+    event of the main stream and the parameter's "gradient ready" call. Same gradients as the
+    in-line order (up to the arrival order of the fp32 reduce-adds), over two accumulated
+    micro-batches."""
+    from forgetrain_b200.models.minicpm4 import MiniCPM4
+    from forgetrain_b200.models.params import ParamStore
+    spec = _spec()
+    grads = []
+    for side in (False, True):
+        st = ParamStore(spec, "cuda", torch.bfloat16)
+        st.init_random(0, "normal", 0.02)
+        m = MiniCPM4(spec, st)
+        if side:
+            m.wgrad_stream = torch.cuda.Stream()
+        seen = []
+        for i, seed in enumerate((1, 2)):
+            t, l = _batch(spec, 1, 256, seed)
+            m.forward_backward(t.cuda(), l.cuda(), None, 0.5, accumulate=i > 0, grad_ready=seen.append)
+        torch.cuda.synchronize()
+        assert not m._wgrad_done                      # every side-stream GEMM was joined
+        assert sorted(set(seen)) == sorted(ps.name for ps in st.specs)
+        grads.append(st.flat_grads.clone())
+    err = (grads[0] - grads[1]).abs().max() / grads[0].abs().max()
+    assert float(err) < 1e-2
