@@ -94,7 +94,6 @@ fa_bwd_kv128_kernel(const __grid_constant__ CUtensorMap tm_kv,    // qkv, boxes 
   const int lane = threadIdx.x & 31;
 
   // work decomposition: kv tile ascending = heavy first
-  const int n_kv_tiles = p.S / FB128_KV;
   const int chunks = p.g / p.hpc;
   int bid = blockIdx.x;
   const int hc = bid % chunks; bid /= chunks;
@@ -107,7 +106,6 @@ fa_bwd_kv128_kernel(const __grid_constant__ CUtensorMap tm_kv,    // qkv, boxes 
   const int qt0 = 2 * j;                         // first 64-row query tile that sees this kv tile
   const int n_q = p.S / FB128_QT - qt0;          // query tiles qt0 .. S/64-1
   const int N = p.hpc * n_q;                     // steps of this CTA
-  (void)n_kv_tiles;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
