@@ -225,6 +225,47 @@ def bench_gemm(args):
                  library_tflops=(fl / lib[k] / 1e9 if k in lib else None))
 
 
+def sweep_gemm(args):
+    """Tile / split sweep per projection shape (the role of the reference's persistent-config
+    sweep, exports/train_engine_0.5B/tests/sweep_v3_persistent.py): every forward / dgrad GEMM
+    with both tile widths and, for the weight gradients, every split-K factor the kernel accepts;
+    one line per candidate and one ``best`` line per GEMM, against the default rule's choice."""
+    from forgetrain_b200.ops import gemm, _lib
+    T = args.tokens
+    torch.manual_seed(0)
+    for name, (N, K) in GEMM_SHAPES[args.shape].items():
+        if args.only and name != args.only:
+            continue
+        x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+        dy = torch.randn(T, N, device="cuda").to(torch.bfloat16)
+        y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+        dx = torch.empty(T, K, device="cuda", dtype=torch.bfloat16)
+        dw = torch.empty(N, K, device="cuda", dtype=torch.float32)
+        fl = 2.0 * T * N * K
+        cands = {
+            "fwd": [({"bn": bn}, (lambda bn=bn: gemm.linear_fwd(x, w, out=y, bn=bn))) for bn in (128, 256)],
+            "dgrad": [({"bn": bn}, (lambda bn=bn: gemm.linear_dgrad(dy, w, out=dx, bn=bn))) for bn in (128, 256)],
+            "wgrad": [({"bn": bn, "splitk": sk},
+                       (lambda bn=bn, sk=sk: gemm.linear_wgrad(dy, x, out=dw, bn=bn, splitk=sk)))
+                      for bn in (128, 256) for sk in (1, 2, 4, 8, 16)],
+        }
+        defaults = {"fwd": lambda: gemm.linear_fwd(x, w, out=y),
+                    "dgrad": lambda: gemm.linear_dgrad(dy, w, out=dx),
+                    "wgrad": lambda: gemm.linear_wgrad(dy, x, out=dw)}
+        for kind, lst in cands.items():
+            t_def = time_ms(defaults[kind], args.iters, args.once)
+            best = None
+            for cfg, fn in lst:
+                t = time_ms(fn, args.iters, args.once)
+                _lib.check_status()
+                emit(kernel=f"sweep_{name}_{kind}", M=T, N=N, K=K, ms=t, tflops=fl / t / 1e9, **cfg)
+                if best is None or t < best[0]:
+                    best = (t, cfg)
+            emit(kernel=f"best_{name}_{kind}", M=T, N=N, K=K, ms=best[0], tflops=fl / best[0] / 1e9,
+                 default_rule_ms=t_def, default_rule_tflops=fl / t_def / 1e9, **best[1])
+
+
 def bench_elem(args):
     from forgetrain_b200.ops import cuda_ops as C, reference as R, _lib
     pk = peaks()
@@ -288,9 +329,12 @@ def main():
     ap.add_argument("--only", default=None)
     ap.add_argument("--once", action="store_true")
     ap.add_argument("--library", action="store_true", help="also time the library kernel (cuBLAS / SDPA)")
+    ap.add_argument("--sweep", action="store_true", help="gemm: sweep tile width and split-K per shape")
     ap.add_argument("--min-mb", type=float, default=1.0)
     ap.add_argument("--max-mb", type=float, default=1024.0)
     args = ap.parse_args()
+    if args.what == "gemm" and args.sweep:
+        return sweep_gemm(args)
     {"attn": bench_attn, "gemm": bench_gemm, "elem": bench_elem, "comm": bench_comm,
      "tp": bench_tp}[args.what](args)
 
