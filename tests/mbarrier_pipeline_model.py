@@ -1,0 +1,337 @@
+"""Host model of the mbarrier pipelines of the attention kernels (csrc/attn_bwd_kv_sm100.cu,
+csrc/attn_bwd_kv128_sm100.cu, csrc/attn_fwd1_sm100.cu): which role waits on which barrier with
+which parity, who arrives, and which resources (TMEM columns, shared-memory buffers) a barrier
+guards. The model exists to search the protocols for two classes of design errors without a GPU:
+
+* deadlock, including the "phase aliasing" kind: an mbarrier only knows the parity of its current
+  phase, so a waiter that is still waiting for completion k when completion k+2 has happened blocks
+  for good. ``Barrier.passed`` is the hardware's test: ``try_wait.parity(p)`` succeeds iff the
+  number of completed phases is odd when p == 0 and even when p == 1.
+* a resource written while its previous content is still to be read (write-after-read), or read
+  before it was written: every buffer carries the step number of its content and the number of
+  readers still due.
+
+Roles are Python generators that yield requests; a scheduler picks a runnable role at random and
+delivers asynchronous completions (TMA loads, tensor-core commits) after random delays. Commits of
+one issuing thread complete in issue order, like the tensor pipe's."""
+from __future__ import annotations
+
+import random
+
+
+class Barrier:
+    def __init__(self, name: str, count: int):
+        self.name, self.count = name, count
+        self.pending = count
+        self.completed = 0          # phases completed so far
+
+    def arrive(self, n: int = 1) -> None:
+        self.pending -= n
+        assert self.pending >= 0, f"{self.name}: more arrivals than its count in one phase"
+        if self.pending == 0:
+            self.completed += 1
+            self.pending = self.count
+
+    def passed(self, parity: int) -> bool:
+        return (self.completed & 1) != (parity & 1)
+
+
+class Resource:
+    """A buffer or a group of TMEM columns: content tag + readers still due."""
+
+    def __init__(self, name: str):
+        self.name = name
+        self.tag = None
+        self.readers_due = 0
+
+    def write(self, tag, readers: int) -> None:
+        assert self.readers_due == 0, \
+            f"{self.name}: overwritten with {tag} while {self.readers_due} reader(s) of {self.tag} are due"
+        self.tag, self.readers_due = tag, readers
+
+    def read(self, tag) -> None:
+        assert self.tag == tag, f"{self.name}: holds {self.tag}, reader expected {tag}"
+        assert self.readers_due > 0, f"{self.name}: more reads of {tag} than announced"
+        self.readers_due -= 1
+
+
+class Deadlock(AssertionError):
+    pass
+
+
+class Sim:
+    """Roles yield ``("wait", barrier, parity)``, ``("arrive", barrier)``, ``("async", delay_rank,
+    fn)`` (fn runs later; asyncs of one ``delay_rank`` keep their order) or ``("step",)``."""
+
+    def __init__(self, seed: int):
+        self.rng = random.Random(seed)
+        self.roles: list[tuple[str, object]] = []
+        self.blocked: dict[int, tuple[Barrier, int]] = {}
+        self.queues: dict[object, list] = {}     # per issuing engine: FIFO of pending completions
+        self.now = 0
+
+    def add(self, name: str, gen) -> None:
+        self.roles.append((name, gen))
+
+    def run(self, limit: int = 2_000_000) -> None:
+        alive = set(range(len(self.roles)))
+        for _ in range(limit):
+            self.now += 1
+            # deliver the head of a random engine queue now and then
+            live_q = [k for k, q in self.queues.items() if q]
+            if live_q and self.rng.random() < 0.35:
+                k = self.rng.choice(live_q)
+                self.queues[k].pop(0)()
+            runnable = [i for i in alive
+                        if i not in self.blocked or self.blocked[i][0].passed(self.blocked[i][1])]
+            if not runnable:
+                live_q = [k for k, q in self.queues.items() if q]
+                if live_q:
+                    k = self.rng.choice(live_q)
+                    self.queues[k].pop(0)()
+                    continue
+                if not alive:
+                    return
+                waits = {self.roles[i][0]: (self.blocked[i][0].name, self.blocked[i][1],
+                                            self.blocked[i][0].completed) for i in alive}
+                raise Deadlock(f"no role can run: {waits}")
+            i = self.rng.choice(runnable)
+            self.blocked.pop(i, None)
+            try:
+                req = next(self.roles[i][1])
+            except StopIteration:
+                alive.discard(i)
+                continue
+            if req[0] == "wait":
+                if not req[1].passed(req[2]):
+                    self.blocked[i] = (req[1], req[2])
+            elif req[0] == "arrive":
+                req[1].arrive()
+            elif req[0] == "async":
+                self.queues.setdefault(req[1], []).append(req[2])
+        raise AssertionError("simulation did not finish")
+
+
+# ---------------------------------------------------------------------------------------------
+# attention backward, TMEM-operand kernels. ``sep`` = S^T and dP^T in separate TMEM columns (the
+# head_dim 128 kernel); else they share columns and dP^T is issued when S^T is in registers.
+# ---------------------------------------------------------------------------------------------
+def backward_kv(seed: int, steps: int, qs: int = 3, sep: bool = False, softmax_threads: int = 4,
+                drain_threads: int = 2, stats_with_stage: bool = True, producer_lag: int = 0) -> None:
+    sim = Sim(seed)
+    ns, nd = softmax_threads, drain_threads
+    B = lambda n, c=1: Barrier(n, c)
+    kv_full = B("kv_full")
+    qdo_full = [B(f"qdo_full{s}") for s in range(qs)]
+    qdo_empty = [B(f"qdo_empty{s}") for s in range(qs)]
+    s_full, s_free = B("s_full"), B("s_free", ns)
+    dp_full, dp_free = B("dp_full"), B("dp_free", ns)
+    p_ready, p_free = B("p_ready", ns), B("p_free")
+    pds_ready, dst_free, ds_free = B("pds_ready", ns), B("dst_free"), B("ds_free")
+    dq_full, dq_drained, dkv_full = B("dq_full"), B("dq_drained", nd), B("dkv_full")
+    # one-phase statistics ring of two slots released by pds_ready (the design that deadlocked)
+    stat_full = [B(f"stat_full{s}") for s in range(2)]
+    stage = [Resource(f"stage{s}") for s in range(qs)]
+    stat = [Resource(f"stat{s}") for s in range(2)]
+    S, dP = Resource("S^T"), Resource("dP^T")
+    SdP = Resource("S^T/dP^T")
+    Pt, dSt, dSs, dQ = Resource("P^T"), Resource("dS^T tmem"), Resource("dS^T smem"), Resource("dQ")
+    N = steps
+
+    def producer():
+        yield ("async", "tma", kv_full.arrive)
+        for n in range(N):
+            s = n % qs
+            for _ in range(int(sim.rng.random() * producer_lag)):   # a producer that falls behind
+                yield ("step",)
+            yield ("wait", qdo_empty[s], ((n // qs) & 1) ^ 1)
+            readers = 4 + (ns if stats_with_stage else 0)     # S, dP, dV, dK (+ statistics)
+            def landed(s=s, n=n, readers=readers):
+                stage[s].write(("qdo", n), readers)
+                qdo_full[s].arrive()
+            yield ("async", "tma", landed)
+            if not stats_with_stage:
+                t = n % 2
+                # this ring's release is the once-per-step pds_ready of step n-2
+                if n >= 2:
+                    yield ("wait", pds_ready, (n - 2) & 1)
+                def stat_landed(t=t, n=n):
+                    stat[t].write(("stat", n), ns)
+                    stat_full[t].arrive()
+                yield ("async", "tma2", stat_landed)
+
+    def mma():
+        def issue(reads, write, done_bars):
+            def fn():
+                for r, tag in reads:
+                    r.read(tag)
+                if write is not None:
+                    write[0].write(write[1], write[2])
+                for b in done_bars:
+                    b.arrive()
+            return ("async", "tensor", fn)
+        yield ("wait", kv_full, 0)
+        yield ("wait", qdo_full[0], 0)
+        Sres = S if sep else SdP
+        dPres = dP if sep else SdP
+        yield issue([(stage[0], ("qdo", 0))], (Sres, ("S", 0), ns), [s_full])
+        if sep:
+            yield issue([(stage[0], ("qdo", 0))], (dPres, ("dP", 0), ns), [dp_full])
+        for n in range(N):
+            st = stage[n % qs]
+            if not sep:
+                yield ("wait", s_free, n & 1)
+                yield issue([(st, ("qdo", n))], (dPres, ("dP", n), ns), [dp_full])
+            yield ("wait", p_ready, n & 1)
+            yield issue([(Pt, ("P", n)), (st, ("qdo", n))], None, [p_free])            # dV
+            if n + 1 < N:
+                nx = stage[(n + 1) % qs]
+                if sep:
+                    yield ("wait", s_free, n & 1)
+                    yield ("wait", qdo_full[(n + 1) % qs], ((n + 1) // qs) & 1)
+                    yield issue([(nx, ("qdo", n + 1))], (Sres, ("S", n + 1), ns), [s_full])
+                    yield ("wait", dp_free, n & 1)
+                    yield issue([(nx, ("qdo", n + 1))], (dPres, ("dP", n + 1), ns), [dp_full])
+                else:
+                    yield ("wait", dp_free, n & 1)
+                    yield ("wait", qdo_full[(n + 1) % qs], ((n + 1) // qs) & 1)
+                    yield issue([(nx, ("qdo", n + 1))], (Sres, ("S", n + 1), ns), [s_full])
+            yield ("wait", pds_ready, n & 1)
+            yield issue([(dSt, ("dS", n)), (st, ("qdo", n))], None,
+                        [dst_free, qdo_empty[n % qs]])                                   # dK
+            if n > 0:
+                yield ("wait", dq_drained, (n - 1) & 1)
+            yield issue([(dSs, ("dS", n))], (dQ, ("dQ", n), nd), [dq_full, ds_free])      # dQ
+        yield ("async", "tensor", dkv_full.arrive)
+
+    def softmax(lag: float):
+        Sres = S if sep else SdP
+        dPres = dP if sep else SdP
+        for n in range(N):
+            for _ in range(int(sim.rng.random() * lag)):
+                yield ("step",)
+            s = n % qs
+            yield ("wait", qdo_full[s], (n // qs) & 1)
+            if stats_with_stage:
+                stage[s].read(("qdo", n))          # the statistics rows of the stage
+            else:
+                yield ("wait", stat_full[n % 2], (n // 2) & 1)
+                stat[n % 2].read(("stat", n))
+            yield ("wait", s_full, n & 1)
+            Sres.read(("S", n))
+            yield ("arrive", s_free)
+            if n > 0:
+                yield ("wait", p_free, (n - 1) & 1)
+            Pt.write(("P", n), 1) if Pt.tag != ("P", n) else None
+            yield ("arrive", p_ready)
+            yield ("wait", dp_full, n & 1)
+            dPres.read(("dP", n))
+            yield ("arrive", dp_free)
+            if n > 0:
+                yield ("wait", dst_free, (n - 1) & 1)
+                yield ("wait", ds_free, (n - 1) & 1)
+            if dSt.tag != ("dS", n):
+                dSt.write(("dS", n), 1)
+                dSs.write(("dS", n), 1)
+            yield ("arrive", pds_ready)
+
+    def drain():
+        for n in range(N):
+            yield ("wait", dq_full, n & 1)
+            dQ.read(("dQ", n))
+            yield ("arrive", dq_drained)
+        yield ("wait", dkv_full, 0)
+
+    sim.add("producer", producer())
+    sim.add("mma", mma())
+    for i in range(ns):
+        sim.add(f"softmax{i}", softmax(lag=0 if i else 6))
+    for i in range(nd):
+        sim.add(f"drain{i}", drain())
+    sim.run()
+
+
+# ---------------------------------------------------------------------------------------------
+# attention forward, one query tile per CTA. ``p_over_s``: the probabilities are written over
+# the score columns and the next score block is issued behind the P V product (head_dim 128).
+# ---------------------------------------------------------------------------------------------
+def forward_one_tile(seed: int, steps: int, stages: int = 3, p_over_s: bool = False,
+                     softmax_threads: int = 4) -> None:
+    sim = Sim(seed)
+    ns = softmax_threads
+    B = lambda n, c=1: Barrier(n, c)
+    q_full = B("q_full")
+    k_full = [B(f"k_full{s}") for s in range(stages)]
+    k_empty = [B(f"k_empty{s}") for s in range(stages)]
+    v_full = [B(f"v_full{s}") for s in range(stages)]
+    v_empty = [B(f"v_empty{s}") for s in range(stages)]
+    s_full, s_free, p_ready, o_done = B("s_full"), B("s_free", ns), B("p_ready", ns), B("o_done")
+    K = [Resource(f"K{s}") for s in range(stages)]
+    V = [Resource(f"V{s}") for s in range(stages)]
+    S, P = Resource("S"), Resource("P")
+    N = steps
+
+    def producer(which, full, empty, bufs):
+        if which == "k":
+            yield ("async", "tma_q", q_full.arrive)
+        for j in range(N):
+            s = j % stages
+            yield ("wait", empty[s], ((j // stages) & 1) ^ 1)
+            def landed(s=s, j=j):
+                bufs[s].write((which, j), 1)
+                full[s].arrive()
+            yield ("async", "tma_" + which, landed)
+
+    def mma():
+        def issue_S(j):
+            def fn():
+                K[j % stages].read(("k", j))
+                if p_over_s and j > 0:
+                    assert P.readers_due == 0, "score block issued over probabilities still to be read"
+                S.write(("S", j), ns)
+                s_full.arrive()
+                k_empty[j % stages].arrive()
+            return ("async", "tensor", fn)
+        def issue_PV(j):
+            def fn():
+                P.read(("P", j))
+                V[j % stages].read(("v", j))
+                o_done.arrive()
+                v_empty[j % stages].arrive()
+            return ("async", "tensor", fn)
+        yield ("wait", q_full, 0)
+        yield ("wait", k_full[0], 0)
+        yield issue_S(0)
+        for j in range(N):
+            if not p_over_s and j + 1 < N:
+                yield ("wait", s_free, j & 1)
+                yield ("wait", k_full[(j + 1) % stages], ((j + 1) // stages) & 1)
+                yield issue_S(j + 1)
+            yield ("wait", v_full[j % stages], (j // stages) & 1)
+            yield ("wait", p_ready, j & 1)
+            yield issue_PV(j)
+            if p_over_s and j + 1 < N:
+                yield ("wait", k_full[(j + 1) % stages], ((j + 1) // stages) & 1)
+                yield issue_S(j + 1)
+
+    def softmax(lag: float):
+        for j in range(N):
+            for _ in range(int(sim.rng.random() * lag)):
+                yield ("step",)
+            yield ("wait", s_full, j & 1)
+            S.read(("S", j))
+            if not p_over_s:
+                yield ("arrive", s_free)
+            if j > 0:
+                yield ("wait", o_done, (j - 1) & 1)
+            if P.tag != ("P", j):
+                P.write(("P", j), 1)
+            yield ("arrive", p_ready)
+        yield ("wait", o_done, (N - 1) & 1)
+
+    sim.add("producer_k", producer("k", k_full, k_empty, K))
+    sim.add("producer_v", producer("v", v_full, v_empty, V))
+    sim.add("mma", mma())
+    for i in range(ns):
+        sim.add(f"softmax{i}", softmax(lag=0 if i else 6))
+    sim.run()

@@ -1,0 +1,46 @@
+"""Random-schedule search of the attention kernels' mbarrier protocols on the host model
+(tests/mbarrier_pipeline_model.py): no schedule may deadlock, overwrite a buffer that still has a
+reader due, or read a buffer before it holds the expected step's data. The one protocol that is
+KNOWN to be wrong (a two-slot statistics ring released by a once-per-step barrier) must be caught,
+which shows the search has teeth."""
+import pytest
+
+import mbarrier_pipeline_model as M
+
+
+@pytest.mark.parametrize("sep,qs", [(False, 3), (True, 3), (False, 2), (True, 4)])
+def test_backward_pipelines_survive_random_schedules(sep, qs):
+    """head_dim 64 (S^T / dP^T share columns) and head_dim 128 (separate columns) backward."""
+    for steps in (1, 2, 3, 7, 12):
+        for seed in range(40):
+            M.backward_kv(seed, steps, qs=qs, sep=sep)
+            M.backward_kv(seed, steps, qs=qs, sep=sep, producer_lag=400)   # and with a slow producer
+
+
+@pytest.mark.parametrize("p_over_s,stages", [(False, 3), (False, 2), (True, 1), (True, 2)])
+def test_forward_one_tile_pipelines_survive_random_schedules(p_over_s, stages):
+    for steps in (1, 2, 3, 8, 17):
+        for seed in range(40):
+            M.forward_one_tile(seed, steps, stages=stages, p_over_s=p_over_s)
+
+
+def test_the_search_finds_the_statistics_ring_that_deadlocked():
+    """Statistics rows in a ring of their own, two slots, released through the once-per-step
+    "dS stored" barrier: a producer that lags more than one step behind waits for a parity that
+    has come round again. The model must find a schedule that shows it."""
+    found = 0
+    for seed in range(200):
+        try:
+            M.backward_kv(seed, 9, qs=3, sep=False, stats_with_stage=False, producer_lag=400)
+        except (M.Deadlock, AssertionError):
+            found += 1
+    assert found > 0
+
+
+def test_barrier_parity_is_the_hardware_test():
+    b = M.Barrier("b", 2)
+    assert b.passed(1) and not b.passed(0)          # fresh barrier: "previous" phase counts as done
+    b.arrive(); assert not b.passed(0)
+    b.arrive(); assert b.passed(0) and not b.passed(1)
+    b.arrive(); b.arrive()
+    assert b.passed(1) and not b.passed(0)          # two completions later the old parity blocks again
