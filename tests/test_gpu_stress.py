@@ -181,6 +181,26 @@ def test_dgrad_gemm_under_neighbour_load():
     assert _stress(cand, _close(ref)) > 10
 
 
+def test_fused_dgrad_swiglu_backward_gemm_under_neighbour_load():
+    """FC2 dgrad with the SwiGLU backward in its epilogue: gate / up boxes come in by TMA with one
+    piece of look-ahead while the main loop's loads share the same queue."""
+    from forgetrain_b200.ops import cuda_ops as C, gemm
+    torch.manual_seed(0)
+    dy = torch.randn(4096, 1024, device="cuda").to(torch.bfloat16)
+    w2 = (torch.randn(1024, 4096, device="cuda") * 0.05).to(torch.bfloat16)
+    y1 = torch.randn(4096, 2 * 4096, device="cuda").to(torch.bfloat16)
+    ref = C.swiglu_bwd(gemm.linear_dgrad(dy, w2), y1)
+    if USE_LIBRARY:
+        cand = lambda: C.swiglu_bwd(dy @ w2, y1)
+        check = _close(ref.float(), rtol=0.05, atol=0.05)
+    else:
+        cand = lambda: gemm.linear_dgrad_swiglu_bwd(dy, w2, y1)
+
+        def check(out):
+            assert torch.equal(out, ref)      # bitwise the two-kernel result, also under load
+    assert _stress(cand, check) > 10
+
+
 def test_wgrad_gemm_with_reduce_add_under_neighbour_load():
     """The fp32 weight gradient with split-K and accumulation: partial tiles leave through TMA
     reduce-adds into a buffer that already holds the previous micro-batch's sum."""
