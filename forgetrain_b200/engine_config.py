@@ -38,7 +38,7 @@ class EngineConfig:
     # ---- communication ----
     comm: str = "fused"                  # "fused": peer-memory kernels; "nccl": library baseline
     wgrad_overlap: bool = True           # reduce buckets while backward is still running
-    wgrad_side_stream: bool = False      # decoder weight-gradient GEMMs on a stream of their own
+    wgrad_side_stream: bool = True       # decoder weight-gradient GEMMs on a stream of their own
     wgrad_bucket_target_elems: int = 100 * 1024 * 1024
     opt_allgather_overlap: bool = True
     async_loss_ar: bool = True           # accepted; the loss all-reduce never blocks the host here

@@ -155,11 +155,14 @@ class Trainer:
         self._fwd_graph = None
         graphable_comm = topo.world == 1 or (self.fused_dp is not None and tp == 1)
         uses_graph = dev.type == "cuda" and (cfg.full_step_cuda_graph or cfg.step_cuda_graph)
-        # Weight-gradient GEMMs of the decoder blocks on a side stream: they then run while the
-        # tensor-parallel collective that follows the data gradient is in flight. Off by default:
-        # with the fused all-gather -> GEMM kernel a second full-grid GEMM on another stream only
-        # delays that kernel's own CTAs, which wait for one another's copies.
-        if cfg.wgrad_side_stream and dev.type == "cuda" and not uses_graph and not cfg.serial_streams:
+        # Weight-gradient GEMMs of the decoder blocks on a side stream: the tail of one GEMM's last
+        # wave then overlaps the start of the next kernel, and with tensor parallelism over NCCL they
+        # run while the collective that follows the data gradient is in flight. Not with the fused
+        # all-gather -> GEMM kernel: a second full-grid GEMM on another stream only delays that
+        # kernel's own CTAs, which wait for one another's copies.
+        fused_tp = tp > 1 and cfg.comm == "fused"
+        if cfg.wgrad_side_stream and dev.type == "cuda" and not uses_graph \
+                and not cfg.serial_streams and not fused_tp:
             self.model.wgrad_stream = torch.cuda.Stream(device=dev)
         if self.opt.opt_stream is not None and not uses_graph:
             self.opt.overlap_forward = True
