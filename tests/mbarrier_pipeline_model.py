@@ -335,3 +335,61 @@ def forward_one_tile(seed: int, steps: int, stages: int = 3, p_over_s: bool = Fa
     for i in range(ns):
         sim.add(f"softmax{i}", softmax(lag=0 if i else 6))
     sim.run()
+
+
+# ---------------------------------------------------------------------------------------------
+# GEMM with the SwiGLU backward in the epilogue: one epilogue warp's two staging sets. For piece i
+# the gate / up boxes land in set i % 2 (TMA load, barrier yb[set]), the warp reads them, writes
+# the results back into the same set and sends them off (TMA store, bulk group); the loads of
+# piece i+1 are issued during piece i, after the stores of piece i-1 have read set (i+1) % 2.
+# ---------------------------------------------------------------------------------------------
+def gemm_epilogue_lookahead(seed: int, pieces: int, tiles_every: int = 4) -> None:
+    sim = Sim(seed)
+    yb = [Barrier("yb0", 1), Barrier("yb1", 1)]
+    tfull = [Barrier("tfull0", 1), Barrier("tfull1", 1)]      # two TMEM accumulators
+    tempty = [Barrier("tempty0", 1), Barrier("tempty1", 1)]
+    sets = [Resource("set0"), Resource("set1")]
+    stores_in_flight: list[int] = []     # bulk groups committed and not yet read, oldest first
+    n_tiles = (pieces + tiles_every - 1) // tiles_every
+
+    def mma():   # fills accumulator t % 2 once the epilogue has released it
+        for t in range(n_tiles):
+            yield ("wait", tempty[t % 2], ((t >> 1) & 1) ^ 1)
+            yield ("async", "tensor", tfull[t % 2].arrive)
+
+    def issue_load(i):
+        s = i % 2
+        def landed():
+            sets[s].write(("in", i), 1)
+            yb[s].arrive()
+        return ("async", "tma_load", landed)
+
+    def warp():
+        if pieces:
+            yield issue_load(0)      # the first piece's boxes: before the first accumulator is awaited
+        for i in range(pieces):
+            s = i % 2
+            t = i // tiles_every
+            if i % tiles_every == 0:
+                yield ("wait", tfull[t % 2], (t >> 1) & 1)
+            yield ("wait", yb[s], (i >> 1) & 1)
+            sets[s].read(("in", i))
+            if i + 1 < pieces:
+                # wait_group_read<0>: every committed store has read its buffer
+                while stores_in_flight:
+                    yield ("step",)
+                yield issue_load(i + 1)
+            sets[s].write(("out", i), 1)
+            def store_read(s=s, i=i):
+                sets[s].read(("out", i))
+                stores_in_flight.remove(i)
+            stores_in_flight.append(i)
+            yield ("async", "tma_store", store_read)
+            if i % tiles_every == tiles_every - 1 or i == pieces - 1:
+                yield ("arrive", tempty[t % 2])
+        while stores_in_flight:
+            yield ("step",)
+
+    sim.add("mma", mma())
+    sim.add("warp", warp())
+    sim.run()

@@ -44,3 +44,11 @@ def test_barrier_parity_is_the_hardware_test():
     b.arrive(); assert b.passed(0) and not b.passed(1)
     b.arrive(); b.arrive()
     assert b.passed(1) and not b.passed(0)          # two completions later the old parity blocks again
+
+
+def test_gemm_epilogue_lookahead_never_overwrites_a_buffer_in_use():
+    """The two staging sets of the fused FC2-dgrad epilogue: a set is reloaded only after the
+    store that was sent from it has read it, whatever the delays of loads and stores."""
+    for pieces in (1, 2, 3, 4, 9, 16):
+        for seed in range(60):
+            M.gemm_epilogue_lookahead(seed, pieces)
