@@ -393,3 +393,128 @@ def gemm_epilogue_lookahead(seed: int, pieces: int, tiles_every: int = 4) -> Non
     sim.add("mma", mma())
     sim.add("warp", warp())
     sim.run()
+
+
+# ---------------------------------------------------------------------------------------------
+# CTA-pair GEMM (the kernel that is not built, csrc/gemm_sm100.cu behind FT_BUILD_PAIR_GEMM): two
+# CTAs, each with its own operand ring; the leader issues every product and its commits arrive at
+# the same-named barrier of BOTH CTAs; both CTAs' loads report to the LEADER's full barrier (one
+# arrival with the expected byte count from the leader's producer, bytes from both); the epilogue
+# threads of both CTAs release an accumulator on the leader's barrier. A CTA must not exit while
+# an arrival addressed to it is still on its way.
+# ---------------------------------------------------------------------------------------------
+class TxBarrier(Barrier):
+    """mbarrier with a transaction count: a phase completes when the pending arrivals AND the
+    outstanding bytes are both zero (bytes may be reported before the arrival that expects them)."""
+
+    def __init__(self, name: str, count: int):
+        super().__init__(name, count)
+        self.tx = 0
+
+    def _check(self) -> None:
+        if self.pending == 0 and self.tx == 0:
+            self.completed += 1
+            self.pending = self.count
+
+    def arrive(self, n: int = 1) -> None:
+        self.pending -= n
+        assert self.pending >= 0, f"{self.name}: more arrivals than its count in one phase"
+        self._check()
+
+    def arrive_expect(self, nbytes: int) -> None:
+        self.tx += nbytes
+        self.arrive()
+
+    def complete_tx(self, nbytes: int) -> None:
+        self.tx -= nbytes
+        self._check()
+
+
+def pair_gemm(seed: int, tiles: int, k_steps: int, stages: int = 6, epi_threads: int = 2) -> None:
+    sim = Sim(seed)
+    E = epi_threads
+    full = [TxBarrier(f"full{s}", 1) for s in range(stages)]                       # leader only
+    empty = [[Barrier(f"empty{c}_{s}", 1) for s in range(stages)] for c in range(2)]
+    tfull = [[Barrier(f"tfull{c}_{b}", 1) for b in range(2)] for c in range(2)]
+    tempty = [Barrier(f"tempty{b}", 2 * E) for b in range(2)]                      # leader only
+    bufs = [[Resource(f"stage{c}_{s}") for s in range(stages)] for c in range(2)]
+    acc = [[Resource(f"acc{c}_{b}") for b in range(2)] for c in range(2)]
+    exited = [False, False]
+    done = [0, 0]            # roles of a CTA that have finished
+    roles_per_cta = [1 + 1 + E, 1 + E]
+
+    def to_cta(c, fn):
+        def deliver():
+            assert not exited[c], f"an arrival reached CTA {c} after it had exited"
+            fn()
+        return deliver
+
+    def producer(c):
+        use = 0
+        for _t in range(tiles):
+            for _k in range(k_steps):
+                s = use % stages
+                yield ("wait", empty[c][s], ((use // stages) & 1) ^ 1)
+                if c == 0:
+                    full[s].arrive_expect(2)       # one unit of bytes per CTA
+                def landed(c=c, s=s, use=use):
+                    bufs[c][s].write(("ops", use), 1)
+                    full[s].complete_tx(1)
+                yield ("async", f"tma{c}", to_cta(0, landed))
+                use += 1
+        # tail: observe the release of every stage once more
+        for _ in range(stages):
+            s = use % stages
+            yield ("wait", empty[c][s], ((use // stages) & 1) ^ 1)
+            use += 1
+        done[c] += 1
+
+    def mma():
+        use = 0
+        for t in range(tiles):
+            b = t & 1
+            yield ("wait", tempty[b], ((t >> 1) & 1) ^ 1)
+            for _k in range(k_steps):
+                s = use % stages
+                yield ("wait", full[s], (use // stages) & 1)
+                def ran(s=s, use=use, b=b, t=t, first=(_k == 0)):
+                    for c in range(2):
+                        bufs[c][s].read(("ops", use))
+                        if first:
+                            acc[c][b].write(("acc", t), E)
+                def released(s=s):
+                    pass
+                yield ("async", "tensor", ran)
+                for c in range(2):     # one commit, delivered to both CTAs' barriers
+                    yield ("async", "tensor", to_cta(c, empty[c][s].arrive))
+                use += 1
+            for c in range(2):
+                yield ("async", "tensor", to_cta(c, tfull[c][b].arrive))
+        for t in range(tiles, tiles + 2):      # tail: both accumulators released by everybody
+            yield ("wait", tempty[t & 1], ((t >> 1) & 1) ^ 1)
+        done[0] += 1
+
+    def epilogue(c):
+        for t in range(tiles):
+            b = t & 1
+            yield ("wait", tfull[c][b], (t >> 1) & 1)
+            acc[c][b].read(("acc", t))
+            yield ("async", f"remote{c}", to_cta(0, tempty[b].arrive))
+        done[c] += 1
+
+    def cta_exit(c):
+        # __syncthreads, cluster barrier, free, cluster barrier: modelled as "both CTAs' roles done"
+        while done[0] < roles_per_cta[0] or done[1] < roles_per_cta[1]:
+            yield ("step",)
+        exited[c] = True
+
+    sim.add("producer0", producer(0))
+    sim.add("producer1", producer(1))
+    sim.add("mma", mma())
+    for c in range(2):
+        for i in range(E):
+            sim.add(f"epilogue{c}_{i}", epilogue(c))
+        sim.add(f"exit{c}", cta_exit(c))
+    sim.run()
+    # nothing may still be on its way once both CTAs are gone
+    assert not any(sim.queues.values()), "arrivals still in flight after both CTAs exited"

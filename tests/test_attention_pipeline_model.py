@@ -52,3 +52,25 @@ def test_gemm_epilogue_lookahead_never_overwrites_a_buffer_in_use():
     for pieces in (1, 2, 3, 4, 9, 16):
         for seed in range(60):
             M.gemm_epilogue_lookahead(seed, pieces)
+
+
+def test_cta_pair_gemm_protocol_survives_random_schedules():
+    """The barrier protocol of the CTA-pair GEMM (not built: it stopped making progress next to
+    other kernels on the GPU): no random schedule of loads, commits and remote arrivals deadlocks
+    it, aliases a phase, reuses a stage or an accumulator too early, or lets an arrival reach a
+    CTA that has exited. The search therefore does not explain the stall seen on the GPU, which
+    supports looking for it in the instructions that no wait limit bounds."""
+    for tiles, k_steps in ((1, 1), (1, 3), (2, 7), (3, 16), (5, 2)):
+        for seed in range(40):
+            M.pair_gemm(seed, tiles, k_steps)
+            M.pair_gemm(seed, tiles, k_steps, stages=2)
+
+
+def test_transaction_barrier_takes_bytes_before_the_expecting_arrival():
+    b = M.TxBarrier("full", 1)
+    b.complete_tx(1)                     # the partner's bytes land first
+    assert b.completed == 0
+    b.arrive_expect(2)
+    assert b.completed == 0              # own bytes still due
+    b.complete_tx(1)
+    assert b.completed == 1 and b.passed(0)
