@@ -518,3 +518,96 @@ def pair_gemm(seed: int, tiles: int, k_steps: int, stages: int = 6, epi_threads:
     sim.run()
     # nothing may still be on its way once both CTAs are gone
     assert not any(sim.queues.values()), "arrivals still in flight after both CTAs exited"
+
+
+# ---------------------------------------------------------------------------------------------
+# attention forward, two query tiles per CTA (csrc/attn_fwd_sm100.cu): one K / V ring shared by
+# two issuing warps (a stage returns to the producer after BOTH have committed it), tile 0 sees
+# one score block fewer than tile 1 on the causal diagonal.
+# ---------------------------------------------------------------------------------------------
+def forward_two_tiles(seed: int, blocks: int, ks: int = 3, vs: int = 3, softmax_threads: int = 2,
+                      p_single_buffer_wait_first: bool = False) -> None:
+    sim = Sim(seed)
+    ns = softmax_threads
+    B = lambda n, c=1: Barrier(n, c)
+    q_full = B("q_full")
+    k_full = [B(f"k_full{s}") for s in range(ks)]
+    k_empty = [B(f"k_empty{s}", 2) for s in range(ks)]
+    v_full = [B(f"v_full{s}") for s in range(vs)]
+    v_empty = [B(f"v_empty{s}", 2) for s in range(vs)]
+    s_full = [B(f"s_full{w}") for w in range(2)]
+    s_free = [B(f"s_free{w}", ns) for w in range(2)]
+    p_ready = [B(f"p_ready{w}", ns) for w in range(2)]
+    o_done = [B(f"o_done{w}") for w in range(2)]
+    K = [Resource(f"K{s}") for s in range(ks)]
+    V = [Resource(f"V{s}") for s in range(vs)]
+    S = [Resource(f"S{w}") for w in range(2)]
+    P = [Resource(f"P{w}") for w in range(2)]
+    n_total = blocks
+    nk = [blocks - 1, blocks]          # tile 0 skips the last block
+
+    def producer(which, full, empty, bufs, depth):
+        if which == "k":
+            yield ("async", "tma_q", q_full.arrive)
+        for j in range(n_total):
+            s = j % depth
+            yield ("wait", empty[s], ((j // depth) & 1) ^ 1)
+            readers = 2 if j < nk[0] else 1
+            def landed(s=s, j=j, readers=readers):
+                bufs[s].write((which, j), readers)
+                full[s].arrive()
+            yield ("async", "tma_" + which, landed)
+
+    def mma(w):
+        def issue_S(j):
+            def fn():
+                K[j % ks].read(("k", j))
+                S[w].write(("S", j), ns)
+                s_full[w].arrive()
+                k_empty[j % ks].arrive()
+            return ("async", "tensor", fn)
+        def issue_PV(j):
+            def fn():
+                P[w].read(("P", j))
+                V[j % vs].read(("v", j))
+                o_done[w].arrive()
+                v_empty[j % vs].arrive()
+            return ("async", "tensor", fn)
+        if nk[w] == 0:
+            return
+        yield ("wait", q_full, 0)
+        yield ("wait", k_full[0], 0)
+        yield issue_S(0)
+        for j in range(nk[w]):
+            if j + 1 < nk[w]:
+                yield ("wait", s_free[w], j & 1)
+                yield ("wait", k_full[(j + 1) % ks], ((j + 1) // ks) & 1)
+                yield issue_S(j + 1)
+            yield ("wait", v_full[j % vs], (j // vs) & 1)
+            yield ("wait", p_ready[w], j & 1)
+            yield issue_PV(j)
+        # (tile 0 never touches the last block and does not return that stage: it is the last
+        # load of the CTA, nobody waits for the stage again)
+
+    def softmax(w, lag):
+        for j in range(nk[w]):
+            for _ in range(int(sim.rng.random() * lag)):
+                yield ("step",)
+            yield ("wait", s_full[w], j & 1)
+            S[w].read(("S", j))
+            yield ("arrive", s_free[w])
+            if j > 0:
+                yield ("wait", o_done[w], (j - 1) & 1)
+            if P[w].tag != ("P", j):
+                P[w].write(("P", j), 1)
+            yield ("arrive", p_ready[w])
+        if nk[w]:
+            yield ("wait", o_done[w], (nk[w] - 1) & 1)
+
+    sim.add("producer_k", producer("k", k_full, k_empty, K, ks))
+    sim.add("producer_v", producer("v", v_full, v_empty, V, vs))
+    for w in range(2):
+        sim.add(f"mma{w}", mma(w))
+        for i in range(ns):
+            sim.add(f"softmax{w}_{i}", softmax(w, lag=0 if i else 5))
+    sim.run()

@@ -74,3 +74,12 @@ def test_transaction_barrier_takes_bytes_before_the_expecting_arrival():
     assert b.completed == 0              # own bytes still due
     b.complete_tx(1)
     assert b.completed == 1 and b.passed(0)
+
+
+@pytest.mark.parametrize("ks,vs", [(3, 3), (1, 1), (2, 1)])
+def test_forward_two_tile_pipeline_survives_random_schedules(ks, vs):
+    """Two query tiles sharing one K / V ring (a stage goes back after BOTH issuing warps have
+    committed it); the first tile sees one block fewer than the second."""
+    for blocks in (2, 3, 4, 9, 16):
+        for seed in range(40):
+            M.forward_two_tiles(seed, blocks, ks=ks, vs=vs)
