@@ -60,8 +60,9 @@ class Deadlock(AssertionError):
 
 
 class Sim:
-    """Roles yield ``("wait", barrier, parity)``, ``("arrive", barrier)``, ``("async", delay_rank,
-    fn)`` (fn runs later; asyncs of one ``delay_rank`` keep their order) or ``("step",)``."""
+    """Roles yield ``("wait", barrier, parity)``, ``("wait_fn", predicate, name)``, ``("arrive",
+    barrier)``, ``("async", delay_rank, fn)`` (fn runs later; asyncs of one ``delay_rank`` keep
+    their order) or ``("step",)``."""
 
     def __init__(self, seed: int):
         self.rng = random.Random(seed)
@@ -73,6 +74,16 @@ class Sim:
     def add(self, name: str, gen) -> None:
         self.roles.append((name, gen))
 
+    @staticmethod
+    def _free(entry) -> bool:
+        what, arg = entry
+        return what.passed(arg) if isinstance(what, Barrier) else what()
+
+    @staticmethod
+    def _describe(entry):
+        what, arg = entry
+        return (what.name, arg, what.completed) if isinstance(what, Barrier) else arg
+
     def run(self, limit: int = 2_000_000) -> None:
         alive = set(range(len(self.roles)))
         for _ in range(limit):
@@ -82,8 +93,7 @@ class Sim:
             if live_q and self.rng.random() < 0.35:
                 k = self.rng.choice(live_q)
                 self.queues[k].pop(0)()
-            runnable = [i for i in alive
-                        if i not in self.blocked or self.blocked[i][0].passed(self.blocked[i][1])]
+            runnable = [i for i in alive if i not in self.blocked or self._free(self.blocked[i])]
             if not runnable:
                 live_q = [k for k, q in self.queues.items() if q]
                 if live_q:
@@ -92,8 +102,7 @@ class Sim:
                     continue
                 if not alive:
                     return
-                waits = {self.roles[i][0]: (self.blocked[i][0].name, self.blocked[i][1],
-                                            self.blocked[i][0].completed) for i in alive}
+                waits = {self.roles[i][0]: self._describe(self.blocked[i]) for i in alive}
                 raise Deadlock(f"no role can run: {waits}")
             i = self.rng.choice(runnable)
             self.blocked.pop(i, None)
@@ -104,6 +113,9 @@ class Sim:
                 continue
             if req[0] == "wait":
                 if not req[1].passed(req[2]):
+                    self.blocked[i] = (req[1], req[2])
+            elif req[0] == "wait_fn":
+                if not req[1]():
                     self.blocked[i] = (req[1], req[2])
             elif req[0] == "arrive":
                 req[1].arrive()
@@ -610,4 +622,38 @@ def forward_two_tiles(seed: int, blocks: int, ks: int = 3, vs: int = 3, softmax_
         sim.add(f"mma{w}", mma(w))
         for i in range(ns):
             sim.add(f"softmax{w}_{i}", softmax(w, lag=0 if i else 5))
+    sim.run()
+
+
+# ---------------------------------------------------------------------------------------------
+# all-gather -> GEMM (csrc/gemm_tp_sm100.cu, mode 1): every CTA's copy warps bring one part of
+# one remote 128-row chunk into local memory and bump that chunk's counter; a CTA's TMA producer
+# may load a remote row block once its counter has reached the number of parts. CTAs therefore
+# wait for one another: the grid has to be resident as a whole. ``resident`` limits how many CTAs
+# run at a time (a CTA takes a slot when one is free and keeps it until it ends).
+# ---------------------------------------------------------------------------------------------
+def allgather_gemm(seed: int, ctas: int, chunks: int, tiles: int, resident: int) -> None:
+    sim = Sim(seed)
+    group = max(1, ctas // chunks)               # CTAs that share one chunk
+    ready = [0] * chunks
+    state = {"finished": 0}
+
+    def cta(i):
+        # CTAs are launched in order as SMs have room: CTA i starts once i - resident + 1 have ended
+        yield ("wait_fn", lambda: state["finished"] >= i - resident + 1, f"launch of CTA {i}")
+        # copy warps: this CTA's part of "its" chunk (at most one chunk per CTA, as in the kernel)
+        c = i // group
+        if c < chunks:
+            yield ("step",)
+            ready[c] += 1
+        # producer: tiles i, i + ctas, ...; local row blocks need no chunk, remote ones wait for theirs
+        for t in range(i, tiles, ctas):
+            need = t % (chunks + 1)              # 0: a local row block
+            if need:
+                yield ("wait_fn", lambda need=need: ready[need - 1] >= group, f"chunk {need - 1}")
+            yield ("step",)
+        state["finished"] += 1
+
+    for i in range(ctas):
+        sim.add(f"cta{i}", cta(i))
     sim.run()

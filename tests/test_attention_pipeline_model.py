@@ -83,3 +83,20 @@ def test_forward_two_tile_pipeline_survives_random_schedules(ks, vs):
     for blocks in (2, 3, 4, 9, 16):
         for seed in range(40):
             M.forward_two_tiles(seed, blocks, ks=ks, vs=vs)
+
+
+def test_allgather_gemm_needs_the_whole_grid_resident():
+    """The all-gather -> GEMM kernel's CTAs wait for chunks that other CTAs of the same grid copy:
+    with every CTA resident the grid always drains; when fewer CTAs can run than the grid has, the
+    resident ones end up waiting for a CTA that cannot start (on the GPU: the bounded wait runs
+    out and reports a status). The host side therefore refuses a grid that the device cannot
+    hold (``tp_grid_fits`` in csrc/gemm_tp_sm100.cu)."""
+    for seed in range(20):
+        M.allgather_gemm(seed, ctas=12, chunks=4, tiles=60, resident=12)
+    stuck = 0
+    for seed in range(20):
+        try:
+            M.allgather_gemm(seed, ctas=12, chunks=4, tiles=60, resident=5)
+        except M.Deadlock:
+            stuck += 1
+    assert stuck == 20
