@@ -201,3 +201,26 @@ def test_fused_fc2_dgrad_swiglu_backward_front_ends_agree():
     sig = torch.sigmoid(g)
     closed = torch.cat([da * sig * (1 + g * (1 - sig)) * u, da * g * sig], dim=1)
     assert torch.allclose(ref, closed, rtol=1e-5, atol=1e-6)
+
+
+def test_weight_gradient_stream_switch_is_inert_on_cpu_and_off_for_fused_tensor_parallelism():
+    """``wgrad_side_stream`` defaults to on; the trainer only creates the stream on a CUDA device,
+    outside graph modes, serial-stream mode and fused tensor parallelism, and without a stream the
+    model's weight-gradient helper is the in-line call."""
+    from forgetrain_b200.engine_config import from_spec
+    from forgetrain_b200.parallel.topology import Topology
+    from forgetrain_b200.trainer import Trainer
+    spec = load_model_spec("tiny", num_layers=2, vocab_size=256, hidden_size=128, ffn_hidden_size=256,
+                           num_attention_heads=4, num_query_groups=2, head_dim=32, seq_length=32,
+                           max_position_embeddings=32)
+    cfg = from_spec(spec, dtype="fp32", comm="nccl")
+    assert cfg.wgrad_side_stream is True
+    tr = Trainer(spec, cfg, Topology(device=torch.device("cpu")), seq_length=32, micro_batch_size=2, seed=0)
+    assert tr.model.wgrad_stream is None and tr.model._wgrad_done == {}
+    g = torch.Generator().manual_seed(0)
+    c = torch.randint(0, 256, (2, 33), generator=g)
+    batch = {"tokens": c[:, :-1].contiguous(), "labels": c[:, 1:].contiguous(),
+             "loss_mask": torch.ones(2, 32)}
+    l0 = float(tr.train_step([batch])["loss"])
+    l1 = float(tr.train_step([batch])["loss"])
+    assert l0 == l0 and l1 == l1 and tr.model._wgrad_done == {}
