@@ -36,6 +36,14 @@ def _as_i32(e: int) -> int:
     return e - (1 << 32) if e & 0x80000000 else e
 
 
+def bump_epoch(e: int) -> int:
+    """The epoch after ``e``. Full 32-bit counters: the device compares
+    ``(int32)(flag - epoch) >= 0``, which is wrap-safe only when host and device count
+    modulo 2^32 alike (a counter that wrapped at 2^31 would find the stale flag already
+    "ahead" and pass every wait on that slot without waiting)."""
+    return (e + 1) & 0xFFFFFFFF
+
+
 class SymmetricBuffers:
     """Symmetric allocations shared by the ranks of one process group."""
 
@@ -91,9 +99,7 @@ class SymmetricBuffers:
         if self._graph_mode:
             raise RuntimeError("peer-memory collectives were captured in a CUDA graph; call "
                                "resync_epochs() before launching them eagerly again")
-        # full 32-bit counters: the device compares (int32)(flag - epoch) >= 0, which is only
-        # wrap-safe when host and device count modulo 2^32 alike
-        self.epoch[slot] = (self.epoch[slot] + 1) & 0xFFFFFFFF
+        self.epoch[slot] = bump_epoch(self.epoch[slot])
         return self.epoch[slot]
 
     def set_epoch(self, slot: int, value: int) -> None:

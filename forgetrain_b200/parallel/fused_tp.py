@@ -25,6 +25,7 @@ import torch.distributed as dist
 
 from ..ops import _lib
 from .tp import TPContext
+from .fused_dp import bump_epoch
 
 c_int, c_float, c_uint, c_ull = ctypes.c_int, ctypes.c_float, ctypes.c_uint, ctypes.c_ulonglong
 
@@ -112,7 +113,7 @@ class FusedTPContext(TPContext):
         base = slot * self.T * self.H * 2
         VP = ctypes.c_void_p * self.size
         a_peers = VP(*[p + base for p in self.pool_ptrs])
-        self.epoch_ag = (self.epoch_ag + 1) & 0x7FFFFFFF
+        self.epoch_ag = bump_epoch(self.epoch_ag)
         rc = _lib.lib().ft_gemm_ag(a_peers, _lib.ptr(w), _lib.ptr(out), c_int(M), c_int(N), c_int(K),
                                    c_int(w.stride(0)), c_int(out.stride(0)), c_int(int(b_mn)),
                                    c_float(alpha), c_int(self.size), c_int(self.rank), self.p_flags,
@@ -148,7 +149,7 @@ class FusedTPContext(TPContext):
         base = half * self.T * self.H * 2
         VP = ctypes.c_void_p * self.size
         d_peers = VP(*[p + base for p in self.part_ptrs])
-        self.epoch_rs = (self.epoch_rs + 1) & 0x7FFFFFFF
+        self.epoch_rs = bump_epoch(self.epoch_rs)
         rc = _lib.lib().ft_gemm_rs(_lib.ptr(x), _lib.ptr(w), d_peers, c_int(M), c_int(N), c_int(K),
                                    c_int(x.stride(0)), c_int(w.stride(0)), c_int(int(b_mn)),
                                    c_float(alpha), c_int(self.size), c_int(self.rank), self.p_flags,
@@ -182,7 +183,7 @@ class FusedTPContext(TPContext):
     def ce_exchange(self, T: int, mask, combined: torch.Tensor, row_loss: torch.Tensor) -> None:
         """One kernel: entry barrier, peer loads of every rank's statistics, combination,
         masked row loss, exit barrier."""
-        self.epoch_ce = (self.epoch_ce + 1) & 0x7FFFFFFF
+        self.epoch_ce = bump_epoch(self.epoch_ce)
         rc = _lib.lib().ft_ce_stats_exchange(
             self.p_ce, self.p_flags, c_int(self.rank), c_int(self.size), ctypes.c_long(0), c_int(T),
             _lib.ptr(mask), _lib.ptr(combined), _lib.ptr(row_loss), c_uint(self.epoch_ce),

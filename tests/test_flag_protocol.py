@@ -101,14 +101,14 @@ def test_host_side_epoch_counter_wraps_modulo_two_to_the_32():
     and the value read back after graph replays all count modulo 2^32, like the device's
     signed-difference comparison: crossing 2^31 or 2^32 never yields an epoch that a stale flag
     already satisfies."""
-    from forgetrain_b200.parallel.fused_dp import _as_i32
+    from forgetrain_b200.parallel.fused_dp import _as_i32, bump_epoch
     world = 2
     boards = FlagBoards(world)
     for start in (0x7FFFFFFE, 0xFFFFFFFE):
         epoch = start
         boards.flags[:] = start                      # what earlier launches left behind
-        for _ in range(4):                           # host: (epoch + 1) & 0xFFFFFFFF
-            epoch = (epoch + 1) & 0xFFFFFFFF
+        for _ in range(4):                           # the host's own increment
+            epoch = bump_epoch(epoch)
             # before anyone signals, the stale flags must NOT pass for the new epoch
             assert boards.wait(0, 0, epoch, limit_s=0.005) is False
             boards.status = [0] * world
@@ -119,3 +119,22 @@ def test_host_side_epoch_counter_wraps_modulo_two_to_the_32():
             # the device base travels through an int32 tensor and back without losing bits
             assert (_as_i32(epoch) & 0xFFFFFFFF) == epoch and -(1 << 31) <= _as_i32(epoch) < (1 << 31)
         assert boards.status == [0, 0]
+
+
+def test_every_host_epoch_counter_uses_the_shared_increment():
+    """The data-parallel and the tensor-parallel collectives keep separate counters; both must
+    step them with ``bump_epoch`` (a private ``& 0x7FFFFFFF`` in one of them would break the
+    wrap-around guarantee checked above)."""
+    import inspect
+    import re
+    from forgetrain_b200.parallel import fused_dp, fused_tp
+    assert fused_dp.bump_epoch(0x7FFFFFFF) == 0x80000000
+    assert fused_dp.bump_epoch(0xFFFFFFFF) == 0
+    for mod in (fused_dp, fused_tp):
+        src = inspect.getsource(mod)
+        assert "0x7FFFFFFF" not in src
+        # every assignment to an epoch counter goes through the helper
+        for m in re.finditer(r"self\.epoch(?:_[a-z]+|\[slot\]) = (.+)", src):
+            rhs = m.group(1)
+            assert "+ 1" not in rhs or "bump_epoch" in rhs, rhs
+    assert len(re.findall(r"bump_epoch\(self\.epoch_", inspect.getsource(fused_tp))) == 3
