@@ -1,6 +1,8 @@
-"""Host model of the mbarrier pipelines of the attention kernels (csrc/attn_bwd_kv_sm100.cu,
-csrc/attn_bwd_kv128_sm100.cu, csrc/attn_fwd1_sm100.cu): which role waits on which barrier with
-which parity, who arrives, and which resources (TMEM columns, shared-memory buffers) a barrier
+"""Host model of the mbarrier pipelines of the tensor-core kernels (attention:
+csrc/attn_bwd_kv_sm100.cu, csrc/attn_bwd_kv128_sm100.cu, csrc/attn_fwd1_sm100.cu,
+csrc/attn_fwd_sm100.cu; GEMM: csrc/gemm_sm100.cu; tensor-parallel GEMM + collective:
+csrc/gemm_tp_sm100.cu): which role waits on which barrier with which parity, who arrives, and
+which resources (TMEM columns, shared-memory buffers, peer-memory planes) a barrier or flag
 guards. The model exists to search the protocols for two classes of design errors without a GPU:
 
 * deadlock, including the "phase aliasing" kind: an mbarrier only knows the parity of its current
@@ -70,6 +72,7 @@ class Sim:
         self.blocked: dict[int, tuple[Barrier, int]] = {}
         self.queues: dict[object, list] = {}     # per issuing engine: FIFO of pending completions
         self.now = 0
+        self.slow_prefix: str | None = None      # queues of this name prefix deliver reluctantly
 
     def add(self, name: str, gen) -> None:
         self.roles.append((name, gen))
@@ -90,6 +93,9 @@ class Sim:
             self.now += 1
             # deliver the head of a random engine queue now and then
             live_q = [k for k, q in self.queues.items() if q]
+            if self.slow_prefix is not None:      # an adversarial schedule: these come as late as possible
+                live_q = [k for k in live_q if not (isinstance(k, str) and k.startswith(self.slow_prefix)
+                                                    and self.rng.random() < 0.95)]
             if live_q and self.rng.random() < 0.35:
                 k = self.rng.choice(live_q)
                 self.queues[k].pop(0)()
@@ -656,4 +662,180 @@ def allgather_gemm(seed: int, ctas: int, chunks: int, tiles: int, resident: int)
 
     for i in range(ctas):
         sim.add(f"cta{i}", cta(i))
+    sim.run()
+
+
+# ---------------------------------------------------------------------------------------------
+# single-CTA GEMM (csrc/gemm_sm100.cu, gemm_bf16_kernel): two producer warps that take the
+# stages of their own parity, one issuing warp, epilogue warps that drain one of two TMEM
+# accumulators. Work items have different numbers of K steps (split-K pieces) and byte counts
+# (half tiles load half of the B boxes). A barrier arrival of the tensor pipe must not reach the
+# CTA after it has exited, which is what the producers' tail waits are for.
+# ---------------------------------------------------------------------------------------------
+def gemm_single_cta(seed: int, k_steps: list[int], stages: int = 4, epi_threads: int = 4,
+                    halves: set[int] = frozenset(), producer_tail: bool = True,
+                    tempty_count: int | None = None, arrival_skew: bool = False) -> None:
+    """``arrival_skew``: commits still complete in issue order, but the arrival that a commit sends
+    to a stage barrier is delivered after a delay of its own, as late as the schedule allows (it may
+    be overtaken by the arrival of a later commit at an accumulator barrier)."""
+    sim = Sim(seed)
+    sim.slow_prefix = "late_"
+    E = epi_threads
+    full = [TxBarrier(f"full{s}", 1) for s in range(stages)]
+    empty = [Barrier(f"empty{s}", 1) for s in range(stages)]
+    tfull = [Barrier(f"tfull{b}", 1) for b in range(2)]
+    tempty = [Barrier(f"tempty{b}", tempty_count or E) for b in range(2)]
+    bufs = [Resource(f"stage{s}") for s in range(stages)]
+    acc = [Resource(f"acc{b}") for b in range(2)]
+    state = {"done": 0, "exited": False}
+    n_roles = 2 + 1 + E
+
+    def guarded(bar):
+        def deliver():
+            assert not state["exited"], "a tensor-pipe arrival reached the CTA after it had exited"
+            bar.arrive()
+        if not arrival_skew or not bar.name.startswith("empty"):
+            return deliver
+        return lambda: sim.queues.setdefault(f"late_{bar.name}", []).append(deliver)
+
+    def producer(pid):
+        use = 0
+        for t, kn in enumerate(k_steps):
+            boxes = 2 if t in halves else 3          # A + half of B, or A + both B boxes
+            for _k in range(kn):
+                s = use % stages
+                if (s & 1) == pid:
+                    yield ("wait", empty[s], ((use // stages) & 1) ^ 1)
+                    full[s].arrive_expect(boxes)
+                    bufs[s].write(("ops", use), 1)   # the stage is the producer's from here on
+                    for j in range(boxes):           # one box per lane, each its own copy
+                        yield ("async", f"tma{pid}_{j}", lambda s=s: full[s].complete_tx(1))
+                use += 1
+        if producer_tail:
+            for _ in range(stages):
+                s = use % stages
+                if (s & 1) == pid:
+                    yield ("wait", empty[s], ((use // stages) & 1) ^ 1)
+                use += 1
+        state["done"] += 1
+
+    def mma():
+        use = 0
+        for t, kn in enumerate(k_steps):
+            b = t & 1
+            yield ("wait", tempty[b], ((t >> 1) & 1) ^ 1)
+            for k in range(kn):
+                s = use % stages
+                yield ("wait", full[s], (use // stages) & 1)
+
+                def ran(s=s, use=use, b=b, t=t, first=(k == 0)):
+                    bufs[s].read(("ops", use))
+                    if first:
+                        acc[b].write(("acc", t), E)
+                yield ("async", "tensor", ran)
+                yield ("async", "tensor", guarded(empty[s]))
+                use += 1
+            yield ("async", "tensor", guarded(tfull[b]))
+        state["done"] += 1
+
+    def epilogue():
+        for t in range(len(k_steps)):
+            b = t & 1
+            yield ("wait", tfull[b], (t >> 1) & 1)
+            acc[b].read(("acc", t))
+            yield ("arrive", tempty[b])
+        state["done"] += 1
+
+    def cta_exit():
+        yield ("wait_fn", lambda: state["done"] >= n_roles, "every role of the CTA")
+        state["exited"] = True
+
+    sim.add("producer0", producer(0))
+    sim.add("producer1", producer(1))
+    sim.add("mma", mma())
+    for i in range(E):
+        sim.add(f"epilogue{i}", epilogue())
+    sim.add("exit", cta_exit())
+    sim.run()
+    assert not any(sim.queues.values()), "arrivals still in flight after the CTA exited"
+
+
+# ---------------------------------------------------------------------------------------------
+# Streams of tensor-parallel launches over several ranks (csrc/gemm_tp_sm100.cu with
+# parallel/fused_tp.py). A rank is one role: its launches run one after the other, like kernels
+# of one stream. Stores into a peer's memory land later, in issue order per source rank (the
+# kernel fences them before it releases its flag); a flag release travels on the same queue when
+# ``fenced`` and overtakes the stores otherwise.
+# ---------------------------------------------------------------------------------------------
+def gemm_reduce_scatter_stream(seed: int, world: int, launches: int, planes: int = 2,
+                               exit_barrier: bool = True, fenced: bool = True) -> None:
+    """GEMM -> reduce-scatter: rank r stores its partial tiles into plane r of every owner (the
+    plane set alternates between ``planes`` halves), the ranks meet in the exit barrier, and each
+    owner's next kernel sums its planes."""
+    sim = Sim(seed)
+    plane = [[[Resource(f"plane[{o}][{h}][{s}]") for s in range(world)] for h in range(planes)]
+             for o in range(world)]
+    flag = [[0] * world for _ in range(world)]        # flag[dst][src]: last epoch signalled
+
+    def rank(r):
+        for n in range(1, launches + 1):
+            h = n % planes
+            for o in range(world):                    # remote owners first, as the kernel does
+                o = (r + 1 + o) % world
+                yield ("async", f"stores{r}", lambda o=o, h=h, n=n: plane[o][h][r].write(n, 1))
+            if exit_barrier:
+                for d in range(world):
+                    if d != r:
+                        def signal(d=d, n=n):
+                            flag[d][r] = n
+                        yield ("async", f"stores{r}" if fenced else f"flags{r}", signal)
+                for s in range(world):
+                    if s != r:
+                        yield ("wait_fn", lambda s=s, n=n: flag[r][s] >= n, f"rank {r}: exit flag of {s}")
+                # own stores: complete when the kernel ends (bulk-store wait before the barrier)
+                yield ("wait_fn", lambda: not sim.queues.get(f"stores{r}"), f"rank {r}: own stores")
+            yield ("step",)
+            for s in range(world):                    # the sum kernel that follows on the stream
+                plane[r][h][s].read(n)
+                yield ("step",)
+
+    for r in range(world):
+        sim.add(f"rank{r}", rank(r))
+    sim.run()
+
+
+def allgather_gemm_stream(seed: int, world: int, launches: int, exit_barrier: bool = True) -> None:
+    """All-gather -> GEMM: before launch n every rank has written its own slot; the kernel tells the
+    peers so, pulls their slots once they have said the same, and leaves through the exit barrier
+    ("I no longer read your slot"), after which the stream's next producer may overwrite the slot."""
+    sim = Sim(seed)
+    slot = [Resource(f"slot{r}") for r in range(world)]
+    ready = [[0] * world for _ in range(world)]       # ready[dst][src]
+    done = [[0] * world for _ in range(world)]
+
+    def rank(r):
+        for n in range(1, launches + 1):
+            slot[r].write(n, world - 1)               # the producer kernel before the launch
+            yield ("step",)
+            for d in range(world):
+                if d != r:
+                    ready[d][r] = n
+            for s in range(world):
+                s = (r + 1 + s) % world
+                if s == r:
+                    continue
+                yield ("wait_fn", lambda s=s, n=n: ready[r][s] >= n, f"rank {r}: slot of {s}")
+                yield ("step",)
+                slot[s].read(n)
+            if exit_barrier:
+                for d in range(world):
+                    if d != r:
+                        done[d][r] = n
+                for s in range(world):
+                    if s != r:
+                        yield ("wait_fn", lambda s=s, n=n: done[r][s] >= n, f"rank {r}: exit flag of {s}")
+            yield ("step",)
+
+    for r in range(world):
+        sim.add(f"rank{r}", rank(r))
     sim.run()

@@ -100,3 +100,74 @@ def test_allgather_gemm_needs_the_whole_grid_resident():
         except M.Deadlock:
             stuck += 1
     assert stuck == 20
+
+
+@pytest.mark.parametrize("stages", [3, 4, 6])
+def test_single_cta_gemm_pipeline_survives_random_schedules(stages):
+    """Work items of different length (split-K pieces of 1 to 9 K steps, half tiles with fewer
+    bytes per stage), odd and even stage counts (the two producers take stages by parity)."""
+    import random
+    for seed in range(40):
+        rng = random.Random(seed)
+        ks = [rng.randint(1, 9) for _ in range(rng.randint(1, 7))]
+        halves = {t for t in range(len(ks)) if rng.random() < 0.3}
+        M.gemm_single_cta(seed, ks, stages=stages, halves=halves)
+    M.gemm_single_cta(0, [], stages=stages)                     # a CTA without work
+
+
+def test_the_gemm_model_sees_what_the_producer_tail_is_for():
+    """While barrier arrivals are delivered in the order of their commits, the epilogue's wait for
+    the last accumulator covers every earlier stage release and the producers' closing waits are
+    redundant. Once an arrival may lag behind a later one, a CTA without those waits can leave
+    while a stage release is still on its way to its shared memory; with them it cannot. A release
+    barrier that expects more epilogue arrivals than there are warps never opens."""
+    for seed in range(40):
+        M.gemm_single_cta(seed, [2, 3, 1], stages=4, producer_tail=False)
+        M.gemm_single_cta(seed, [2, 3, 1], stages=4, producer_tail=True, arrival_skew=True)
+    late = 0
+    for seed in range(40):
+        try:
+            M.gemm_single_cta(seed, [2, 3, 1], stages=4, producer_tail=False, arrival_skew=True)
+        except AssertionError as e:
+            assert "after it had exited" in str(e) or "still in flight" in str(e)
+            late += 1
+    assert late > 0
+    with pytest.raises(M.Deadlock):
+        M.gemm_single_cta(0, [2, 2, 2, 2], stages=4, epi_threads=4, tempty_count=5)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_reduce_scatter_planes_are_never_overwritten_before_they_are_summed(world):
+    for seed in range(25):
+        M.gemm_reduce_scatter_stream(seed, world, launches=6)
+
+
+def test_the_reduce_scatter_model_sees_why_there_are_two_plane_sets_a_barrier_and_a_fence():
+    """One plane set: a fast peer's next launch overwrites a plane that the owner has not summed yet.
+    No exit barrier: the owner sums a plane that has not arrived. A flag that overtakes the stores
+    (no fence before the release): the same. Each is found within a few seeds."""
+    def fails(**kw):
+        n = 0
+        for seed in range(40):
+            try:
+                M.gemm_reduce_scatter_stream(seed, 4, launches=6, **kw)
+            except AssertionError:
+                n += 1
+        return n
+    assert fails(planes=1) > 0
+    assert fails(exit_barrier=False) > 0
+    assert fails(fenced=False) > 0
+    assert fails() == 0
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_gathered_slots_are_rewritten_only_after_every_peer_has_read_them(world):
+    for seed in range(25):
+        M.allgather_gemm_stream(seed, world, launches=6)
+    broken = 0
+    for seed in range(40):
+        try:
+            M.allgather_gemm_stream(seed, world, launches=6, exit_barrier=False)
+        except AssertionError:
+            broken += 1
+    assert broken > 0
