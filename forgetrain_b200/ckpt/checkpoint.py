@@ -108,12 +108,25 @@ def save_checkpoint(save_dir: str | os.PathLike, step: int, *, params: dict, par
     return path
 
 
+def latest_step_dir(root: str | os.PathLike, pattern: str = "training_state.pt") -> Path | None:
+    """The ``step_<N>`` directory under ``root`` with the largest N that holds a finished file
+    matching ``pattern``. By step NUMBER: names are zero-padded to 7 digits, so a plain sort
+    would put step 10,000,000 before step 9,999,999; directories in which the writer never got
+    to its rename are not resume points."""
+    cands = []
+    for p in Path(root).glob("step_*"):
+        num = p.name[len("step_"):]
+        if num.isdigit() and any(p.glob(pattern)):
+            cands.append((int(num), p))
+    return max(cands)[1] if cands else None
+
+
 def latest_checkpoint(root: str | os.PathLike) -> Path | None:
     root = Path(root)
     if (root / "training_state.pt").exists():
         return root / "training_state.pt"
-    cands = sorted(p for p in root.glob("step_*") if (p / "training_state.pt").exists())
-    return cands[-1] / "training_state.pt" if cands else None
+    d = latest_step_dir(root)
+    return d / "training_state.pt" if d is not None else None
 
 
 def load_resume_checkpoint(path: str | os.PathLike, expected_vocab: int | None = None) -> dict:

@@ -401,9 +401,8 @@ class Trainer:
                 self.opt.sync_master_from_params()
             return {"step": 0, "num_samples": self.num_samples, "dataloader_state": None}
         if p.is_dir() and not any(p.glob("rank_*.pt")) and not (p / "training_state.pt").exists():
-            cands = sorted(q for q in p.glob("step_*") if any(q.glob("rank_*.pt")))
-            if cands:
-                p = cands[-1]
+            from .ckpt.checkpoint import latest_step_dir
+            p = latest_step_dir(p, "rank_*.pt") or p
         rank_files = sorted(p.glob("rank_*.pt"), key=lambda q: int(q.stem.split("_")[1])) \
             if p.is_dir() else []
         tp, tpr = self.topo.tp_size, self.topo.tp_rank
