@@ -129,6 +129,11 @@ _ENV_MAP: dict[str, tuple[str, Callable[[str], Any]]] = {
     "LR_WARMUP_ITERS": ("warmup_iters", int),
     "LR_WSD_DECAY_ITERS": ("wsd_decay_iters", int),
     "CLIP_GRAD": ("max_grad_norm", float),
+    # the reference's whole-step graph has settings of its own; here both graphs share one set
+    # (listed before the native names, so those win when both are given)
+    "STEP_CUDA_GRAPH_FULL_WARMUP": ("step_cuda_graph_warmup", int),
+    "STEP_CUDA_GRAPH_FULL_TOL": ("step_cuda_graph_tol", float),
+    "STEP_CUDA_GRAPH_FULL_SANITY": ("step_cuda_graph_sanity", lambda v: v.lower() in _BOOL_TRUE),
     "STEP_CUDA_GRAPH_WARMUP": ("step_cuda_graph_warmup", int),
     "STEP_CUDA_GRAPH_TOL": ("step_cuda_graph_tol", float),
     "STEP_CUDA_GRAPH_SANITY": ("step_cuda_graph_sanity", lambda v: v.lower() in _BOOL_TRUE),
@@ -176,6 +181,10 @@ LEGACY_FIELD_ALIASES: dict[str, tuple[str, Callable[[Any], Any]]] = {
     "lr_wsd_decay_iters": ("wsd_decay_iters", int),
     "clip_grad": ("max_grad_norm", float),
     "step_cuda_graph_full": ("full_step_cuda_graph", bool),
+    # the whole-step graph shares the compute-step graph's warm-up / sanity settings here
+    "step_cuda_graph_full_warmup": ("step_cuda_graph_warmup", int),
+    "step_cuda_graph_full_tol": ("step_cuda_graph_tol", float),
+    "step_cuda_graph_full_sanity": ("step_cuda_graph_sanity", bool),
     "fp32_mode": ("dtype", lambda on: "fp32" if on else "bf16"),
 }
 
@@ -189,6 +198,7 @@ LEGACY_NOOP_FIELDS = frozenset({
     "te_rope", "fp32_allreduce", "fp32_grad_accum", "accum_stream_overlap", "multi_tensor_adam",
     "custom_gemm", "use_fused_norm_bwd", "norm_bwd_nan_diag", "step_cuda_graph_accum",
     "step_cuda_graph_reducer", "step_cuda_graph_nccl_opt", "step_cuda_graph_optimizer",
+    "step_cuda_graph_nccl_opt_warmup", "step_cuda_graph_optimizer_warmup",
     "forward_cuda_graph_warmup", "forward_cuda_graph_tol", "forward_cuda_graph_sanity",
     "forward_cuda_graph_sample_stride",
     "fused_rope", "fused_rope_pack", "fused_residual_rmsnorm", "fused_rope_qkv",

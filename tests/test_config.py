@@ -97,6 +97,39 @@ def test_legacy_field_names_translate_or_drop():
     assert (env.max_grad_norm, env.full_step_cuda_graph, env.warmup_iters) == (2.0, True, 7)
 
 
+# every field name of the reference's two EngineConfig classes (0.5B engine_config.py:132-277,
+# 8B engine_config.py:107-192): the names are the contract a config written for it relies on
+_REFERENCE_FIELDS_05B = """fused_ops fuse_ce fuse_swiglu fuse_rmsnorm_residual fuse_rope fuse_rope_doc_aware
+fuse_adam_sync fuse_gemm_pad fuse_direct_attn fuse_inplace_residual fuse_index_add_emb_bwd use_span_based_attn
+fp32_mode unfused_mode te_rope fp32_allreduce fp32_grad_accum accum_stream_overlap multi_tensor_adam custom_gemm
+forward_cuda_graph_warmup forward_cuda_graph_tol forward_cuda_graph_sanity forward_cuda_graph_sample_stride
+step_cuda_graph_accum step_cuda_graph_reducer step_cuda_graph_full step_cuda_graph_full_warmup
+step_cuda_graph_full_tol step_cuda_graph_full_sanity step_cuda_graph_nccl_opt step_cuda_graph_nccl_opt_warmup
+step_cuda_graph_optimizer step_cuda_graph_optimizer_warmup use_fused_norm_bwd norm_bwd_nan_diag vocab_size""".split()
+_REFERENCE_FIELDS_8B = """fused_rope fused_rope_pack fused_residual_rmsnorm fused_rope_qkv fused_attn_rmsnorm_bwd
+fused_mlp_residual_rmsnorm fused_dw_reduce fused_rope_fp32cos ag_fwd_overlap adam_ag_pipeline gpu_norm_clip
+fused_ce defer_wgrad_sync fused_swiglu dw_reduce_rows_per_block direct_attn dsl_attn_fwd rope_bhsd custom_gemm
+padded_vocab_size lr_warmup_iters lr_wsd_decay_iters clip_grad""".split()
+
+
+def test_every_field_name_of_the_reference_that_is_not_a_field_here_is_translated_or_dropped():
+    import dataclasses
+    own = {f.name for f in dataclasses.fields(ec.EngineConfig)}
+    for name in _REFERENCE_FIELDS_05B + _REFERENCE_FIELDS_8B:
+        assert name not in own
+        assert (name in ec.LEGACY_FIELD_ALIASES) != (name in ec.LEGACY_NOOP_FIELDS), name
+    cfg, dropped = ec.from_legacy({"step_cuda_graph_full_warmup": 5, "step_cuda_graph_full_tol": 0.25,
+                                   "step_cuda_graph_full_sanity": False,
+                                   "step_cuda_graph_optimizer_warmup": 3})
+    assert (cfg.step_cuda_graph_warmup, cfg.step_cuda_graph_tol, cfg.step_cuda_graph_sanity) == (5, 0.25, False)
+    assert dropped == ["step_cuda_graph_optimizer_warmup"]
+    env = ec.from_env({"STEP_CUDA_GRAPH_FULL_WARMUP": "7", "STEP_CUDA_GRAPH_FULL_TOL": "0.5",
+                       "STEP_CUDA_GRAPH_FULL_SANITY": "0"})
+    assert (env.step_cuda_graph_warmup, env.step_cuda_graph_tol, env.step_cuda_graph_sanity) == (7, 0.5, False)
+    both = ec.from_env({"STEP_CUDA_GRAPH_FULL_WARMUP": "7", "STEP_CUDA_GRAPH_WARMUP": "2"})
+    assert both.step_cuda_graph_warmup == 2
+
+
 def test_cli_accepts_reference_spellings(capsys):
     from forgetrain_b200.cli import build_parser
     a = build_parser().parse_args(["pretrain", "--clip-grad", "0.25", "--lr-warmup-iters", "5",
