@@ -66,6 +66,8 @@ def init_topology(tp_size: int = 1, device: str | None = None, backend: str | No
     topo = Topology(rank=rank, world=world, local_rank=local_rank, tp_size=tp_size,
                     dp_size=world // tp_size, tp_rank=rank % tp_size, dp_rank=rank // tp_size,
                     device=dev, backend=backend if world > 1 else "none")
+    global _current
+    _current = topo
     if world == 1:
         return topo
     if not dist.is_initialized():
@@ -100,5 +102,72 @@ def init_topology(tp_size: int = 1, device: str | None = None, backend: str | No
 
 
 def shutdown() -> None:
+    global _current
+    _current = None
     if dist.is_available() and dist.is_initialized():
         dist.destroy_process_group()
+
+
+# -----------------------------------------------------------------------------------------
+# The process's topology as module-level accessors, for code that does not carry the object
+# around (the reference's nccl modules offer the same: 0.5B nccl.py:61-76, 8B nccl.py:77-104).
+# Before ``init_topology`` they describe a single process.
+# -----------------------------------------------------------------------------------------
+_current: Topology | None = None
+
+
+def current() -> Topology:
+    return _current if _current is not None else Topology()
+
+
+def is_distributed() -> bool:
+    return current().world > 1
+
+
+def get_rank() -> int:
+    return current().rank
+
+
+def get_world_size() -> int:
+    return current().world
+
+
+def get_dp_group():
+    return current().dp_group
+
+
+def get_dp_rank() -> int:
+    return current().dp_rank
+
+
+def get_dp_size() -> int:
+    return current().dp_size
+
+
+def get_tp_group():
+    return current().tp_group
+
+
+def get_tp_rank() -> int:
+    return current().tp_rank
+
+
+def get_tp_size() -> int:
+    return current().tp_size
+
+
+def barrier() -> None:
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+
+
+def allreduce_loss(local_loss: torch.Tensor, dp_group=None, dp_size: int | None = None) -> float:
+    """Mean of a scalar loss over the data-parallel ranks, in place; returns it as a float (a
+    host synchronisation). Defaults to the current topology's data-parallel group."""
+    topo = current()
+    n = topo.dp_size if dp_size is None else dp_size
+    if n > 1:
+        dist.all_reduce(local_loss, op=dist.ReduceOp.SUM,
+                        group=topo.dp_group if dp_group is None else dp_group)
+        local_loss.div_(n)
+    return float(local_loss)

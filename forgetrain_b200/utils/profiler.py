@@ -18,9 +18,47 @@ from pathlib import Path
 
 import torch
 
-SEGMENTS = ("step_start", "microbatches", "reduce_scatter", "grad_norm", "optimizer",
-            "loss_allreduce", "allgather")
-DEEP_SEGMENTS = ("mb_data", "mb_fwd", "mb_ce", "mb_bwd", "mb_accum")
+# closing-mark names of the main loop and of a micro-batch in deep mode (the reference's
+# SEG_* / DEEP_PHASE_* constants, profiling.py:180-204)
+SEG_STEP_START, SEG_MICROBATCHES, SEG_REDUCE_SCATTER = "step_start", "microbatches", "reduce_scatter"
+SEG_GRAD_NORM, SEG_OPTIMIZER, SEG_LOSS_ALLREDUCE, SEG_ALLGATHER = \
+    "grad_norm", "optimizer", "loss_allreduce", "allgather"
+DEEP_PHASE_DATA, DEEP_PHASE_FWD, DEEP_PHASE_CE, DEEP_PHASE_BWD, DEEP_PHASE_ACCUM = \
+    "mb_data", "mb_fwd", "mb_ce", "mb_bwd", "mb_accum"
+SEGMENTS = (SEG_STEP_START, SEG_MICROBATCHES, SEG_REDUCE_SCATTER, SEG_GRAD_NORM, SEG_OPTIMIZER,
+            SEG_LOSS_ALLREDUCE, SEG_ALLGATHER)
+DEEP_SEGMENTS = DEEP_PHASE_ORDER = (DEEP_PHASE_DATA, DEEP_PHASE_FWD, DEEP_PHASE_CE, DEEP_PHASE_BWD,
+                                    DEEP_PHASE_ACCUM)
+
+
+def _bucket_summary(records: list[dict], key: str, total_key: str | None = None) -> dict:
+    names: dict[str, list[float]] = {}
+    for r in records:
+        for k, v in (r.get(key) or {}).items():
+            names.setdefault(k, []).append(v)
+        if total_key is not None and total_key in r:
+            names.setdefault("total", []).append(r[total_key])
+    out = {}
+    for k, vals in names.items():
+        s = sorted(vals)
+        out[k] = {"n": len(s), "mean": statistics.fmean(s), "median": statistics.median(s),
+                  "p90": s[min(len(s) - 1, int(0.9 * len(s)))],
+                  "std": statistics.pstdev(s) if len(s) > 1 else 0.0, "total": sum(s)}
+    return out
+
+
+def summarize_segments(records: list[dict]) -> dict:
+    """``{segment: {n, mean, median, p90, std, total}}`` over step records (those of a written
+    profile or any subset of them, e.g. without the first steps); ``"total"`` is the whole step.
+    No records give ``{}``. Counterpart of the reference's ``summarize_segments``
+    (profiling.py:592-606)."""
+    return _bucket_summary(records, "segments_ms", "total_ms")
+
+
+def summarize_host_phases(records: list[dict]) -> dict:
+    """The same statistics over the host-side intervals (``host_timer``); records without them
+    are skipped (reference profiling.py:609-621)."""
+    return _bucket_summary(records, "host_ms")
 
 
 class _HostEvent:
@@ -92,24 +130,16 @@ class StepProfiler:
         self.active = False
 
     def summary(self) -> dict:
-        names: dict[str, list[float]] = {}
-        for r in self.records:
-            for k, v in r["segments_ms"].items():
-                names.setdefault(k, []).append(v)
-            names.setdefault("total", []).append(r["total_ms"])
-        out = {}
-        for k, vals in names.items():
-            s = sorted(vals)
-            out[k] = {"n": len(s), "mean": statistics.fmean(s), "median": statistics.median(s),
-                      "p90": s[min(len(s) - 1, int(0.9 * len(s)))],
-                      "std": statistics.pstdev(s) if len(s) > 1 else 0.0, "total": sum(s)}
-        return out
+        return summarize_segments(self.records)
 
     def write(self) -> str | None:
         if self.rank != 0:
             return None
         doc = {"schema_version": 2, "range": [self.start, self.end], "deep_mode": self.deep,
                "records": self.records, "summary": self.summary()}
+        host = summarize_host_phases(self.records)
+        if host:
+            doc["host_summary"] = host
         path = Path(self.output)
         path.parent.mkdir(parents=True, exist_ok=True)
         tmp = path.with_suffix(path.suffix + ".tmp")

@@ -422,6 +422,22 @@ def test_summary_statistics(tmp_path):
     assert one.summary()["optimizer"]["std"] == 0.0
 
 
+def test_module_level_summaries_work_on_any_subset_of_the_records(tmp_path):
+    from forgetrain_b200.utils.profiler import summarize_host_phases, summarize_segments
+    p = StepProfiler(0, 4, str(tmp_path / "p.json"), use_cuda=False, clock=_Clock(), host_timer=True)
+    for s in range(4):
+        _step(p, s, names=("microbatches", "optimizer"))
+    assert summarize_segments([]) == {} and summarize_host_phases([]) == {}
+    assert summarize_segments(p.records) == p.summary()
+    tail = summarize_segments(p.records[2:])                    # e.g. without the warm-up steps
+    assert tail["optimizer"]["n"] == 2 and tail["total"]["n"] == 2
+    host = summarize_host_phases(p.records)
+    assert set(host) == {"microbatches", "optimizer"} and host["optimizer"]["n"] == 4
+    doc = json.loads(open(p.write()).read())
+    assert doc["host_summary"]["optimizer"]["n"] == 4
+    assert summarize_host_phases([{"step": 0, "segments_ms": {"a": 1.0}, "total_ms": 1.0}]) == {}
+
+
 def test_write_is_atomic_creates_directories_and_is_rank_zero_only(tmp_path):
     out = tmp_path / "a" / "b" / "prof.json"
     p = StepProfiler(0, 1, str(out), use_cuda=False, clock=_Clock(), deep=True)

@@ -385,3 +385,29 @@ def test_mtp_losses_are_averaged_over_microbatches_and_ranks_and_reported(tmp_pa
     segs = doc["records"][0]["segments_ms"]
     assert {"mb_data", "microbatches", "reduce_scatter", "grad_norm", "optimizer",
             "loss_allreduce", "allgather"} <= set(segs)
+
+
+# ------------------------------------------------------------------------------------------
+def _accessor_worker(rank, world):
+    import training_engine_tensor.nccl as N
+    before = (N.get_rank(), N.get_world_size(), N.is_distributed())
+    topo = N.init_topology(2, device="cpu")
+    loss = torch.tensor(float(1 + topo.dp_rank))
+    mean = N.allreduce_loss(loss)
+    N.barrier()
+    after = (N.get_rank(), N.get_world_size(), N.is_distributed(), N.get_tp_rank(), N.get_tp_size(),
+             N.get_dp_rank(), N.get_dp_size(), N.get_tp_group() is topo.tp_group,
+             N.get_dp_group() is topo.dp_group)
+    return before, after, mean
+
+
+def test_module_level_topology_accessors_follow_init_topology():
+    """The accessors of ``training_engine_tensor.nccl`` describe one process before the groups are
+    up and the rank's place in the TP x DP mesh afterwards (4 ranks: TP groups {0,1},{2,3}, DP
+    groups {0,2},{1,3}); ``allreduce_loss`` averages over the data-parallel group."""
+    res = run_ranks(_accessor_worker, 4)
+    for rank in range(4):
+        before, after, mean = res[rank]
+        assert before == (0, 1, False)
+        assert after == (rank, 4, True, rank % 2, 2, rank // 2, 2, True, True)
+        assert mean == 1.5
