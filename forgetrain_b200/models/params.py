@@ -326,8 +326,14 @@ class ParamStore:
             self.params[ps.name].copy_(shard.to(self.dtype))
             del full, shard
 
-    def load_named(self, tensors: dict[str, torch.Tensor], full_tensors: bool = True) -> None:
+    def load_named(self, tensors: dict[str, torch.Tensor], full_tensors: bool = True,
+                   keep_missing: tuple[str, ...] = ()) -> None:
+        """Copy named tensors into the flat buffer. A parameter whose name starts with one of
+        ``keep_missing`` may be absent from ``tensors`` and then keeps its current value (the
+        MTP head when the source is a plain language-model checkpoint)."""
         for ps in self.specs:
+            if ps.name not in tensors and ps.name.startswith(keep_missing) and keep_missing:
+                continue
             t = tensors[ps.name]
             if full_tensors:
                 t = shard_for_tp(ps, t, self.spec, self.tp_rank, self.tp_size)

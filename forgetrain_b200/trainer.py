@@ -400,6 +400,13 @@ class Trainer:
             else:
                 self.opt.sync_master_from_params()
             return {"step": 0, "num_samples": self.num_samples, "dataloader_state": None}
+        from .ckpt import hf_import
+        if hf_import.is_hf_folder(p):
+            # a HuggingFace export: full tensors, no optimizer state; every rank keeps its shard
+            self.store.load_named(hf_import.load_hf_folder(p, self.spec), full_tensors=True,
+                                  keep_missing=("mtp.",))
+            self.opt.sync_master_from_params()
+            return {"step": 0, "num_samples": 0, "dataloader_state": None}
         if p.is_dir() and not any(p.glob("rank_*.pt")) and not (p / "training_state.pt").exists():
             from .ckpt.checkpoint import latest_step_dir
             p = latest_step_dir(p, "rank_*.pt") or p

@@ -241,3 +241,44 @@ def test_streaming_loader_checkpoint_ignores_prefetch_read_ahead(tmp_path):
                              **kw)
     assert [s["loss"] for s in rest["steps"]] == pytest.approx([s["loss"] for s in full["steps"]][2:],
                                                                abs=1e-6)
+
+
+def test_a_huggingface_folder_loads_back_into_the_engine(tmp_path):
+    """Export, then start a new trainer from the exported folder: same parameters (bf16 export of
+    bf16-representable values is exact), same loss on the same batch, optimizer moments at zero;
+    a folder of another architecture is refused."""
+    from forgetrain_b200.ckpt import hf_import
+    from forgetrain_b200.ckpt.convert_to_hf import convert
+    from forgetrain_b200.engine_config import from_spec
+    from forgetrain_b200.parallel.topology import Topology
+    from forgetrain_b200.trainer import Trainer
+    spec = load_model_spec("tiny", tie_embeddings=False)
+    cfg = from_spec(spec, dtype="fp32", comm="nccl")
+    a = Trainer(spec, cfg, Topology(), seq_length=32, micro_batch_size=2, seed=3)
+    a.store.flat_params.copy_(a.store.flat_params.to(torch.bfloat16).float())   # representable in bf16
+    a.opt.sync_master_from_params()
+    a.save(tmp_path / "run", 1, async_io=False)
+    out = convert(str(tmp_path / "run" / "step_0000001"), str(tmp_path / "hf"), "tiny")
+    assert hf_import.is_hf_folder(out) and not hf_import.is_hf_folder(tmp_path / "run")
+    b = Trainer(spec, cfg, Topology(), seq_length=32, micro_batch_size=2, seed=99)
+    st = b.load(out)
+    assert st["step"] == 0 and not b.opt.exp_avg.any()
+    for name in a.store.offsets:
+        assert torch.equal(a.store.params[name], b.store.params[name]), name
+    g = torch.Generator().manual_seed(0)
+    c = torch.randint(0, spec.vocab_size, (2, 33), generator=g)
+    batch = [{"tokens": c[:, :-1].contiguous(), "labels": c[:, 1:].contiguous(), "loss_mask": torch.ones(2, 32)}]
+    assert float(a.train_step(batch)["loss"]) == float(b.train_step(batch)["loss"])
+    other = load_model_spec("tiny", tie_embeddings=False, num_layers=2)
+    with pytest.raises(ValueError, match="num_hidden_layers"):
+        hf_import.load_hf_folder(out, other)
+    # a folder whose output table differs from its embedding cannot feed a run with tied tables
+    from forgetrain_b200.ckpt.convert_to_hf import to_hf_state_dict
+    tied = load_model_spec("tiny", tie_embeddings=True)
+    t = Trainer(tied, from_spec(tied, dtype="fp32", comm="nccl"), Topology(), seq_length=32,
+                micro_batch_size=2, seed=3)
+    sd, was_tied = to_hf_state_dict({n: t.store.params[n] for n in t.store.offsets}, tied, torch.float32)
+    assert was_tied and "output.weight" not in hf_import.from_hf_state_dict(sd, tied)
+    sd["lm_head.weight"] = sd["lm_head.weight"] + 1
+    with pytest.raises(ValueError, match="ties the two tables"):
+        hf_import.from_hf_state_dict(sd, tied)
