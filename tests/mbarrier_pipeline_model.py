@@ -839,3 +839,72 @@ def allgather_gemm_stream(seed: int, world: int, launches: int, exit_barrier: bo
     for r in range(world):
         sim.add(f"rank{r}", rank(r))
     sim.run()
+
+
+# ---------------------------------------------------------------------------------------------
+# Data-parallel step over several ranks (trainer.py, optim/adamw.py, parallel/fused_dp.py,
+# csrc/comm.cu): forward and backward read the parameter buckets; the squared gradient norm is
+# all-reduced (every rank passes it after its last read of the old parameters); then, bucket by
+# bucket in forward-consumption order on a side stream, the fused AdamW kernel pushes this rank's
+# updated shard into EVERY rank's parameter buffer and leaves through an exit barrier; the next
+# forward waits for a bucket's event right before the first layer that reads it.
+# ---------------------------------------------------------------------------------------------
+def dp_param_pipeline(seed: int, world: int, steps: int, n_buckets: int = 3,
+                      norm_allreduce: bool = True, exit_barrier: bool = True) -> None:
+    sim = Sim(seed)
+    # shard[r][b][s]: rank r's copy of bucket b, the shard owned by rank s
+    shard = [[[Resource(f"params[{r}][{b}][{s}]") for s in range(world)] for b in range(n_buckets)]
+             for r in range(world)]
+    for r in range(world):
+        for b in range(n_buckets):
+            for s in range(world):
+                shard[r][b][s].write(0, 2)            # version 0, read by forward and backward of step 1
+    norm_seen = [[0] * world for _ in range(world)]   # norm_seen[dst][src]: last step signalled
+    done = [[[0] * world for _ in range(world)] for _ in range(n_buckets)]    # exit flags per bucket
+    gathered = [[0] * n_buckets for _ in range(world)]                        # event per bucket
+
+    def main_stream(r):
+        for n in range(1, steps + 1):
+            for b in reversed(range(n_buckets)):      # forward: embedding's bucket (last) first
+                yield ("wait_fn", lambda b=b, n=n: gathered[r][b] >= n - 1, f"rank {r}: bucket {b} of step {n - 1}")
+                for s in range(world):
+                    shard[r][b][s].read(n - 1)
+                yield ("step",)
+            for b in range(n_buckets):                # backward: data gradients read the weights
+                for s in range(world):
+                    shard[r][b][s].read(n - 1)
+                yield ("step",)
+            if norm_allreduce:
+                for d in range(world):
+                    norm_seen[d][r] = n
+                for s in range(world):
+                    yield ("wait_fn", lambda s=s, n=n: norm_seen[r][s] >= n, f"rank {r}: norm of {s}")
+            # hand the step over to the side stream (an event in the engine)
+            handed[r] = n
+            yield ("step",)
+
+    handed = [0] * world
+
+    def side_stream(r):
+        for n in range(1, steps + 1):
+            yield ("wait_fn", lambda n=n: handed[r] >= n, f"rank {r}: gradients of step {n}")
+            for b in reversed(range(n_buckets)):
+                for d in range(world):                # update + push of the own shard to every rank
+                    yield ("async", f"push{r}", lambda d=d, b=b, n=n: shard[d][b][r].write(n, 2))
+                if exit_barrier:
+                    for d in range(world):
+                        def signal(d=d, b=b, n=n):
+                            done[b][d][r] = n
+                        yield ("async", f"push{r}", signal)       # released after the stores (fence)
+                    for s in range(world):
+                        yield ("wait_fn", lambda s=s, b=b, n=n: done[b][r][s] >= n,
+                               f"rank {r}: exit flag of {s} for bucket {b}")
+                else:
+                    yield ("wait_fn", lambda: not sim.queues.get(f"push{r}"), f"rank {r}: own pushes")
+                gathered[r][b] = n
+                yield ("step",)
+
+    for r in range(world):
+        sim.add(f"main{r}", main_stream(r))
+        sim.add(f"side{r}", side_stream(r))
+    sim.run()

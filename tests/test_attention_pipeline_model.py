@@ -171,3 +171,26 @@ def test_gathered_slots_are_rewritten_only_after_every_peer_has_read_them(world)
         except AssertionError:
             broken += 1
     assert broken > 0
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_parameter_buckets_are_replaced_only_between_a_steps_last_read_and_the_next_first_read(world):
+    for seed in range(20):
+        M.dp_param_pipeline(seed, world, steps=4)
+
+
+def test_the_parameter_pipeline_model_sees_what_the_norm_all_reduce_and_the_exit_barrier_are_for():
+    """Without the all-reduce of the gradient norm a fast rank pushes new parameters into a peer that
+    is still reading the old ones; without the exit barrier a rank's next forward reads a bucket
+    into which a peer's shard has not been pushed yet."""
+    def fails(**kw):
+        n = 0
+        for seed in range(40):
+            try:
+                M.dp_param_pipeline(seed, 4, steps=4, **kw)
+            except AssertionError:
+                n += 1
+        return n
+    assert fails(norm_allreduce=False) > 0
+    assert fails(exit_barrier=False) > 0
+    assert fails() == 0
