@@ -19,15 +19,15 @@ def _port() -> int:
         return s.getsockname()[1]
 
 
-def _run(command: str, steps: int, *extra: str) -> dict[int, float]:
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+def _run(command: str, steps: int, *extra: str, ranks: int = 2, mesh: str = "world=2 dp=2 tp=1") -> dict[int, float]:
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks),
            "--master-addr", "127.0.0.1", "--master-port", str(_port()),
            "-m", "training_engine_tensor", command, "--model", "tiny", "--device", "cpu", "--dtype", "fp32",
            "--num-steps", str(steps), "--global-batch-size", "4", "--micro-batch-size", "2",
            "--seq-length", "256", "--seed", "0", "--max-lr", "1e-3", "--tie-embeddings", *extra]
     r = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
-    assert "world=2 dp=2 tp=1" in r.stdout and "DONE" in r.stdout
+    assert mesh in r.stdout and "DONE" in r.stdout
     return {int(m.group(1)): float(m.group(2))
             for m in re.finditer(r"iteration +(\d+) \| loss ([0-9.E+-]+)", r.stdout)}
 
@@ -45,3 +45,18 @@ def test_two_cpu_ranks_train_save_and_resume_bit_for_bit(tmp_path):
     assert {k: whole[k] for k in (1, 2, 3, 4, 5)} == first
     assert resumed == {6: whole[6], 7: whole[7]}
     assert (run / "step_0000007" / "training_state.pt").exists()
+
+
+def test_four_cpu_ranks_tensor_parallel_match_data_parallel_and_their_checkpoint_moves(tmp_path):
+    """The same run as TP=2 x DP=2 (sequence-parallel activations, vocabulary-parallel tables and
+    loss) follows the DP=2 losses to fp32 summation order; its per-rank shard files resume on two
+    ranks without tensor parallelism into the data-parallel run's next step."""
+    run = tmp_path / "tp"
+    tp = _run("pretrain", 3, "--tensor-parallel-size", "2", "--sequence-parallel", "--save-dir", str(run),
+              "--save-interval", "3", ranks=4, mesh="world=4 dp=2 tp=2")
+    dp = _run("pretrain", 4)
+    for k in (1, 2, 3):
+        assert abs(tp[k] - dp[k]) < 5e-6 * dp[k], (k, tp[k], dp[k])
+    assert sorted(p.name for p in (run / "step_0000003").glob("rank_*.pt")) == ["rank_0.pt", "rank_1.pt"]
+    moved = _run("train", 1, "--resume", str(run / "step_0000003"))
+    assert abs(moved[4] - dp[4]) < 5e-6 * dp[4]
