@@ -22,7 +22,7 @@ EXTERNAL_ENV_WHITELIST = frozenset({
     "NCCL_PROTO", "NCCL_MIN_NCHANNELS", "NCCL_NVLS_ENABLE", "NCCL_IB_QPS",
     "TORCH_NCCL_HEARTBEAT_TIMEOUT_SEC", "OUTPUT_DIR", "HF_HOME", "TOKENIZERS_PARALLELISM",
     "FT_PEAK_TFLOPS", "FT_B200_NO_AUTOBUILD", "FT_COMM_MULTIMEM", "FT_COMM_TIMEOUT_MS",
-    "FT_COMM_CTAS", "FT_B200_LIB", "FT_FUSE_ADAM_AG", "FT_FUSE_FC1_SWIGLU",
+    "FT_COMM_CTAS", "FT_B200_LIB", "FT_FUSE_ADAM_AG", "FT_FUSE_FC1_SWIGLU", "FT_INJECT_FAILURE",
 })
 
 
@@ -324,6 +324,8 @@ _SWITCH_NOTES = {
     "FT_COMM_CTAS": "CTAs per fused data-parallel collective launch (default 96)",
     "FT_FUSE_ADAM_AG": "0: AdamW and the parameter all-gather as two kernels instead of one",
     "FT_FUSE_FC1_SWIGLU": "0: FC1 and SwiGLU as two kernels instead of one",
+    "FT_INJECT_FAILURE": "recovery tests: `step=K[,rank=R][,once=PATH][,exit=CODE]` makes rank R fail on "
+                         "the host right before step K (utils/fault_injection.py)",
 }
 
 

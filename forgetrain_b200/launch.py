@@ -20,6 +20,18 @@ Stages
 ``hf_pretrain``          the short HF-dataset pretrain of ``entry_hf_pretrain.sh``: ``pretrain`` with
                          no periodic saves unless ``SAVE_DIR`` is given.
 
+Recovery
+--------
+``AUTO_RESUME=1``   when ``SAVE_DIR`` already holds a finished checkpoint (a ``step_<N>`` directory
+                    with ``training_state.pt`` or ``rank_<R>.pt`` files), the job continues from
+                    the newest one whatever the stage says: ``train --resume SAVE_DIR/step_<N>``
+                    with ``NUM_STEPS`` reduced by N, so that a relaunched job ends where the
+                    original one would have.
+``MAX_RESTARTS=K``  the launcher stays in front of ``torch.distributed.run`` and, when it exits with
+                    an error, starts it again (at most K times) with ``AUTO_RESUME`` on. The
+                    reference has no recovery of its own (a failed job is resubmitted by hand with
+                    ``RESUME_DIR``); this is that resubmission, automated.
+
 Node topology follows the PyTorchJob convention the reference's scripts rely on: ``WORLD_SIZE`` is
 the number of nodes and ``RANK`` the node rank *of the launcher's own environment*; the launcher
 then gives every worker its global rank.
@@ -132,12 +144,22 @@ def plan_from_env(env: dict, nproc_per_node: int | None = None,
     if resume is not None and save_dir is not None and \
             os.path.abspath(resume) == os.path.abspath(save_dir):
         raise LaunchError("RESUME_DIR and SAVE_DIR must differ (a resumed run never overwrites its source)")
+    steps_done = 0
+    if _get(env, "AUTO_RESUME", "0") == "1" and save_dir is not None:
+        point = find_restart_point(save_dir)
+        if point is not None:
+            # continue this job's own run: the newest finished checkpoint wins over the stage's
+            # starting point (random init, Megatron export or the previous phase's RESUME_DIR)
+            sub, resume, ckpt_root = "train", point[1], None
+            steps_done = point[0]
 
     args: list[str] = ["--model", _get(env, "MODEL", "0.5b")]
     if ckpt_root is not None:
         args += ["--checkpoint-root", ckpt_root]
     for name, flag, default in _VALUE_FLAGS:
         v = _get(env, name, default)
+        if name == "NUM_STEPS" and v is not None and steps_done:
+            v = str(max(0, int(v) - steps_done))     # --num-steps counts the steps of THIS launch
         if v is not None:
             args += [flag, v]
     tf = _get(env, "HF_TEXT_FIELD")
@@ -169,6 +191,22 @@ def plan_from_env(env: dict, nproc_per_node: int | None = None,
                       master_addr=_get(env, "MASTER_ADDR", "127.0.0.1"),
                       master_port=int(_get(env, "MASTER_PORT", "29500")),
                       cli_args=tuple(args), child_env=child)
+
+
+def find_restart_point(save_dir: str) -> tuple[int, str] | None:
+    """``(N, path)`` of the newest ``step_<N>`` directory under ``save_dir`` that holds a finished
+    checkpoint (a single-file one or the per-rank shards of a tensor-parallel run), else None."""
+    from .ckpt.checkpoint import latest_step_dir
+    if not os.path.isdir(save_dir):
+        return None
+    best = None
+    for pattern in ("training_state.pt", "rank_*.pt"):
+        d = latest_step_dir(save_dir, pattern)
+        if d is not None:
+            n = int(d.name[len("step_"):])
+            if best is None or n > best[0]:
+                best = (n, str(d))
+    return best
 
 
 def env_from_job_spec(path: str, base_env: dict | None = None) -> dict:
@@ -210,6 +248,8 @@ def main(argv: list[str] | None = None) -> int:
     p = argparse.ArgumentParser(prog="forgetrain_b200.launch", description=__doc__.split("\n\n")[0])
     p.add_argument("--dry-run", action="store_true", help="print the plan and exit")
     p.add_argument("--nproc-per-node", type=int, default=None)
+    p.add_argument("--max-restarts", type=int, default=None,
+                   help="restart a failed job from its newest checkpoint up to this many times (MAX_RESTARTS)")
     p.add_argument("--job-spec", default=None,
                    help="scheduler job spec (JSON) whose task.envVars are laid over the environment")
     p.add_argument("extra", nargs=argparse.REMAINDER, help="after --: flags passed to the training CLI")
@@ -224,14 +264,45 @@ def main(argv: list[str] | None = None) -> int:
     print(describe(plan), flush=True)
     if a.dry_run:
         return 0
-    env = job_env
-    env.update(plan.child_env)
-    # the launcher's own RANK / WORLD_SIZE are node-level; workers get theirs from the launcher
-    env.pop("RANK", None)
-    env.pop("WORLD_SIZE", None)
-    cmd = plan.command()
-    os.execvpe(cmd[0], cmd, env)
-    return 0  # not reached
+    max_restarts = a.max_restarts if a.max_restarts is not None else int(_get(job_env, "MAX_RESTARTS", "0"))
+
+    def worker_env(pl: LaunchPlan) -> dict:
+        env = dict(job_env)
+        env.update(pl.child_env)
+        # the launcher's own RANK / WORLD_SIZE are node-level; workers get theirs from the launcher
+        env.pop("RANK", None)
+        env.pop("WORLD_SIZE", None)
+        return env
+
+    if max_restarts <= 0:
+        cmd = plan.command()
+        os.execvpe(cmd[0], cmd, worker_env(plan))
+        return 0  # not reached
+    return supervise(plan, job_env, a.nproc_per_node, extra, max_restarts, worker_env)
+
+
+def supervise(plan: LaunchPlan, job_env: dict, nproc_per_node, extra, max_restarts: int, worker_env,
+              run=None) -> int:
+    """Run the plan as a child process; after a failure plan again with ``AUTO_RESUME`` on (the
+    newest finished checkpoint of ``SAVE_DIR``, fewer steps left) and start it again, at most
+    ``max_restarts`` times. Returns the exit code of the last attempt. ``run(cmd, env) -> int`` is
+    replaceable for tests."""
+    import subprocess
+    run = run or (lambda cmd, env: subprocess.call(cmd, env=env))
+    attempt = 0
+    while True:
+        steps = plan.cli_args[plan.cli_args.index("--num-steps") + 1] if "--num-steps" in plan.cli_args else None
+        if steps == "0":
+            print("=== nothing left to do: the newest checkpoint is at the last step ===", flush=True)
+            return 0
+        rc = run(plan.command(), worker_env(plan))
+        if rc == 0 or attempt >= max_restarts:
+            return rc
+        attempt += 1
+        env = dict(job_env)
+        env["AUTO_RESUME"] = "1"
+        plan = plan_from_env(env, nproc_per_node, extra)
+        print(f"=== attempt {attempt} of {max_restarts} after exit code {rc} ===\n{describe(plan)}", flush=True)
 
 
 if __name__ == "__main__":

@@ -515,7 +515,9 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
                f"world={topo.world} dp={topo.dp_size} tp={topo.tp_size} mbs={micro_batch_size} "
                f"seq={seq_length} microbatches={num_local_microbatches} dtype={cfg.dtype} "
                f"comm={cfg.comm} data={'synthetic' if data_source is None else 'custom'}")
+    from .utils.fault_injection import maybe_fail
     for step in range(start_step, start_step + num_steps):
+        maybe_fail(step + 1, topo.rank)      # recovery tests: FT_INJECT_FAILURE, host side only
         if cuda:
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()

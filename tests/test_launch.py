@@ -1,11 +1,15 @@
 """Job launcher: stage selection, validation, and the command it builds
 (behaviour of the reference's scripts/entry_train.sh:274-455 and entry_hf_pretrain.sh)."""
+import os
 import subprocess
 import sys
+from pathlib import Path
 
 import pytest
 
 from forgetrain_b200 import launch
+
+ROOT = Path(__file__).resolve().parent.parent
 
 
 def _plan(env, **kw):
@@ -116,3 +120,140 @@ def test_bundled_job_specs_give_valid_plans():
         if "gsm8k" in f.name:
             assert ns.hf_text_template == "Question: {question}\nAnswer: {answer}"
             assert "--save-dir" not in plan.cli_args
+
+
+# ---------------------------------------------------------------------------------------------
+# recovery: AUTO_RESUME / MAX_RESTARTS
+# ---------------------------------------------------------------------------------------------
+def _finished(save_dir, step, name="training_state.pt"):
+    d = save_dir / f"step_{step:07d}"
+    d.mkdir(parents=True, exist_ok=True)
+    (d / name).write_bytes(b"x")
+    return d
+
+
+def test_auto_resume_continues_from_the_newest_finished_checkpoint(tmp_path):
+    from forgetrain_b200.launch import find_restart_point, plan_from_env
+    save = tmp_path / "run"
+    env = {"STAGE": "stable", "SYNTHETIC_DATA": "1", "SAVE_DIR": str(save), "NUM_STEPS": "10",
+           "AUTO_RESUME": "1", "NPROC_PER_NODE": "2"}
+    fresh = plan_from_env(env)
+    assert fresh.subcommand == "pretrain" and "--resume" not in fresh.cli_args      # nothing to resume yet
+    assert find_restart_point(str(save)) is None
+    _finished(save, 2)
+    _finished(save, 6)
+    (save / "step_0000008").mkdir()                                    # the writer never finished this one
+    (save / "step_0000008" / "training_state.pt.tmp").write_bytes(b"half")
+    assert find_restart_point(str(save)) == (6, str(save / "step_0000006"))
+    plan = plan_from_env(env)
+    args = list(plan.cli_args)
+    assert plan.subcommand == "train"
+    assert args[args.index("--resume") + 1] == str(save / "step_0000006")
+    assert args[args.index("--num-steps") + 1] == "4"                   # 10 in all, 6 done
+    assert args[args.index("--save-dir") + 1] == str(save)
+    # tensor-parallel shard files count as a finished checkpoint too, and the newest of both kinds wins
+    _finished(save, 7, "rank_0.pt")
+    assert find_restart_point(str(save))[0] == 7
+    # off by default
+    off = plan_from_env({**env, "AUTO_RESUME": "0"})
+    assert off.subcommand == "pretrain" and "--resume" not in off.cli_args
+    # a Megatron start is replaced as well: the job's own checkpoint has everything
+    mg = plan_from_env({**env, "STAGE": "decay_from_megatron", "CHECKPOINT_ROOT": "/ckpt/mg"})
+    assert "--checkpoint-root" not in mg.cli_args and "--resume" in mg.cli_args
+
+
+def test_supervisor_restarts_a_failed_job_with_fewer_steps_and_gives_up_after_the_limit(tmp_path):
+    from forgetrain_b200 import launch
+    save = tmp_path / "run"
+    env = {"STAGE": "stable", "SYNTHETIC_DATA": "1", "SAVE_DIR": str(save), "NUM_STEPS": "6",
+           "NPROC_PER_NODE": "2"}
+    calls = []
+
+    def run_fails_once(cmd, child_env):
+        calls.append(list(cmd))
+        if len(calls) == 1:
+            _finished(save, 4)                     # got as far as step 4, then died
+            return 1
+        return 0
+    plan = launch.plan_from_env(env)
+    rc = launch.supervise(plan, env, None, (), 2, lambda pl: dict(env), run=run_fails_once)
+    assert rc == 0 and len(calls) == 2
+    assert "pretrain" in calls[0] and "--resume" not in calls[0]
+    second = calls[1]
+    assert "train" in second and second[second.index("--resume") + 1] == str(save / "step_0000004")
+    assert second[second.index("--num-steps") + 1] == "2"
+
+    calls.clear()
+    rc = launch.supervise(launch.plan_from_env(env), env, None, (), 2, lambda pl: dict(env),
+                          run=lambda cmd, e: calls.append(cmd) or 3)
+    assert rc == 3 and len(calls) == 3              # the first attempt and two restarts
+
+    # a job whose newest checkpoint is already the last step has nothing left to run
+    _finished(save, 6)
+    calls.clear()
+    done = launch.plan_from_env({**env, "AUTO_RESUME": "1"})
+    assert launch.supervise(done, env, None, (), 2, lambda pl: dict(env),
+                            run=lambda cmd, e: calls.append(cmd) or 0) == 0
+    assert calls == []
+
+
+def test_fault_injection_spec_and_once_marker(tmp_path):
+    from forgetrain_b200.utils.fault_injection import InjectedFailure, maybe_fail, parse
+    assert parse(None) is None and parse("") is None
+    assert parse("step=3") == {"step": 3, "rank": 0, "once": None, "exit": None}
+    assert parse("step=3, rank=1, once=/x/y")["once"] == "/x/y"
+    for bad in ("rank=1", "step", "step=3,when=now"):
+        with pytest.raises(ValueError):
+            parse(bad)
+    marker = tmp_path / "m"
+    env = {"FT_INJECT_FAILURE": f"step=3,rank=1,once={marker}"}
+    maybe_fail(2, 1, env)                           # another step
+    maybe_fail(3, 0, env)                           # another rank
+    assert not marker.exists()
+    with pytest.raises(InjectedFailure, match="before step 3 on rank 1"):
+        maybe_fail(3, 1, env)
+    assert marker.exists()
+    maybe_fail(3, 1, env)                           # the relaunched job passes the same step
+    maybe_fail(3, 1, {})                            # no variable: nothing happens
+
+
+def test_a_rank_that_fails_mid_run_is_recovered_by_the_launcher_and_the_run_ends_identical(tmp_path):
+    """Two CPU ranks, a host-side failure of rank 1 right before step 5 of 6: the launcher sees the
+    failed attempt, resumes from the step-4 checkpoint for the two remaining steps, and the final
+    checkpoint equals that of a run that was never interrupted."""
+    import socket
+    import torch
+
+    def port():
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            return s.getsockname()[1]
+
+    def job(save, **more):
+        env = dict(os.environ)
+        env.update({"STAGE": "stable", "SYNTHETIC_DATA": "1", "MODEL": "tiny", "NUM_STEPS": "6",
+                    "GLOBAL_BATCH_SIZE": "4", "MICRO_BATCH_SIZE": "2", "SEQ_LENGTH": "64", "SEED": "0",
+                    "SAVE_DIR": str(save), "SAVE_INTERVAL": "2", "NPROC_PER_NODE": "2",
+                    "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port())})
+        env.pop("RANK", None)
+        env.pop("WORLD_SIZE", None)
+        env.update(more)
+        return subprocess.run([sys.executable, "-m", "forgetrain_b200.launch", "--", "--device", "cpu",
+                               "--dtype", "fp32"], cwd=ROOT, env=env, capture_output=True, text=True,
+                              timeout=600)
+
+    marker = tmp_path / "failed_once"
+    r = job(tmp_path / "a", MAX_RESTARTS="2", FT_INJECT_FAILURE=f"step=5,rank=1,once={marker}")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert marker.exists() and "attempt 1 of 2" in r.stdout and "attempt 2 of 2" not in r.stdout
+    assert "injected failure before step 5 on rank 1" in r.stdout + r.stderr
+    assert f"resumed from {tmp_path / 'a' / 'step_0000004'} at step 4" in r.stdout
+    whole = job(tmp_path / "b")
+    assert whole.returncode == 0, whole.stdout[-3000:] + whole.stderr[-3000:]
+    a = torch.load(tmp_path / "a" / "step_0000006" / "training_state.pt", weights_only=False)
+    b = torch.load(tmp_path / "b" / "step_0000006" / "training_state.pt", weights_only=False)
+    assert a["step"] == b["step"] == 6
+    for name in b["params"]:
+        assert torch.equal(a["params"][name], b["params"][name]), name
+    for name in b["optimizer_state"]["exp_avg_sq"]:
+        assert torch.equal(a["optimizer_state"]["exp_avg_sq"][name], b["optimizer_state"]["exp_avg_sq"][name])
