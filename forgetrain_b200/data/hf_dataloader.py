@@ -230,6 +230,49 @@ def render_text(example: dict, text_field, template: str | None) -> str:
     return "\n".join(str(example[f]) for f in fields if example.get(f))
 
 
+class LocalRows(list):
+    """Rows of local data files as a list of dicts (indexable and sized like a ``datasets.Dataset``;
+    the text column is detected from the first row)."""
+
+
+def load_local_files(fmt: str, files: str) -> LocalRows:
+    """Read ``--hf-data-files`` (one path, a comma-separated list, or a glob) without the ``datasets``
+    package: ``json`` (one object per line, or one array per file), ``text`` (one document per
+    line, column ``text``), ``csv`` (header row) and ``parquet`` (through pyarrow)."""
+    import csv
+    import glob
+    import json
+    paths: list[str] = []
+    for part in str(files).split(","):
+        part = part.strip()
+        hits = sorted(glob.glob(part)) if any(c in part for c in "*?[") else [part]
+        paths += hits
+    if not paths:
+        raise FileNotFoundError(f"--hf-data-files {files!r} matches no file")
+    rows = LocalRows()
+    for path in paths:
+        if fmt in ("json", "jsonl"):
+            with open(path, encoding="utf-8") as f:
+                head = f.read(1)
+                f.seek(0)
+                if head == "[":
+                    rows.extend(json.load(f))
+                else:
+                    rows.extend(json.loads(line) for line in f if line.strip())
+        elif fmt == "text":
+            with open(path, encoding="utf-8") as f:
+                rows.extend({"text": line.rstrip("\n")} for line in f)
+        elif fmt == "csv":
+            with open(path, encoding="utf-8", newline="") as f:
+                rows.extend(csv.DictReader(f))
+        elif fmt == "parquet":
+            import pyarrow.parquet as pq
+            rows.extend(pq.read_table(path).to_pylist())
+        else:
+            raise ValueError(f"--hf-data-format {fmt!r}: expected json, text, csv or parquet")
+    return rows
+
+
 def build_hf_dataloader(args, spec, micro_batch_size: int, seq_length: int, topo,
                         tokenizer=None, dataset=None) -> PackedTokenLoader:
     """Build the loader from CLI arguments. ``tokenizer`` / ``dataset`` may be injected (tests,
@@ -246,8 +289,20 @@ def build_hf_dataloader(args, spec, micro_batch_size: int, seq_length: int, topo
             if topo.world > 1 and dist.is_initialized():
                 dist.barrier()
     if dataset is None:
-        from datasets import load_dataset
-        if args.hf_data_files:
+        try:
+            from datasets import load_dataset
+        except ImportError:
+            load_dataset = None
+        if args.hf_data_files and load_dataset is None:
+            # local files need no `datasets` package: read them with the standard library / pyarrow
+            dataset = load_local_files(args.hf_data_format or "json", args.hf_data_files)
+            if topo.rank == 0:
+                print(f"[hf_dataloader] `datasets` is not installed: read {len(dataset)} rows from "
+                      f"{args.hf_data_files} directly", flush=True)
+        elif load_dataset is None:
+            raise SystemExit("--hf-dataset needs the `datasets` package (or local files through "
+                             "--hf-data-files with --hf-data-format json | text | parquet | csv)")
+        elif args.hf_data_files:
             fmt = args.hf_data_format or "json"
             dataset = load_dataset(fmt, data_files=args.hf_data_files, split=args.hf_dataset_split)
         else:

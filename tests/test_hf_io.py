@@ -282,3 +282,64 @@ def test_a_huggingface_folder_loads_back_into_the_engine(tmp_path):
     sd["lm_head.weight"] = sd["lm_head.weight"] + 1
     with pytest.raises(ValueError, match="ties the two tables"):
         hf_import.from_hf_state_dict(sd, tied)
+
+
+def _word_tokenizer(folder, words):
+    """A word-level tokenizer saved the way ``AutoTokenizer.from_pretrained`` reads it."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+    vocab = {"<unk>": 0, "<s>": 1, "</s>": 2, **{w: i + 3 for i, w in enumerate(words)}}
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    fast = PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="<unk>", bos_token="<s>", eos_token="</s>")
+    fast.save_pretrained(str(folder))
+    return fast
+
+
+def test_local_data_files_are_read_without_the_datasets_package(tmp_path):
+    import json
+    from forgetrain_b200.data.hf_dataloader import load_local_files
+    (tmp_path / "a.jsonl").write_text("\n".join(json.dumps({"text": f"doc {i}", "id": i}) for i in range(3)) + "\n")
+    (tmp_path / "b.json").write_text(json.dumps([{"text": "doc 3", "id": 3}]))
+    (tmp_path / "c.txt").write_text("first line\nsecond line\n")
+    (tmp_path / "d.csv").write_text("title,body\nt0,b0\nt1,b1\n")
+    rows = load_local_files("json", f"{tmp_path}/a.jsonl,{tmp_path}/b.json")
+    assert [r["id"] for r in rows] == [0, 1, 2, 3] and len(rows) == 4 and rows[2]["text"] == "doc 2"
+    assert [r["text"] for r in load_local_files("text", str(tmp_path / "*.txt"))] == ["first line", "second line"]
+    assert load_local_files("csv", str(tmp_path / "d.csv"))[1] == {"title": "t1", "body": "b1"}
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    pq.write_table(pa.table({"text": ["p0", "p1"]}), tmp_path / "e.parquet")
+    assert [r["text"] for r in load_local_files("parquet", str(tmp_path / "e.parquet"))] == ["p0", "p1"]
+    with pytest.raises(FileNotFoundError):
+        load_local_files("json", str(tmp_path / "nothing*.json"))
+    with pytest.raises(ValueError, match="expected json"):
+        load_local_files("arrow", str(tmp_path / "a.jsonl"))
+
+
+def test_cli_trains_on_local_files_with_a_saved_tokenizer(tmp_path):
+    """`--hf-data-files` + `--tokenizer-path` end to end on CPU, whether or not the `datasets`
+    package is there: text column detected, documents tokenised, packed and trained on."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    words = [f"w{i}" for i in range(200)]
+    _word_tokenizer(tmp_path / "tok", words)
+    g = torch.Generator().manual_seed(0)
+    with open(tmp_path / "corpus.jsonl", "w") as f:
+        for _ in range(300):
+            n = int(torch.randint(5, 60, (1,), generator=g))
+            ids = torch.randint(0, 200, (n,), generator=g).tolist()
+            f.write(json.dumps({"content": " ".join(words[i] for i in ids)}) + "\n")
+    root = Path(__file__).resolve().parent.parent
+    r = subprocess.run([sys.executable, "-m", "training_engine_tensor", "pretrain", "--model", "tiny", "--device", "cpu",
+                        "--num-steps", "3", "--micro-batch-size", "2", "--global-batch-size", "2", "--seq-length", "64",
+                        "--hf-dataset", "local", "--hf-data-files", str(tmp_path / "corpus.jsonl"),
+                        "--hf-data-format", "json", "--tokenizer-path", str(tmp_path / "tok"),
+                        "--random-init"], cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "text_fields=['content']" in r.stdout and "iteration        3" in r.stdout and "DONE" in r.stdout
+    losses = [float(x) for x in __import__("re").findall(r"\| loss ([0-9.E+-]+)", r.stdout)]
+    # 203 distinct token ids out of a 4096-entry vocabulary: the loss drops fast below ln(4096)
+    assert len(losses) == 3 and losses[-1] < losses[0]
