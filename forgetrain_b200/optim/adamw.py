@@ -265,8 +265,12 @@ class ShardedAdamW:
             self.wait_bucket(i)
 
     # ------------------------------------------------------------------ checkpoint support
-    def gather_full_state(self) -> dict[str, dict[str, torch.Tensor]]:
-        """Rank-count independent optimizer state: per-parameter fp32 tensors on CPU."""
+    def gather_full_state(self, keep: bool = True) -> dict[str, dict[str, torch.Tensor]]:
+        """Rank-count independent optimizer state: per-parameter fp32 tensors on CPU. A collective
+        over the data-parallel group: every rank must call it. A rank that will not write the
+        checkpoint passes ``keep=False``: it takes part in the gathers and returns empty
+        dictionaries instead of holding a host copy of the whole state (three fp32 tensors per
+        parameter, 48 GB for one tensor-parallel half of the 8B model)."""
         out = {"master_weights": {}, "exp_avg": {}, "exp_avg_sq": {}}
         for field, flat in (("master_weights", self.master), ("exp_avg", self.exp_avg),
                             ("exp_avg_sq", self.exp_avg_sq)):
@@ -283,6 +287,8 @@ class ShardedAdamW:
                         full = torch.cat(parts)
                 else:
                     full = shard
+                if not keep:
+                    continue
                 for name in b.params:
                     o = b.param_offsets[name]
                     n_el = self.store.numel(name)

@@ -356,7 +356,9 @@ class Trainer:
         """Rank-count independent checkpoint: DP shards of the optimizer state are gathered;
         with TP > 1 every TP rank of DP rank 0 writes its own ``rank_<R>.pt`` shard."""
         self.finish_step()        # the parameters read below are complete on this stream
-        opt_state = self.opt.gather_full_state()
+        # only the ranks that write a file keep the gathered state on the host
+        writes = self.topo.rank == 0 if self.topo.tp_size == 1 else self.topo.dp_rank == 0
+        opt_state = self.opt.gather_full_state(keep=writes)
         opt_state["step_count"] = self.opt.step_count
         opt_state["num_samples"] = self.num_samples
         names = [ps.name for ps in self.store.specs]

@@ -647,3 +647,15 @@ def test_optimizer_state_per_rank_is_one_nth(monkeypatch):
     total = out[0][0].flat_params.numel()
     for _, opt in out:
         assert opt.master.numel() * world == total
+
+
+def test_ranks_that_do_not_write_take_part_in_the_gathers_without_keeping_the_state(monkeypatch):
+    world = 4
+    sim, out = _ranks(world, 1, monkeypatch)
+    sim.calls.clear()
+    states = sim.run(lambda r: out[r][1].gather_full_state(keep=(r == 0)))
+    n_gathers = len([c for c in sim.calls if c.startswith("all_gather")])
+    assert n_gathers == 3 * len(out[0][1].buckets)               # the same collectives as before
+    assert set(states[0]["exp_avg"]) == set(out[0][0].offsets)
+    for s in states[1:]:
+        assert s == {"master_weights": {}, "exp_avg": {}, "exp_avg_sq": {}}
