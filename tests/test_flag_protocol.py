@@ -138,3 +138,67 @@ def test_every_host_epoch_counter_uses_the_shared_increment():
             rhs = m.group(1)
             assert "+ 1" not in rhs or "bump_epoch" in rhs, rhs
     assert len(re.findall(r"bump_epoch\(self\.epoch_", inspect.getsource(fused_tp))) == 3
+
+
+def test_epoch_bookkeeping_of_the_symmetric_buffers_through_capture_replay_and_resync(monkeypatch):
+    """The host state machine of ``SymmetricBuffers`` itself (no device: the native library is
+    replaced by a stand-in whose "advance" node adds to the base tensor, as a replay would): eager
+    epochs count up per slot; inside a capture the launch arguments are 1, 2, ... relative to the
+    base, which starts at the eager epochs; every replay advances the base by what one step
+    consumes; an eager launch after a capture is refused until ``resync_epochs`` has read the base
+    back, after which eager epochs continue behind the last replay, also across 2^31."""
+    import ctypes
+    import torch
+    from forgetrain_b200.parallel import fused_dp
+    replays = []
+
+    class FakeLib:
+        def ft_comm_epoch_advance(self, base_ptr, add, stream):
+            replays.append(list(add))
+            return 0
+
+    class FakeLibModule:
+        @staticmethod
+        def lib():
+            return FakeLib()
+        ptr = staticmethod(lambda t: t)
+        stream = staticmethod(lambda: None)
+        check_rc = staticmethod(lambda rc, what: None)
+
+    monkeypatch.setattr(fused_dp, "_lib", FakeLibModule)
+    for start in (0, 0x7FFFFFF0):
+        replays.clear()
+        s = object.__new__(fused_dp.SymmetricBuffers)
+        s.epoch = [start] * fused_dp.NUM_FLAG_SLOTS
+        s.epoch_base = torch.zeros(fused_dp.NUM_FLAG_SLOTS, dtype=torch.int32)
+        s._capturing, s._graph_mode, s._used = False, False, [0] * fused_dp.NUM_FLAG_SLOTS
+        # eager: absolute epochs, per slot
+        assert [s.next_epoch(0), s.next_epoch(0), s.next_epoch(2)] == \
+            [(start + 1) & 0xFFFFFFFF, (start + 2) & 0xFFFFFFFF, (start + 1) & 0xFFFFFFFF]
+        s.set_epoch(1, s.epoch[0])
+        assert s.epoch[1] == s.epoch[0]
+        # capture: relative epochs, the base holds the eager ones
+        s.begin_capture()
+        assert [int(x) & 0xFFFFFFFF for x in s.epoch_base.tolist()] == s.epoch
+        rel = [s.next_epoch(0), s.next_epoch(0), s.next_epoch(0), s.next_epoch(2)]
+        assert rel == [1, 2, 3, 1]
+        s.set_epoch(1, rel[2])
+        s.end_capture()
+        assert replays[-1][:3] == [3, 3, 1] and s._graph_mode and not s._capturing
+        with pytest.raises(RuntimeError, match="resync_epochs"):
+            s.next_epoch(0)
+        # five replays: the graph's last node adds what one step consumes (done here by hand)
+        per = torch.tensor(replays[-1], dtype=torch.int64)
+        total = (torch.tensor([fused_dp._as_i32(e) for e in s.epoch], dtype=torch.int64) + 5 * per)
+        s.epoch_base.copy_(((total + 2 ** 31) % 2 ** 32 - 2 ** 31).to(torch.int32))
+        s.resync_epochs()
+        assert not s._graph_mode and not s.epoch_base.any()
+        assert s.epoch[0] == (start + 2 + 15) & 0xFFFFFFFF and s.epoch[2] == (start + 1 + 5) & 0xFFFFFFFF
+        assert s.next_epoch(0) == (start + 2 + 16) & 0xFFFFFFFF      # eager again, behind the last replay
+        # a second capture while in graph mode resyncs by itself
+        s.begin_capture()
+        s.next_epoch(0)
+        s.end_capture()
+        s.epoch_base += 1
+        s.begin_capture()
+        assert s.epoch[0] == (start + 2 + 16 + 1) & 0xFFFFFFFF and s._capturing
