@@ -12,7 +12,9 @@
   gradients are written in place by the wgrad GEMM, never copied.
 * Tensor parallelism: column-parallel weights (wqkv, wfc1, embeddings, head) are sharded on
   rows, row-parallel weights (wo, w2) on columns; every rank initialises the full tensor from
-  the same seed and keeps its shard, so results do not depend on the TP degree.
+  the same seed and keeps its shard, so results do not depend on the TP degree as long as the
+  vocabulary is a multiple of ``8 * tp``; otherwise the vocabulary shards carry zero-initialised
+  pad rows that take part in the softmax (Megatron's padded-vocabulary convention).
 """
 from __future__ import annotations
 
