@@ -411,3 +411,27 @@ def test_module_level_topology_accessors_follow_init_topology():
         assert before == (0, 1, False)
         assert after == (rank, 4, True, rank % 2, 2, rank // 2, 2, True, True)
         assert mean == 1.5
+
+
+# ------------------------------------------------------------------------------------------
+def _padded_vocab_worker(rank, world, tp):
+    from forgetrain_b200.parallel.topology import init_topology
+    from forgetrain_b200.trainer import Trainer
+    spec = _spec(vocab_size=500, tie_embeddings=False)
+    topo = init_topology(tp, device="cpu")
+    tr = Trainer(spec, _cfg(spec, tensor_parallel_size=tp, sequence_parallel=tp > 1), topo,
+                 seq_length=64, micro_batch_size=2, seed=0)
+    data = _batches(7, 1, 2, 64, spec.vocab_size)
+    return float(tr.train_step(data)["loss"]), tr.model.vocab_rows
+
+
+def test_padded_vocabulary_rows_take_part_in_the_softmax_like_megatrons():
+    """500 tokens over two ranks: 256 rows per rank, 12 zero-initialised pad rows in all. Their
+    columns are in the softmax, so the first loss is above the TP = 1 loss by about
+    log(1 + 12 / 500) (exactly that if every logit were zero)."""
+    import math
+    one, rows1 = run_ranks(_padded_vocab_worker, 1, 1)[0]
+    two, rows2 = run_ranks(_padded_vocab_worker, 2, 2)[0]
+    assert rows1 == 500 and rows2 == 256
+    shift = two - one
+    assert 0.5 * math.log(1 + 12 / 500) < shift < 1.2 * math.log(1 + 12 / 500), shift
