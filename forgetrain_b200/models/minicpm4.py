@@ -291,8 +291,6 @@ class MiniCPM4:
         done = self._wgrad_done.pop(n_qkv, None)
         if done is not None:
             torch.cuda.current_stream().wait_event(done)
-        if tp.replica_size > 1:
-            self._reduce_kv_replicas(g[n_qkv])
         emit(n_qkv)
         del dqkv
         dh = ops.rmsnorm_bwd(dn1, sv.h_in, p[n_an], sv.rs1, dh, g[n_an], accumulate)
@@ -300,11 +298,22 @@ class MiniCPM4:
         self._emit_after_wgrad(emit, n_wo)
         return dh
 
-    def _reduce_kv_replicas(self, gqkv: torch.Tensor) -> None:
-        """k / v rows are replicated over the ranks of one KV group: sum their gradients."""
-        D = self.spec.head_dim
-        kv = gqkv[self.local_g * D:]
-        self.tp.replica_all_reduce_(kv)
+    def finalize_grad(self, name: str) -> None:
+        """The tensor-parallel collectives that complete the gradient of parameter ``name``; to be
+        called ONCE per optimizer step, when the gradient has been accumulated over all
+        micro-batches and before it is reduced over the data-parallel group (the trainer does so
+        from its "gradient ready" callback). Two kinds of parameters need one: norm weights under
+        sequence parallelism (every rank has seen its token shard only) and the k / v rows of the
+        fused QKV weight when one KV group is replicated over several ranks. Summing a buffer
+        that still accumulates would count the earlier micro-batches once per rank."""
+        tp = self.tp
+        if not tp.enabled:
+            return
+        ps = self.store.by_name.get(name)
+        if ps is not None and ps.is_norm and tp.sequence_parallel:
+            tp.all_reduce_(self.g[name])
+        elif tp.replica_size > 1 and name.endswith("attention.wqkv.weight"):
+            tp.replica_all_reduce_(self.g[name][self.local_g * self.spec.head_dim:])
 
     def embedding_backward(self, tokens, dh, accumulate: bool, emit, extra=None):
         sp, g, tp = self.spec, self.g, self.tp

@@ -216,9 +216,9 @@ class Trainer:
         self.opt.wait_all_gathers()
 
     def _grad_ready(self, name: str) -> None:
-        ps = self.store.by_name.get(name)
-        if ps is not None and ps.is_norm and self.tp_ctx.sequence_parallel:
-            self.tp_ctx.all_reduce_(self.store.grads[name])
+        """The gradient of ``name`` is complete on this rank (last micro-batch): finish it over
+        the tensor-parallel group where that is needed, then hand it to the bucket reducer."""
+        self.model.finalize_grad(name)
         self.reducer.on_grad_ready(name)
 
     @torch.no_grad()

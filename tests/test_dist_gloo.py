@@ -76,14 +76,14 @@ def test_dp2_matches_gradient_accumulation_and_loss_decreases():
 
 
 # ------------------------------------------------------------------------------------------
-def _tp_worker(rank, world, sp, steps, tp=2, heads=4):
+def _tp_worker(rank, world, sp, steps, tp=2, heads=4, micro_batches=1):
     from forgetrain_b200.parallel.topology import init_topology
     from forgetrain_b200.trainer import Trainer
     spec = _spec(tie_embeddings=False, num_attention_heads=heads)
     topo = init_topology(tp, device="cpu", num_kv_groups=spec.num_query_groups)
     tr = Trainer(spec, _cfg(spec, tensor_parallel_size=tp, sequence_parallel=sp), topo, seq_length=64,
                  micro_batch_size=2, seed=0)
-    data = _batches(7, 1, 2, 64, spec.vocab_size)
+    data = _batches(7, micro_batches, 2, 64, spec.vocab_size)
     losses, norms = [], []
     for _ in range(steps):
         out = tr.train_step(data)
@@ -143,6 +143,23 @@ def test_tp4_with_replicated_kv_heads_matches_tp1():
         out = tr.train_step(data)
         assert float(out["loss"]) == pytest.approx(res[0][0][i], abs=3e-4)
         assert float(out["grad_norm"]) == pytest.approx(res[0][1][i], rel=2e-3)
+
+
+def test_tp4_with_replicated_kv_heads_and_gradient_accumulation_matches_tp1():
+    """The sum of the k / v gradients over the replicas of a KV group is taken once, when the
+    gradient is complete: summing the buffer after every micro-batch would count the earlier
+    micro-batches once per replica (the first loss after an update would still agree, the
+    gradient norm and everything after it would not)."""
+    from forgetrain_b200.parallel.topology import Topology
+    from forgetrain_b200.trainer import Trainer
+    res = run_ranks(_tp_worker, 4, True, 3, 4, 8, 3)
+    spec = _spec(tie_embeddings=False, num_attention_heads=8)
+    tr = Trainer(spec, _cfg(spec), Topology(), seq_length=64, micro_batch_size=2, seed=0)
+    data = _batches(7, 3, 2, 64, spec.vocab_size)
+    for i in range(3):
+        out = tr.train_step(data)
+        assert float(out["loss"]) == pytest.approx(res[0][0][i], abs=5e-6)
+        assert float(out["grad_norm"]) == pytest.approx(res[0][1][i], rel=5e-6)
 
 
 # ------------------------------------------------------------------------------------------
