@@ -134,6 +134,11 @@ class StreamingTokenLoader:
         self._order_epoch, self._order = -1, None
         self._history: dict[int, dict] = {}
 
+    # every data-parallel rank walks its own documents: a checkpoint has to keep one state per rank
+    # (see pack_rank_states / select_rank_state); a packed or synthetic source is positioned by the
+    # number of batches drawn alone, which is the same on every rank
+    per_rank_state = True
+
     def __iter__(self):
         return self
 
@@ -192,6 +197,28 @@ class StreamingTokenLoader:
             self.epoch, self.pos = int(st["epoch"]), int(st["pos"])
             self.buf = list(st.get("buf", []))
             self.batches_drawn = int(st.get("batches_drawn", 0))
+
+
+def pack_rank_states(states: list[dict]) -> dict:
+    """The ``dataloader_state`` entry of a checkpoint for a source with ``per_rank_state``: the
+    states of all data-parallel ranks, in rank order."""
+    return {"kind": "per_rank", "dp_size": len(states), "ranks": list(states)}
+
+
+def select_rank_state(st: dict | None, dp_rank: int, dp_size: int, log=None) -> dict:
+    """What ``source.load_state_dict`` gets on this rank. A per-rank entry written at another
+    data-parallel size cannot be mapped (the ranks' document slices differ): the stream then starts
+    at the beginning of the pass the first rank was in, and ``log`` is told."""
+    if not st or st.get("kind") != "per_rank":
+        return st or {}
+    if int(st["dp_size"]) == dp_size:
+        return st["ranks"][dp_rank]
+    if log is not None:
+        log(f"dataloader state was written by {st['dp_size']} data-parallel ranks, this run has {dp_size}: "
+            f"each rank restarts its document stream at the beginning of the current pass")
+    first = st["ranks"][0]
+    return {"kind": first.get("kind"), "epoch": first.get("epoch", 0), "pos": 0, "buf": [],
+            "batches_drawn": first.get("batches_drawn", 0)}
 
 
 _COMMON_TEXT_COLUMNS = ("text", "content", "input", "sentence", "document")

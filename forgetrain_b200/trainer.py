@@ -501,7 +501,9 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
         state = trainer.load(resume)
         start_step = int(state.get("step", 0))
         if hasattr(source, "load_state_dict"):
-            source.load_state_dict(state.get("dataloader_state") or {})
+            from .data.hf_dataloader import select_rank_state
+            source.load_state_dict(select_rank_state(state.get("dataloader_state"), topo.dp_rank,
+                                                     topo.dp_size, log=lambda m: _log(topo, m)))
         _log(topo, f"resumed from {resume} at step {start_step}")
     consumed = int(getattr(source, "batches_drawn", 0))   # batches the model has actually seen
     prefetch = DataPrefetcher(source, topo.device, depth=cfg.data_prefetch_depth)
@@ -578,6 +580,12 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
                 ds = dict(getattr(source, "state_dict", dict)())
                 if "batches_drawn" in ds:   # the prefetcher reads ahead: record what was consumed
                     ds["batches_drawn"] = consumed
+            if getattr(source, "per_rank_state", False) and topo.dp_size > 1:
+                # every data-parallel rank is somewhere else in its own documents
+                from .data.hf_dataloader import pack_rank_states
+                states = [None] * topo.dp_size
+                dist.all_gather_object(states, ds, group=topo.dp_group)
+                ds = pack_rank_states(states)
             trainer.save(save_dir, done, dataloader_state=ds)
     ckpt.wait_for_async_save()
     if profiler:

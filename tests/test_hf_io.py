@@ -343,3 +343,58 @@ def test_cli_trains_on_local_files_with_a_saved_tokenizer(tmp_path):
     losses = [float(x) for x in __import__("re").findall(r"\| loss ([0-9.E+-]+)", r.stdout)]
     # 203 distinct token ids out of a 4096-entry vocabulary: the loss drops fast below ln(4096)
     assert len(losses) == 3 and losses[-1] < losses[0]
+
+
+def test_per_rank_stream_states_are_packed_and_selected():
+    from forgetrain_b200.data.hf_dataloader import pack_rank_states, select_rank_state
+    states = [{"kind": "stream", "epoch": 1, "pos": 5 + r, "buf": [r], "batches_drawn": 9} for r in range(4)]
+    packed = pack_rank_states(states)
+    assert packed["kind"] == "per_rank" and packed["dp_size"] == 4
+    assert select_rank_state(packed, 2, 4) == states[2]
+    notes = []
+    other = select_rank_state(packed, 1, 2, log=notes.append)
+    assert other == {"kind": "stream", "epoch": 1, "pos": 0, "buf": [], "batches_drawn": 9}
+    assert len(notes) == 1 and "4 data-parallel ranks" in notes[0]
+    # states that are the same on every rank pass through untouched
+    plain = {"kind": "packed", "batches_drawn": 7}
+    assert select_rank_state(plain, 3, 8) is plain and select_rank_state(None, 0, 1) == {}
+
+
+def test_streamed_documents_resume_on_every_data_parallel_rank(tmp_path):
+    """Two ranks stream their own halves of a local corpus (`--hf-stream`); the checkpoint keeps one
+    stream position per rank, so the resumed job sees exactly the batches the uninterrupted one saw
+    (with rank 0's position on every rank, rank 1 would re-read other documents)."""
+    import json
+    import re
+    import socket
+    import subprocess
+    import sys
+    from pathlib import Path
+    words = [f"w{i}" for i in range(300)]
+    _word_tokenizer(tmp_path / "tok", words)
+    g = torch.Generator().manual_seed(0)
+    with open(tmp_path / "corpus.jsonl", "w") as f:
+        for _ in range(400):
+            n = int(torch.randint(5, 90, (1,), generator=g))
+            f.write(json.dumps({"text": " ".join(words[i] for i in torch.randint(0, 300, (n,), generator=g).tolist())}) + "\n")
+    root = Path(__file__).resolve().parent.parent
+
+    def run(command, steps, *extra):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                            "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "training_engine_tensor",
+                            command, "--model", "tiny", "--device", "cpu", "--dtype", "fp32", "--micro-batch-size", "2",
+                            "--global-batch-size", "8", "--seq-length", "64", "--seed", "0", "--num-steps", str(steps),
+                            "--hf-dataset", "local", "--hf-data-files", str(tmp_path / "corpus.jsonl"),
+                            "--hf-data-format", "json", "--tokenizer-path", str(tmp_path / "tok"), "--hf-stream", *extra],
+                           cwd=root, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+        return {int(m.group(1)): float(m.group(2)) for m in re.finditer(r"iteration +(\d+) \| loss ([0-9.E+-]+)", r.stdout)}
+
+    whole = run("pretrain", 5, "--random-init", "--save-dir", str(tmp_path / "run"), "--save-interval", "3")
+    st = torch.load(tmp_path / "run" / "step_0000003" / "training_state.pt", weights_only=False)["dataloader_state"]
+    assert st["kind"] == "per_rank" and st["dp_size"] == 2 and st["ranks"][0] != st["ranks"][1]
+    resumed = run("train", 2, "--resume", str(tmp_path / "run" / "step_0000003"))
+    assert resumed == {4: whole[4], 5: whole[5]}
