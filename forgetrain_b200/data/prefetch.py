@@ -33,6 +33,10 @@ class DataPrefetcher:
         self.exhausted = False
         self.skipped = 0
         self.bytes_last = 0
+        # batches taken from the source so far (skipped ones included), and how many of them lie
+        # at or before the batch handed out last: the position a checkpoint has to record
+        self.drawn = 0
+        self.consumed_from_source = 0
 
     def _fetch_one(self) -> bool:
         while True:
@@ -41,6 +45,7 @@ class DataPrefetcher:
             except StopIteration:
                 self.exhausted = True
                 return False
+            self.drawn += 1
             m = host.get("loss_mask")
             if self.skip_all_masked and m is not None and float(m.sum()) == 0.0:
                 self.skipped += 1
@@ -58,7 +63,7 @@ class DataPrefetcher:
         else:
             dev = {k: (v.to(self.device) if torch.is_tensor(v) else v) for k, v in host.items()}
             ev = None
-        self.queue.append((dev, ev, host, nbytes))
+        self.queue.append((dev, ev, host, nbytes, self.drawn))
         return True
 
     def _fill(self) -> None:
@@ -73,7 +78,8 @@ class DataPrefetcher:
         self._fill()
         if not self.queue:
             raise StopIteration
-        dev, ev, host, nbytes = self.queue.popleft()
+        dev, ev, host, nbytes, position = self.queue.popleft()
+        self.consumed_from_source = position
         if ev is not None:
             if self.cuda:
                 cur = torch.cuda.current_stream()

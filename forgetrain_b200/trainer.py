@@ -505,7 +505,7 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
             source.load_state_dict(select_rank_state(state.get("dataloader_state"), topo.dp_rank,
                                                      topo.dp_size, log=lambda m: _log(topo, m)))
         _log(topo, f"resumed from {resume} at step {start_step}")
-    consumed = int(getattr(source, "batches_drawn", 0))   # batches the model has actually seen
+    consumed_at_start = consumed = int(getattr(source, "batches_drawn", 0))
     prefetch = DataPrefetcher(source, topo.device, depth=cfg.data_prefetch_depth)
     profiler = profiler_from_config(cfg, rank=topo.rank)
     tokens_per_step = micro_batch_size * seq_length * num_local_microbatches * topo.dp_size
@@ -529,7 +529,9 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
         if profiler:
             profiler.begin_step(step)
         mbs = [next(prefetch) for _ in range(num_local_microbatches)]
-        consumed += num_local_microbatches
+        # position in the source of the last batch the model sees this step (all-masked batches
+        # that the prefetcher dropped on the way count, what it has read ahead does not)
+        consumed = consumed_at_start + prefetch.consumed_from_source
         if dump_inputs_dir and topo.rank == 0:
             Path(dump_inputs_dir).mkdir(parents=True, exist_ok=True)
             torch.save({k: v.cpu() for k, v in mbs[0].items()},

@@ -465,3 +465,17 @@ def test_constructor_rejects_an_empty_range(tmp_path):
         StepProfiler(3, 3, str(tmp_path / "p.json"), use_cuda=False)
     with pytest.raises(ValueError):
         StepProfiler(4, 2, str(tmp_path / "p.json"), use_cuda=False)
+
+
+def test_the_checkpoint_position_counts_dropped_batches_but_not_the_read_ahead():
+    """A resumed source must continue right after the last batch the model saw: batches the
+    prefetcher dropped on the way there have been passed, batches it has only read ahead have not."""
+    pf, _ = _pf(_batches(10, masked={1, 2, 6}), 3)
+    assert pf.consumed_from_source == 0
+    seen = []
+    for _ in range(4):
+        b = next(pf)
+        seen.append((int(b["tokens"][0, 0]), pf.consumed_from_source))
+    #   batch 0 is item 1 of the source; batch 3 comes after two dropped ones: item 4; ...
+    assert seen == [(0, 1), (3, 4), (4, 5), (5, 6)]
+    assert pf.drawn > pf.consumed_from_source                   # the read-ahead is further along
