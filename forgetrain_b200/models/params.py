@@ -329,17 +329,49 @@ class ParamStore:
             del full, shard
 
     def load_named(self, tensors: dict[str, torch.Tensor], full_tensors: bool = True,
-                   keep_missing: tuple[str, ...] = ()) -> None:
-        """Copy named tensors into the flat buffer. A parameter whose name starts with one of
-        ``keep_missing`` may be absent from ``tensors`` and then keeps its current value (the
-        MTP head when the source is a plain language-model checkpoint)."""
-        for ps in self.specs:
-            if ps.name not in tensors and ps.name.startswith(keep_missing) and keep_missing:
+                   keep_missing: tuple[str, ...] = (), log=None) -> None:
+        """Copy named tensors into the flat buffer, after checking that they describe THIS model.
+
+        * A parameter whose name starts with one of ``keep_missing`` may be absent and then keeps
+          its current value (the MTP head when the source is a plain language-model checkpoint).
+        * ``output.weight`` absent from the source of a run with untied tables is taken from the
+          embedding: that is what a checkpoint with tied tables means.
+        * Anything else that is missing, a tensor the model has no parameter for (``mtp.*`` of a
+          source with an MTP head excepted: the auxiliary head is dropped), or a shape that does
+          not fit is an error that names the parameter, instead of a partial load.
+        """
+        note = log or (lambda m: None)
+        own = {ps.name for ps in self.specs}
+        extra = sorted(n for n in tensors if n not in own and not n.startswith("mtp."))
+        if extra:
+            raise ValueError(f"the checkpoint has {len(extra)} tensors this model has no parameter for "
+                             f"({', '.join(extra[:4])}{', ...' if len(extra) > 4 else ''}): another "
+                             f"--model, --num-layers or --tie-embeddings than the run that wrote it?")
+        if any(n.startswith("mtp.") and n not in own for n in tensors):
+            note("the checkpoint's MTP head is not used by this run and is dropped")
+        missing, plan = [], []
+        for ps in self.specs:               # first pass: everything is checked before anything is copied
+            if ps.name in tensors:
+                t = tensors[ps.name]
+            elif keep_missing and ps.name.startswith(keep_missing):
                 continue
-            t = tensors[ps.name]
+            elif ps.name == "output.weight" and "tok_embeddings.weight" in tensors:
+                note("the checkpoint ties the output table to the embedding: output.weight starts as its copy")
+                t = tensors["tok_embeddings.weight"]
+            else:
+                missing.append(ps.name)
+                continue
             if full_tensors:
                 t = shard_for_tp(ps, t, self.spec, self.tp_rank, self.tp_size)
-            self.params[ps.name].copy_(t.to(self.dtype))
+            if tuple(t.shape) != tuple(self.params[ps.name].shape):
+                raise ValueError(f"{ps.name}: the checkpoint holds {tuple(t.shape)}, this model needs "
+                                 f"{tuple(self.params[ps.name].shape)}")
+            plan.append((ps.name, t))
+        if missing:
+            raise KeyError(f"the checkpoint lacks {len(missing)} parameters of this model "
+                           f"({', '.join(missing[:4])}{', ...' if len(missing) > 4 else ''})")
+        for name, t in plan:
+            self.params[name].copy_(t.to(self.dtype))
 
     def named_cpu_params(self) -> dict[str, torch.Tensor]:
         return {ps.name: self.params[ps.name].detach().to("cpu").clone() for ps in self.specs}

@@ -308,8 +308,16 @@ class ShardedAdamW:
                     a, z = max(p_lo, s_lo), min(p_lo + n_el, s_hi)
                     if z <= a:
                         continue
-                    t = src[name].reshape(-1)[a - p_lo:z - p_lo]
-                    flat[base + a - s_lo:base + z - s_lo].copy_(t.to(flat.device))
+                    dst = flat[base + a - s_lo:base + z - s_lo]
+                    if name not in src:
+                        # a parameter the source run did not have (an untied output table, a new
+                        # MTP head): master weights from the loaded parameters, moments at zero
+                        if field == "master_weights":
+                            dst.copy_(self.store.flat_params[a:z].float())
+                        else:
+                            dst.zero_()
+                        continue
+                    dst.copy_(src[name].reshape(-1)[a - p_lo:z - p_lo].to(flat.device))
         self.step_count = int(step_count)
         if self.step_dev is not None:
             self.step_dev.fill_(self.step_count)

@@ -378,6 +378,7 @@ class Trainer:
 
     def load(self, path) -> dict:
         p = Path(path)
+        note = (lambda m: print(f"[load] {m}", flush=True)) if self.topo.rank == 0 else (lambda m: None)
         from .ckpt import megatron_import as mg
         if mg.is_megatron_root(p):
             # a Megatron export: full tensors by Megatron names (+ optional Adam state); every
@@ -385,7 +386,7 @@ class Trainer:
             log = print if self.topo.rank == 0 else (lambda *_: None)
             n_mtp = self.cfg.mtp_num_layers
             tensors = mg.load_megatron_checkpoint(p, self.spec, n_mtp, log=log)
-            self.store.load_named(tensors, full_tensors=True)
+            self.store.load_named(tensors, full_tensors=True, keep_missing=("mtp.",), log=log)
             ost = mg.load_megatron_optimizer_state(p, log=log)
             if ost is not None:
                 from .models.params import shard_for_tp
@@ -406,7 +407,7 @@ class Trainer:
         if hf_import.is_hf_folder(p):
             # a HuggingFace export: full tensors, no optimizer state; every rank keeps its shard
             self.store.load_named(hf_import.load_hf_folder(p, self.spec), full_tensors=True,
-                                  keep_missing=("mtp.",))
+                                  keep_missing=("mtp.",), log=note)
             self.opt.sync_master_from_params()
             return {"step": 0, "num_samples": 0, "dataloader_state": None}
         if p.is_dir() and not any(p.glob("rank_*.pt")) and not (p / "training_state.pt").exists():
@@ -418,7 +419,7 @@ class Trainer:
         if rank_files and len(rank_files) == tp and tp > 1:
             # same tensor-parallel degree: every rank reads its own shard
             state = torch.load(p / f"rank_{tpr}.pt", map_location="cpu", weights_only=False)
-            self.store.load_named(state["params"], full_tensors=False)
+            self.store.load_named(state["params"], full_tensors=False, keep_missing=("mtp.",), log=note)
         else:
             # a checkpoint of another tensor-parallel degree (or of none): rebuild the full
             # tensors, then keep this rank's shard of parameters and optimizer state
@@ -438,7 +439,7 @@ class Trainer:
                     state["optimizer_state"] = merged
             else:
                 state = ckpt.load_resume_checkpoint(p, expected_vocab=self.spec.vocab_size)
-            self.store.load_named(state["params"], full_tensors=True)
+            self.store.load_named(state["params"], full_tensors=True, keep_missing=("mtp.",), log=note)
             ost = state.get("optimizer_state")
             if ost and tp > 1:
                 by_name = {ps.name: ps for ps in self.store.specs}

@@ -96,3 +96,80 @@ def test_async_save_snapshots_host_tensors(tmp_path, monkeypatch):
     ck.wait_for_async_save()
     st = ck.load_resume_checkpoint(tmp_path / "step_0000001")
     assert float(st["params"]["w"].sum()) == 0.0
+
+
+# ---------------------------------------------------------------------------------------------
+# loading named tensors into a model: what is accepted, what is refused
+# ---------------------------------------------------------------------------------------------
+def _store(**kw):
+    from forgetrain_b200.config import load_model_spec
+    from forgetrain_b200.models.params import ParamStore
+    base = dict(num_layers=2, vocab_size=128, hidden_size=128, ffn_hidden_size=256, num_attention_heads=4,
+                num_query_groups=2, head_dim=32)
+    mtp = kw.pop("mtp", 0)
+    base.update(kw)
+    st = ParamStore(load_model_spec("tiny", **base), "cpu", torch.float32, mtp_num_layers=mtp)
+    st.init_random(1)
+    return st
+
+
+def test_a_checkpoint_of_another_architecture_is_refused_by_name():
+    big, small = _store(num_layers=3, tie_embeddings=False), _store(tie_embeddings=False)
+    tensors = big.named_cpu_params()
+    with pytest.raises(ValueError, match=r"6 tensors this model has no parameter for \(layers\.2\."):
+        small.load_named(tensors)
+    with pytest.raises(KeyError, match=r"lacks 6 parameters of this model \(layers\.2\."):
+        big.load_named(small.named_cpu_params())
+    wide = _store(ffn_hidden_size=512, tie_embeddings=False).named_cpu_params()
+    with pytest.raises(ValueError, match=r"feed_forward\.wfc1\.weight: the checkpoint holds \(1024, 128\), this model needs \(512, 128\)"):
+        small.load_named(wide)
+    # a refused checkpoint leaves the model as it was, also when the misfit is its last tensor
+    before = small.flat_params.clone()
+    odd = _store(tie_embeddings=False).named_cpu_params()
+    odd["tok_embeddings.weight"] = torch.zeros(64, 128)
+    with pytest.raises(ValueError, match="tok_embeddings.weight"):
+        small.load_named(odd)
+    assert torch.equal(small.flat_params, before)
+
+
+def test_tied_checkpoint_into_untied_run_and_plain_checkpoint_into_mtp_run():
+    tied, untied = _store(tie_embeddings=True), _store(tie_embeddings=False)
+    notes = []
+    untied.load_named(tied.named_cpu_params(), log=notes.append)
+    assert torch.equal(untied.params["output.weight"], tied.params["tok_embeddings.weight"])
+    assert len(notes) == 1 and "output.weight starts as its copy" in notes[0]
+    # the other way would throw the trained output table away
+    with pytest.raises(ValueError, match="output.weight"):
+        tied.load_named(untied.named_cpu_params())
+    # an MTP run started from a plain checkpoint keeps its freshly initialised head ...
+    mtp = _store(tie_embeddings=False, mtp=1)
+    head = mtp.params["mtp.layers.0.eh_proj.weight"].clone()
+    mtp.load_named(untied.named_cpu_params(), keep_missing=("mtp.",))
+    assert torch.equal(mtp.params["mtp.layers.0.eh_proj.weight"], head)
+    assert torch.equal(mtp.params["layers.1.attention.wo.weight"], untied.params["layers.1.attention.wo.weight"])
+    # ... and without the permission the missing head is an error
+    with pytest.raises(KeyError, match="mtp.layers.0"):
+        mtp.load_named(untied.named_cpu_params())
+    # a plain run drops the head of an MTP checkpoint, and says so
+    notes.clear()
+    untied.load_named(mtp.named_cpu_params(), log=notes.append)
+    assert notes == ["the checkpoint's MTP head is not used by this run and is dropped"]
+
+
+def test_optimizer_state_without_a_parameter_starts_that_parameter_fresh():
+    from forgetrain_b200.optim.adamw import ShardedAdamW
+    from forgetrain_b200.parallel.buckets import compute_grad_buckets
+    tied, untied = _store(tie_embeddings=True), _store(tie_embeddings=False)
+    a = ShardedAdamW(tied, compute_grad_buckets(tied.entries(), 1, 10 ** 9), 1, 0, None)
+    tied.flat_grads.normal_()
+    a.compute_clip(tied.flat_grads.pow(2).sum().reshape(1))
+    a.step(1e-3)
+    state = a.gather_full_state()
+    untied.load_named(tied.named_cpu_params())
+    b = ShardedAdamW(untied, compute_grad_buckets(untied.entries(), 1, 10 ** 9), 1, 0, None)
+    b.load_full_state(state, 1)
+    got = b.gather_full_state()
+    assert torch.equal(got["exp_avg"]["layers.0.attention.wo.weight"], state["exp_avg"]["layers.0.attention.wo.weight"])
+    assert not got["exp_avg"]["output.weight"].any() and not got["exp_avg_sq"]["output.weight"].any()
+    assert torch.equal(got["master_weights"]["output.weight"], untied.params["output.weight"])
+    assert b.step_count == 1
