@@ -125,7 +125,7 @@ def test_a_checkpoint_of_another_architecture_is_refused_by_name():
         small.load_named(wide)
     # a refused checkpoint leaves the model as it was, also when the misfit is its last tensor
     before = small.flat_params.clone()
-    odd = _store(tie_embeddings=False).named_cpu_params()
+    odd = {n: t * 2 for n, t in _store(tie_embeddings=False).named_cpu_params().items()}
     odd["tok_embeddings.weight"] = torch.zeros(64, 128)
     with pytest.raises(ValueError, match="tok_embeddings.weight"):
         small.load_named(odd)
