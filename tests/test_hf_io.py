@@ -398,3 +398,27 @@ def test_streamed_documents_resume_on_every_data_parallel_rank(tmp_path):
     assert st["kind"] == "per_rank" and st["dp_size"] == 2 and st["ranks"][0] != st["ranks"][1]
     resumed = run("train", 2, "--resume", str(tmp_path / "run" / "step_0000003"))
     assert resumed == {4: whole[4], 5: whole[5]}
+
+
+def test_loader_builder_reads_local_files_itself_when_datasets_cannot_be_imported(tmp_path, monkeypatch, capsys):
+    import json
+    import sys
+
+    class Tok:
+        eos_token_id = 9
+
+        def __call__(self, text, add_special_tokens=False):
+            return {"input_ids": [ord(c) % 50 + 10 for c in text]}
+    (tmp_path / "c.jsonl").write_text("\n".join(json.dumps({"body": "abcdefgh" * 6}) for _ in range(6)) + "\n")
+    monkeypatch.setitem(sys.modules, "datasets", None)          # `import datasets` now raises ImportError
+    args = types.SimpleNamespace(hf_text_field=None, hf_text_template=None, max_packed_rows=None,
+                                 tokenizer_path=None, hf_data_files=str(tmp_path / "c.jsonl"),
+                                 hf_data_format="json", hf_dataset="local", hf_dataset_split="train",
+                                 hf_dataset_config=None)
+    loader = build_hf_dataloader(args, _spec(), 1, 16, Topology(), tokenizer=Tok())
+    out = capsys.readouterr().out
+    assert "`datasets` is not installed: read 6 rows" in out and "text_fields=['body']" in out
+    assert loader.rows.shape[1] == 17 and loader.rows.shape[0] >= 6
+    args.hf_data_files = None                                   # a hub dataset does need the package
+    with pytest.raises(SystemExit, match="datasets"):
+        build_hf_dataloader(args, _spec(), 1, 16, Topology(), tokenizer=Tok())
