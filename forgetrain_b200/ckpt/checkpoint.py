@@ -133,6 +133,9 @@ def load_resume_checkpoint(path: str | os.PathLike, expected_vocab: int | None =
     """Load a checkpoint (a ``training_state.pt`` file, a step directory, or a save root whose
     latest step is taken). Validates the format version and the vocabulary size."""
     p = Path(path)
+    if not p.exists():
+        raise FileNotFoundError(f"checkpoint {str(p)!r} does not exist (expected a training_state.pt file, a "
+                                f"step_<N> directory or a save directory that holds some)")
     if p.is_dir():
         f = latest_checkpoint(p)
         if f is None:

@@ -136,6 +136,9 @@ def load_model_spec(name_or_path: str | os.PathLike = "tiny", **overrides) -> Mo
     """Load a built-in spec by name (``tiny``, ``0.5b``, ``8b``) or a ``model_spec.toml`` path."""
     key = str(name_or_path).lower()
     path = SPEC_DIR / BUILTIN_SPECS[key] if key in BUILTIN_SPECS else Path(name_or_path)
+    if not path.is_file():
+        raise FileNotFoundError(f"model {str(name_or_path)!r} is neither a built-in spec "
+                                f"({', '.join(sorted(BUILTIN_SPECS))}) nor a model_spec.toml file")
     with open(path, "rb") as f:
         doc = tomllib.load(f)
     fields = {f.name for f in dataclasses.fields(ModelSpec)}
