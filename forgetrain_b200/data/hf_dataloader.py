@@ -206,13 +206,17 @@ def pack_rank_states(states: list[dict]) -> dict:
 
 
 def select_rank_state(st: dict | None, dp_rank: int, dp_size: int, log=None) -> dict:
-    """What ``source.load_state_dict`` gets on this rank. A per-rank entry written at another
-    data-parallel size cannot be mapped (the ranks' document slices differ): the stream then starts
-    at the beginning of the pass the first rank was in, and ``log`` is told."""
+    """What ``source.load_state_dict`` gets on this rank. Written at another data-parallel size,
+    the entry of a source that is positioned by a count of batches (synthetic, packed) is taken
+    from the first rank; that of a streamed dataset cannot be mapped (the ranks' document slices
+    differ): the stream then starts at the beginning of the pass the first rank was in, and
+    ``log`` is told."""
     if not st or st.get("kind") != "per_rank":
         return st or {}
     if int(st["dp_size"]) == dp_size:
         return st["ranks"][dp_rank]
+    if (st["ranks"][0] or {}).get("kind") != "stream":
+        return st["ranks"][0] or {}      # positioned by a count of batches: any rank's state will do
     if log is not None:
         log(f"dataloader state was written by {st['dp_size']} data-parallel ranks, this run has {dp_size}: "
             f"each rank restarts its document stream at the beginning of the current pass")

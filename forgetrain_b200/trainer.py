@@ -583,8 +583,9 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
                 ds = dict(getattr(source, "state_dict", dict)())
                 if "batches_drawn" in ds:   # the prefetcher reads ahead: record what was consumed
                     ds["batches_drawn"] = consumed
-            if getattr(source, "per_rank_state", False) and topo.dp_size > 1:
-                # every data-parallel rank is somewhere else in its own documents
+            if topo.dp_size > 1 and isinstance(ds, dict):
+                # every data-parallel rank may be somewhere else in its own data: a streamed
+                # dataset always is, any source is once a rank has dropped an all-masked batch
                 from .data.hf_dataloader import pack_rank_states
                 states = [None] * topo.dp_size
                 dist.all_gather_object(states, ds, group=topo.dp_group)

@@ -355,6 +355,9 @@ def test_per_rank_stream_states_are_packed_and_selected():
     other = select_rank_state(packed, 1, 2, log=notes.append)
     assert other == {"kind": "stream", "epoch": 1, "pos": 0, "buf": [], "batches_drawn": 9}
     assert len(notes) == 1 and "4 data-parallel ranks" in notes[0]
+    counted = pack_rank_states([{"kind": "packed", "batches_drawn": 7}, {"kind": "packed", "batches_drawn": 7}])
+    assert select_rank_state(counted, 0, 1, log=notes.append) == {"kind": "packed", "batches_drawn": 7}
+    assert len(notes) == 1                                      # no note: nothing is lost
     # states that are the same on every rank pass through untouched
     plain = {"kind": "packed", "batches_drawn": 7}
     assert select_rank_state(plain, 3, 8) is plain and select_rank_state(None, 0, 1) == {}
