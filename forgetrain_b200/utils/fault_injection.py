@@ -45,6 +45,12 @@ def maybe_fail(next_step: int, rank: int, env=None) -> None:
             return
         os.write(fd, f"failed before step {next_step} on rank {rank}\n".encode())
         os.close(fd)
+    try:        # leave with nothing of this rank in flight on a device
+        import torch
+        if torch.cuda.is_available() and torch.cuda.is_initialized():
+            torch.cuda.synchronize()
+    except ImportError:
+        pass
     if spec["exit"] is not None:
         os._exit(spec["exit"])
     raise InjectedFailure(f"injected failure before step {next_step} on rank {rank}")
