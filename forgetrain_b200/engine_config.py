@@ -50,6 +50,7 @@ class EngineConfig:
     # ---- activation recomputation (memory for time) ----
     recompute_attn: bool = False         # attention output / log-sum-exp rebuilt in backward
     recompute_mlp: bool = False          # FC1 output and SwiGLU activation rebuilt in backward
+    mask_vocab_padding: bool = False     # TP: keep the vocabulary's pad columns out of the softmax
     # ---- CUDA graphs ----
     forward_cuda_graph: bool = False
     step_cuda_graph: bool = False
@@ -121,6 +122,7 @@ _ENV_MAP: dict[str, tuple[str, Callable[[str], Any]]] = {
     "SEQUENCE_PARALLEL": ("sequence_parallel", lambda v: v.lower() in _BOOL_TRUE),
     "RECOMPUTE_ATTN": ("recompute_attn", lambda v: v.lower() in _BOOL_TRUE),
     "RECOMPUTE_MLP": ("recompute_mlp", lambda v: v.lower() in _BOOL_TRUE),
+    "MASK_VOCAB_PADDING": ("mask_vocab_padding", lambda v: v.lower() in _BOOL_TRUE),
     "FORWARD_CUDA_GRAPH": ("forward_cuda_graph", lambda v: v.lower() in _BOOL_TRUE),
     "STEP_CUDA_GRAPH": ("step_cuda_graph", lambda v: v.lower() in _BOOL_TRUE),
     "FULL_STEP_CUDA_GRAPH": ("full_step_cuda_graph", lambda v: v.lower() in _BOOL_TRUE),

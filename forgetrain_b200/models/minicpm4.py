@@ -182,8 +182,19 @@ class MiniCPM4:
         h, branch = self.forward_hidden(tokens, position_ids)
         return self.head_forward(h, branch)
 
+    # Under tensor parallelism the vocabulary shards are padded to a multiple of 8 rows; by default
+    # the pad columns are part of the softmax (Megatron's padded-vocabulary convention). True:
+    # their logits are set far below every real one before the loss, so they carry no probability
+    # and no gradient, and the loss is the one a run without tensor parallelism computes.
+    mask_vocab_padding = False
+    _PAD_LOGIT = -30000.0      # finite (no inf - inf in a running maximum), exp() of it is 0 in fp32
+
     def loss_and_dlogits(self, logits, labels, loss_mask, loss_scale: float):
         tp = self.tp
+        if self.mask_vocab_padding and tp.enabled:
+            real = self.spec.vocab_size - self.vocab_start      # real columns of this rank's shard
+            if real < logits.shape[1]:
+                logits[:, max(real, 0):] = self._PAD_LOGIT
         return ops.cross_entropy_fwd_bwd(
             logits, labels, loss_mask, loss_scale, vocab_start=self.vocab_start,
             stats_reduce=tp.stats_reduce if tp.enabled else None,

@@ -97,6 +97,7 @@ class Trainer:
             self.store.init_random(seed, cfg.init_scheme, cfg.init_std)
         self.model = MiniCPM4(spec, self.store, self.tp_ctx, max_seq_len=max_seq_len or seq_length,
                               recompute_attn=cfg.recompute_attn, recompute_mlp=cfg.recompute_mlp)
+        self.model.mask_vocab_padding = cfg.mask_vocab_padding
         self.mtp = None
         if cfg.mtp_num_layers > 0:
             from .models.mtp import MTPHead

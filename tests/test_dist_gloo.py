@@ -431,15 +431,17 @@ def test_module_level_topology_accessors_follow_init_topology():
 
 
 # ------------------------------------------------------------------------------------------
-def _padded_vocab_worker(rank, world, tp):
+def _padded_vocab_worker(rank, world, tp, mask=False, steps=1):
     from forgetrain_b200.parallel.topology import init_topology
     from forgetrain_b200.trainer import Trainer
     spec = _spec(vocab_size=500, tie_embeddings=False)
     topo = init_topology(tp, device="cpu")
-    tr = Trainer(spec, _cfg(spec, tensor_parallel_size=tp, sequence_parallel=tp > 1), topo,
-                 seq_length=64, micro_batch_size=2, seed=0)
+    tr = Trainer(spec, _cfg(spec, tensor_parallel_size=tp, sequence_parallel=tp > 1, mask_vocab_padding=mask),
+                 topo, seq_length=64, micro_batch_size=2, seed=0)
     data = _batches(7, 1, 2, 64, spec.vocab_size)
-    return float(tr.train_step(data)["loss"]), tr.model.vocab_rows
+    losses = [float(tr.train_step(data)["loss"]) for _ in range(steps)]
+    pad = tr.store.params["output.weight"][max(0, spec.vocab_size - tr.model.vocab_start):]
+    return (losses[0] if steps == 1 else losses), tr.model.vocab_rows, float(pad.abs().sum())
 
 
 def test_padded_vocabulary_rows_take_part_in_the_softmax_like_megatrons():
@@ -447,8 +449,21 @@ def test_padded_vocabulary_rows_take_part_in_the_softmax_like_megatrons():
     columns are in the softmax, so the first loss is above the TP = 1 loss by about
     log(1 + 12 / 500) (exactly that if every logit were zero)."""
     import math
-    one, rows1 = run_ranks(_padded_vocab_worker, 1, 1)[0]
-    two, rows2 = run_ranks(_padded_vocab_worker, 2, 2)[0]
+    one, rows1, _ = run_ranks(_padded_vocab_worker, 1, 1)[0]
+    two, rows2, _ = run_ranks(_padded_vocab_worker, 2, 2)[0]
     assert rows1 == 500 and rows2 == 256
     shift = two - one
     assert 0.5 * math.log(1 + 12 / 500) < shift < 1.2 * math.log(1 + 12 / 500), shift
+
+
+def test_masked_vocabulary_padding_gives_the_loss_of_a_run_without_tensor_parallelism():
+    """``mask_vocab_padding``: the pad columns carry no probability and no gradient, so TP = 2 over a
+    vocabulary of 500 follows TP = 1 to fp32 rounding and the pad rows of the output table stay
+    zero, where the default convention trains them."""
+    one = run_ranks(_padded_vocab_worker, 1, 1, True, 3)[0][0]
+    res = run_ranks(_padded_vocab_worker, 2, 2, True, 3)
+    for rank in range(2):
+        assert res[rank][0] == pytest.approx(one, abs=5e-6)
+    assert res[1][2] == 0.0                                   # rank 1 holds the 12 pad rows
+    default = run_ranks(_padded_vocab_worker, 2, 2, False, 3)
+    assert default[1][2] > 0.0
