@@ -28,7 +28,9 @@ Recovery
                     with ``NUM_STEPS`` reduced by N, so that a relaunched job ends where the
                     original one would have.
 ``MAX_RESTARTS=K``  the launcher stays in front of ``torch.distributed.run`` and, when it exits with
-                    an error, starts it again (at most K times) with ``AUTO_RESUME`` on. The
+                    an error, starts it again (at most K times) with ``AUTO_RESUME`` on. A SIGTERM
+                    sent to the launcher is passed on to the job (whose ranks finish their step,
+                    write a checkpoint and leave) and is not followed by a restart. The
                     reference has no recovery of its own (a failed job is resubmitted by hand with
                     ``RESUME_DIR``); this is that resubmission, automated.
 
@@ -287,8 +289,25 @@ def supervise(plan: LaunchPlan, job_env: dict, nproc_per_node, extra, max_restar
     newest finished checkpoint of ``SAVE_DIR``, fewer steps left) and start it again, at most
     ``max_restarts`` times. Returns the exit code of the last attempt. ``run(cmd, env) -> int`` is
     replaceable for tests."""
+    import signal
     import subprocess
-    run = run or (lambda cmd, env: subprocess.call(cmd, env=env))
+    stop = {"requested": False, "child": None}
+
+    def forward(signum, frame):           # a pre-emption notice goes to the job and ends the loop
+        stop["requested"] = True
+        if stop["child"] is not None and stop["child"].poll() is None:
+            stop["child"].send_signal(signum)
+
+    def run_child(cmd, env):
+        stop["child"] = subprocess.Popen(cmd, env=env)
+        return stop["child"].wait()
+
+    if run is None:
+        run = run_child
+        try:
+            signal.signal(signal.SIGTERM, forward)
+        except ValueError:                # not the main thread: leave the default behaviour
+            pass
     attempt = 0
     while True:
         steps = plan.cli_args[plan.cli_args.index("--num-steps") + 1] if "--num-steps" in plan.cli_args else None
@@ -296,7 +315,7 @@ def supervise(plan: LaunchPlan, job_env: dict, nproc_per_node, extra, max_restar
             print("=== nothing left to do: the newest checkpoint is at the last step ===", flush=True)
             return 0
         rc = run(plan.command(), worker_env(plan))
-        if rc == 0 or attempt >= max_restarts:
+        if rc == 0 or attempt >= max_restarts or stop["requested"]:
             return rc
         attempt += 1
         env = dict(job_env)

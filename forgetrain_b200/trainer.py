@@ -458,6 +458,40 @@ class Trainer:
         return state
 
 
+class _StopRequest:
+    """SIGTERM (a scheduler's pre-emption notice, also what ``torch.distributed.run`` forwards to its
+    workers) and SIGUSR1 ask the loop to stop: the running step is finished, every rank learns of
+    the request in the step's own all-reduce, a checkpoint is written when there is a
+    ``save_dir``, and the loop returns normally, so the job can be continued with ``--resume``
+    (or by the launcher's ``AUTO_RESUME``). Handlers are installed in the main thread only and the
+    previous ones put back afterwards."""
+
+    def __init__(self):
+        import signal
+        import threading
+        self.requested = False
+        self._old = {}
+        if threading.current_thread() is not threading.main_thread():
+            return
+        for sig in (signal.SIGTERM, signal.SIGUSR1):
+            try:
+                self._old[sig] = signal.signal(sig, self._handler)
+            except (ValueError, OSError):
+                pass
+
+    def _handler(self, signum, frame):
+        self.requested = True
+
+    def restore(self):
+        import signal
+        for sig, old in self._old.items():
+            try:
+                signal.signal(sig, old)
+            except (ValueError, OSError):
+                pass
+        self._old = {}
+
+
 class LossReadback:
     """Asynchronous read-back of (loss, grad_norm): 8 bytes, device -> pinned host."""
     nbytes = 8
@@ -522,6 +556,7 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
                f"seq={seq_length} microbatches={num_local_microbatches} dtype={cfg.dtype} "
                f"comm={cfg.comm} data={'synthetic' if data_source is None else 'custom'}")
     from .utils.fault_injection import maybe_fail
+    stop = _StopRequest()                    # SIGTERM / SIGUSR1: checkpoint after the running step
     for step in range(start_step, start_step + num_steps):
         maybe_fail(step + 1, topo.rank)      # recovery tests: FT_INJECT_FAILURE, host side only
         if cuda:
@@ -547,10 +582,11 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
             _lib.check_status(topo.device)
         else:
             dt = time.perf_counter() - t0
-        if topo.world > 1:  # step time = max over ranks
-            tt = torch.tensor([dt], dtype=torch.float64, device=topo.device)
+        stopping = stop.requested
+        if topo.world > 1:  # step time = max over ranks; a stop request of any rank is everybody's
+            tt = torch.tensor([dt, float(stopping)], dtype=torch.float64, device=topo.device)
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            dt = float(tt)
+            dt, stopping = float(tt[0]), bool(tt[1] > 0)
         if profiler:
             profiler.end_step()
         loss, gnorm = float(out["loss"]), float(out["grad_norm"])
@@ -576,8 +612,8 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
         if not math.isfinite(loss):
             raise FloatingPointError(f"non-finite loss at step {step + 1}")
         done = step + 1
-        if save_dir and ckpt.should_save_after_step(done, start_step + num_steps, save_interval,
-                                                    start_step):
+        if save_dir and (stopping or ckpt.should_save_after_step(done, start_step + num_steps,
+                                                                  save_interval, start_step)):
             if hasattr(source, "state_dict_at"):   # a stream cannot be rewound by a count alone
                 ds = source.state_dict_at(consumed)
             else:
@@ -592,6 +628,11 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
                 dist.all_gather_object(states, ds, group=topo.dp_group)
                 ds = pack_rank_states(states)
             trainer.save(save_dir, done, dataloader_state=ds)
+        if stopping:
+            _log(topo, f"[signal] stop requested: {'checkpoint written at' if save_dir else 'no --save-dir, leaving at'} "
+                       f"step {done} of {start_step + num_steps}")
+            break
+    stop.restore()
     ckpt.wait_for_async_save()
     if profiler:
         profiler.write()

@@ -84,3 +84,50 @@ def test_status_word_codes_have_messages():
     from forgetrain_b200.ops import _lib
     assert set(_lib.STATUS_MESSAGES) == {1, 2, 3, 4, 5, 6}
     assert "peer" in _lib.STATUS_MESSAGES[5]
+
+
+def test_sigterm_finishes_the_step_writes_a_checkpoint_and_leaves_normally(tmp_path):
+    """A pre-emption notice in the middle of a run: the process is sent SIGTERM once it has logged
+    a few iterations; it finishes the step it is in, saves, exits with code 0, and the saved step
+    resumes into the same losses as a run that was never interrupted."""
+    import re
+    import signal
+    import subprocess
+    import sys
+    import time
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    base = [sys.executable, "-u", "-m", "training_engine_tensor", "pretrain", "--model", "tiny", "--device", "cpu",
+            "--dtype", "fp32", "--micro-batch-size", "2", "--global-batch-size", "2", "--seq-length", "64",
+            "--seed", "0"]
+    p = subprocess.Popen(base + ["--num-steps", "400", "--save-dir", str(tmp_path / "run")], cwd=root,
+                         stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    lines = []
+    deadline = time.time() + 300
+    while time.time() < deadline:
+        line = p.stdout.readline()
+        if not line:
+            break
+        lines.append(line)
+        if "iteration        3 " in line:
+            p.send_signal(signal.SIGTERM)
+            break
+    rest, _ = p.communicate(timeout=300)
+    out = "".join(lines) + rest
+    assert p.returncode == 0, out[-2000:]
+    m = re.search(r"\[signal\] stop requested: checkpoint written at step (\d+) of 400", out)
+    assert m, out[-2000:]
+    stopped = int(m.group(1))
+    assert 3 <= stopped < 400 and (tmp_path / "run" / f"step_{stopped:07d}" / "training_state.pt").exists()
+    assert f"iteration {stopped + 1:8d} " not in out
+    losses = {int(a): float(b) for a, b in re.findall(r"iteration +(\d+) \| loss ([0-9.E+-]+)", out)}
+    r = subprocess.run(base[:4] + ["train"] + base[5:] + ["--num-steps", "2", "--resume",
+                                                          str(tmp_path / "run" / f"step_{stopped:07d}")],
+                       cwd=root, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    resumed = {int(a): float(b) for a, b in re.findall(r"iteration +(\d+) \| loss ([0-9.E+-]+)", r.stdout)}
+    whole = subprocess.run(base + ["--num-steps", str(stopped + 2)], cwd=root, capture_output=True, text=True,
+                           timeout=300)
+    ref = {int(a): float(b) for a, b in re.findall(r"iteration +(\d+) \| loss ([0-9.E+-]+)", whole.stdout)}
+    assert {k: ref[k] for k in losses} == losses
+    assert resumed == {stopped + 1: ref[stopped + 1], stopped + 2: ref[stopped + 2]}

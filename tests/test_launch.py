@@ -257,3 +257,49 @@ def test_a_rank_that_fails_mid_run_is_recovered_by_the_launcher_and_the_run_ends
         assert torch.equal(a["params"][name], b["params"][name]), name
     for name in b["optimizer_state"]["exp_avg_sq"]:
         assert torch.equal(a["optimizer_state"]["exp_avg_sq"][name], b["optimizer_state"]["exp_avg_sq"][name])
+
+
+def test_a_stop_signal_to_the_supervising_launcher_reaches_the_ranks_and_is_not_followed_by_a_restart(tmp_path):
+    """SIGTERM to the launcher (what a scheduler sends before it takes the node away): it is passed
+    on to ``torch.distributed.run`` and from there to both ranks, which agree on a step, write its
+    checkpoint and leave; the launcher does not start the job again although restarts are allowed.
+    A relaunch with ``AUTO_RESUME`` then continues from that step."""
+    import re
+    import signal
+    import socket
+    import time
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ)
+    env.update({"STAGE": "stable", "SYNTHETIC_DATA": "1", "MODEL": "tiny", "NUM_STEPS": "400",
+                "GLOBAL_BATCH_SIZE": "4", "MICRO_BATCH_SIZE": "2", "SEQ_LENGTH": "64", "SEED": "0",
+                "SAVE_DIR": str(tmp_path / "run"), "SAVE_INTERVAL": "1000", "NPROC_PER_NODE": "2",
+                "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "MAX_RESTARTS": "3",
+                "PYTHONUNBUFFERED": "1"})
+    env.pop("RANK", None)
+    env.pop("WORLD_SIZE", None)
+    p = subprocess.Popen([sys.executable, "-u", "-m", "forgetrain_b200.launch", "--", "--device", "cpu",
+                          "--dtype", "fp32"], cwd=ROOT, env=env, stdout=subprocess.PIPE,
+                         stderr=subprocess.STDOUT, text=True)
+    lines = []
+    deadline = time.time() + 300
+    while time.time() < deadline:
+        line = p.stdout.readline()
+        if not line:
+            break
+        lines.append(line)
+        if "iteration        3 " in line:
+            p.send_signal(signal.SIGTERM)
+            break
+    rest, _ = p.communicate(timeout=300)
+    out = "".join(lines) + rest
+    m = re.search(r"\[signal\] stop requested: checkpoint written at step (\d+) of 400", out)
+    assert m, out[-3000:]
+    stopped = int(m.group(1))
+    assert (tmp_path / "run" / f"step_{stopped:07d}" / "training_state.pt").exists()
+    assert "attempt 1 of 3" not in out                      # a requested stop is not a failure to retry
+    plan = launch.plan_from_env({**env, "AUTO_RESUME": "1"})
+    args = list(plan.cli_args)
+    assert args[args.index("--resume") + 1] == str(tmp_path / "run" / f"step_{stopped:07d}")
+    assert args[args.index("--num-steps") + 1] == str(400 - stopped)
