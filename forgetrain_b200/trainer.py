@@ -463,33 +463,80 @@ class _StopRequest:
     workers) and SIGUSR1 ask the loop to stop: the running step is finished, every rank learns of
     the request in the step's own all-reduce, a checkpoint is written when there is a
     ``save_dir``, and the loop returns normally, so the job can be continued with ``--resume``
-    (or by the launcher's ``AUTO_RESUME``). Handlers are installed in the main thread only and the
-    previous ones put back afterwards."""
+    (or by the launcher's ``AUTO_RESUME``).
+
+    The same signal also reaches the survivors of a job that lost a rank, and those sit in a
+    collective that will never return, where no Python-level handler runs. So the signal is taken
+    from the interpreter's wake-up descriptor by a watcher thread: it raises the flag and, if the
+    ranks have not agreed on a stopping step within the grace period (``max(5 s, 3 steps)``), ends
+    the process the way the signal would have. Installed in the main thread only; ``restore``
+    puts the previous handlers back."""
+
+    GRACE_S = 5.0
 
     def __init__(self):
         import signal
+        import socket
         import threading
         self.requested = False
-        self._old = {}
+        self.agreed = False          # set by the loop once all ranks know of the request
+        self.step_s = 0.0            # duration of the last step, for the grace period
+        self._old, self._old_fd, self._pair = {}, None, None
         if threading.current_thread() is not threading.main_thread():
             return
-        for sig in (signal.SIGTERM, signal.SIGUSR1):
-            try:
+        try:
+            r, w = socket.socketpair()
+            r.setblocking(True)
+            w.setblocking(False)
+            self._old_fd = signal.set_wakeup_fd(w.fileno(), warn_on_full_buffer=False)
+            self._pair = (r, w)
+            for sig in (signal.SIGTERM, signal.SIGUSR1):
                 self._old[sig] = signal.signal(sig, self._handler)
-            except (ValueError, OSError):
-                pass
+        except (ValueError, OSError):
+            return
+        self._watch = {int(signal.SIGTERM), int(signal.SIGUSR1)}
+        threading.Thread(target=self._watcher, name="stop-request", daemon=True).start()
 
     def _handler(self, signum, frame):
         self.requested = True
 
+    def _watcher(self):
+        import time
+        r = self._pair[0]
+        while True:
+            try:
+                data = r.recv(16)
+            except OSError:
+                return
+            if not data:
+                return
+            if not any(b in self._watch for b in data):
+                continue
+            self.requested = True
+            deadline = time.monotonic() + max(self.GRACE_S, 3.0 * self.step_s)
+            while time.monotonic() < deadline:
+                if self.agreed or self._pair is None:
+                    return
+                time.sleep(0.05)
+            if not self.agreed and self._pair is not None:
+                os._exit(143)        # the others are not coming: leave as the signal asked
+
     def restore(self):
         import signal
+        pair, self._pair = self._pair, None
         for sig, old in self._old.items():
             try:
                 signal.signal(sig, old)
             except (ValueError, OSError):
                 pass
         self._old = {}
+        if pair is not None:
+            try:
+                signal.set_wakeup_fd(self._old_fd if self._old_fd is not None else -1)
+            except (ValueError, OSError):
+                pass
+            for sock in pair:
+                sock.close()
 
 
 class LossReadback:
@@ -587,6 +634,9 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
             tt = torch.tensor([dt, float(stopping)], dtype=torch.float64, device=topo.device)
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             dt, stopping = float(tt[0]), bool(tt[1] > 0)
+        stop.step_s = dt
+        if stopping:
+            stop.agreed = True
         if profiler:
             profiler.end_step()
         loss, gnorm = float(out["loss"]), float(out["grad_norm"])
