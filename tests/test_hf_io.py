@@ -425,3 +425,31 @@ def test_loader_builder_reads_local_files_itself_when_datasets_cannot_be_importe
     args.hf_data_files = None                                   # a hub dataset does need the package
     with pytest.raises(SystemExit, match="datasets"):
         build_hf_dataloader(args, _spec(), 1, 16, Topology(), tokenizer=Tok())
+
+
+def test_every_parameter_survives_shard_and_unshard_for_random_geometries():
+    """Property: for any head / group / degree combination the engine accepts (also degrees above
+    the KV groups, and vocabularies so small that the last ranks hold padding only), the shards have
+    the advertised local shape and merge back to the full tensor exactly."""
+    from hypothesis import given, settings, strategies as hst
+    from forgetrain_b200.models.params import all_param_specs, local_shape, shard_for_tp, unshard_from_tp
+
+    @settings(max_examples=120, deadline=None)
+    @given(groups=hst.sampled_from([1, 2, 4]), per_group=hst.sampled_from([1, 2, 4, 8]),
+           tp=hst.sampled_from([1, 2, 4, 8]), vocab=hst.integers(40, 300), tie=hst.booleans())
+    def check(groups, per_group, tp, vocab, tie):
+        if tp > groups and (tp % groups or per_group % (tp // groups)):
+            return
+        if tp <= groups and groups % tp:
+            return
+        spec = load_model_spec("tiny", num_layers=1, vocab_size=vocab, hidden_size=32, ffn_hidden_size=16 * tp,
+                               num_attention_heads=groups * per_group, num_query_groups=groups, head_dim=8,
+                               tie_embeddings=tie)
+        g = torch.Generator().manual_seed(0)
+        for ps in all_param_specs(spec):
+            full = torch.randn(ps.shape, generator=g)
+            parts = [shard_for_tp(ps, full, spec, r, tp) for r in range(tp)]
+            assert all(tuple(p.shape) == tuple(local_shape(ps, spec, tp)) for p in parts), ps.name
+            assert torch.equal(unshard_from_tp(ps, parts, spec), full), ps.name
+
+    check()
