@@ -1,10 +1,13 @@
-"""Environment check: ``python -m forgetrain_b200.doctor [--build]``.
+"""Environment check: ``python -m forgetrain_b200.doctor [--build] [--json] [--self-test]``.
 
 Prints what the engine will find on this machine (interpreter, PyTorch, CUDA device and its
 compute capability, compilers, the in-tree native libraries, the measured-peak file used for the
 MFU lines, the distributed backends) and exits 0 when a training run can start here: on a GPU box
 that means an sm_100 device plus a loadable native library, elsewhere the CPU path. The counterpart
-of the reference's "verify install" step (0.5B README.md:149-153)."""
+of the reference's "verify install" step (0.5B README.md:149-153). ``--self-test`` also trains: three
+steps of a small model on the device this machine offers (two decoder blocks of the 0.5B geometry on a
+GPU through the native kernels, the tiny spec in fp32 on the CPU otherwise) and checks that the loss
+of a repeated batch falls."""
 from __future__ import annotations
 
 import json
@@ -52,9 +55,40 @@ def collect(build: bool = False) -> dict:
     return info
 
 
+def self_test() -> dict:
+    """Three optimizer steps on one repeated batch; returns ``{"device", "losses", "ok"}``."""
+    import torch
+    from .config import load_model_spec
+    from .engine_config import from_spec
+    from .parallel.topology import Topology
+    from .trainer import Trainer
+    cuda = torch.cuda.is_available()
+    if cuda:
+        torch.cuda.set_device(0)
+        spec = load_model_spec("0.5b", num_layers=2, seq_length=512, max_position_embeddings=512)
+        dev, dtype, seq, mbs = torch.device("cuda", 0), "bf16", 512, 2
+    else:
+        spec = load_model_spec("tiny", num_layers=2, seq_length=64, max_position_embeddings=64)
+        dev, dtype, seq, mbs = torch.device("cpu"), "fp32", 64, 2
+    cfg = from_spec(spec, dtype=dtype, comm="nccl", warmup_iters=0, max_lr=1e-3)
+    trainer = Trainer(spec, cfg, Topology(device=dev), seq_length=seq, micro_batch_size=mbs, seed=0)
+    chunk = torch.randint(0, spec.vocab_size, (mbs, seq + 1), generator=torch.Generator().manual_seed(0))
+    batch = {"tokens": chunk[:, :-1].contiguous().to(dev), "labels": chunk[:, 1:].contiguous().to(dev),
+             "loss_mask": torch.ones(mbs, seq, device=dev)}
+    losses = [float(trainer.train_step([batch])["loss"]) for _ in range(3)]
+    if cuda:
+        from .ops import _lib
+        torch.cuda.synchronize()
+        _lib.check_status()
+    ok = all(l == l and abs(l) < 1e4 for l in losses) and losses[-1] < losses[0]
+    return {"device": str(dev), "losses": losses, "ok": ok}
+
+
 def main(argv: list[str] | None = None) -> int:
     argv = sys.argv[1:] if argv is None else argv
     info = collect(build="--build" in argv)
+    if "--self-test" in argv and (info["can_train_on_gpu"] or not info["cuda_available"]):
+        info["self_test"] = self_test()
     if "--json" in argv:
         print(json.dumps(info, indent=1))
     else:
@@ -70,6 +104,12 @@ def main(argv: list[str] | None = None) -> int:
             print(f"note: {p}")
         print("GPU training: " + ("ready" if info["can_train_on_gpu"] else "not available here")
               + "; CPU path: ready")
+        if "self_test" in info:
+            t = info["self_test"]
+            print(f"self-test on {t['device']}: losses {' -> '.join(f'{l:.4f}' for l in t['losses'])}: "
+                  + ("ok" if t["ok"] else "FAILED"))
+    if "self_test" in info and not info["self_test"]["ok"]:
+        return 1
     return 0 if (info["can_train_on_gpu"] or not info["cuda_available"]) else 1
 
 

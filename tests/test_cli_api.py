@@ -246,6 +246,18 @@ def test_doctor_reports_the_environment():
         assert info["can_train_on_gpu"] is False and doctor.main([]) == 0
 
 
+def test_doctor_self_test_trains_a_few_steps(capsys):
+    from forgetrain_b200 import doctor
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("the CPU form of the self-test")
+    assert doctor.main(["--self-test"]) == 0
+    out = capsys.readouterr().out
+    assert "self-test on cpu: losses" in out and out.rstrip().endswith(": ok")
+    t = doctor.self_test()
+    assert t["ok"] and len(t["losses"]) == 3 and t["losses"][2] < t["losses"][0]
+
+
 def test_batch_defaults_come_from_the_model_spec():
     """No batch flags: micro-batch, sequence length and global batch are the model spec's
     (the reference pins the same in tests/test_cli_defaults.py)."""
