@@ -2,7 +2,8 @@
 must follow, to fp32 rounding, the single-process run that sees the same micro-batches in one
 gradient-accumulation loop. The cases pair switches that meet in the same code (gradient
 accumulation with tensor-parallel gradient collectives, tied tables with vocabulary parallelism,
-recomputation with document positions, the MTP head with sharded and unsharded optimizers)."""
+recomputation with document positions, the MTP head with sharded and unsharded optimizers). Tensor
+parallelism above the KV groups with gradient accumulation is in ``test_dist_gloo.py``."""
 import os
 import sys
 
@@ -57,8 +58,6 @@ CASES = {
     # name: (ranks, tp, micro-batches of the whole job, spec overrides, config of the ranks, config of the one process, positions)
     "tied tables, TP=2 x DP=2, two micro-batches per rank, replicated residual stream":
         (4, 2, 4, dict(tie_embeddings=True), dict(sequence_parallel=False), {}, False),
-    "TP=4 over two KV groups, tied tables, sequence parallel, two micro-batches":
-        (4, 4, 2, dict(tie_embeddings=True), dict(sequence_parallel=True), {}, False),
     "recomputation with document positions, TP=2 sequence parallel, two micro-batches":
         (2, 2, 2, {}, dict(sequence_parallel=True, recompute_attn=True, recompute_mlp=True), {}, True),
     "two MTP layers with recomputation, DP=2":
