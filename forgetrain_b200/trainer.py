@@ -473,11 +473,14 @@ class _StopRequest:
     puts the previous handlers back."""
 
     GRACE_S = 5.0
+    _live = None                 # the instance whose handlers are installed, if any
 
     def __init__(self):
         import signal
         import socket
         import threading
+        if _StopRequest._live is not None:      # a loop that ended in an exception left its own
+            _StopRequest._live.restore()
         self.requested = False
         self.agreed = False          # set by the loop once all ranks know of the request
         self.step_s = 0.0            # duration of the last step, for the grace period
@@ -495,6 +498,7 @@ class _StopRequest:
         except (ValueError, OSError):
             return
         self._watch = {int(signal.SIGTERM), int(signal.SIGUSR1)}
+        _StopRequest._live = self
         threading.Thread(target=self._watcher, name="stop-request", daemon=True).start()
 
     def _handler(self, signum, frame):
@@ -523,6 +527,8 @@ class _StopRequest:
 
     def restore(self):
         import signal
+        if _StopRequest._live is self:
+            _StopRequest._live = None
         pair, self._pair = self._pair, None
         for sig, old in self._old.items():
             try:

@@ -131,3 +131,18 @@ def test_sigterm_finishes_the_step_writes_a_checkpoint_and_leaves_normally(tmp_p
     ref = {int(a): float(b) for a, b in re.findall(r"iteration +(\d+) \| loss ([0-9.E+-]+)", whole.stdout)}
     assert {k: ref[k] for k in losses} == losses
     assert resumed == {stopped + 1: ref[stopped + 1], stopped + 2: ref[stopped + 2]}
+
+
+def test_stop_request_handlers_are_put_back_also_after_a_loop_that_raised():
+    import signal
+    from forgetrain_b200.trainer import _StopRequest
+    before = signal.getsignal(signal.SIGTERM)
+    a = _StopRequest()                      # a loop that raises never calls restore() ...
+    assert signal.getsignal(signal.SIGTERM) == a._handler
+    b = _StopRequest()                      # ... the next one cleans up after it
+    assert a._pair is None and signal.getsignal(signal.SIGTERM) == b._handler
+    assert not b.requested
+    signal.raise_signal(signal.SIGUSR1)
+    assert b.requested and not a.requested
+    b.restore()
+    assert signal.getsignal(signal.SIGTERM) == before and _StopRequest._live is None
