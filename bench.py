@@ -147,7 +147,7 @@ def run_reference(args) -> int:
         cmd = [sys.executable, "-m", "training_engine_tensor", "pretrain",
                "--num-steps", str(args.steps + args.warmup), "--micro-batch-size", str(args.mbs),
                "--global-batch-size", str(args.mbs * max(args.gpus, 1)), "--seq-length", str(args.seq),
-               "--hf-dataset", os.path.join(work, "corpus.jsonl"), "--hf-tokenizer", work]
+               "--hf-dataset", os.path.join(work, "data"), "--tokenizer-path", os.path.join(work, "tok")]
         out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=780)
         if out.returncode != 0:
             tail = " | ".join((out.stderr or out.stdout).strip().splitlines()[-3:])
@@ -173,19 +173,25 @@ def run_reference(args) -> int:
 
 
 def _write_reference_corpus(work: str, seq: int, rows: int) -> None:
-    """A local JSON-lines corpus of random words and a word-level tokenizer for it."""
+    """What the reference's ``pretrain`` needs in place of a synthetic source: ``work/data`` with a
+    JSON-lines corpus of random words (a directory, which its ``datasets.load_dataset(path,
+    split="train")`` call resolves to the json builder; the tokenizer files must not sit next to
+    it or they would be read as data) and ``work/tok`` with a word-level tokenizer that
+    ``AutoTokenizer.from_pretrained`` loads (its ``--tokenizer-path``)."""
     import random
-    os.makedirs(work, exist_ok=True)
+    data, tokdir = os.path.join(work, "data"), os.path.join(work, "tok")
+    os.makedirs(data, exist_ok=True)
+    os.makedirs(tokdir, exist_ok=True)
     rnd = random.Random(0)
     vocab = [f"w{i}" for i in range(4096)]
-    with open(os.path.join(work, "corpus.jsonl"), "w") as f:
+    with open(os.path.join(data, "corpus.jsonl"), "w") as f:
         for _ in range(rows):
             f.write(json.dumps({"text": " ".join(rnd.choice(vocab) for _ in range(seq + 8))}) + "\n")
     from tokenizers import Tokenizer, models, pre_tokenizers
     tok = Tokenizer(models.WordLevel({w: i for i, w in enumerate(["<unk>", "</s>"] + vocab)}, unk_token="<unk>"))
     tok.pre_tokenizer = pre_tokenizers.Whitespace()
-    tok.save(os.path.join(work, "tokenizer.json"))
-    with open(os.path.join(work, "tokenizer_config.json"), "w") as f:
+    tok.save(os.path.join(tokdir, "tokenizer.json"))
+    with open(os.path.join(tokdir, "tokenizer_config.json"), "w") as f:
         json.dump({"tokenizer_class": "PreTrainedTokenizerFast", "eos_token": "</s>", "unk_token": "<unk>"}, f)
 
 

@@ -54,16 +54,29 @@ def test_clock_record_from_nvidia_smi_csv():
 
 
 def test_reference_corpus_and_tokenizer_are_written_locally(tmp_path):
+    """The reference's CLI loads its data with ``datasets.load_dataset(<--hf-dataset>, split="train")``
+    and its tokenizer with ``AutoTokenizer.from_pretrained(<--tokenizer-path>)`` (0.5B
+    hf_dataloader.py:28-60,228-234): both calls must work on what the arm writes."""
+    import pytest
     b = _bench()
     b._write_reference_corpus(str(tmp_path), seq=32, rows=5)
-    rows = [json.loads(l) for l in (tmp_path / "corpus.jsonl").read_text().splitlines()]
+    rows = [json.loads(l) for l in (tmp_path / "data" / "corpus.jsonl").read_text().splitlines()]
     assert len(rows) == 5 and all(len(r["text"].split()) == 40 for r in rows)
-    from tokenizers import Tokenizer
-    tok = Tokenizer.from_file(str(tmp_path / "tokenizer.json"))
-    ids = tok.encode(rows[0]["text"]).ids
+    assert sorted(p.name for p in (tmp_path / "data").iterdir()) == ["corpus.jsonl"]
+    from transformers import AutoTokenizer
+    tok = AutoTokenizer.from_pretrained(str(tmp_path / "tok"), trust_remote_code=True)
+    ids = tok(rows[0]["text"], add_special_tokens=False)["input_ids"]
     assert len(ids) == 40 and min(ids) >= 2          # every word is in the vocabulary
-    cfg = json.loads((tmp_path / "tokenizer_config.json").read_text())
-    assert cfg["eos_token"] == "</s>"
+    assert tok.eos_token == "</s>" and tok.eos_token_id == 1
+    datasets = pytest.importorskip("datasets")
+    ds = datasets.load_dataset(str(tmp_path / "data"), name=None, split="train")
+    assert len(ds) == 5 and ds.column_names == ["text"] and ds[0]["text"] == rows[0]["text"]
+
+
+def test_reference_arm_uses_the_flags_of_the_reference_command_line():
+    src = (ROOT / "bench.py").read_text()
+    assert '"--tokenizer-path"' in src and "--hf-tokenizer" not in src
+    assert '"--hf-dataset", os.path.join(work, "data")' in src
 
 
 def test_command_line_defaults_match_the_documented_contract():
