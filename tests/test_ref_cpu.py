@@ -146,3 +146,53 @@ def test_fused_fc2_dgrad_swiglu_backward_reference_equals_the_two_op_composition
     g, u = y1.float()[:, :24], y1.float()[:, 24:]
     sig = torch.sigmoid(g)
     assert rel(gf, torch.cat([da * sig * (1 + g * (1 - sig)) * u, da * g * sig], dim=1)) < 1e-5
+
+
+# ---------------------------------------------------------------------------------------------
+# random shapes: the two statements agree wherever the kernels may be asked to run
+# ---------------------------------------------------------------------------------------------
+def test_attention_cross_entropy_and_gemm_agree_on_random_geometries():
+    from hypothesis import given, settings, strategies as hst
+
+    @settings(max_examples=25, deadline=None)
+    @given(batch=hst.integers(1, 3), seq=hst.integers(1, 40), groups=hst.integers(1, 3),
+           per_group=hst.integers(1, 4), half_dim=hst.integers(1, 6), seed=hst.integers(0, 1000))
+    def attention(batch, seq, groups, per_group, half_dim, seed):
+        D = 2 * half_dim
+        g = torch.Generator().manual_seed(seed)
+        qkv = torch.randn(batch * seq, groups * (per_group + 2) * D, generator=g)
+        out_c, lse_c = C.attention_fwd(qkv, batch, groups, per_group, D)
+        out_r, lse_r = R.attention_fwd(qkv, batch, groups, per_group, D)
+        assert rel(out_c, out_r) < 2e-5 and rel(lse_c, lse_r) < 2e-5
+        dout = torch.randn(out_r.shape, generator=g)
+        d_c = C.attention_bwd(dout, qkv, out_r, lse_r, batch, groups, per_group, D)
+        d_r = R.attention_bwd(dout, qkv, out_r, lse_r, batch, groups, per_group, D)
+        assert rel(d_c, d_r) < 5e-5
+
+    @settings(max_examples=40, deadline=None)
+    @given(rows=hst.integers(1, 30), vocab=hst.integers(2, 90), start=hst.integers(0, 40),
+           masked=hst.floats(0.0, 0.9), scale=hst.sampled_from([1.0, 0.25]), seed=hst.integers(0, 1000))
+    def cross_entropy(rows, vocab, start, masked, scale, seed):
+        g = torch.Generator().manual_seed(seed)
+        logits = 3 * torch.randn(rows, vocab, generator=g)
+        labels = torch.randint(0, vocab + 2 * start + 1, (rows,), generator=g)   # also outside the shard
+        mask = (torch.rand(rows, generator=g) >= masked).float()
+        lc, dc = C.cross_entropy_fwd_bwd(logits.clone(), labels, mask, scale, vocab_start=start)
+        lr_, dr = R.cross_entropy_fwd_bwd(logits.clone(), labels, mask, scale, vocab_start=start)
+        assert float(lc) == pytest.approx(float(lr_), rel=2e-5, abs=2e-6)
+        assert (dc.float() - dr.float()).abs().max() < 2e-6
+
+    @settings(max_examples=40, deadline=None)
+    @given(M=hst.integers(1, 50), N=hst.integers(1, 50), K=hst.integers(1, 70), alpha=hst.sampled_from([1.0, 0.7]),
+           seed=hst.integers(0, 1000))
+    def gemm(M, N, K, alpha, seed):
+        g = torch.Generator().manual_seed(seed)
+        x, w, dy = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g), torch.randn(M, N, generator=g)
+        assert rel(C.linear_fwd(x, w, alpha), R.linear_fwd(x, w, alpha)) < 1e-5
+        assert rel(C.linear_dgrad(dy, w, alpha), R.linear_dgrad(dy, w, alpha)) < 1e-5
+        want = R.linear_wgrad(dy, x, torch.zeros(N, K), False)
+        assert rel(C.linear_wgrad(dy, x), want) < 1e-5 or float(want.norm()) < 1e-6
+
+    attention()
+    cross_entropy()
+    gemm()
