@@ -118,7 +118,7 @@ def test_reducer_norm_exclusion():
 from hypothesis import given, settings, strategies as hst
 
 
-@settings(max_examples=200, deadline=None)
+@settings(max_examples=200, deadline=None, derandomize=True)
 @given(world=hst.integers(1, 16), units=hst.lists(hst.integers(1, 40), min_size=1, max_size=30),
        target_units=hst.integers(1, 120))
 def test_bucket_layout_invariants(world, units, target_units):

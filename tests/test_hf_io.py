@@ -434,7 +434,7 @@ def test_every_parameter_survives_shard_and_unshard_for_random_geometries():
     from hypothesis import given, settings, strategies as hst
     from forgetrain_b200.models.params import all_param_specs, local_shape, shard_for_tp, unshard_from_tp
 
-    @settings(max_examples=120, deadline=None)
+    @settings(max_examples=120, deadline=None, derandomize=True)
     @given(groups=hst.sampled_from([1, 2, 4]), per_group=hst.sampled_from([1, 2, 4, 8]),
            tp=hst.sampled_from([1, 2, 4, 8]), vocab=hst.integers(40, 300), tie=hst.booleans())
     def check(groups, per_group, tp, vocab, tie):

@@ -154,7 +154,7 @@ def test_fused_fc2_dgrad_swiglu_backward_reference_equals_the_two_op_composition
 def test_attention_cross_entropy_and_gemm_agree_on_random_geometries():
     from hypothesis import given, settings, strategies as hst
 
-    @settings(max_examples=25, deadline=None)
+    @settings(max_examples=25, deadline=None, derandomize=True)
     @given(batch=hst.integers(1, 3), seq=hst.integers(1, 40), groups=hst.integers(1, 3),
            per_group=hst.integers(1, 4), half_dim=hst.integers(1, 6), seed=hst.integers(0, 1000))
     def attention(batch, seq, groups, per_group, half_dim, seed):
@@ -169,7 +169,7 @@ def test_attention_cross_entropy_and_gemm_agree_on_random_geometries():
         d_r = R.attention_bwd(dout, qkv, out_r, lse_r, batch, groups, per_group, D)
         assert rel(d_c, d_r) < 5e-5
 
-    @settings(max_examples=40, deadline=None)
+    @settings(max_examples=40, deadline=None, derandomize=True)
     @given(rows=hst.integers(1, 30), vocab=hst.integers(2, 90), start=hst.integers(0, 40),
            masked=hst.floats(0.0, 0.9), scale=hst.sampled_from([1.0, 0.25]), seed=hst.integers(0, 1000))
     def cross_entropy(rows, vocab, start, masked, scale, seed):
@@ -182,16 +182,20 @@ def test_attention_cross_entropy_and_gemm_agree_on_random_geometries():
         assert float(lc) == pytest.approx(float(lr_), rel=2e-5, abs=2e-6)
         assert (dc.float() - dr.float()).abs().max() < 2e-6
 
-    @settings(max_examples=40, deadline=None)
+    @settings(max_examples=40, deadline=None, derandomize=True)
     @given(M=hst.integers(1, 50), N=hst.integers(1, 50), K=hst.integers(1, 70), alpha=hst.sampled_from([1.0, 0.7]),
            seed=hst.integers(0, 1000))
     def gemm(M, N, K, alpha, seed):
         g = torch.Generator().manual_seed(seed)
         x, w, dy = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g), torch.randn(M, N, generator=g)
-        assert rel(C.linear_fwd(x, w, alpha), R.linear_fwd(x, w, alpha)) < 1e-5
-        assert rel(C.linear_dgrad(dy, w, alpha), R.linear_dgrad(dy, w, alpha)) < 1e-5
-        want = R.linear_wgrad(dy, x, torch.zeros(N, K), False)
-        assert rel(C.linear_wgrad(dy, x), want) < 1e-5 or float(want.norm()) < 1e-6
+        # sums with cancellation: the error is bounded against the sum of the magnitudes, not
+        # against a result that may be close to zero
+        def close(got, want, bound):
+            assert float((got.float() - want.float()).abs().max()) <= 1e-5 * float(bound.max()) + 1e-7
+
+        close(C.linear_fwd(x, w, alpha), R.linear_fwd(x, w, alpha), x.abs() @ w.abs().t())
+        close(C.linear_dgrad(dy, w, alpha), R.linear_dgrad(dy, w, alpha), dy.abs() @ w.abs())
+        close(C.linear_wgrad(dy, x), R.linear_wgrad(dy, x, torch.zeros(N, K), False), dy.abs().t() @ x.abs())
 
     attention()
     cross_entropy()
