@@ -137,6 +137,27 @@ def check_status(device=None, reset: bool = True) -> None:
             f"forgetrain_b200 kernel reported status {code}: {STATUS_MESSAGES.get(code, '?')}")
 
 
+# What the entry points' negative return codes mean (one convention across the library; the exact
+# condition is at the `return` site of the entry point in csrc/).
+_RC_HINTS = {
+    -1: "a shape or size precondition does not hold (dimension <= 0, or not a multiple the kernel needs)",
+    -2: "an argument combination the entry point does not take (see its comment in csrc/)",
+    -3: "a device memset or the scratch buffer of the call failed",
+    -4: "no TMA descriptor for the first operand: base pointer not 16-byte aligned, or leading dimension "
+        "not a multiple of 16 bytes",
+    -5: "no TMA descriptor for the second operand: base pointer not 16-byte aligned, or leading dimension "
+        "not a multiple of 16 bytes",
+    -6: "no TMA descriptor for an output: base pointer not 16-byte aligned, or leading dimension not a "
+        "multiple of 16 bytes",
+    -7: "the grid of a kernel whose CTAs wait for one another would not be resident at once",
+    -8: "no TMA descriptor for a scratch buffer of the call (the attention backward's fp32 accumulator)",
+    -10: "the kernel's dynamic shared memory could not be reserved",
+    -11: "the kernel launch failed",
+    -100: "the kernel launch failed",
+}
+
+
 def check_rc(rc: int, what: str) -> None:
     if rc != 0:
-        raise RuntimeError(f"{what} failed with code {rc}")
+        hint = _RC_HINTS.get(int(rc))
+        raise RuntimeError(f"{what} failed with code {rc}" + (f": {hint}" if hint else ""))

@@ -85,3 +85,20 @@ def test_every_native_call_matches_its_c_prototype():
     assert compared > 300                               # the check did look at the calls
     # every entry point has a caller (the TMA-descriptor cache reset is a debugging aid)
     assert set(protos) - called <= {"ft_tmap_cache_clear"}, sorted(set(protos) - called)
+
+
+def test_every_return_code_of_the_native_entry_points_has_a_hint():
+    """``check_rc`` explains a failed call: each negative code that an entry point can return is in
+    its table, so no user is left with a bare number."""
+    from forgetrain_b200.ops import _lib
+    codes = set()
+    for f in CSRC.glob("*.cu"):
+        codes |= {int(c) for c in re.findall(r"return (-\d+);", f.read_text())}
+    assert codes and codes <= set(_lib._RC_HINTS), sorted(codes - set(_lib._RC_HINTS))
+    try:
+        _lib.check_rc(-4, "ft_gemm_bf16")
+    except RuntimeError as e:
+        assert "ft_gemm_bf16 failed with code -4: no TMA descriptor for the first operand" in str(e)
+    else:
+        raise AssertionError("check_rc did not raise")
+    _lib.check_rc(0, "anything")
