@@ -30,7 +30,10 @@ Recovery
 ``MAX_RESTARTS=K``  the launcher stays in front of ``torch.distributed.run`` and, when it exits with
                     an error, starts it again (at most K times) with ``AUTO_RESUME`` on. A SIGTERM
                     sent to the launcher is passed on to the job (whose ranks finish their step,
-                    write a checkpoint and leave) and is not followed by a restart. The
+                    write a checkpoint and leave) and is not followed by a restart. On several
+                    nodes every node runs its own launcher: when one node's ranks fail, the other
+                    nodes' ranks lose their peers, fail too, and all launchers meet again at the
+                    rendezvous of the next attempt (``SAVE_DIR`` must be storage every node sees). The
                     reference has no recovery of its own (a failed job is resubmitted by hand with
                     ``RESUME_DIR``); this is that resubmission, automated.
 
