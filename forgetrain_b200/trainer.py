@@ -233,6 +233,21 @@ class Trainer:
             return self._fwd_graph(tokens, position_ids)
         return self.model.forward(tokens, position_ids)
 
+    def nonfinite_report(self, limit: int = 6) -> str:
+        """Which parameters and gradients hold NaN / Inf on this rank (after a non-finite loss: the
+        first thing one wants to know; the reference has a NaN diagnostic inside its norm backward
+        kernel for the same purpose, triton_kernels.py:725-803). Synchronises."""
+        bad = []
+        for kind, views in (("parameter", self.store.params), ("gradient", self.store.grads)):
+            for name, t in views.items():
+                n = int((~torch.isfinite(t.float())).sum())
+                if n:
+                    bad.append(f"{kind} {name}: {n} of {t.numel()} values")
+        if not bad:
+            return "parameters and gradients of this rank are finite (the loss itself overflowed)"
+        more = f" and {len(bad) - limit} more" if len(bad) > limit else ""
+        return "non-finite values in " + "; ".join(bad[:limit]) + more
+
     def current_lr(self) -> float:
         c = self.cfg
         return compute_lr(self.opt.step_count, c.max_lr, c.min_lr, c.warmup_iters, c.lr_decay_iters,
@@ -666,7 +681,7 @@ def run_training_loop(*, spec: ModelSpec, cfg: EngineConfig, topo: Topology, num
                 _log(topo, f"[LOSS] step={step + 1} global_loss={loss:.8f} grad_norm={gnorm:.6f} "
                            f"time_s={dt:.4f} mfu_e2e_standard={rec['mfu_e2e_standard']:.4f}")
         if not math.isfinite(loss):
-            raise FloatingPointError(f"non-finite loss at step {step + 1}")
+            raise FloatingPointError(f"non-finite loss at step {step + 1}; {trainer.nonfinite_report()}")
         done = step + 1
         if save_dir and (stopping or ckpt.should_save_after_step(done, start_step + num_steps,
                                                                   save_interval, start_step)):

@@ -146,3 +146,33 @@ def test_stop_request_handlers_are_put_back_also_after_a_loop_that_raised():
     assert b.requested and not a.requested
     b.restore()
     assert signal.getsignal(signal.SIGTERM) == before and _StopRequest._live is None
+
+
+def test_a_non_finite_loss_names_the_tensors_that_hold_the_bad_values():
+    import torch
+    from forgetrain_b200.config import load_model_spec
+    from forgetrain_b200.engine_config import from_spec
+    from forgetrain_b200.parallel.topology import Topology
+    from forgetrain_b200.trainer import Trainer, run_training_loop
+    spec = load_model_spec("tiny", num_layers=2, seq_length=32, max_position_embeddings=32)
+    cfg = from_spec(spec, dtype="fp32", comm="nccl")
+    tr = Trainer(spec, cfg, Topology(), seq_length=32, micro_batch_size=2, seed=0)
+    assert tr.nonfinite_report().startswith("parameters and gradients of this rank are finite")
+    tr.store.params["layers.1.attention.wo.weight"][0, :3] = float("nan")
+    tr.store.grads["norm.weight"][5] = float("inf")
+    rep = tr.nonfinite_report()
+    assert "parameter layers.1.attention.wo.weight: 3 of" in rep and "gradient norm.weight: 1 of" in rep
+
+    class Poisoned:
+        """A source whose very first batch makes the loss NaN through a poisoned label mask."""
+        def __iter__(self):
+            return self
+
+        def __next__(self):
+            c = torch.randint(0, spec.vocab_size, (2, 33))
+            return {"tokens": c[:, :-1].contiguous(), "labels": c[:, 1:].contiguous(),
+                    "loss_mask": torch.full((2, 32), float("nan"))}
+
+    with pytest.raises(FloatingPointError, match=r"non-finite loss at step 1; .*(finite|non-finite values in)"):
+        run_training_loop(spec=spec, cfg=cfg, topo=Topology(), num_steps=2, micro_batch_size=2, seq_length=32,
+                          data_source=Poisoned())
