@@ -11,9 +11,18 @@ def pytest_configure(config):
 
 
 def pytest_collection_modifyitems(config, items):
-    """Every GPU test gets a hard time limit (when pytest-timeout is installed): a device-side
-    wait that never ends blocks the host inside the CUDA runtime, where only a watchdog thread
-    that ends the process can still act."""
+    """GPU tests are skipped on a machine without a CUDA device. With one, every GPU test gets a
+    hard time limit (when pytest-timeout is installed): a device-side wait that never ends blocks
+    the host inside the CUDA runtime, where only a watchdog thread that ends the process can
+    still act."""
+    import torch
+    if not torch.cuda.is_available():
+        # a machine without a CUDA device: GPU tests are skipped, not failed. (With a device they
+        # run, and fail loudly if the native library cannot be loaded: nothing is skipped there.)
+        skip = pytest.mark.skip(reason="needs a CUDA device")
+        for item in items:
+            if item.get_closest_marker("gpu"):
+                item.add_marker(skip)
     if not config.pluginmanager.hasplugin("timeout"):
         return
     for item in items:
